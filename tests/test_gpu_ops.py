@@ -1,0 +1,440 @@
+"""Per-op parity: the CUDA path (through the C ABI) against the CPU oracle on the same seeded inputs.
+
+Bar (north star): |gpu - cpu| <= 1e-5 + 1e-4 * |cpu| per element, f32, with a guard against
+degenerate all-zero outputs in the style of crates/vearo/tests/fused_attention_parity.rs:114-116.
+Every case is written once, as a function of the tensor class, and run on both sides.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 1e-5, 1e-4
+
+
+@pytest.fixture(scope="module")
+def vb():
+    import vearo_b200 as v
+    v.init()
+    return v
+
+
+def assert_close(gpu, cpu, name="", atol=ATOL, rtol=RTOL, guard=True):
+    gpu = np.asarray(gpu); cpu = np.asarray(cpu)
+    assert gpu.shape == cpu.shape, (name, gpu.shape, cpu.shape)
+    if cpu.size == 0:
+        return
+    assert np.isfinite(gpu).all(), name
+    if guard and cpu.size > 4:
+        assert np.abs(cpu).max() > 1e-6, "degenerate oracle output in " + name
+    err = np.abs(gpu - cpu) - (atol + rtol * np.abs(cpu))
+    assert err.max() <= 0, "%s: worst excess %.3e at %s (gpu %r cpu %r)" % (
+        name, err.max(), np.unravel_index(err.argmax(), err.shape), gpu.flat[err.argmax()], cpu.flat[err.argmax()])
+
+
+def both(vb, fn, **kw):
+    """Run `fn(T, mod)` on the oracle and on the GPU; compare every returned array."""
+    orc.reset_all()
+    cpu = fn(orc.Tensor, orc)
+    cpu = [c.numpy() for c in cpu]
+    vb.zero_gradients(); vb.reset_active_tape()
+    gpu = fn(vb.Tensor, vb)
+    gpu = [g.numpy() for g in gpu]
+    vb.check_errors()
+    assert len(cpu) == len(gpu)
+    for i, (g, c) in enumerate(zip(gpu, cpu)):
+        assert_close(g, c, "%s[%d]" % (fn.__name__, i), **kw)
+
+
+def rnd(seed, *shape, scale=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape) * scale).astype(np.float32)
+
+
+# ---- elementwise + broadcasting (crates/vearo-backend-cuda/src/lib.rs:1643-1699, 1713-1826) ----------
+@pytest.mark.parametrize("sa,sb", [((2, 3), (2, 3)), ((1, 3), (2, 1)), ((4, 5, 6), (6,)), ((4, 5, 6), (1,)), ((1,), (7, 3)),
+                                   ((3, 1, 5), (4, 1)), ((1037,), (1037,)), ((2, 0, 3), (3,)), ((8, 16, 64), (8, 1, 64))])
+def test_binary_broadcast(vb, sa, sb):
+    a, b = rnd(1, *sa), rnd(2, *sb) + 3.0
+
+    def case(T, m):
+        x, y = T.from_numpy(a), T.from_numpy(b)
+        return [x.add(y), x.sub(y), x.mul(y), x.div(y)]
+    both(vb, case, guard=False)
+
+
+def test_binary_on_views(vb):
+    a, b = rnd(3, 6, 4), rnd(4, 4, 6)
+
+    def case(T, m):
+        x, y = T.from_numpy(a), T.from_numpy(b)
+        return [x.transpose(0, 1).add(y), x.mul(y.transpose(0, 1)), x.reshape([2, 3, 4]).permute([2, 0, 1]).contiguous()]
+    both(vb, case)
+
+
+@pytest.mark.parametrize("sa,sb,ta,tb", [((5, 7), (7, 3), False, False), ((130, 70), (70, 129), False, False), ((64, 32), (48, 32), False, True),
+                                         ((32, 64), (32, 48), True, False), ((2, 3, 9, 5), (2, 3, 5, 4), False, False),
+                                         ((4, 16, 8), (8, 12), False, False), ((1, 6, 8), (5, 8, 7), False, False), ((3, 0, 4), (4, 5), False, False)])
+def test_matmul(vb, sa, sb, ta, tb):
+    a, b = rnd(5, *sa), rnd(6, *sb)
+
+    def case(T, m):
+        x, y = T.from_numpy(a), T.from_numpy(b)
+        if ta: x = x.transpose(len(sa) - 2, len(sa) - 1)
+        if tb: y = y.transpose(len(sb) - 2, len(sb) - 1)
+        return [x.matmul(y)]
+    both(vb, case, guard=False)
+
+
+def test_matmul_backward_with_broadcast_batch(vb):
+    a, b = rnd(7, 3, 10, 6), rnd(8, 6, 5)
+
+    def case(T, m):
+        x, y = T.from_numpy(a, True), T.from_numpy(b, True)
+        out = x.matmul(y)
+        out.mul(out).reshape([1, 150]).matmul(T.from_numpy(np.ones((150, 1), np.float32))).reshape([1]).backward()
+        return [out, x.grad(), y.grad()]
+    both(vb, case)
+
+
+def test_linear_fused_matches_reference_op_sequence(vb):
+    """Linear::forward = transpose, matmul, add (crates/vearo-nn/src/lib.rs:120-128); the fused
+    `linear` op must give the same values and gradients as that sequence on the oracle."""
+    x0, w0, b0 = rnd(9, 4, 9, 24), rnd(10, 17, 24), rnd(11, 17)
+    tgt = rnd(12, 4, 9, 17)
+
+    def run(T, fused):
+        x, w, b = T.from_numpy(x0, True), T.from_numpy(w0, True), T.from_numpy(b0, True)
+        y = x.linear(w, b) if fused else x.matmul(w.transpose(0, 1)).add(b)
+        loss = y.mul(T.from_numpy(tgt)).reshape([1, tgt.size]).matmul(T.from_numpy(np.ones((tgt.size, 1), np.float32))).reshape([1])
+        loss.backward()
+        return [t.numpy() for t in (y, x.grad(), w.grad().contiguous(), b.grad())]
+    orc.reset_all()
+    cpu = run(orc.Tensor, False)
+    for fused in (True, False):
+        vb.zero_gradients(); vb.reset_active_tape()
+        for g, c, n in zip(run(vb.Tensor, fused), cpu, "y gx gw gb".split()):
+            assert_close(g, c, "linear fused=%s %s" % (fused, n))
+
+
+# ---- activations, reductions, softmax --------------------------------------------------------------
+def test_relu_gelu_forward_backward(vb):
+    a = rnd(13, 33, 129, scale=2.0)
+    a.flat[:4] = [0.0, -0.0, 1e-30, -1e-30]
+    go = rnd(14, 33, 129)
+
+    def case(T, m):
+        outs = []
+        for name in ("relu", "gelu"):
+            x = T.from_numpy(a, True)
+            y = getattr(x, name)()
+            y.mul(T.from_numpy(go)).reshape([1, a.size]).matmul(T.from_numpy(np.ones((a.size, 1), np.float32))).reshape([1]).backward()
+            outs += [y, x.grad()]
+        return outs
+    both(vb, case)
+
+
+@pytest.mark.parametrize("shape,dim", [((6, 11), 1), ((6, 11), 0), ((3, 4, 7), 1), ((5, 1024), 1), ((2, 3, 5000), 2)])
+def test_sum_mean_softmax(vb, shape, dim):
+    a, go = rnd(15, *shape), rnd(16, *shape)
+
+    def case(T, m):
+        x = T.from_numpy(a, True)
+        y = x.softmax(dim)
+        n = a.size
+        y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        x2 = T.from_numpy(a)
+        return [y, x.grad(), x2.sum(dim, False), x2.sum(dim, True), x2.mean(dim, False), x2.transpose(0, 1).sum(0, False)]
+    both(vb, case)
+
+
+def test_sum_mean_backward(vb):
+    a = rnd(17, 5, 6)
+
+    def case(T, m):
+        x = T.from_numpy(a, True)
+        x.mul(x).mean(1, False).sum(0, False).backward()
+        return [x.grad()]
+    both(vb, case)
+
+
+@pytest.mark.parametrize("target", [(7,), (1, 7), (5, 1), (3, 1, 1), (1,), (3, 5, 7), (5, 7)])
+def test_reduce_to(vb, target):
+    g = rnd(18, 3, 5, 7)
+    orc.reset_all()
+    cpu = orc.Tensor.from_numpy(g).reduce_to(target).numpy()
+    import ctypes as C
+    t = vb.Tensor.from_numpy(g)
+    out = vb.VbTensor()
+    dims = (C.c_int64 * len(target))(*target)
+    vb.vb_check(vb.lib().vb_reduce_to(C.byref(t.desc()), dims, len(target), C.byref(out)), "vb_reduce_to")
+    got = np.empty(target, np.float32)
+    vb.vb_check(vb.lib().vb_read(out.slot, 0, got.ctypes.data_as(vb.c_f32p), got.size))
+    vb.vb_check(vb.lib().vb_release(out.slot, None))
+    assert_close(got, cpu, "reduce_to %r" % (target,))
+
+
+# ---- layernorm -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,c", [(5, 12), (64, 768), (33, 100), (7, 1024), (3, 13), (4, 2048), (257, 256)])
+def test_layernorm_forward_backward(vb, rows, c):
+    x0, w0, b0, go = rnd(19, rows, c) * 2 + 0.5, rnd(20, c), rnd(21, c), rnd(22, rows, c)
+
+    def case(T, m):
+        x, w, b = T.from_numpy(x0), T.from_numpy(w0), T.from_numpy(b0)
+        y = x.layernorm(w, b, 1e-5)
+        xr = T.from_numpy(x0, True); wr = T.from_numpy(w0, True); br = T.from_numpy(b0, True)
+        n = x0.size
+        xr.layernorm(wr, br, 1e-5).mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [y, xr.grad(), wr.grad(), br.grad()]
+    both(vb, case)
+
+
+def test_layernorm_3d_and_noncontiguous(vb):
+    x0, w0, b0 = rnd(23, 6, 8, 16), rnd(24, 16), rnd(25, 16)
+
+    def case(T, m):
+        x = T.from_numpy(x0)
+        return [x.layernorm(T.from_numpy(w0), T.from_numpy(b0), 1e-5),
+                x.transpose(0, 1).layernorm(T.from_numpy(w0), T.from_numpy(b0), 1e-5),
+                T.from_numpy(np.zeros((2, 0, 16), np.float32)).layernorm(T.from_numpy(w0), T.from_numpy(b0), 1e-5)]
+    both(vb, case)
+
+
+def test_layernorm_backward_is_bit_reproducible(vb):
+    x0, w0, go = rnd(26, 4096, 768), rnd(27, 768), rnd(28, 4096, 768)
+    outs = []
+    for _ in range(2):
+        x, w, b, g = (vb.Tensor.from_numpy(a) for a in (x0, w0, np.zeros(768, np.float32), go))
+        import ctypes as C
+        gx, gw, gb = vb.VbTensor(), vb.VbTensor(), vb.VbTensor()
+        vb.vb_check(vb.lib().vb_layernorm_backward(C.byref(x.desc()), C.byref(w.desc()), C.byref(b.desc()), C.byref(g.desc()), 1e-5,
+                                                   C.byref(gx), C.byref(gw), C.byref(gb)))
+        res = []
+        for t in (gx, gw, gb):
+            a = np.empty(t.shape, np.float32)
+            vb.vb_check(vb.lib().vb_read(t.slot, 0, a.ctypes.data_as(vb.c_f32p), a.size))
+            vb.vb_check(vb.lib().vb_release(t.slot, None))
+            res.append(a)
+        outs.append(res)
+    for a, b in zip(*outs):
+        assert (a.view(np.uint32) == b.view(np.uint32)).all()
+    # size-independent property: with gamma fixed, each dx row sums to ~0
+    assert np.abs(outs[0][0].sum(1)).max() < 1e-3
+
+
+# ---- embedding / cross-entropy --------------------------------------------------------------------------
+def test_embedding_forward_backward(vb):
+    w0 = rnd(29, 50, 24); ids = np.random.default_rng(30).integers(0, 50, (3, 17)).astype(np.float32); go = rnd(31, 3, 17, 24)
+    ids[0, :5] = 7   # repeated ids accumulate
+
+    def case(T, m):
+        w = T.from_numpy(w0, True)
+        y = T.from_numpy(ids).embedding(w)
+        n = go.size
+        y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [y, w.grad()]
+    both(vb, case)
+
+
+@pytest.mark.parametrize("ids,msg", [([-1.0, 0.0], "negative"), ([2.0, 0.0], "out of")])
+def test_invalid_ids_are_reported_not_skipped(vb, ids, msg):
+    """CPU contract (crates/vearo-backend-cpu/src/lib.rs:2865-2899): invalid ids are an error."""
+    w = vb.Tensor.from_numpy(np.zeros((2, 3), np.float32))
+    vb.Tensor.from_numpy(np.array(ids, np.float32)).embedding(w)
+    with pytest.raises(vb.VearoError, match=msg):
+        vb.check_errors()
+    vb.check_errors()   # flag is cleared by the read
+    vb.Tensor.from_numpy(np.zeros((2, 2), np.float32)).cross_entropy(vb.Tensor.from_numpy(np.array(ids, np.float32)))
+    with pytest.raises(vb.VearoError, match=msg):
+        vb.check_errors()
+
+
+@pytest.mark.parametrize("rows,v", [(6, 11), (4, 1000), (3, 50304), (9, 4097)])
+def test_cross_entropy(vb, rows, v):
+    l0 = rnd(32, rows, v, scale=3.0); t0 = np.random.default_rng(33).integers(0, v, rows).astype(np.float32)
+
+    def case(T, m):
+        l = T.from_numpy(l0, True)
+        loss = l.cross_entropy(T.from_numpy(t0))
+        loss.backward()
+        return [loss, l.grad()]
+    both(vb, case, guard=False)
+
+
+def test_cross_entropy_stability_and_backward_without_stats(vb):
+    import ctypes as C
+    loss = vb.Tensor.from_numpy(np.array([[1000.0, -1000.0]], np.float32)).cross_entropy(vb.Tensor.from_numpy(np.array([0.0], np.float32)))
+    assert abs(loss.numpy()[0]) < 1e-4 and loss.shape == (1,)
+    l0 = rnd(34, 5, 777, scale=2.0); t0 = np.random.default_rng(35).integers(0, 777, 5).astype(np.float32)
+    orc.reset_all()
+    cpu = orc.Tensor.from_numpy(l0).cross_entropy_backward(orc.Tensor.from_numpy(t0), orc.Tensor.from_numpy(np.array([0.5], np.float32))).numpy()
+    l, t, g = vb.Tensor.from_numpy(l0), vb.Tensor.from_numpy(t0), vb.Tensor.from_numpy(np.array([0.5], np.float32))
+    out = vb.VbTensor()
+    vb.vb_check(vb.lib().vb_cross_entropy_backward(C.byref(l.desc()), C.byref(t.desc()), C.byref(g.desc()), None, C.byref(out)))
+    got = np.empty((5, 777), np.float32)
+    vb.vb_check(vb.lib().vb_read(out.slot, 0, got.ctypes.data_as(vb.c_f32p), got.size))
+    vb.vb_check(vb.lib().vb_release(out.slot, None))
+    assert_close(got, cpu, "ce backward (no stats)")
+
+
+# ---- conv / pool / batchnorm (crates/vearo-backend-cuda/src/lib.rs:1829-1979, crates/vearo/tests/batchnorm.rs) ----
+@pytest.mark.parametrize("stride,pad,k", [(1, 1, 3), (2, 0, 3), (1, 0, 2), (2, 1, 3)])
+def test_conv2d_forward_backward(vb, stride, pad, k):
+    x0, w0, b0 = rnd(36, 3, 4, 9, 8), rnd(37, 5, 4, k, k), rnd(38, 5)
+
+    def case(T, m):
+        x, w, b = T.from_numpy(x0, True), T.from_numpy(w0, True), T.from_numpy(b0, True)
+        y = x.conv2d(w, b, stride, pad)
+        go = np.sin(np.arange(int(np.prod(y.shape)), dtype=np.float32) * 0.37 + 1).reshape(y.shape)
+        n = go.size
+        y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [y, x.grad(), w.grad(), b.grad()]
+    both(vb, case)
+
+
+@pytest.mark.parametrize("k,s,p", [(2, 2, 0), (3, 2, 1), (3, 1, 1), (2, 1, 0)])
+def test_pools_forward_backward(vb, k, s, p):
+    x0 = rnd(39, 2, 3, 9, 7)
+    x0[0, 0, :2, :2] = 5.0   # ties: the first maximum in scan order wins
+
+    def case(T, m):
+        outs = []
+        for name in ("maxpool2d", "avgpool2d"):
+            x = T.from_numpy(x0, True)
+            y = getattr(x, name)(k, s, p)
+            go = np.cos(np.arange(int(np.prod(y.shape)), dtype=np.float32) * 0.11 + 2).reshape(y.shape)
+            n = go.size
+            y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+            outs += [y, x.grad()]
+        return outs
+    both(vb, case)
+
+
+@pytest.mark.parametrize("training", [True, False])
+def test_batchnorm(vb, training):
+    x0 = rnd(40, 6, 5, 7, 4) * 2 + 1; g0, b0, go = rnd(41, 5), rnd(42, 5), rnd(43, 6, 5, 7, 4)
+    rm0 = np.linspace(-0.5, 0.5, 5).astype(np.float32); rv0 = np.linspace(0.5, 1.5, 5).astype(np.float32)
+
+    def case(T, m):
+        x, g, b = T.from_numpy(x0, True), T.from_numpy(g0, True), T.from_numpy(b0, True)
+        rm, rv = T.from_numpy(rm0), T.from_numpy(rv0)
+        y = x.batchnorm(g, b, rm, rv, training, 0.1, 1e-5)
+        n = go.size
+        y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [y, rm, rv, x.grad(), g.grad(), b.grad()]
+    both(vb, case)
+
+
+# ---- attention (crates/vearo/tests/fused_attention_parity.rs) ------------------------------------------------
+@pytest.mark.parametrize("B,H,S,dk,masked", [(2, 3, 6, 4, True), (1, 2, 33, 16, True), (2, 2, 130, 64, True), (1, 1, 7, 8, False)])
+def test_fused_attention(vb, B, H, S, dk, masked):
+    idx = np.arange(B * H * S * dk, dtype=np.float32)
+    fill = lambda ph: (np.sin(0.37 * idx + ph) / 2 + np.cos(0.11 * idx + ph) / 4).reshape(B, H, S, dk).astype(np.float32)
+    q0, k0, v0, go = fill(0.0), fill(1.0), fill(2.0), fill(3.0)
+    mask0 = np.triu(np.full((S, S), -1e9, np.float32), 1)
+
+    def case(T, m):
+        q, k, v = T.from_numpy(q0, True), T.from_numpy(k0, True), T.from_numpy(v0, True)
+        mask = T.from_numpy(mask0) if masked else None
+        o = q.fused_attention(k, v, mask)
+        n = go.size
+        o.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [o, q.grad(), k.grad(), v.grad()]
+    both(vb, case)
+
+
+def test_fused_attention_on_head_split_views(vb):
+    """q, k, v as the [B,S,H,dk] -> transpose(1,2) views MultiHeadAttention feeds (crates/vearo-nn/src/lib.rs:598-600)."""
+    B, S, H, dk = 2, 9, 3, 8
+    q0, k0, v0 = rnd(44, B, S, H * dk), rnd(45, B, S, H * dk), rnd(46, B, S, H * dk)
+    m4 = rnd(47, B, 1, S, S)
+
+    def case(T, m):
+        q, k, v = (T.from_numpy(a).reshape([B, S, H, dk]).transpose(1, 2) for a in (q0, k0, v0))
+        return [q.fused_attention(k, v, T.from_numpy(m4)), q.fused_attention(k, v, None)]
+    both(vb, case)
+
+
+# ---- optimizers ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["adamw", "sgd"])
+def test_optimizer_steps_match_oracle(vb, kind):
+    w0 = [rnd(48, 37), rnd(49, 5, 1031), rnd(50, 16384 * 2 + 3)]
+    gs = [[rnd(100 + 10 * s + i, *w.shape) for i, w in enumerate(w0)] for s in range(3)]
+
+    def case(T, m):
+        ws = [T.from_numpy(w, True) for w in w0]
+        opt = m.AdamW(ws, 1e-2, 0.9, 0.999, 1e-8, 0.1) if kind == "adamw" else m.SGD(ws, 0.1, 0.9, 0.01)
+        for s in range(3):
+            m.zero_gradients(); m.reset_active_tape()
+            loss = None
+            for w, g in zip(ws[:2] if s == 1 else ws, gs[s]):   # step 1: the last parameter gets no gradient
+                n = g.size
+                term = w.mul(T.from_numpy(g)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1])
+                loss = term if loss is None else loss.add(term)
+            loss.backward()
+            opt.step()
+        return ws
+    both(vb, case)
+
+
+def test_clip_grad_norm_known_answer_and_fused_clip(vb):
+    """crates/vearo-optim/src/lib.rs:438-459: grads [6, 8] -> norm 10, clipped to [3, 4]."""
+    x = vb.Tensor.from_numpy(np.array([3.0, 4.0], np.float32), True)
+    x.mul(x).sum(0, False).backward()
+    norm = vb.clip_grad_norm([x], 5.0)
+    assert abs(norm - 10.0) < 1e-4
+    np.testing.assert_allclose(x.grad().numpy(), [3.0, 4.0], atol=1e-3)
+    # fused clip + SGD step equals clip, then step, on the oracle
+    w0, g0 = rnd(51, 1000), rnd(52, 1000)
+
+    def case(T, m):
+        w = T.from_numpy(w0, True)
+        opt = m.SGD([w], 0.1, 0.0, 0.0)
+        w.mul(T.from_numpy(g0)).sum(0, False).backward()
+        if m is orc:
+            n = m.clip_grad_norm([w], 1.0); opt.step()
+        else:
+            n = opt.clip_and_step(1.0)
+        return [w, T.from_numpy(np.array([n], np.float32))]
+    both(vb, case)
+
+
+def test_single_tensor_adamw_through_raw_abi(vb):
+    """vb_adamw_step is the drop-in for Tensor::adamw_step (crates/vearo-core/src/tensor.rs:931-1023)."""
+    import ctypes as C
+    w0, gsteps = rnd(53, 4099), [rnd(54 + i, 4099) for i in range(3)]
+    orc.reset_all()
+    w = orc.Tensor.from_numpy(w0, True); opt = orc.AdamW([w], 3e-3, 0.9, 0.999, 1e-8, 0.05)
+    for g in gsteps:
+        orc.zero_gradients(); orc.reset_active_tape()
+        w.mul(orc.Tensor.from_numpy(g)).sum(0).backward(); opt.step()
+    L = vb.lib()
+    slots = [C.c_uint32(0) for _ in range(4)]
+    for s in slots:
+        vb.vb_check(L.vb_alloc(4099, 1, C.byref(s)))
+    vb.vb_check(L.vb_write(slots[0].value, 0, w0.ctypes.data_as(vb.c_f32p), 4099))
+    wt = vb.VbTensor.contiguous(slots[0].value, (4099,)); gt = vb.VbTensor.contiguous(slots[1].value, (4099,))
+    for t, g in enumerate(gsteps, 1):
+        vb.vb_check(L.vb_write(slots[1].value, 0, g.ctypes.data_as(vb.c_f32p), 4099))
+        vb.vb_check(L.vb_adamw_step(C.byref(wt), C.byref(gt), slots[2].value, slots[3].value, t, 3e-3, 0.9, 0.999, 1e-8, 0.05))
+    got = np.empty(4099, np.float32)
+    vb.vb_check(L.vb_read(slots[0].value, 0, got.ctypes.data_as(vb.c_f32p), 4099))
+    for s in slots:
+        vb.vb_check(L.vb_release(s.value, None))
+    assert_close(got, w.numpy(), "vb_adamw_step")
+
+
+def test_slot_lifecycle(vb):
+    """Refcount protocol of the slot table (mirrors crates/vearo-core/src/lib.rs:194-226)."""
+    import ctypes as C
+    L = vb.lib()
+    before = vb.memory_stats()["live_slots"]
+    s = C.c_uint32(0)
+    vb.vb_check(L.vb_alloc(100, 1, C.byref(s)))
+    vb.vb_check(L.vb_retain(s.value))
+    freed = C.c_int(-1)
+    vb.vb_check(L.vb_release(s.value, C.byref(freed))); assert freed.value == 0
+    vb.vb_check(L.vb_release(s.value, C.byref(freed))); assert freed.value == 1
+    assert L.vb_release(s.value, C.byref(freed)) != 0          # already gone: an error, not a crash
+    assert vb.memory_stats()["live_slots"] == before

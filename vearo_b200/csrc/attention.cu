@@ -1,0 +1,166 @@
+// Row kernels of scaled-dot-product attention; the matrix products around them run on the GEMM
+// kernels (QK^T, PV, and the four backward products), with the score / probability matrices kept
+// in HBM ([B,H,S,S] f32; 180 GB of HBM3e makes that the simple choice at S = 1024).
+//
+// Semantics: crates/vearo-backend-cpu/src/lib.rs:2416-2458 (forward row) and 2573-2591 (backward
+// row): score = (q.k) * scale + mask, p = exp(score - max) * (1 / (sum + 1e-9)) — note the 1e-9
+// and the reciprocal-multiply, which plain softmax does not have — and
+// ds = p * (dp - sum_j dp_j * p_j).  The additive mask is right-aligned to [B,H,Sq,Sk] with
+// size-1 dims broadcast (lib.rs:2395-2404, 2430-2442); a [S,S] causal mask stays L2-resident.
+//
+// Both kernels are HBM-bound: one CTA of 128 threads per row, the row held in registers
+// (up to 4096 columns), one read and one write of the matrix.
+#include "common.h"
+
+namespace vb {
+
+__device__ __forceinline__ float a_wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float a_wmax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float a_bsum(float v, float* red) {
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = a_wsum(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  return a_wsum(lane < nw ? red[lane] : 0.0f);
+}
+__device__ __forceinline__ float a_bmax(float v, float* red) {
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = a_wmax(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  return a_wmax(lane < nw ? red[lane] : -INFINITY);
+}
+
+struct MaskStrides { i64 b, h, q, k; };
+
+// s holds scale * (q.k) on entry and the probabilities on exit.
+template <int EPT>
+__global__ void __launch_bounds__(128) k_attn_softmax(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
+                                                      i64 H, i64 sq, i64 sk) {
+  __shared__ float red[32];
+  i64 row = blockIdx.x;                 // (b * H + h) * sq + i
+  i64 i = row % sq, bh = row / sq, h = bh % H, b = bh / H;
+  float* r = s + row * sk;
+  const float* mrow = mask ? mask + b * ms.b + h * ms.h + i * ms.q : nullptr;
+  float v[EPT];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    i64 j = threadIdx.x + (i64)e * 128;
+    if (j < sk) {
+      float x = r[j];
+      if (mrow) x += mrow[j * ms.k];
+      v[e] = x;
+      if (x > mx) mx = x;
+    } else v[e] = -INFINITY;
+  }
+  mx = a_bmax(mx, red);
+  float sum = 0.0f;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    i64 j = threadIdx.x + (i64)e * 128;
+    if (j < sk) { v[e] = expf(v[e] - mx); sum += v[e]; }
+  }
+  sum = a_bsum(sum, red);
+  float inv = 1.0f / (sum + 1e-9f);
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    i64 j = threadIdx.x + (i64)e * 128;
+    if (j < sk) r[j] = v[e] * inv;
+  }
+}
+// Rows longer than 4096: values are re-read from global memory (L1/L2-hot) instead of registers.
+__global__ void __launch_bounds__(256) k_attn_softmax_long(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
+                                                           i64 H, i64 sq, i64 sk) {
+  __shared__ float red[32];
+  i64 row = blockIdx.x;
+  i64 i = row % sq, bh = row / sq, h = bh % H, b = bh / H;
+  float* r = s + row * sk;
+  const float* mrow = mask ? mask + b * ms.b + h * ms.h + i * ms.q : nullptr;
+  float mx = -INFINITY;
+  for (i64 j = threadIdx.x; j < sk; j += blockDim.x) { float x = r[j]; if (mrow) x += mrow[j * ms.k]; r[j] = x; if (x > mx) mx = x; }
+  mx = a_bmax(mx, red);
+  float sum = 0.0f;
+  for (i64 j = threadIdx.x; j < sk; j += blockDim.x) { float e = expf(r[j] - mx); r[j] = e; sum += e; }
+  sum = a_bsum(sum, red);
+  float inv = 1.0f / (sum + 1e-9f);
+  for (i64 j = threadIdx.x; j < sk; j += blockDim.x) r[j] *= inv;
+}
+
+int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale) {
+  (void)causal; (void)scale;
+  i64 rows = b * h * sq;
+  if (rows <= 0 || sk <= 0) return VB_OK;
+  ProfScope prof("attn_softmax", 2.0 * (double)rows * (double)sk * 4.0);
+  MaskStrides ms{0, 0, 0, 0};
+  if (mask) ms = MaskStrides{mstr[0], mstr[1], mstr[2], mstr[3]};
+  cudaStream_t st = ctx().stream;
+  unsigned g = (unsigned)rows;
+  if (sk <= 128) k_attn_softmax<1><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
+  else if (sk <= 256) k_attn_softmax<2><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
+  else if (sk <= 512) k_attn_softmax<4><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
+  else if (sk <= 1024) k_attn_softmax<8><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
+  else if (sk <= 2048) k_attn_softmax<16><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
+  else if (sk <= 4096) k_attn_softmax<32><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
+  else k_attn_softmax_long<<<g, 256, 0, st>>>(s, mask, ms, h, sq, sk);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+// dp holds dO.V^T on entry and scale * p * (dp - sum(dp * p)) on exit.
+template <int EPT>
+__global__ void __launch_bounds__(128) k_attn_softmax_bwd(const float* __restrict__ p, float* __restrict__ dp, i64 sk, float scale) {
+  __shared__ float red[32];
+  const float* pr = p + (i64)blockIdx.x * sk;
+  float* dr = dp + (i64)blockIdx.x * sk;
+  float pv[EPT], dv[EPT];
+  float dot = 0.0f;
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    i64 j = threadIdx.x + (i64)e * 128;
+    if (j < sk) { pv[e] = pr[j]; dv[e] = dr[j]; dot = fmaf(dv[e], pv[e], dot); } else { pv[e] = 0.0f; dv[e] = 0.0f; }
+  }
+  dot = a_bsum(dot, red);
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    i64 j = threadIdx.x + (i64)e * 128;
+    if (j < sk) dr[j] = (pv[e] * (dv[e] - dot)) * scale;
+  }
+}
+__global__ void __launch_bounds__(256) k_attn_softmax_bwd_long(const float* __restrict__ p, float* __restrict__ dp, i64 sk, float scale) {
+  __shared__ float red[32];
+  const float* pr = p + (i64)blockIdx.x * sk;
+  float* dr = dp + (i64)blockIdx.x * sk;
+  float dot = 0.0f;
+  for (i64 j = threadIdx.x; j < sk; j += blockDim.x) dot = fmaf(dr[j], pr[j], dot);
+  dot = a_bsum(dot, red);
+  for (i64 j = threadIdx.x; j < sk; j += blockDim.x) dr[j] = (pr[j] * (dr[j] - dot)) * scale;
+}
+int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, float scale, bool causal, i64 sq) {
+  (void)causal; (void)sq;
+  if (rows <= 0 || sk <= 0) return VB_OK;
+  ProfScope prof("attn_softmax_bwd", 3.0 * (double)rows * (double)sk * 4.0);
+  cudaStream_t st = ctx().stream;
+  unsigned g = (unsigned)rows;
+  if (sk <= 128) k_attn_softmax_bwd<1><<<g, 128, 0, st>>>(p, dp, sk, scale);
+  else if (sk <= 256) k_attn_softmax_bwd<2><<<g, 128, 0, st>>>(p, dp, sk, scale);
+  else if (sk <= 512) k_attn_softmax_bwd<4><<<g, 128, 0, st>>>(p, dp, sk, scale);
+  else if (sk <= 1024) k_attn_softmax_bwd<8><<<g, 128, 0, st>>>(p, dp, sk, scale);
+  else if (sk <= 2048) k_attn_softmax_bwd<16><<<g, 128, 0, st>>>(p, dp, sk, scale);
+  else if (sk <= 4096) k_attn_softmax_bwd<32><<<g, 128, 0, st>>>(p, dp, sk, scale);
+  else k_attn_softmax_bwd_long<<<g, 256, 0, st>>>(p, dp, sk, scale);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+}  // namespace vb

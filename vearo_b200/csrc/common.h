@@ -1,0 +1,165 @@
+// Internal declarations shared by the runtime, the kernels and the C-ABI layer.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+#include "../../include/vearo_b200.h"
+
+namespace vb {
+
+using i64 = int64_t;
+
+// Bits of the device error word (reported as VB_ERR_BAD_INDEX by vb_check_errors).
+enum : int { ERRBIT_NEG_ID = 1, ERRBIT_OOB_ID = 2, ERRBIT_WAIT_TIMEOUT = 4 };
+
+struct Ctx {
+  bool ready = false;
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;       // compute stream: every kernel of the library
+  cudaStream_t comm_stream = nullptr;  // collectives
+  cudaEvent_t ev_compute = nullptr, ev_comm = nullptr;
+  int* d_err = nullptr;                // device error word
+  float* d_scalars = nullptr;          // small device scratch for scalars (norms, loss partials)
+  float* h_pinned = nullptr;           // pinned host mirror for small reads
+};
+Ctx& ctx();
+
+// Thread-local error text + status helpers.
+int set_error(int status, const std::string& msg);
+#define VB_CHECK(cond, msg) do { if (!(cond)) return ::vb::set_error(VB_ERR_INVALID, std::string(__func__) + ": " + (msg)); } while (0)
+#define VB_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return ::vb::set_error(VB_ERR_CUDA, std::string(__func__) + ": " #expr ": " + cudaGetErrorString(e_)); } while (0)
+#define VB_TRY(expr) do { int s_ = (expr); if (s_ != VB_OK) return s_; } while (0)
+#define VB_LAUNCH_CHECK() VB_CUDA(cudaGetLastError())
+
+// Slots / arena (runtime.cu).
+int slot_alloc(i64 numel, bool zero, vb_slot* out);
+int slot_ptr(vb_slot s, float** p, i64* numel = nullptr);
+int slot_release(vb_slot s, int* freed);
+int slot_retain(vb_slot s);
+// Raw cached device scratch, stream-ordered reuse; never shows up in the slot table.
+int scratch_alloc(size_t bytes, void** p);
+void scratch_free(void* p);
+
+// Tensor-descriptor helpers.
+inline i64 numel(const vb_tensor& t) { i64 n = 1; for (int i = 0; i < t.rank; ++i) n *= t.dims[i]; return n; }
+inline bool is_contiguous(const vb_tensor& t) {
+  i64 s = 1;
+  for (int i = t.rank - 1; i >= 0; --i) { if (t.dims[i] != 1 && t.strides[i] != s) return false; s *= t.dims[i]; }
+  return true;
+}
+inline void set_contiguous(vb_tensor& t, int rank, const i64* dims) {
+  t.rank = rank; t.offset = 0;
+  i64 s = 1;
+  for (int i = 0; i < VB_MAX_RANK; ++i) { t.dims[i] = 0; t.strides[i] = 0; }
+  for (int i = rank - 1; i >= 0; --i) { t.dims[i] = dims[i]; t.strides[i] = s; s *= dims[i]; }
+}
+inline bool same_shape(const vb_tensor& a, const vb_tensor& b) {
+  if (a.rank != b.rank) return false;
+  for (int i = 0; i < a.rank; ++i) if (a.dims[i] != b.dims[i]) return false;
+  return true;
+}
+int tensor_ptr(const vb_tensor* t, float** p);           // slot base + offset, validated
+int new_output(vb_tensor* out, int rank, const i64* dims, bool zero = false);  // fresh contiguous slot
+// A contiguous device pointer for `t`: the tensor itself when already contiguous, else a strided
+// copy into scratch (owned by `Temp`, returned to the arena when it goes out of scope).
+struct Temp {
+  void* p = nullptr;
+  ~Temp() { if (p) scratch_free(p); }
+};
+int contiguous_ptr(const vb_tensor* t, const float** p, Temp& hold);
+
+// Strided index descriptor passed by value to generic kernels.
+struct Strided {
+  int rank;
+  i64 dims[VB_MAX_RANK];
+  i64 sa[VB_MAX_RANK];
+  i64 sb[VB_MAX_RANK];
+};
+
+// ---- kernel launchers (one family per .cu file); all enqueue on ctx().stream -------------
+// elementwise.cu
+int launch_binary(int op, const float* a, const float* b, float* out, i64 n);                       // same shape, contiguous
+int launch_binary_rowvec(int op, const float* a, const float* b, float* out, i64 n, i64 c, bool b_is_vec); // b (or a) is a length-c vector over the last dim
+int launch_binary_scalar(int op, const float* a, const float* b, float* out, i64 n, bool b_is_scalar);
+int launch_binary_strided(int op, const float* a, const float* b, float* out, i64 n, const Strided& s);
+int launch_unary(int op, const float* x, float* out, i64 n);          // 0 relu 1 gelu
+int launch_unary_backward(int op, const float* x, const float* g, float* out, i64 n);  // 0 relu 1 gelu
+int launch_scale(const float* x, float alpha, float* out, i64 n);
+int launch_axpy(float* dst, const float* src, i64 n);                 // dst += src
+int launch_fill(float* dst, float v, i64 n);
+int launch_strided_copy(const float* src, float* dst, i64 n, const Strided& s);   // dst contiguous; s.sa = src strides
+// reduce.cu
+int launch_sum_axis(const float* x, float* out, i64 outer, i64 d, i64 inner, bool mean);
+int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulate);   // out[c] (+)= sum_r x[r,c]
+int launch_reduce_general(const float* g, float* out, i64 out_numel, const Strided& kept, const Strided& red, i64 red_count);
+int launch_softmax_rows(const float* x, float* out, i64 rows, i64 d);
+int launch_softmax_strided(const float* x, float* out, i64 outer, i64 d, i64 inner);
+int launch_softmax_backward_rows(const float* x, const float* g, float* out, i64 rows, i64 d);
+int launch_softmax_backward_strided(const float* x, const float* g, float* out, i64 outer, i64 d, i64 inner);
+// norm.cu
+int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps);
+int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps);
+int launch_batchnorm(const float* x, const float* gamma, const float* beta, float* rm, float* rv, float* out,
+                     i64 n, i64 c, i64 hw, bool training, float momentum, float eps);
+int launch_batchnorm_backward(const float* x, const float* gamma, const float* rm, const float* rv, const float* g,
+                              float* gx, float* gw, float* gb, i64 n, i64 c, i64 hw, bool training, float eps);
+// loss.cu
+int launch_embedding(const float* ids, const float* w, float* out, i64 n, i64 vocab, i64 d);
+int launch_embedding_backward(const float* ids, const float* g, float* gw, i64 n, i64 vocab, i64 d);   // gw pre-zeroed
+int launch_cross_entropy(const float* logits, const float* targets, float* loss, float* stats, i64 rows, i64 v);
+int launch_cross_entropy_backward(const float* logits, const float* targets, const float* gout, const float* stats,
+                                  float* gl, i64 rows, i64 v);
+// conv.cu
+int launch_conv2d(const float* x, const float* w, const float* b, float* out, i64 n, i64 cin, i64 h, i64 wd,
+                  i64 cout, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad);
+int launch_conv2d_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb,
+                           i64 n, i64 cin, i64 h, i64 wd, i64 cout, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad);
+int launch_maxpool2d(const float* x, float* out, i64 nc, i64 h, i64 w, i64 oh, i64 ow, i64 k, i64 s, i64 p);
+int launch_maxpool2d_backward(const float* x, const float* g, float* gx, i64 nc, i64 h, i64 w, i64 oh, i64 ow, i64 k, i64 s, i64 p);
+int launch_avgpool2d(const float* x, float* out, i64 nc, i64 h, i64 w, i64 oh, i64 ow, i64 k, i64 s, i64 p);
+int launch_avgpool2d_backward(const float* g, float* gx, i64 nc, i64 h, i64 w, i64 oh, i64 ow, i64 k, i64 s, i64 p);
+
+// gemm.cu: C[b] = alpha * A[b] . B[b] (+ beta * C[b]) (+ bias[n]); A logical [M,K], B logical [K,N],
+// every operand addressed through element strides, two batch levels (b = b1 * nb2 + b2).
+struct GemmArgs {
+  const float* A; const float* B; float* C; const float* bias;   // bias: length N or null
+  i64 M, N, K;
+  i64 a_rs, a_cs;   // A[m,k] = A[m*a_rs + k*a_cs]
+  i64 b_rs, b_cs;   // B[k,n] = B[k*b_rs + n*b_cs]
+  i64 c_rs, c_cs;
+  i64 nb1, nb2;     // batch counts (>= 1)
+  i64 a_b1, a_b2, b_b1, b_b2, c_b1, c_b2;   // batch strides (0 = broadcast)
+  float alpha, beta;
+};
+int launch_gemm(const GemmArgs& g);
+inline GemmArgs gemm_args() { GemmArgs g{}; g.nb1 = g.nb2 = 1; g.alpha = 1.0f; g.beta = 0.0f; return g; }
+
+// attention.cu
+int launch_attn_softmax(float* s, const float* mask, const i64 mask_strides[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale);
+int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 sk, float scale, bool causal, i64 sq);
+
+// optim.cu
+struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param; };
+int launch_adamw_single(float* w, const float* g, float* m, float* v, i64 n, float lr, float b1, float b2, float eps, float wd,
+                        float bc1, float bc2);
+int launch_sgd_single(float* w, const float* g, float* vel, i64 n, float lr, float mu, float wd);
+int launch_sumsq_chunks(const OptChunk* chunks, int nchunks, const uint8_t* active, float* partials);
+int launch_sum_partials(const float* partials, int n, float* out);      // out[0] = sum (single block, fixed order)
+int launch_opt_multi(const OptChunk* chunks, int nchunks, const uint8_t* active, int kind, const float* normsq,
+                     float max_norm, float grad_scale, float lr, float b1, float b2, float eps, float wd, float mu,
+                     float bc1, float bc2);
+int launch_scale_inplace_by_clip(float* g, i64 n, const float* normsq, float max_norm);
+
+
+// prof.cu: optional per-family kernel timing with CUDA events on the compute stream.  Off by
+// default (zero cost); the benchmark switches it on for a separate, untimed pass.
+struct ProfScope {
+  int idx = -1;
+  ProfScope(const char* family, double units);   // units: algorithmic bytes or flops of this launch
+  ~ProfScope();
+};
+
+}  // namespace vb

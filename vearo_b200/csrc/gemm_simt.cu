@@ -1,0 +1,106 @@
+// Strided batched FP32 GEMM on the CUDA cores: C = alpha * A.B (+ beta * C) (+ bias).
+//
+// The general-shape kernel of the library: any M, N, K, any element strides on every operand
+// (so transposed views, head-split views of [B,S,H,dk] and broadcast batches need no copy), two
+// batch levels.  Exact FP32 multiply-adds, k ascending inside a tile.  Shapes that satisfy the
+// alignment rules of the tensor-core kernel (gemm_tc.cu) are routed there by launch_gemm; this one
+// keeps the rest (tiny MLP layers, odd sizes, unaligned views).
+//
+// Tiling: 128x128 CTA tile, 16-deep k slices, 256 threads, 8x8 outputs per thread held as four
+// 4x4 quadrants so that shared-memory reads are 128-bit and conflict-free.
+#include "common.h"
+
+namespace vb {
+
+int launch_gemm_tc(const GemmArgs& g, bool* handled);   // gemm_tc.cu
+
+namespace {
+constexpr int BM = 128, BN = 128, BK = 16, PAD = 4;
+
+__global__ void __launch_bounds__(256) k_gemm_simt(GemmArgs g) {
+  __shared__ __align__(16) float As[BK][BM + PAD];
+  __shared__ __align__(16) float Bs[BK][BN + PAD];
+  const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
+  const i64 m0 = (i64)blockIdx.y * BM, n0 = (i64)blockIdx.x * BN;
+  const i64 nbatch = g.nb1 * g.nb2;
+  const bool a_kmajor = g.a_cs == 1 || g.a_rs != 1;   // walk k fastest unless m is the contiguous axis
+  const bool b_nmajor = g.b_cs == 1 || g.b_rs != 1;
+  for (i64 bz = blockIdx.z; bz < nbatch; bz += gridDim.z) {
+    const i64 b1 = bz / g.nb2, b2 = bz % g.nb2;
+    const float* A = g.A + b1 * g.a_b1 + b2 * g.a_b2;
+    const float* B = g.B + b1 * g.b_b1 + b2 * g.b_b2;
+    float* C = g.C + b1 * g.c_b1 + b2 * g.c_b2;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+    for (i64 k0 = 0; k0 < g.K; k0 += BK) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        int kk, mm;
+        if (a_kmajor) { kk = t & 15; mm = (t >> 4) + 16 * i; } else { mm = t & 127; kk = (t >> 7) + 2 * i; }
+        i64 m = m0 + mm, k = k0 + kk;
+        As[kk][mm] = (m < g.M && k < g.K) ? A[m * g.a_rs + k * g.a_cs] : 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        int kk, nn;
+        if (b_nmajor) { nn = t & 127; kk = (t >> 7) + 2 * i; } else { kk = t & 15; nn = (t >> 4) + 16 * i; }
+        i64 n = n0 + nn, k = k0 + kk;
+        Bs[kk][nn] = (n < g.N && k < g.K) ? B[k * g.b_rs + n * g.b_cs] : 0.0f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) {
+        float4 a0 = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+        float4 a1 = *reinterpret_cast<const float4*>(&As[kk][64 + ty * 4]);
+        float4 b0 = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+        float4 b1v = *reinterpret_cast<const float4*>(&Bs[kk][64 + tx * 4]);
+        float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        float b[8] = {b0.x, b0.y, b0.z, b0.w, b1v.x, b1v.y, b1v.z, b1v.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      i64 m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+      if (m >= g.M) continue;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        i64 n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+        if (n >= g.N) continue;
+        float v = g.alpha * acc[i][j];
+        float* c = C + m * g.c_rs + n * g.c_cs;
+        if (g.beta != 0.0f) v += g.beta * *c;
+        if (g.bias) v += g.bias[n];
+        *c = v;
+      }
+    }
+  }
+}
+}  // namespace
+
+int launch_gemm_simt(const GemmArgs& g) {
+  if (g.M <= 0 || g.N <= 0 || g.nb1 * g.nb2 <= 0) return VB_OK;
+  i64 nb = g.nb1 * g.nb2;
+  ProfScope prof("gemm_simt", 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
+  dim3 grid((unsigned)((g.N + BN - 1) / BN), (unsigned)((g.M + BM - 1) / BM), (unsigned)(nb > 65535 ? 65535 : nb));
+  k_gemm_simt<<<grid, 256, 0, ctx().stream>>>(g);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+int launch_gemm(const GemmArgs& g) {
+  if (g.M <= 0 || g.N <= 0 || g.nb1 * g.nb2 <= 0) return VB_OK;
+  bool handled = false;
+  VB_TRY(launch_gemm_tc(g, &handled));
+  if (handled) return VB_OK;
+  return launch_gemm_simt(g);
+}
+
+}  // namespace vb

@@ -1,0 +1,405 @@
+// Tensor dispatch + record, the tape, and the backward walk.
+//
+// Mirrors crates/vearo-core/src/tensor.rs:1365-1970 (each op: run the backend, then record when
+// autograd is on and an input requires grad) and crates/vearo-autograd/src/lib.rs:129-197 (tape,
+// generation-tagged node tokens, lazily created leaf nodes) and :429-792 (backward_impl: reverse
+// walk, one arm per op, `existing + new` accumulation, gradients published for leaves only).
+//
+// What differs from the reference, by design: every arm stays on the device (the reference
+// downloads gradients for reduce_to and builds ReLU / GELU masks on the host, lib.rs:316-403);
+// op attributes are plain fields, not formatted strings; the tape is moved, not cloned; a
+// gradient whose storage nobody else holds is accumulated in place; node gradients and saved
+// activations are dropped as soon as the walk has passed them; and a leaf's gradient is
+// published the moment its last contribution has arrived (its earliest consumer on the tape),
+// which is what allows gradient exchange to overlap the rest of the walk.
+#include "vearo_host.h"
+#include <algorithm>
+#include <cmath>
+#include <unordered_map>
+
+namespace vearo {
+
+void check(int status, const char* what) {
+  if (status != VB_OK) throw Error(std::string(what) + ": " + vb_last_error());
+}
+Storage::~Storage() { if (slot) vb_release(slot, nullptr); }
+
+// ---- Tensor basics ---------------------------------------------------------------------------
+static vb_tensor contiguous_desc(const std::vector<i64>& shape) {
+  if (shape.size() > VB_MAX_RANK) throw Error("rank > 8 is not supported");
+  vb_tensor t{}; t.rank = (int)shape.size();
+  i64 s = 1;
+  for (int i = t.rank - 1; i >= 0; --i) { t.dims[i] = shape[i]; t.strides[i] = s; s *= shape[i]; }
+  return t;
+}
+Tensor Tensor::adopt(const vb_tensor& t) { Tensor r; r.st_ = std::make_shared<Storage>(t.slot); r.d_ = t; return r; }
+Tensor Tensor::view_of(const Tensor& base, const vb_tensor& d) { Tensor r; r.st_ = base.st_; r.d_ = d; r.d_.slot = base.d_.slot; return r; }
+Tensor Tensor::zeros(const std::vector<i64>& shape) {
+  vb_tensor t = contiguous_desc(shape);
+  i64 n = 1; for (i64 d : shape) n *= d;
+  check(vb_alloc(n, 1, &t.slot), "alloc");
+  return adopt(t);
+}
+Tensor Tensor::from_f32(const float* data, const std::vector<i64>& shape) {
+  vb_tensor t = contiguous_desc(shape);
+  i64 n = 1; for (i64 d : shape) n *= d;
+  check(vb_alloc(n, 0, &t.slot), "alloc");
+  Tensor r = adopt(t);
+  if (n) check(vb_write(t.slot, 0, data, n), "write");
+  return r;
+}
+bool Tensor::is_contiguous() const {
+  i64 s = 1;
+  for (int i = d_.rank - 1; i >= 0; --i) { if (d_.dims[i] != 1 && d_.strides[i] != s) return false; s *= d_.dims[i]; }
+  return true;
+}
+Tensor Tensor::contiguous() const {
+  if (is_contiguous()) return *this;
+  vb_tensor o; check(vb_contiguous(&d_, &o), "contiguous");
+  Tensor r = adopt(o);
+  r.meta_->requires_grad = meta_->requires_grad; r.meta_->node = meta_->node;
+  return r;
+}
+std::vector<float> Tensor::to_vec_f32() const {
+  Tensor c = contiguous();
+  std::vector<float> v((size_t)numel());
+  if (!v.empty()) check(vb_read(c.d_.slot, c.d_.offset, v.data(), (i64)v.size()), "read");
+  return v;
+}
+void Tensor::write_f32(const float* data) const {
+  if (!is_contiguous()) throw Error("write_f32 needs a contiguous tensor");
+  if (numel()) check(vb_write(d_.slot, d_.offset, data, numel()), "write");
+}
+
+// ---- tape ------------------------------------------------------------------------------------
+namespace {
+enum class Op { Add, Sub, Mul, Div, Matmul, Reshape, Transpose, Permute, Relu, Gelu, Softmax, LayerNorm, Embedding,
+                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, Leaf };
+struct Node {
+  int id = 0; Op op = Op::Leaf;
+  std::vector<int> inputs;
+  std::vector<Tensor> saved;
+  i64 a0 = 0, a1 = 0, a2 = 0; float f0 = 0.0f;
+  std::vector<i64> axes;
+  Tensor extra;             // attention probabilities / cross-entropy row statistics
+  Tensor leaf;              // for Leaf nodes: the tensor itself
+};
+struct Tape { std::vector<Node> nodes; uint32_t generation = 0; };
+thread_local Tape t_tape;
+thread_local bool t_enabled = true, t_training = true;
+thread_local std::unordered_map<vb_slot, Tensor> t_grads;
+
+struct Sinks {
+  std::unordered_map<vb_slot, int> index;
+  std::vector<Tensor> sinks;
+  void (*on_ready)(int, void*) = nullptr; void* user = nullptr;
+};
+thread_local Sinks t_sinks;
+
+i64 pack(uint32_t gen, uint32_t idx) { return ((i64)gen << 32) | idx; }
+int live_index(const Tensor& t) {
+  i64 tok = t.node_id();
+  if (tok < 0 || (uint32_t)(tok >> 32) != t_tape.generation) return -1;
+  return (int)(tok & 0xffffffff);
+}
+// Tape::push (lib.rs:151-189)
+Node& push(Op op, const std::vector<const Tensor*>& ins, Tensor& out) {
+  std::vector<int> ids;
+  for (const Tensor* in : ins) {
+    int live = live_index(*in);
+    if (live >= 0) ids.push_back(live);
+    else if (in->requires_grad()) {
+      Node leaf; leaf.id = (int)t_tape.nodes.size(); leaf.op = Op::Leaf; leaf.leaf = *in;
+      in->set_node_id(pack(t_tape.generation, (uint32_t)leaf.id));
+      ids.push_back(leaf.id);
+      t_tape.nodes.push_back(std::move(leaf));
+    } else ids.push_back(-1);
+  }
+  Node n; n.id = (int)t_tape.nodes.size(); n.op = op; n.inputs = ids;
+  for (const Tensor* in : ins) n.saved.push_back(*in);
+  out.set_node_id(pack(t_tape.generation, (uint32_t)n.id));
+  t_tape.nodes.push_back(std::move(n));
+  return t_tape.nodes.back();
+}
+Node* record(Op op, const std::vector<const Tensor*>& ins, Tensor& out) {
+  if (!t_enabled) return nullptr;
+  bool any = false;
+  for (const Tensor* t : ins) any = any || t->requires_grad();
+  if (!any) return nullptr;
+  out.set_requires_grad(true);
+  return &push(op, ins, out);
+}
+}  // namespace
+
+namespace autograd {
+void set_enabled(bool e) { t_enabled = e; }
+bool is_enabled() { return t_enabled; }
+void set_training(bool t) { t_training = t; }
+bool is_training() { return t_training; }
+void reset_active_tape() { t_tape.nodes.clear(); t_tape.generation++; }
+void zero_gradients() { t_grads.clear(); }
+size_t tape_len() { return t_tape.nodes.size(); }
+void register_grad_sinks(const std::vector<Tensor>& params, const std::vector<Tensor>& sinks, void (*on_ready)(int, void*), void* user) {
+  t_sinks = Sinks();
+  for (size_t i = 0; i < params.size(); ++i) t_sinks.index[params[i].slot()] = (int)i;
+  t_sinks.sinks = sinks; t_sinks.on_ready = on_ready; t_sinks.user = user;
+}
+void clear_grad_sinks(void* user) { if (t_sinks.user == user) t_sinks = Sinks(); }
+}  // namespace autograd
+
+// ---- ops ---------------------------------------------------------------------------------------
+#define VB_OUT1(call, what) vb_tensor o_; check(call, what); Tensor out = Tensor::adopt(o_)
+Tensor Tensor::add(const Tensor& o) const { VB_OUT1(vb_add(&d_, &o.d_, &o_), "add"); record(Op::Add, {this, &o}, out); return out; }
+Tensor Tensor::sub(const Tensor& o) const { VB_OUT1(vb_sub(&d_, &o.d_, &o_), "sub"); record(Op::Sub, {this, &o}, out); return out; }
+Tensor Tensor::mul(const Tensor& o) const { VB_OUT1(vb_mul(&d_, &o.d_, &o_), "mul"); record(Op::Mul, {this, &o}, out); return out; }
+Tensor Tensor::div(const Tensor& o) const { VB_OUT1(vb_div(&d_, &o.d_, &o_), "div"); record(Op::Div, {this, &o}, out); return out; }
+Tensor Tensor::matmul(const Tensor& o) const { VB_OUT1(vb_matmul(&d_, &o.d_, &o_), "matmul"); record(Op::Matmul, {this, &o}, out); return out; }
+Tensor Tensor::relu() const { VB_OUT1(vb_relu(&d_, &o_), "relu"); record(Op::Relu, {this}, out); return out; }
+Tensor Tensor::gelu() const { VB_OUT1(vb_gelu(&d_, &o_), "gelu"); record(Op::Gelu, {this}, out); return out; }
+Tensor Tensor::sum(int dim, bool keep) const {
+  VB_OUT1(vb_sum(&d_, dim, keep, &o_), "sum");
+  if (Node* n = record(Op::Sum, {this}, out)) { n->a0 = dim; n->a1 = keep; }
+  return out;
+}
+Tensor Tensor::mean(int dim, bool keep) const {
+  VB_OUT1(vb_mean(&d_, dim, keep, &o_), "mean");
+  if (Node* n = record(Op::Mean, {this}, out)) { n->a0 = dim; n->a1 = keep; }
+  return out;
+}
+Tensor Tensor::softmax(int dim) const {
+  VB_OUT1(vb_softmax(&d_, dim, &o_), "softmax");
+  if (Node* n = record(Op::Softmax, {this}, out)) n->a0 = dim;
+  return out;
+}
+Tensor Tensor::layernorm(const Tensor& w, const Tensor& b, float eps) const {
+  VB_OUT1(vb_layernorm(&d_, &w.d_, &b.d_, eps, &o_), "layernorm");
+  if (Node* n = record(Op::LayerNorm, {this, &w, &b}, out)) n->f0 = eps;
+  return out;
+}
+Tensor Tensor::embedding(const Tensor& weight) const {
+  VB_OUT1(vb_embedding(&d_, &weight.d_, &o_), "embedding");
+  record(Op::Embedding, {this, &weight}, out);
+  return out;
+}
+Tensor Tensor::cross_entropy(const Tensor& targets) const {
+  bool rec = t_enabled && (requires_grad() || targets.requires_grad());
+  vb_tensor o_, st_;
+  check(vb_cross_entropy(&d_, &targets.d_, &o_, rec ? &st_ : nullptr), "cross_entropy");
+  Tensor out = Tensor::adopt(o_);
+  Tensor stats; if (rec) stats = Tensor::adopt(st_);
+  if (Node* n = record(Op::CrossEntropy, {this, &targets}, out)) n->extra = stats;
+  return out;
+}
+Tensor Tensor::conv2d(const Tensor& w, const Tensor& b, int stride, int padding) const {
+  VB_OUT1(vb_conv2d(&d_, &w.d_, &b.d_, stride, padding, &o_), "conv2d");
+  if (Node* n = record(Op::Conv2d, {this, &w, &b}, out)) { n->a0 = stride; n->a1 = padding; }
+  return out;
+}
+Tensor Tensor::maxpool2d(int k, int s, int p) const {
+  VB_OUT1(vb_maxpool2d(&d_, k, s, p, &o_), "maxpool2d");
+  if (Node* n = record(Op::MaxPool2d, {this}, out)) { n->a0 = k; n->a1 = s; n->a2 = p; }
+  return out;
+}
+Tensor Tensor::avgpool2d(int k, int s, int p) const {
+  VB_OUT1(vb_avgpool2d(&d_, k, s, p, &o_), "avgpool2d");
+  if (Node* n = record(Op::AvgPool2d, {this}, out)) { n->a0 = k; n->a1 = s; n->a2 = p; }
+  return out;
+}
+Tensor Tensor::batchnorm(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const {
+  VB_OUT1(vb_batchnorm(&d_, &gamma.d_, &beta.d_, &rm.d_, &rv.d_, training, momentum, eps, &o_), "batchnorm");
+  if (Node* n = record(Op::BatchNorm, {this, &gamma, &beta, &rm, &rv}, out)) { n->a0 = training; n->f0 = eps; }
+  return out;
+}
+Tensor Tensor::fused_attention(const Tensor& k, const Tensor& v, const Tensor* mask) const {
+  std::vector<const Tensor*> ins = {this, &k, &v};
+  if (mask) ins.push_back(mask);
+  bool rec = false;
+  if (t_enabled) for (const Tensor* t : ins) rec = rec || t->requires_grad();
+  vb_tensor o_, p_;
+  check(vb_fused_attention(&d_, &k.d_, &v.d_, mask ? &mask->d_ : nullptr, &o_, rec ? &p_ : nullptr), "fused_attention");
+  Tensor out = Tensor::adopt(o_);
+  Tensor probs; if (rec) probs = Tensor::adopt(p_);
+  if (Node* n = record(Op::FusedAttention, ins, out)) n->extra = probs;
+  return out;
+}
+Tensor Tensor::linear(const Tensor& weight, const Tensor* bias) const {
+  VB_OUT1(vb_linear(&d_, &weight.d_, bias ? &bias->d_ : nullptr, &o_), "linear");
+  std::vector<const Tensor*> ins = {this, &weight};
+  if (bias) ins.push_back(bias);
+  record(Op::Linear, ins, out);
+  return out;
+}
+// reshape / transpose / permute: views (tensor.rs:493-642); reshape of a strided view copies first.
+Tensor Tensor::reshape(const std::vector<i64>& shape) const {
+  i64 n = 1; for (i64 d : shape) n *= d;
+  if (n != numel()) throw Error("Reshape numel must match");
+  Tensor c = contiguous();
+  vb_tensor d = contiguous_desc(shape); d.offset = c.d_.offset;
+  Tensor out = view_of(c, d);
+  out.meta_->requires_grad = c.requires_grad(); out.meta_->node = c.node_id();
+  if (t_enabled && requires_grad()) { out.set_requires_grad(true); push(Op::Reshape, {this}, out); }
+  return out;
+}
+Tensor Tensor::transpose(int d0, int d1) const {
+  if (d0 < 0 || d1 < 0 || d0 >= d_.rank || d1 >= d_.rank) throw Error("transpose dims out of bounds");
+  vb_tensor d = d_;
+  std::swap(d.dims[d0], d.dims[d1]); std::swap(d.strides[d0], d.strides[d1]);
+  Tensor out = view_of(*this, d);
+  out.meta_->requires_grad = requires_grad(); out.meta_->node = node_id();
+  if (t_enabled && requires_grad()) { Node& n = push(Op::Transpose, {this}, out); n.a0 = d0; n.a1 = d1; }
+  return out;
+}
+Tensor Tensor::permute(const std::vector<i64>& axes) const {
+  if ((int)axes.size() != d_.rank) throw Error("permute needs one axis per dim");
+  vb_tensor d = d_;
+  for (int i = 0; i < d_.rank; ++i) { d.dims[i] = d_.dims[axes[i]]; d.strides[i] = d_.strides[axes[i]]; }
+  Tensor out = view_of(*this, d);
+  out.meta_->requires_grad = requires_grad(); out.meta_->node = node_id();
+  if (t_enabled && requires_grad()) { Node& n = push(Op::Permute, {this}, out); n.axes = axes; }
+  return out;
+}
+
+// ---- backward ----------------------------------------------------------------------------------
+namespace {
+Tensor reduce_to(const Tensor& g, const std::vector<i64>& target) {
+  if (g.shape() == target) return g;
+  vb_tensor o; check(vb_reduce_to(&g.desc(), target.data(), (int)target.size(), &o), "reduce_to");
+  return Tensor::adopt(o);
+}
+Tensor scaled(const Tensor& g, float a) { vb_tensor o; check(vb_scale(&g.desc(), a, &o), "scale"); return Tensor::adopt(o); }
+// expand_reduce_grad (lib.rs:410-425): zeros of the input shape + the (re-inserted) reduced gradient
+Tensor expand_reduce_grad(const Tensor& go, const std::vector<i64>& in_shape, int dim, bool keep) {
+  Tensor gk = go;
+  if (!keep) { std::vector<i64> d = go.shape(); d.insert(d.begin() + dim, 1); gk = go.reshape(d); }
+  return Tensor::zeros(in_shape).add(gk);
+}
+struct Restore { ~Restore() { t_enabled = true; } };
+
+void publish_leaf(const Node& leaf, Tensor& grad) {
+  vb_slot key = leaf.leaf.slot();
+  auto it = t_sinks.index.find(key);
+  if (it != t_sinks.index.end()) {
+    const Tensor& sink = t_sinks.sinks[it->second];
+    if (sink.numel() != grad.numel()) throw Error("gradient sink size mismatch");
+    check(vb_copy(&sink.desc(), &grad.desc()), "copy into gradient buffer");
+    t_grads[key] = sink;
+    if (t_sinks.on_ready) t_sinks.on_ready(it->second, t_sinks.user);
+  } else t_grads[key] = grad;
+}
+}  // namespace
+
+void Tensor::backward() const {
+  if (numel() != 1) throw Error("backward can only be called on scalar tensors");
+  t_enabled = false;
+  Restore restore;
+  int out_idx = live_index(*this);
+  if (out_idx < 0) return;
+  std::vector<Node> nodes = std::move(t_tape.nodes);
+  t_tape.nodes.clear();
+  const int N = (int)nodes.size();
+  // earliest consumer of every node: once the walk has processed it, that node's gradient is final
+  std::vector<int> first_use(N, N);
+  for (const Node& n : nodes) for (int in : n.inputs) if (in >= 0 && n.id < first_use[in]) first_use[in] = n.id;
+  std::vector<Tensor> gm(N);
+  { float one = 1.0f; gm[out_idx] = Tensor::from_f32(&one, shape()); }
+  t_grads.clear();
+  for (int ni = N - 1; ni >= 0; --ni) {
+    Node& node = nodes[ni];
+    if (!gm[ni].defined()) { node.saved.clear(); node.extra = Tensor(); continue; }
+    if (node.op == Op::Leaf) continue;
+    Tensor go = std::move(gm[ni]); gm[ni] = Tensor();
+    const std::vector<Tensor>& sv = node.saved;
+    std::vector<Tensor> gin;
+    switch (node.op) {
+      case Op::Add: gin = {reduce_to(go, sv[0].shape()), reduce_to(go, sv[1].shape())}; break;
+      case Op::Sub: gin = {reduce_to(go, sv[0].shape()), reduce_to(scaled(go, -1.0f), sv[1].shape())}; break;
+      case Op::Mul: gin = {reduce_to(go.mul(sv[1]), sv[0].shape()), reduce_to(go.mul(sv[0]), sv[1].shape())}; break;
+      case Op::Div: {
+        Tensor gl = go.div(sv[1]);
+        Tensor gr = scaled(go, -1.0f).mul(sv[0]).div(sv[1].mul(sv[1]));
+        gin = {reduce_to(gl, sv[0].shape()), reduce_to(gr, sv[1].shape())}; break;
+      }
+      case Op::Matmul: {
+        Tensor lt = sv[0].transpose(sv[0].rank() - 2, sv[0].rank() - 1);
+        Tensor rt = sv[1].transpose(sv[1].rank() - 2, sv[1].rank() - 1);
+        gin = {reduce_to(go.matmul(rt), sv[0].shape()), reduce_to(lt.matmul(go), sv[1].shape())}; break;
+      }
+      case Op::Reshape: gin = {go.reshape(sv[0].shape())}; break;
+      case Op::Transpose: gin = {go.transpose((int)node.a0, (int)node.a1)}; break;
+      case Op::Permute: { std::vector<i64> inv(node.axes.size()); for (size_t i = 0; i < node.axes.size(); ++i) inv[node.axes[i]] = (i64)i; gin = {go.permute(inv)}; break; }
+      case Op::Relu: { vb_tensor o; check(vb_relu_backward(&sv[0].desc(), &go.desc(), &o), "relu_backward"); gin = {Tensor::adopt(o)}; break; }
+      case Op::Gelu: { vb_tensor o; check(vb_gelu_backward(&sv[0].desc(), &go.desc(), &o), "gelu_backward"); gin = {Tensor::adopt(o)}; break; }
+      case Op::Softmax: { vb_tensor o; check(vb_softmax_backward(&sv[0].desc(), &go.desc(), (int)node.a0, &o), "softmax_backward"); gin = {Tensor::adopt(o)}; break; }
+      case Op::LayerNorm: {
+        vb_tensor gx, gw, gb;
+        check(vb_layernorm_backward(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), &go.desc(), node.f0, &gx, &gw, &gb), "layernorm_backward");
+        gin = {Tensor::adopt(gx), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
+      }
+      case Op::BatchNorm: {
+        vb_tensor gx, gw, gb;
+        check(vb_batchnorm_backward(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), &sv[3].desc(), &sv[4].desc(), &go.desc(),
+                                    (int)node.a0, node.f0, &gx, &gw, &gb), "batchnorm_backward");
+        gin = {Tensor::adopt(gx), Tensor::adopt(gw), Tensor::adopt(gb), Tensor(), Tensor()}; break;
+      }
+      case Op::Embedding: { vb_tensor o; check(vb_embedding_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), &o), "embedding_backward"); gin = {Tensor(), Tensor::adopt(o)}; break; }
+      case Op::CrossEntropy: {
+        vb_tensor o;
+        check(vb_cross_entropy_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), node.extra.defined() ? &node.extra.desc() : nullptr, &o), "cross_entropy_backward");
+        gin = {Tensor::adopt(o), Tensor()}; break;
+      }
+      case Op::FusedAttention: {
+        vb_tensor dq, dk, dv;
+        check(vb_fused_attention_backward(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), sv.size() > 3 ? &sv[3].desc() : nullptr, &go.desc(),
+                                          node.extra.defined() ? &node.extra.desc() : nullptr, &dq, &dk, &dv), "fused_attention_backward");
+        gin = {Tensor::adopt(dq), Tensor::adopt(dk), Tensor::adopt(dv)};
+        if (sv.size() > 3) gin.push_back(Tensor());
+        break;
+      }
+      case Op::Conv2d: {
+        vb_tensor gi, gw, gb;
+        check(vb_conv2d_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), (int)node.a0, (int)node.a1, &gi, &gw, &gb), "conv2d_backward");
+        gin = {Tensor::adopt(gi), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
+      }
+      case Op::MaxPool2d: { vb_tensor o; check(vb_maxpool2d_backward(&sv[0].desc(), &go.desc(), (int)node.a0, (int)node.a1, (int)node.a2, &o), "maxpool2d_backward"); gin = {Tensor::adopt(o)}; break; }
+      case Op::AvgPool2d: { vb_tensor o; check(vb_avgpool2d_backward(&sv[0].desc(), &go.desc(), (int)node.a0, (int)node.a1, (int)node.a2, &o), "avgpool2d_backward"); gin = {Tensor::adopt(o)}; break; }
+      case Op::Sum: gin = {expand_reduce_grad(go, sv[0].shape(), (int)node.a0, node.a1 != 0)}; break;
+      case Op::Mean: {
+        Tensor e = expand_reduce_grad(go, sv[0].shape(), (int)node.a0, node.a1 != 0);
+        gin = {scaled(e, 1.0f / (float)sv[0].shape()[node.a0])}; break;
+      }
+      case Op::Linear: {
+        bool need_x = node.inputs[0] >= 0, need_w = node.inputs[1] >= 0, need_b = sv.size() > 2 && node.inputs[2] >= 0;
+        vb_tensor gx, gw, gb;
+        check(vb_linear_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), need_x ? &gx : nullptr, need_w ? &gw : nullptr, need_b ? &gb : nullptr), "linear_backward");
+        gin = {need_x ? Tensor::adopt(gx) : Tensor(), need_w ? Tensor::adopt(gw) : Tensor()};
+        if (sv.size() > 2) gin.push_back(need_b ? Tensor::adopt(gb) : Tensor());
+        break;
+      }
+      case Op::Leaf: break;
+    }
+    go = Tensor();
+    for (size_t i = 0; i < node.inputs.size(); ++i) {
+      int id = node.inputs[i];
+      if (id < 0 || !gin[i].defined()) continue;
+      if (!gm[id].defined()) gm[id] = gin[i];
+      else if (gm[id].storage_unique() && gm[id].is_contiguous() && gm[id].shape() == gin[i].shape())
+        check(vb_accumulate(&gm[id].desc(), &gin[i].desc()), "accumulate");          // existing += new
+      else gm[id] = gm[id].add(gin[i]);                                              // existing + new (lib.rs:736-737)
+    }
+    gin.clear();
+    // leaves whose last contribution this was: publish now
+    for (int id : node.inputs)
+      if (id >= 0 && nodes[id].op == Op::Leaf && first_use[id] == ni && gm[id].defined()) { publish_leaf(nodes[id], gm[id]); gm[id] = Tensor(); }
+    node.saved.clear(); node.extra = Tensor();
+  }
+  t_tape.generation++;
+}
+
+bool Tensor::grad(Tensor* out) const {
+  auto it = t_grads.find(d_.slot);
+  if (it == t_grads.end()) return false;
+  *out = it->second;
+  return true;
+}
+
+}  // namespace vearo

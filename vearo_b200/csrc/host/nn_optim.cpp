@@ -1,0 +1,231 @@
+// Layers, the five workload graphs, and the optimizers, above the C ABI.
+//
+// Layers follow crates/vearo-nn/src/lib.rs: Linear (63-137), LayerNorm (510-543),
+// MultiHeadAttention (546-633), TransformerBlock pre-LN (636-688), SimpleGPT (691-808).  Where the
+// reference emits `transpose -> matmul -> add` for a Linear, this host layer issues one fused
+// `linear` op (a GEMM with a bias epilogue and a single backward node); the unfused ops stay
+// available on Tensor for arbitrary graphs.  Parameters are created zero-filled / unit-filled and
+// are meant to be overwritten by the caller (tests and benchmarks upload seeded arrays), in the
+// order of the reference's `parameters()` methods.
+//
+// Optimizers follow crates/vearo-optim/src/lib.rs: AdamW::step (105-123), SGD::step (33-46),
+// clip_grad_norm (360-383), CosineSchedule::lr_at (336-348) — with state on the device and one
+// fused launch for all parameters.
+#include "vearo_host.h"
+#include <cmath>
+
+namespace vearo {
+namespace nn {
+
+static Tensor filled(const std::vector<i64>& shape, float v) {
+  i64 n = 1; for (i64 d : shape) n *= d;
+  std::vector<float> h((size_t)n, v);
+  Tensor t = Tensor::from_f32(h.data(), shape);
+  t.set_requires_grad(true);
+  return t;
+}
+static Tensor param_zeros(const std::vector<i64>& shape) { Tensor t = Tensor::zeros(shape); t.set_requires_grad(true); return t; }
+
+Linear::Linear(i64 in, i64 out, bool b) : has_bias(b) {
+  if (in <= 0) throw Error("in_features must be greater than 0");
+  weight = param_zeros({out, in});
+  if (b) bias = param_zeros({out});
+}
+Tensor Linear::forward(const Tensor& x) const { return x.linear(weight, has_bias ? &bias : nullptr); }
+void Linear::parameters(std::vector<Tensor>& out) const { out.push_back(weight); if (has_bias) out.push_back(bias); }
+
+LayerNorm::LayerNorm(i64 dim, float e) : eps(e) { weight = filled({dim}, 1.0f); bias = filled({dim}, 0.0f); }
+
+MultiHeadAttention::MultiHeadAttention(i64 d, i64 h) : q(d, d, true), k(d, d, true), v(d, d, true), o(d, d, true), n_head(h), n_embd(d) {
+  if (d % h != 0) throw Error("n_embd must be divisible by n_head");
+}
+Tensor MultiHeadAttention::forward(const Tensor& x, const Tensor* mask) const {
+  std::vector<i64> s = x.shape();
+  i64 b = s[0], t = s[1], d = n_embd, h = n_head, dk = d / h;
+  Tensor qq = q.forward(x).reshape({b, t, h, dk}).transpose(1, 2);
+  Tensor kk = k.forward(x).reshape({b, t, h, dk}).transpose(1, 2);
+  Tensor vv = v.forward(x).reshape({b, t, h, dk}).transpose(1, 2);
+  Tensor a = qq.fused_attention(kk, vv, mask);
+  return o.forward(a.transpose(1, 2).reshape({b, t, d}));
+}
+void MultiHeadAttention::parameters(std::vector<Tensor>& out) const { q.parameters(out); k.parameters(out); v.parameters(out); o.parameters(out); }
+
+TransformerBlock::TransformerBlock(i64 d, i64 h, i64 ff) : ln1(d), ln2(d), attn(d, h), fc1(d, ff, true), fc2(ff, d, true) {}
+Tensor TransformerBlock::forward(const Tensor& x, const Tensor* mask) const {
+  Tensor x1 = x.add(attn.forward(ln1.forward(x), mask));
+  return x1.add(fc2.forward(fc1.forward(ln2.forward(x1)).gelu()));
+}
+void TransformerBlock::parameters(std::vector<Tensor>& out) const {
+  ln1.parameters(out); attn.parameters(out); ln2.parameters(out); fc1.parameters(out); fc2.parameters(out);
+}
+
+SimpleGPT::SimpleGPT(i64 vocab, i64 max_seq, i64 d, i64 h, i64 n_layer, i64 ff) : ln_f(d), lm_head(d, vocab, false), n_embd(d) {
+  tok = param_zeros({vocab, d}); pos = param_zeros({max_seq, d});
+  for (i64 i = 0; i < n_layer; ++i) blocks.emplace_back(d, h, ff);
+}
+std::vector<Tensor> SimpleGPT::parameters() const {
+  std::vector<Tensor> p = {tok, pos};
+  for (const auto& b : blocks) b.parameters(p);
+  ln_f.parameters(p); lm_head.parameters(p);
+  return p;
+}
+// SimpleGPT::forward (lib.rs:741-793).  The reference rebuilds the position ids and the causal
+// mask on the CPU device at every call; here they are uploaded once per (B, S) and reused.
+Tensor SimpleGPT::loss(const Tensor& ids, const Tensor& targets) {
+  std::vector<i64> s = ids.shape();
+  i64 b = s[0], t = s[1];
+  if (b != cached_b_ || t != cached_s_) {
+    std::vector<float> pd((size_t)(b * t)), md((size_t)(t * t), 0.0f);
+    for (i64 r = 0; r < b; ++r) for (i64 c = 0; c < t; ++c) pd[r * t + c] = (float)c;
+    for (i64 r = 0; r < t; ++r) for (i64 c = r + 1; c < t; ++c) md[r * t + c] = -1e9f;
+    pos_ids_ = Tensor::from_f32(pd.data(), {b, t});
+    mask_ = Tensor::from_f32(md.data(), {t, t});
+    cached_b_ = b; cached_s_ = t;
+  }
+  Tensor h = ids.embedding(tok).add(pos_ids_.embedding(pos));
+  for (const auto& blk : blocks) h = blk.forward(h, &mask_);
+  Tensor logits = lm_head.forward(ln_f.forward(h).reshape({b * t, n_embd}));
+  return logits.cross_entropy(targets.reshape({b * t}));
+}
+
+MLP::MLP(const std::vector<i64>& sizes) { for (size_t i = 0; i + 1 < sizes.size(); ++i) layers.emplace_back(sizes[i], sizes[i + 1], true); }
+std::vector<Tensor> MLP::parameters() const { std::vector<Tensor> p; for (const auto& l : layers) l.parameters(p); return p; }
+Tensor MLP::forward(const Tensor& x) const {
+  Tensor h = x;
+  for (size_t i = 0; i < layers.size(); ++i) { h = layers[i].forward(h); if (i + 1 < layers.size()) h = h.relu(); }
+  return h;
+}
+Tensor MLP::loss(const Tensor& x, const Tensor& y) { Tensor diff = forward(x).sub(y); return diff.mul(diff).mean(0, false); }
+
+ConvNet::ConvNet(const std::vector<i64>& ch, i64 n_class) : fc(ch.back(), n_class, true) {
+  for (size_t i = 0; i + 1 < ch.size(); ++i) {
+    Stage st;
+    st.w = param_zeros({ch[i + 1], ch[i], 3, 3}); st.b = param_zeros({ch[i + 1]});
+    st.gamma = filled({ch[i + 1]}, 1.0f); st.beta = filled({ch[i + 1]}, 0.0f);
+    std::vector<float> ones((size_t)ch[i + 1], 1.0f);
+    st.rm = Tensor::zeros({ch[i + 1]}); st.rv = Tensor::from_f32(ones.data(), {ch[i + 1]});
+    stages.push_back(st);
+  }
+}
+std::vector<Tensor> ConvNet::parameters() const {
+  std::vector<Tensor> p;
+  for (const auto& s : stages) { p.push_back(s.w); p.push_back(s.b); p.push_back(s.gamma); p.push_back(s.beta); }
+  fc.parameters(p);
+  return p;
+}
+Tensor ConvNet::loss(const Tensor& x, const Tensor& labels) {
+  Tensor h = x;
+  for (const auto& s : stages)
+    h = h.conv2d(s.w, s.b, 1, 1).batchnorm(s.gamma, s.beta, s.rm, s.rv, autograd::is_training(), momentum, eps).relu().maxpool2d(2, 2, 0);
+  std::vector<i64> sh = h.shape();
+  h = h.avgpool2d((int)sh[2], (int)sh[2], 0).reshape({sh[0], sh[1]});
+  return fc.forward(h).cross_entropy(labels);
+}
+
+FusedOpBench::FusedOpBench(i64 c, i64 v) : ln(c), head(c, v, false) {}
+std::vector<Tensor> FusedOpBench::parameters() const { std::vector<Tensor> p; ln.parameters(p); head.parameters(p); return p; }
+Tensor FusedOpBench::loss(const Tensor& x, const Tensor& labels) { return head.forward(ln.forward(x).gelu()).cross_entropy(labels); }
+
+}  // namespace nn
+
+namespace optim {
+
+Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params, bool data_parallel) : cfg_(cfg), params_(params), dp_(data_parallel) {
+  // one flat gradient arena, parameters in registration order, every view 16-byte aligned
+  i64 total = 0;
+  std::vector<i64> offs;
+  for (const Tensor& p : params_) {
+    if (!p.is_contiguous()) throw Error("optimizer parameters must be contiguous");
+    offs.push_back(total); total += (p.numel() + 3) & ~i64(3);
+  }
+  arena_ = Tensor::zeros({total > 0 ? total : 1});
+  std::vector<vb_tensor> pd, gd;
+  for (size_t i = 0; i < params_.size(); ++i) {
+    vb_tensor d = params_[i].desc(); d.slot = arena_.slot(); d.offset = offs[i];
+    i64 s = 1; for (int k = d.rank - 1; k >= 0; --k) { d.strides[k] = s; s *= d.dims[k]; }
+    sinks_.push_back(Tensor::view_of(arena_, d));
+    pd.push_back(params_[i].desc()); gd.push_back(d);
+  }
+  check(vb_opt_create(&cfg_, pd.data(), gd.data(), (int)params_.size(), &opt_), "opt_create");
+  int rank = 0;
+  check(vb_dp_world(&rank, &world_), "dp_world");
+  if (!dp_) world_ = 1;
+  // buckets: contiguous arena ranges of >= 32 MiB, cut from the END of the arena backwards, because
+  // gradients become final in roughly reverse parameter order during the backward walk
+  bucket_of_.assign(params_.size(), 0);
+  const i64 target = (32ll << 20) / 4;
+  i64 end = total; int cnt = 0; i64 acc = 0;
+  std::vector<Bucket> rev;
+  for (int i = (int)params_.size() - 1; i >= 0; --i) {
+    acc = end - offs[i]; ++cnt;
+    bucket_of_[i] = (int)rev.size();
+    if (acc >= target || i == 0) { rev.push_back(Bucket{offs[i], acc, cnt, cnt}); end = offs[i]; cnt = 0; }
+  }
+  buckets_ = rev;
+  ready_.assign(params_.size(), 0);
+  autograd::register_grad_sinks(params_, sinks_, &Optimizer::on_ready, this);
+}
+Optimizer::~Optimizer() {
+  autograd::clear_grad_sinks(this);
+  if (opt_ >= 0) vb_opt_destroy(opt_);
+}
+void Optimizer::on_ready(int idx, void* self) {
+  Optimizer* o = (Optimizer*)self;
+  if (o->ready_[idx]) return;
+  o->ready_[idx] = 1;
+  if (o->world_ <= 1) return;
+  Bucket& b = o->buckets_[o->bucket_of_[idx]];
+  if (--b.pending == 0) check(vb_dp_allreduce(o->arena_.slot(), b.offset, b.numel), "dp_allreduce");
+}
+// Buckets with a parameter that received no gradient this step are still reduced (every rank must
+// issue the same collectives): their stale ranges are zeroed first.
+void Optimizer::finish_reduce() {
+  if (world_ > 1) {
+    for (size_t i = 0; i < params_.size(); ++i)
+      if (!ready_[i]) {
+        check(vb_fill(&sinks_[i].desc(), 0.0f), "fill");
+        Bucket& b = buckets_[bucket_of_[i]];
+        if (--b.pending == 0) check(vb_dp_allreduce(arena_.slot(), b.offset, b.numel), "dp_allreduce");
+      }
+    check(vb_dp_finish(30000), "dp_finish");
+    for (Bucket& b : buckets_) b.pending = b.nparams;
+  }
+}
+void Optimizer::step() {
+  finish_reduce();
+  check(vb_opt_step(opt_, ready_.data(), 0.0f, 1.0f / (float)world_, nullptr), "opt_step");
+  std::fill(ready_.begin(), ready_.end(), 0);
+}
+float Optimizer::clip_and_step(float max_norm, bool read_norm) {
+  finish_reduce();
+  float norm = 0.0f;
+  check(vb_opt_step(opt_, ready_.data(), max_norm, 1.0f / (float)world_, read_norm ? &norm : nullptr), "opt_step");
+  std::fill(ready_.begin(), ready_.end(), 0);
+  return norm;
+}
+void Optimizer::set_lr(float lr) { cfg_.lr = lr; check(vb_opt_set_lr(opt_, lr), "opt_set_lr"); }
+
+float clip_grad_norm(const std::vector<Tensor>& params, float max_norm) {
+  std::vector<vb_tensor> gd;
+  std::vector<Tensor> hold;
+  for (const Tensor& p : params) {
+    Tensor g;
+    if (!p.grad(&g)) continue;
+    if (!g.is_contiguous()) throw Error("clip_grad_norm expects contiguous grads");
+    hold.push_back(g); gd.push_back(g.desc());
+  }
+  float norm = 0.0f;
+  check(vb_clip_grad_norm(gd.data(), (int)gd.size(), max_norm, &norm), "clip_grad_norm");
+  return norm;
+}
+float cosine_lr(float base, float min_lr, uint32_t warmup, uint32_t total, uint32_t step) {
+  if (step < warmup) return base * ((float)step + 1.0f) / ((float)warmup + 1.0f);
+  if (step > total) return min_lr;
+  uint32_t denom = total > warmup ? total - warmup : 0; if (denom < 1) denom = 1;
+  float progress = (float)(step - warmup) / (float)denom;
+  float coeff = 0.5f * (1.0f + std::cos(3.14159265358979323846f * progress));
+  return min_lr + coeff * (base - min_lr);
+}
+
+}  // namespace optim
+}  // namespace vearo

@@ -1,0 +1,323 @@
+// LayerNorm and BatchNorm2d, forward and backward.
+//
+// LayerNorm follows crates/vearo-backend-cpu/src/lib.rs:667-858: two-pass mean / biased variance,
+// r = 1/sqrt(var + eps), y = ((x - mean) * r) * w + b;  backward recomputes mean and r per row,
+// a = sum(g*w), c = sum(g*w*xhat), dx = (C*g*w - a - xhat*c) * r / C, dw += g*xhat, db += g.
+// BatchNorm follows lib.rs:2067-2364 (biased batch variance for normalisation, Bessel factor only
+// in the running value, eval mode uses the running statistics).
+//
+// LayerNorm backward is the HBM-bound kernel of this file: one warp owns a row, reads x and g
+// exactly once into registers (128-bit loads), reduces with warp shuffles, and keeps its share of
+// dw/db in registers across all the rows it visits; partial dw/db rows (one per CTA) are then
+// summed in a fixed order by the column-sum kernel.  No atomics, bit-reproducible.
+// Algorithmic bytes per call: 3 * rows * C * 4 (read x, read g, write dx).
+#include "common.h"
+
+namespace vb {
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float bsum(float v, float* red) {
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = wsum(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  float r = lane < nw ? red[lane] : 0.0f;
+  return wsum(r);
+}
+
+// ---- LayerNorm, warp-per-row register-resident path (C % 4 == 0, C <= 128 * VPT) ------------
+template <int VPT>
+__global__ void __launch_bounds__(256) k_ln_fwd_warp(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                                     float* __restrict__ out, i64 rows, int C, float eps) {
+  int lane = threadIdx.x & 31;
+  i64 warp = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5;
+  i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
+  float fc = (float)C;
+  for (i64 r = warp; r < rows; r += nwarps) {
+    const float4* xr = reinterpret_cast<const float4*>(x + r * C);
+    float4 v[VPT];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      v[i] = col < C ? xr[i * 32 + lane] : make_float4(0, 0, 0, 0);
+      s += v[i].x + v[i].y + v[i].z + v[i].w;
+    }
+    float mean = wsum(s) / fc;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      if (col < C) { float a = v[i].x - mean, bb = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean; q += a * a + bb * bb + c * c + d * d; }
+    }
+    float inv = 1.0f / sqrtf(wsum(q) / fc + eps);
+    float4* orow = reinterpret_cast<float4*>(out + r * C);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      if (col < C) {
+        float4 ww = *reinterpret_cast<const float4*>(w + col), bb = *reinterpret_cast<const float4*>(b + col), o;
+        o.x = ((v[i].x - mean) * inv) * ww.x + bb.x; o.y = ((v[i].y - mean) * inv) * ww.y + bb.y;
+        o.z = ((v[i].z - mean) * inv) * ww.z + bb.z; o.w = ((v[i].w - mean) * inv) * ww.w + bb.w;
+        orow[i * 32 + lane] = o;
+      }
+    }
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(256) k_ln_bwd_warp(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ g,
+                                                     float* __restrict__ gx, float* __restrict__ part_w, float* __restrict__ part_b,
+                                                     i64 rows, int C, float eps) {
+  extern __shared__ float sm[];   // [warps][2][C] for the end-of-kernel combine
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  i64 warp = (i64)blockIdx.x * nw + wid;
+  i64 nwarps = (i64)gridDim.x * nw;
+  float fc = (float)C;
+  float4 aw[VPT], ab[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) { aw[i] = make_float4(0, 0, 0, 0); ab[i] = make_float4(0, 0, 0, 0); }
+  for (i64 r = warp; r < rows; r += nwarps) {
+    const float4* xr = reinterpret_cast<const float4*>(x + r * C);
+    const float4* gr = reinterpret_cast<const float4*>(g + r * C);
+    float4 v[VPT], gg[VPT];
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      bool ok = col < C;
+      v[i] = ok ? xr[i * 32 + lane] : make_float4(0, 0, 0, 0);
+      gg[i] = ok ? gr[i * 32 + lane] : make_float4(0, 0, 0, 0);
+      s += v[i].x + v[i].y + v[i].z + v[i].w;
+    }
+    float mean = wsum(s) / fc;
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      if (col < C) { float a = v[i].x - mean, bb = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean; q += a * a + bb * bb + c * c + d * d; }
+    }
+    float inv = 1.0f / sqrtf(wsum(q) / fc + eps);
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      if (col < C) {
+        float4 ww = *reinterpret_cast<const float4*>(w + col);
+        // x-hat overwrites x, g*w is recomputed below
+        v[i].x = (v[i].x - mean) * inv; v[i].y = (v[i].y - mean) * inv; v[i].z = (v[i].z - mean) * inv; v[i].w = (v[i].w - mean) * inv;
+        float p0 = gg[i].x * ww.x, p1 = gg[i].y * ww.y, p2 = gg[i].z * ww.z, p3 = gg[i].w * ww.w;
+        s1 += p0 + p1 + p2 + p3;
+        s2 += p0 * v[i].x + p1 * v[i].y + p2 * v[i].z + p3 * v[i].w;
+        aw[i].x += gg[i].x * v[i].x; aw[i].y += gg[i].y * v[i].y; aw[i].z += gg[i].z * v[i].z; aw[i].w += gg[i].w * v[i].w;
+        ab[i].x += gg[i].x; ab[i].y += gg[i].y; ab[i].z += gg[i].z; ab[i].w += gg[i].w;
+      }
+    }
+    s1 = wsum(s1); s2 = wsum(s2);
+    float4* orow = reinterpret_cast<float4*>(gx + r * C);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int col = (i * 32 + lane) * 4;
+      if (col < C) {
+        float4 ww = *reinterpret_cast<const float4*>(w + col), o;
+        o.x = (fc * gg[i].x * ww.x - s1 - v[i].x * s2) * inv / fc;
+        o.y = (fc * gg[i].y * ww.y - s1 - v[i].y * s2) * inv / fc;
+        o.z = (fc * gg[i].z * ww.z - s1 - v[i].z * s2) * inv / fc;
+        o.w = (fc * gg[i].w * ww.w - s1 - v[i].w * s2) * inv / fc;
+        orow[i * 32 + lane] = o;
+      }
+    }
+  }
+  // combine the warps of this CTA in warp order, then write one partial row per CTA
+  float* sw = sm + (size_t)wid * 2 * C;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int col = (i * 32 + lane) * 4;
+    if (col < C) { *reinterpret_cast<float4*>(sw + col) = aw[i]; *reinterpret_cast<float4*>(sw + C + col) = ab[i]; }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+    float t = 0.0f;
+    for (int k = 0; k < nw; ++k) t += sm[(size_t)k * 2 * C + c];
+    if (c < C) part_w[(i64)blockIdx.x * C + c] = t; else part_b[(i64)blockIdx.x * C + (c - C)] = t;
+  }
+}
+
+// ---- LayerNorm, generic path (any C): one block per row, rows re-read from L1/L2 ------------
+__global__ void k_ln_fwd_block(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                               float* __restrict__ out, float* __restrict__ stats, i64 C, float eps) {
+  __shared__ float red[32];
+  const float* xr = x + (i64)blockIdx.x * C;
+  float fc = (float)C;
+  float s = 0.0f;
+  for (i64 i = threadIdx.x; i < C; i += blockDim.x) s += xr[i];
+  float mean = bsum(s, red) / fc;
+  float q = 0.0f;
+  for (i64 i = threadIdx.x; i < C; i += blockDim.x) { float d = xr[i] - mean; q += d * d; }
+  float inv = 1.0f / sqrtf(bsum(q, red) / fc + eps);
+  if (out) for (i64 i = threadIdx.x; i < C; i += blockDim.x) out[(i64)blockIdx.x * C + i] = ((xr[i] - mean) * inv) * w[i] + b[i];
+  if (stats && threadIdx.x == 0) { stats[2 * (i64)blockIdx.x] = mean; stats[2 * (i64)blockIdx.x + 1] = inv; }
+}
+__global__ void k_ln_bwd_block(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ g,
+                               const float* __restrict__ stats, float* __restrict__ gx, i64 C) {
+  __shared__ float red[32];
+  i64 r = blockIdx.x;
+  const float* xr = x + r * C; const float* gr = g + r * C;
+  float mean = stats[2 * r], inv = stats[2 * r + 1], fc = (float)C;
+  float s1 = 0.0f, s2 = 0.0f;
+  for (i64 i = threadIdx.x; i < C; i += blockDim.x) { float xh = (xr[i] - mean) * inv, p = gr[i] * w[i]; s1 += p; s2 += p * xh; }
+  s1 = bsum(s1, red); s2 = bsum(s2, red);
+  for (i64 i = threadIdx.x; i < C; i += blockDim.x) {
+    float xh = (xr[i] - mean) * inv;
+    gx[r * C + i] = (fc * gr[i] * w[i] - s1 - xh * s2) * inv / fc;
+  }
+}
+__global__ void k_ln_bwd_cols(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ stats,
+                              float* __restrict__ gw, float* __restrict__ gb, i64 rows, i64 C) {
+  i64 c = blockIdx.x * (i64)blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float a = 0.0f, b = 0.0f;
+  for (i64 r = 0; r < rows; ++r) { float gg = g[r * C + c]; a += gg * ((x[r * C + c] - stats[2 * r]) * stats[2 * r + 1]); b += gg; }
+  gw[c] = a; gb[c] = b;
+}
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps) {
+  if (rows <= 0 || c <= 0) return VB_OK;
+  cudaStream_t st = ctx().stream;
+  ProfScope prof("layernorm_fwd", 2.0 * (double)rows * (double)c * 4.0);
+  bool fast = (c % 4 == 0) && c <= 1024 && al16(x) && al16(w) && al16(b) && al16(out);
+  if (fast) {
+    int vpt = (int)((c + 127) / 128);
+    i64 blocks = (rows + 7) / 8; i64 cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
+#define LN_FWD(V) case V: k_ln_fwd_warp<V><<<(unsigned)blocks, 256, 0, st>>>(x, w, b, out, rows, (int)c, eps); break;
+    switch (vpt) { LN_FWD(1) LN_FWD(2) LN_FWD(3) LN_FWD(4) LN_FWD(5) LN_FWD(6) LN_FWD(7) LN_FWD(8) }
+#undef LN_FWD
+  } else {
+    int t = 32; while (t < 256 && t * 4 < c) t <<= 1;
+    k_ln_fwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, b, out, nullptr, c, eps);
+  }
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps) {
+  if (c <= 0) return VB_OK;
+  cudaStream_t st = ctx().stream;
+  if (rows <= 0) { VB_TRY(launch_fill(gw, 0.0f, c)); return launch_fill(gb, 0.0f, c); }
+  ProfScope prof("layernorm_bwd", 3.0 * (double)rows * (double)c * 4.0);
+  bool fast = (c % 4 == 0) && c <= 1024 && al16(x) && al16(w) && al16(g) && al16(gx);
+  if (fast) {
+    int vpt = (int)((c + 127) / 128);
+    const int warps = 8;
+    i64 blocks = (rows + warps - 1) / warps; i64 cap = (i64)ctx().sm_count * 2; if (blocks > cap) blocks = cap;
+    size_t smem = (size_t)warps * 2 * c * sizeof(float);   // <= 64 KiB at C = 1024
+    void* part = nullptr;
+    VB_TRY(scratch_alloc((size_t)(2 * blocks * c) * sizeof(float), &part));
+    float* pw = (float*)part; float* pb = pw + blocks * c;
+#define LN_BWD(V) case V: \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(k_ln_bwd_warp<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      k_ln_bwd_warp<V><<<(unsigned)blocks, warps * 32, smem, st>>>(x, w, g, gx, pw, pb, rows, (int)c, eps); break;
+    switch (vpt) { LN_BWD(1) LN_BWD(2) LN_BWD(3) LN_BWD(4) LN_BWD(5) LN_BWD(6) LN_BWD(7) LN_BWD(8) }
+#undef LN_BWD
+    int rc = launch_colsum(pw, gw, blocks, c, false);
+    if (rc == VB_OK) rc = launch_colsum(pb, gb, blocks, c, false);
+    scratch_free(part);
+    VB_TRY(rc);
+  } else {
+    void* stats = nullptr;
+    VB_TRY(scratch_alloc((size_t)(2 * rows) * sizeof(float), &stats));
+    int t = 32; while (t < 256 && t * 4 < c) t <<= 1;
+    k_ln_fwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, w, nullptr, (float*)stats, c, eps);
+    k_ln_bwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, g, (const float*)stats, gx, c);
+    k_ln_bwd_cols<<<(unsigned)((c + 127) / 128), 128, 0, st>>>(x, g, (const float*)stats, gw, gb, rows, c);
+    scratch_free(stats);
+  }
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+// ---- BatchNorm2d: one CTA per channel, x is [n, c, hw] ---------------------------------------
+__global__ void k_bn_fwd(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                         float* __restrict__ rm, float* __restrict__ rv, float* __restrict__ out,
+                         i64 n, i64 c, i64 hw, bool training, float momentum, float eps) {
+  __shared__ float red[32];
+  i64 cc = blockIdx.x;
+  i64 cnt = n * hw;
+  float m = (float)cnt;
+  float mean, var;
+  if (training) {
+    float s = 0.0f;
+    for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) s += x[((i / hw) * c + cc) * hw + i % hw];
+    mean = bsum(s, red) / m;
+    float q = 0.0f;
+    for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) { float d = x[((i / hw) * c + cc) * hw + i % hw] - mean; q += d * d; }
+    var = bsum(q, red) / m;
+    if (threadIdx.x == 0) {
+      float bessel = m > 1.0f ? m / (m - 1.0f) : 1.0f;
+      rm[cc] = (1.0f - momentum) * rm[cc] + momentum * mean;
+      rv[cc] = (1.0f - momentum) * rv[cc] + momentum * var * bessel;
+    }
+  } else { mean = rm[cc]; var = rv[cc]; }
+  float inv = 1.0f / sqrtf(var + eps), ga = gamma[cc], be = beta[cc];
+  for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) {
+    i64 idx = ((i / hw) * c + cc) * hw + i % hw;
+    out[idx] = ((x[idx] - mean) * inv) * ga + be;
+  }
+}
+int launch_batchnorm(const float* x, const float* gamma, const float* beta, float* rm, float* rv, float* out,
+                     i64 n, i64 c, i64 hw, bool training, float momentum, float eps) {
+  if (n * c * hw <= 0) return VB_OK;
+  k_bn_fwd<<<(unsigned)c, 1024, 0, ctx().stream>>>(x, gamma, beta, rm, rv, out, n, c, hw, training, momentum, eps);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+__global__ void k_bn_bwd(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ rm, const float* __restrict__ rv,
+                         const float* __restrict__ g, float* __restrict__ gx, float* __restrict__ gw, float* __restrict__ gb,
+                         i64 n, i64 c, i64 hw, bool training, float eps) {
+  __shared__ float red[32];
+  i64 cc = blockIdx.x;
+  i64 cnt = n * hw;
+  float m = (float)cnt;
+  float mean, var;
+  if (training) {
+    float s = 0.0f;
+    for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) s += x[((i / hw) * c + cc) * hw + i % hw];
+    mean = bsum(s, red) / m;
+    float q = 0.0f;
+    for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) { float d = x[((i / hw) * c + cc) * hw + i % hw] - mean; q += d * d; }
+    var = bsum(q, red) / m;
+  } else { mean = rm[cc]; var = rv[cc]; }
+  float inv = 1.0f / sqrtf(var + eps);
+  float sdy = 0.0f, sdyx = 0.0f;
+  for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) {
+    i64 idx = ((i / hw) * c + cc) * hw + i % hw;
+    float dy = g[idx];
+    sdy += dy; sdyx += dy * ((x[idx] - mean) * inv);
+  }
+  sdy = bsum(sdy, red); sdyx = bsum(sdyx, red);
+  if (threadIdx.x == 0) { gb[cc] = sdy; gw[cc] = sdyx; }
+  float ga = gamma[cc];
+  for (i64 i = threadIdx.x; i < cnt; i += blockDim.x) {
+    i64 idx = ((i / hw) * c + cc) * hw + i % hw;
+    float dy = g[idx];
+    if (training) { float xh = (x[idx] - mean) * inv; gx[idx] = (ga * inv / m) * (m * dy - sdy - xh * sdyx); }
+    else gx[idx] = dy * ga * inv;
+  }
+}
+int launch_batchnorm_backward(const float* x, const float* gamma, const float* rm, const float* rv, const float* g,
+                              float* gx, float* gw, float* gb, i64 n, i64 c, i64 hw, bool training, float eps) {
+  if (c <= 0) return VB_OK;
+  if (n * hw <= 0) { VB_TRY(launch_fill(gw, 0.0f, c)); return launch_fill(gb, 0.0f, c); }
+  k_bn_bwd<<<(unsigned)c, 1024, 0, ctx().stream>>>(x, gamma, rm, rv, g, gx, gw, gb, n, c, hw, training, eps);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+}  // namespace vb
