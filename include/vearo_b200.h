@@ -191,6 +191,8 @@ int vb_opt_step(int opt, const uint8_t* active, float max_norm, float grad_scale
  * "gelu_bwd", "cross_entropy_bwd", "adamw", "attn_softmax", ...): total milliseconds, number of
  * launches, and the summed algorithmic units (bytes for HBM-bound families, flops for GEMMs).
  * vb_profile_families writes a comma-separated list of the families seen so far. */
+/* Number of kernel-launcher invocations so far (each enqueues at least one kernel of this library). */
+int vb_launch_count(int64_t* count);
 int vb_profile_enable(int on);
 int vb_profile_reset(void);
 int vb_profile_read(const char* family, double* total_ms, int64_t* launches, double* units);

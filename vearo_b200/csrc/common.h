@@ -32,7 +32,8 @@ int set_error(int status, const std::string& msg);
 #define VB_CHECK(cond, msg) do { if (!(cond)) return ::vb::set_error(VB_ERR_INVALID, std::string(__func__) + ": " + (msg)); } while (0)
 #define VB_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return ::vb::set_error(VB_ERR_CUDA, std::string(__func__) + ": " #expr ": " + cudaGetErrorString(e_)); } while (0)
 #define VB_TRY(expr) do { int s_ = (expr); if (s_ != VB_OK) return s_; } while (0)
-#define VB_LAUNCH_CHECK() VB_CUDA(cudaGetLastError())
+extern int64_t g_launcher_calls;   // launcher invocations since start (each enqueues one or more kernels)
+#define VB_LAUNCH_CHECK() do { ++::vb::g_launcher_calls; VB_CUDA(cudaGetLastError()); } while (0)
 
 // Slots / arena (runtime.cu).
 int slot_alloc(i64 numel, bool zero, vb_slot* out);
