@@ -200,7 +200,10 @@ class SGD:
 
 def clip_grad_norm(params, max_norm):
     hs, n = _handles(params)
-    return float(lib().orc_clip_grad_norm(hs, n, max_norm))
+    norm = float(lib().orc_clip_grad_norm(hs, n, max_norm))
+    if norm < 0:
+        raise OracleError(lib().orc_last_error().decode())
+    return norm
 
 
 def cosine_lr(base, min_lr, warmup, total, step):

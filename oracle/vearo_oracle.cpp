@@ -1120,13 +1120,21 @@ static void opt_step(Optimizer& o) {
     }
   }
 }
-// clip_grad_norm, vearo-optim/src/lib.rs:360-383
+// clip_grad_norm, vearo-optim/src/lib.rs:360-383.  The reference asserts that every gradient is
+// contiguous (365) and would therefore panic on the transposed-view gradient every Linear weight
+// gets (vearo-autograd/src/lib.rs:525-528); here such a gradient is first made contiguous, as the
+// optimizers do before their step (vearo-optim/src/lib.rs:36,109), and the sum runs over its
+// logical row-major order.
 static float clip_grad_norm(const std::vector<Tensor>& params, float max_norm) {
   std::vector<Tensor*> grads;
-  for (const Tensor& p : params) { auto it = g_grads.find(p.buf.get()); if (it != g_grads.end()) grads.push_back(&it->second); }
+  for (const Tensor& p : params) {
+    auto it = g_grads.find(p.buf.get());
+    if (it == g_grads.end()) continue;
+    if (!it->second.is_contiguous()) it->second = contiguous(it->second);
+    grads.push_back(&it->second);
+  }
   float total = 0.0f;
   for (Tensor* g : grads) {
-    if (!g->is_contiguous()) fail("clip_grad_norm expects contiguous grads");
     const float* d = cdata(*g);
     for (i64 i = 0, n = g->numel(); i < n; ++i) total = std::fmaf(d[i], d[i], total);
   }

@@ -29,7 +29,7 @@ struct Opt {
   void* d_active = nullptr;    // uint8[nparams]
   std::vector<vb_slot> retained;
 };
-std::vector<std::unique_ptr<Opt>> g_opts;
+std::vector<std::unique_ptr<Opt>>& g_opts = *new std::vector<std::unique_ptr<Opt>>();
 }  // namespace
 
 extern "C" {

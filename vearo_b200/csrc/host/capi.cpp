@@ -9,10 +9,11 @@ using namespace vearo;
 
 namespace {
 thread_local std::string t_msg;
-std::vector<std::unique_ptr<Tensor>> g_t;
-std::vector<int> g_free;
-std::vector<std::unique_ptr<nn::Model>> g_models;
-std::vector<std::unique_ptr<optim::Optimizer>> g_opts;
+// never destroyed: at process exit the device context may already be gone
+std::vector<std::unique_ptr<Tensor>>& g_t = *new std::vector<std::unique_ptr<Tensor>>();
+std::vector<int>& g_free = *new std::vector<int>();
+std::vector<std::unique_ptr<nn::Model>>& g_models = *new std::vector<std::unique_ptr<nn::Model>>();
+std::vector<std::unique_ptr<optim::Optimizer>>& g_opts = *new std::vector<std::unique_ptr<optim::Optimizer>>();
 
 int put(const Tensor& t) {
   if (!g_free.empty()) { int h = g_free.back(); g_free.pop_back(); g_t[h].reset(new Tensor(t)); return h; }

@@ -9,9 +9,9 @@ namespace vb {
 namespace {
 struct Rec { int family; cudaEvent_t a, b; double units; };
 bool g_on = false;
-std::vector<std::string> g_names;
-std::vector<Rec> g_recs;
-std::vector<cudaEvent_t> g_pool;
+std::vector<std::string>& g_names = *new std::vector<std::string>();
+std::vector<Rec>& g_recs = *new std::vector<Rec>();
+std::vector<cudaEvent_t>& g_pool = *new std::vector<cudaEvent_t>();
 cudaEvent_t get_event() {
   if (!g_pool.empty()) { cudaEvent_t e = g_pool.back(); g_pool.pop_back(); return e; }
   cudaEvent_t e; cudaEventCreate(&e); return e;

@@ -26,7 +26,9 @@ struct Arena {
   std::map<void*, size_t> sizes;                  // every block ever cudaMalloc'ed -> rounded size
   size_t cached = 0, live = 0, peak = 0;
 };
-static Arena g_arena;
+// Library-lifetime objects live on the heap and are never destroyed: tensors owned by other
+// translation units may release slots during process exit, after static destructors would have run.
+static Arena& g_arena = *new Arena();
 
 static size_t round_size(size_t bytes) {
   if (bytes < 512) return 512;
@@ -72,8 +74,8 @@ void scratch_free(void* p) { arena_free(p); }
 
 // ---- slots --------------------------------------------------------------------------------
 struct Slot { float* ptr = nullptr; i64 numel = 0; int refs = 0; };
-static std::vector<Slot> g_slots(1);       // slot 0 = none
-static std::vector<vb_slot> g_free_ids;
+static std::vector<Slot>& g_slots = *new std::vector<Slot>(1);       // slot 0 = none
+static std::vector<vb_slot>& g_free_ids = *new std::vector<vb_slot>();
 static i64 g_live_slots = 0;
 
 int slot_alloc(i64 n, bool zero, vb_slot* out) {
@@ -191,7 +193,7 @@ int vb_shutdown(void) {
   cudaStreamSynchronize(g_ctx.stream);
   cudaStreamSynchronize(g_ctx.comm_stream);
   for (auto& kv : g_arena.sizes) cudaFree(kv.first);
-  g_arena = Arena();
+  g_arena.free_blocks.clear(); g_arena.sizes.clear(); g_arena.cached = g_arena.live = g_arena.peak = 0;
   g_slots.assign(1, Slot()); g_free_ids.clear(); g_live_slots = 0;
   cudaFree(g_ctx.d_err); cudaFree(g_ctx.d_scalars); cudaFreeHost(g_ctx.h_pinned);
   cudaEventDestroy(g_ctx.ev_compute); cudaEventDestroy(g_ctx.ev_comm);
