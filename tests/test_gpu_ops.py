@@ -438,3 +438,61 @@ def test_slot_lifecycle(vb):
     vb.vb_check(L.vb_release(s.value, C.byref(freed))); assert freed.value == 1
     assert L.vb_release(s.value, C.byref(freed)) != 0          # already gone: an error, not a crash
     assert vb.memory_stats()["live_slots"] == before
+
+
+# ---- tensor-core GEMM (3xTF32 on tcgen05): sizes large enough to leave the CUDA-core kernel -----------------
+@pytest.mark.parametrize("M,N,K,ta,tb", [
+    (300, 260, 200, False, False),    # partial tiles in M, N and K; B needs the K-contiguous repack
+    (256, 512, 768, False, True),     # both operands K-contiguous as stored: x . W^T
+    (512, 192, 136, True, False),     # A transposed view (weight-gradient shape), narrow N
+    (128, 64, 2048, True, True),      # BN = 64 tile
+    (256, 256, 8192, False, True),    # few tiles, long K: split-K
+    (1000, 1000, 72, False, True),    # short K (attention-score shape)
+])
+def test_matmul_tensor_core(vb, M, N, K, ta, tb):
+    a = rnd(60, *((K, M) if ta else (M, K)), scale=0.05)
+    b = rnd(61, *((N, K) if tb else (K, N)), scale=0.05)
+
+    def case(T, m):
+        x, y = T.from_numpy(a), T.from_numpy(b)
+        if ta: x = x.transpose(0, 1)
+        if tb: y = y.transpose(0, 1)
+        return [x.matmul(y)]
+    both(vb, case)
+    # the split-precision product must sit at FP32 accuracy, far from plain TF32's 1e-3
+    x = vb.Tensor.from_numpy(a); y = vb.Tensor.from_numpy(b)
+    if ta: x = x.transpose(0, 1)
+    if tb: y = y.transpose(0, 1)
+    got = x.matmul(y).numpy().astype(np.float64)
+    ref = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
+    scale = np.abs(a.T if ta else a).astype(np.float64) @ np.abs(b.T if tb else b).astype(np.float64)
+    assert (np.abs(got - ref) / scale).max() < 2e-6
+
+
+def test_matmul_tensor_core_batched_views(vb):
+    """Head-split views [B,S,H,dk] -> [B,H,S,dk] consumed in place, both batch levels strided."""
+    B, S, H, dk = 2, 256, 4, 64
+    q0, k0, v0 = rnd(62, B, S, H * dk, scale=0.3), rnd(63, B, S, H * dk, scale=0.3), rnd(64, B, S, H * dk, scale=0.3)
+
+    def case(T, m):
+        q, k, v = (T.from_numpy(a).reshape([B, S, H, dk]).transpose(1, 2) for a in (q0, k0, v0))
+        s = q.matmul(k.transpose(2, 3))
+        return [s, s.matmul(v), s.transpose(2, 3).matmul(v)]
+    both(vb, case)
+
+
+def test_linear_tensor_core_with_bias_and_backward(vb):
+    x0, w0, b0, go = rnd(65, 512, 384, scale=0.5), rnd(66, 640, 384, scale=0.05), rnd(67, 640), rnd(68, 512, 640, scale=0.1)
+
+    def run(T, fused):
+        x, w, b = T.from_numpy(x0, True), T.from_numpy(w0, True), T.from_numpy(b0, True)
+        y = x.linear(w, b) if fused else x.matmul(w.transpose(0, 1)).add(b)
+        n = go.size
+        y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [t.numpy() for t in (y, x.grad(), w.grad().contiguous(), b.grad())]
+    orc.reset_all()
+    cpu = run(orc.Tensor, False)
+    vb.zero_gradients(); vb.reset_active_tape()
+    for g, c, n in zip(run(vb.Tensor, True), cpu, "y gx gw gb".split()):
+        assert_close(g, c, "linear(tc) " + n)
+    vb.check_errors()
