@@ -472,7 +472,7 @@ def test_matmul_tensor_core(vb, M, N, K, ta, tb):
 def test_matmul_tensor_core_batched_views(vb):
     """Head-split views [B,S,H,dk] -> [B,H,S,dk] consumed in place, both batch levels strided."""
     B, S, H, dk = 2, 256, 4, 64
-    q0, k0, v0 = rnd(62, B, S, H * dk, scale=0.3), rnd(63, B, S, H * dk, scale=0.3), rnd(64, B, S, H * dk, scale=0.3)
+    q0, k0, v0 = rnd(62, B, S, H * dk, scale=0.1), rnd(63, B, S, H * dk, scale=0.1), rnd(64, B, S, H * dk, scale=0.3)
 
     def case(T, m):
         q, k, v = (T.from_numpy(a).reshape([B, S, H, dk]).transpose(1, 2) for a in (q0, k0, v0))
