@@ -148,6 +148,25 @@ int vb_contiguous(const vb_tensor* x, vb_tensor* out);                /* device-
                                                                          round trip of vearo-core tensor.rs:349-368 */
 int vb_fill(const vb_tensor* dst, float value);
 
+/* ---- allocation-free LayerNorm backward (no counterpart in the reference) ------------------
+ * For callers that cannot allocate device memory where they need this kernel: code running inside a
+ * region where the allocator must not be touched, a loop with a fixed memory budget, a plugin that owns
+ * nothing but the buffers it was handed.  vb_layernorm_backward takes scratch for the per-CTA partial
+ * sums of dgamma / dbeta from the library's arena (and its outputs too); this variant allocates nothing:
+ * inputs and outputs are the caller's raw device pointers (contiguous f32, x / grad_out / gx of
+ * rows * c elements, w / gw / gb of c elements) and the partial sums go to a fixed 2.4 MB array inside
+ * the library image, present on every GPU that loads the library until the process exits.
+ *   - Limits: c a multiple of 4 and <= 1024; x, w, grad_out, gx 16-byte aligned.  Anything else is
+ *     rejected with VB_ERR_UNSUPPORTED and a message; use vb_layernorm_backward there.
+ *   - The first call on each device looks up the array's device address; make that call before
+ *     starting any stream capture.  Later calls do no set-up.
+ *   - All calls share the one array: two calls whose kernels may overlap on the GPU (different
+ *     streams) race on it.  Calls on one stream are safe back to back; nothing needs clearing between
+ *     them, since every partial row is rewritten in full.
+ *   - `stream` is a cudaStream_t (NULL = the default stream).  vb_init is not required. */
+int vb_layernorm_backward_noalloc(const float* x, const float* w, const float* grad_out, float* gx, float* gw, float* gb,
+                                  int64_t rows, int64_t c, float eps, void* stream);
+
 /* ---- fused linear-layer entry points (extras the binding may ignore) ---------------------
  * y = x . W^T + bias in one GEMM (Linear::forward, vearo-nn/src/lib.rs:120-128), and its
  * backward: gx = gy . W, gw = gy^T . x summed over all leading dims, gb = column sum of gy —

@@ -320,4 +320,81 @@ int launch_batchnorm_backward(const float* x, const float* gamma, const float* r
   return VB_OK;
 }
 
+
+// ---- LayerNorm backward without any allocation --------------------------------------------------
+// Some callers cannot allocate device memory at the point where they need this kernel: code that
+// runs inside a region where the allocator is off limits (a framework's capture or replay phase, a
+// real-time loop with a fixed memory budget, a plugin that was handed buffers and nothing else).
+// The regular entry point takes per-CTA partial sums of dgamma / dbeta from the arena; this variant
+// keeps them in a fixed array that is part of the library image instead.  The array is sized for
+// C <= 1024 and at most 296 CTAs: 2 * 296 * 1024 floats = 2.4 MB, resident on every GPU that loads
+// the library, for as long as the process lives.
+namespace {
+constexpr int kNoAllocMaxC = 1024;
+constexpr int kNoAllocMaxCtas = 296;
+static __device__ __align__(256) float g_ln_bwd_noalloc_scratch[2 * kNoAllocMaxCtas * kNoAllocMaxC];
+
+// The array's name is only meaningful in device code; host code needs its device address, looked up
+// once per device with that device current.
+struct NoAllocDevice { bool ready = false; float* scratch = nullptr; int sm_count = 0; };
+NoAllocDevice g_noalloc_dev[64];
+
+__global__ void k_ln_noalloc_finish(const float* __restrict__ part_w, const float* __restrict__ part_b,
+                                    float* __restrict__ gw, float* __restrict__ gb, int ctas, int C) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float a = 0.0f, b = 0.0f;
+  for (int i = 0; i < ctas; ++i) { a += part_w[(i64)i * C + c]; b += part_b[(i64)i * C + c]; }
+  gw[c] = a; gb[c] = b;
+}
+__global__ void k_ln_noalloc_zero(float* gw, float* gb, int C) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < C) { gw[c] = 0.0f; gb[c] = 0.0f; }
+}
+}  // namespace
 }  // namespace vb
+
+extern "C" int vb_layernorm_backward_noalloc(const float* x, const float* w, const float* grad_out, float* gx, float* gw, float* gb,
+                                             int64_t rows, int64_t c, float eps, void* stream) {
+  using namespace vb;
+  if (!x || !w || !grad_out || !gx || !gw || !gb) return set_error(VB_ERR_INVALID, "vb_layernorm_backward_noalloc: null pointer");
+  if (rows < 0 || c <= 0) return set_error(VB_ERR_INVALID, "vb_layernorm_backward_noalloc: bad shape");
+  if (c > kNoAllocMaxC || (c & 3))
+    return set_error(VB_ERR_UNSUPPORTED, "vb_layernorm_backward_noalloc: the row length must be a multiple of 4 and at most 1024 "
+                                         "(the fixed scratch array is sized for that); use vb_layernorm_backward for other sizes");
+  if (!al16(x) || !al16(w) || !al16(grad_out) || !al16(gx))
+    return set_error(VB_ERR_UNSUPPORTED, "vb_layernorm_backward_noalloc: x, w, grad_out and gx must be 16-byte aligned");
+  int dev = 0;
+  VB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(VB_ERR_UNSUPPORTED, "vb_layernorm_backward_noalloc: device ordinal out of range");
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.ready) {   // first call on this device: resolve the array's device address (not capturable; do it before any stream capture)
+    float* p = nullptr;
+    VB_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_bwd_noalloc_scratch));
+    VB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    d.scratch = p; d.ready = true;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const int C = (int)c;
+  if (rows == 0) {
+    k_ln_noalloc_zero<<<(C + 255) / 256, 256, 0, st>>>(gw, gb, C);
+    VB_CUDA(cudaGetLastError());
+    return VB_OK;
+  }
+  const int warps = 8;
+  i64 ctas = (rows + warps - 1) / warps;
+  i64 cap = (i64)d.sm_count * 2; if (cap > kNoAllocMaxCtas) cap = kNoAllocMaxCtas;
+  if (ctas > cap) ctas = cap;
+  // every CTA overwrites its own partial row in full, so nothing in the array needs clearing first
+  float* pw = d.scratch; float* pb = d.scratch + (size_t)kNoAllocMaxCtas * kNoAllocMaxC;
+  size_t smem = (size_t)warps * 2 * C * sizeof(float);
+  int vpt = (C + 127) / 128;
+#define LN_BWD_NA(V) case V: \
+    if (smem > 48 * 1024) VB_CUDA(cudaFuncSetAttribute(k_ln_bwd_warp<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    k_ln_bwd_warp<V><<<(unsigned)ctas, warps * 32, smem, st>>>(x, w, grad_out, gx, pw, pb, rows, C, eps); break;
+  switch (vpt) { LN_BWD_NA(1) LN_BWD_NA(2) LN_BWD_NA(3) LN_BWD_NA(4) LN_BWD_NA(5) LN_BWD_NA(6) LN_BWD_NA(7) LN_BWD_NA(8) }
+#undef LN_BWD_NA
+  k_ln_noalloc_finish<<<(C + 127) / 128, 128, 0, st>>>(pw, pb, gw, gb, (int)ctas, C);
+  VB_CUDA(cudaGetLastError());
+  return VB_OK;
+}
