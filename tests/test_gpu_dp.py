@@ -46,4 +46,9 @@ def test_two_ranks_match_single_process(tmp_path):
     np.testing.assert_allclose(two[0]["norms"], one["norms"], rtol=1e-4, atol=1e-6)
     np.testing.assert_allclose((two[0]["losses"] + two[1]["losses"]) / 2, one["losses"], rtol=1e-4, atol=1e-6)
     for k in keys:
+        i = int(k[1:])
+        if i >= 2 and (i - 2) % 16 == 5 and i < 2 + 16 * 2:
+            # the key-projection bias: its exact gradient is zero (a constant added to every key shifts all scores
+            # of a row equally), so what AdamW normalises there is rounding noise and the two runs need not agree
+            continue
         np.testing.assert_allclose(two[0][k], one[k], rtol=2e-3, atol=2e-5, err_msg=k)
