@@ -29,6 +29,7 @@
 // error word, drains what it has in flight, frees its tensor memory and returns.
 #include "common.h"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace vb {
 
@@ -36,7 +37,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;                    // f32 columns per stage: 64-byte rows, SWIZZLE_64B
-constexpr int kThreads = 192;
+constexpr int kConvWarps = 8;                 // converter / epilogue warps
+constexpr int kThreads = 64 + 32 * kConvWarps;
 constexpr uint32_t kSpinLimit = 1u << 20; // polls of try_wait (each waits a bounded time) before giving up
 
 struct TcParams {
@@ -46,6 +48,8 @@ struct TcParams {
   i64 nb1, nb2;
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
   int bn, stages, splits, kblocks_per_split;
+  int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
+  int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
   float alpha, beta;
   int* err;
 };
@@ -94,9 +98,25 @@ __device__ __forceinline__ uint64_t make_desc_k_sw64(uint32_t smem_addr) {
   d |= (uint64_t)4 << 61;                              // layout type: SWIZZLE_64B
   return d;
 }
-// Instruction descriptor: D = F32, A = B = TF32, both K-major, M = 128, N = bn.
-__device__ __forceinline__ uint32_t make_idesc(int bn) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Shared-memory matrix descriptor, MN-major.  For 32-bit operands the only MN-major layout the tensor core accepts
+// is the 128-byte swizzle with a 32-byte base: the tile is a row of 32-float (128-byte) MN blocks, each block BK rows
+// (k) of 128 bytes; blocks are 2048 bytes apart (leading offset), groups of 4 k rows 512 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((BK * 128) >> 4) << 16;              // leading byte offset: next 32-wide MN block
+  d |= (uint64_t)(512 >> 4) << 32;                     // stride byte offset: next group of 4 k rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;                              // layout type: SWIZZLE_128B_BASE32B
+  return d;
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t base, int ks, int mn_major) {
+  return mn_major ? make_desc_mn_sw128(base + ks * 1024) : make_desc_k_sw64(base + ks * 32);
+}
+// Instruction descriptor: D = F32, A = B = TF32, M = 128, N = bn, operand majors as given.
+__device__ __forceinline__ uint32_t make_idesc(int bn, int a_mn, int b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
+         ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -147,7 +167,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   const int nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&conv[s], 4); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&conv[s], kConvWarps); mbar_init(&empty[s], 1); }
     mbar_init(tmem_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -171,8 +191,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         uint8_t* st = smem + (size_t)s * stage_bytes;
         mbar_arrive_expect_tx(&full[s], raw_bytes);
         int k = (int)((kb0 + kb) * BK);
-        tma_load_4d(st, &map_a, &full[s], k, (int)(tile_m * BM), p.a_bcast2 ? 0 : b2, p.a_bcast1 ? 0 : b1);
-        tma_load_4d(st + a_bytes, &map_b, &full[s], k, (int)(tile_n * bn), p.b_bcast2 ? 0 : b2, p.b_bcast1 ? 0 : b1);
+        const int ab2 = p.a_bcast2 ? 0 : b2, ab1 = p.a_bcast1 ? 0 : b1, bb2 = p.b_bcast2 ? 0 : b2, bb1 = p.b_bcast1 ? 0 : b1;
+        if (!p.a_mn) tma_load_4d(st, &map_a, &full[s], k, (int)(tile_m * BM), ab2, ab1);
+        else for (int j = 0; j < BM / 32; ++j) tma_load_4d(st + j * (BK * 128), &map_a, &full[s], (int)(tile_m * BM) + 32 * j, k, ab2, ab1);
+        if (!p.b_mn) tma_load_4d(st + a_bytes, &map_b, &full[s], k, (int)(tile_n * bn), bb2, bb1);
+        else for (int j = 0; j < bn / 32; ++j) tma_load_4d(st + a_bytes + j * (BK * 128), &map_b, &full[s], (int)(tile_n * bn) + 32 * j, k, bb2, bb1);
         issued = kb + 1;
       }
       // after an abort: give the copies already issued a bounded time to land before the CTA exits
@@ -186,7 +209,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ---- MMA issuer ---------------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(bn);
+      const uint32_t idesc = make_idesc(bn, p.a_mn, p.b_mn);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         int s = kb % stages; uint32_t ph = (uint32_t)(kb / stages) & 1;
@@ -197,9 +220,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         uint32_t a_hi = st, b_hi = st + a_bytes, a_lo = st + raw_bytes, b_lo = st + raw_bytes + a_bytes;
 #pragma unroll
         for (int ks = 0; ks < BK / 8; ++ks) {
-          uint32_t off = ks * 32;   // 8 f32 = 32 bytes along K inside the 64-byte swizzle atom
-          uint64_t da_hi = make_desc_k_sw64(a_hi + off), db_hi = make_desc_k_sw64(b_hi + off);
-          uint64_t da_lo = make_desc_k_sw64(a_lo + off), db_lo = make_desc_k_sw64(b_lo + off);
+          // one MMA covers 8 k: 32 bytes along a K-major row, or one 1024-byte k group of an MN-major tile
+          uint64_t da_hi = make_desc(a_hi, ks, p.a_mn), db_hi = make_desc(b_hi, ks, p.b_mn);
+          uint64_t da_lo = make_desc(a_lo, ks, p.a_mn), db_lo = make_desc(b_lo, ks, p.b_mn);
           mma_tf32(tmem_base, da_lo, db_hi, idesc, (kb | ks) ? 1u : 0u);
           mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
           mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
@@ -210,7 +233,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     }
   } else {
     // ---- converters, then epilogue ------------------------------------------------------------
-    const int cw = warp - 2, ct = cw * 32 + lane;            // 0..127
+    const int cw = warp - 2, ct = cw * 32 + lane;            // 0 .. 32*kConvWarps-1
+    constexpr int kConvThreads = 32 * kConvWarps;
     bool ok = true;
     for (int kb = 0; kb < nkb && ok; ++kb) {
       int s = kb % stages; uint32_t ph = (uint32_t)(kb / stages) & 1;
@@ -218,12 +242,25 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       if (!ok) break;
       float4* hi = (float4*)(smem + (size_t)s * stage_bytes);
       float4* lo = (float4*)(smem + (size_t)s * stage_bytes + raw_bytes);
-      const int n4 = (int)(raw_bytes / 16);
-      for (int i = ct; i < n4; i += 128) {
-        float4 x = hi[i], h, l;
-        h.x = tf32_rna(x.x); h.y = tf32_rna(x.y); h.z = tf32_rna(x.z); h.w = tf32_rna(x.w);
-        l.x = tf32_rna(x.x - h.x); l.y = tf32_rna(x.y - h.y); l.z = tf32_rna(x.z - h.z); l.w = tf32_rna(x.w - h.w);
-        hi[i] = h; lo[i] = l;
+      const int n4 = (int)(raw_bytes / 16);      // 768, 1024 or 1536: a multiple of kConvThreads
+      if (p.raw_hi) {
+#pragma unroll 3
+        for (int i = ct; i < n4; i += kConvThreads) {
+          float4 x = hi[i], l;
+          l.x = tf32_rna(x.x - __uint_as_float(__float_as_uint(x.x) & 0xffffe000u));
+          l.y = tf32_rna(x.y - __uint_as_float(__float_as_uint(x.y) & 0xffffe000u));
+          l.z = tf32_rna(x.z - __uint_as_float(__float_as_uint(x.z) & 0xffffe000u));
+          l.w = tf32_rna(x.w - __uint_as_float(__float_as_uint(x.w) & 0xffffe000u));
+          lo[i] = l;
+        }
+      } else {
+#pragma unroll 3
+        for (int i = ct; i < n4; i += kConvThreads) {
+          float4 x = hi[i], h, l;
+          h.x = tf32_rna(x.x); h.y = tf32_rna(x.y); h.z = tf32_rna(x.z); h.w = tf32_rna(x.w);
+          l.x = tf32_rna(x.x - h.x); l.y = tf32_rna(x.y - h.y); l.z = tf32_rna(x.z - h.z); l.w = tf32_rna(x.w - h.w);
+          hi[i] = h; lo[i] = l;
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
       __syncwarp();
@@ -240,7 +277,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       float* out = direct ? p.C + (i64)b1 * p.c_b1 + (i64)b2 * p.c_b2 + row * p.c_rs
                           : p.partial + (((i64)split * nbatch + bz) * p.M + row) * p.N;
       const bool vec_ok = direct ? ((p.c_rs & 3) == 0 && (((uintptr_t)p.C | (uintptr_t)(p.c_b1 * 4) | (uintptr_t)(p.c_b2 * 4)) & 15) == 0) : ((p.N & 3) == 0);
-      for (int c0 = 0; c0 < bn; c0 += 32) {
+      const int half = (warp - 2) >> 2, ncol_half = bn / 2;      // two warps share a lane quarter; each takes half the columns
+      for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
         i64 col0 = tile_n * bn + c0;
         if (col0 >= p.N) break;
         uint32_t r[32];
@@ -339,7 +377,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-struct Operand { const float* p; i64 rows, rs, b1, b2; bool bc1, bc2; };   // K-contiguous [rows, K]
+struct Operand { const float* p; i64 rows, rs, b1, b2; bool bc1, bc2; bool mn; };   // [rows, K]; rs = row stride (K-major) or k stride (MN-major)
 
 bool tma_ok(const Operand& o, i64 nb1, i64 nb2) {
   if ((uintptr_t)o.p & 15) return false;
@@ -351,14 +389,16 @@ bool tma_ok(const Operand& o, i64 nb1, i64 nb2) {
 }
 int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int box_rows) {
   i64 d2 = o.bc2 ? 1 : nb2, d3 = o.bc1 ? 1 : nb1;
-  cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)o.rows, (cuuint64_t)d2, (cuuint64_t)d3};
+  // K-major: dims {K, rows}, one box of BK x box_rows, 64-byte swizzle.  MN-major: dims {rows, K}, boxes of 32 x BK, 128-byte swizzle on 32-byte units.
+  i64 inner = o.mn ? o.rows : K, outer = o.mn ? K : o.rows;
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)d2, (cuuint64_t)d3};
   // a batch level of extent 1 never advances: any 16-byte-multiple stride is acceptable there
-  i64 s2 = d2 > 1 ? o.b2 : o.rs * (o.rows > 0 ? o.rows : 1), s3 = d3 > 1 ? o.b1 : s2 * d2;
+  i64 s2 = d2 > 1 ? o.b2 : o.rs * (outer > 0 ? outer : 1), s3 = d3 > 1 ? o.b1 : s2 * d2;
   cuuint64_t strides[3] = {(cuuint64_t)o.rs * 4, (cuuint64_t)s2 * 4, (cuuint64_t)s3 * 4};
-  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)(o.mn ? 32 : BK), (cuuint32_t)(o.mn ? BK : box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)o.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           o.mn ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(VB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
   return VB_OK;
 }
@@ -379,8 +419,13 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   Temp hold_a, hold_b;
   auto prepare = [&](const float* p, i64 rows, i64 rs, i64 cs, i64 sb1, i64 sb2, Temp& hold, Operand* o) -> int {
     bool bc1 = g.nb1 > 1 && sb1 == 0, bc2 = g.nb2 > 1 && sb2 == 0;
-    *o = Operand{p, rows, rs, sb1, sb2, bc1, bc2};
+    *o = Operand{p, rows, rs, sb1, sb2, bc1, bc2, false};
     if (cs == 1 && tma_ok(*o, g.nb1, g.nb2)) return VB_OK;
+    // MN-contiguous (a transposed view): consumed in place through MN-major descriptors
+    static int no_mn = -1;
+    if (no_mn < 0) { const char* e = getenv("VB200_TC_NO_MN"); no_mn = (e && e[0] == '1') ? 1 : 0; }
+    Operand mn{p, rows, cs, sb1, sb2, bc1, bc2, true};
+    if (!no_mn && rs == 1 && rows >= 32 && tma_ok(mn, g.nb1, g.nb2)) { *o = mn; return VB_OK; }
     // repack into K-contiguous scratch, one plane per (non-broadcast) batch
     i64 e1 = bc1 ? 1 : g.nb1, e2 = bc2 ? 1 : g.nb2;
     i64 Kp = (g.K + 3) & ~i64(3);
@@ -390,7 +435,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (grid.y > 65535 || grid.z > 65535) return set_error(VB_ERR_UNSUPPORTED, "operand too tall to repack");
     k_repack_kmajor<<<grid, block, 0, ctx().stream>>>(p, (float*)hold.p, rows, g.K, Kp, rs, cs, e2, bc1 ? 0 : sb1, bc2 ? 0 : sb2);
     VB_LAUNCH_CHECK();
-    *o = Operand{(const float*)hold.p, rows, Kp, e2 * rows * Kp, rows * Kp, bc1, bc2};
+    *o = Operand{(const float*)hold.p, rows, Kp, e2 * rows * Kp, rows * Kp, bc1, bc2, false};
     return VB_OK;
   };
   Operand oa, ob;
@@ -399,6 +444,11 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
 
   TcParams p{};
   p.bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
+  if (p.bn == 256) {   // wave quantisation: with few 256-wide tiles, 128-wide ones fill the SMs better
+    i64 t256 = ((g.M + BM - 1) / BM) * ((g.N + 255) / 256) * nb, t128 = ((g.M + BM - 1) / BM) * ((g.N + 127) / 128) * nb;
+    auto eff = [&](i64 t) { i64 waves = (t + ctx().sm_count - 1) / ctx().sm_count; return (double)t / (double)(waves * ctx().sm_count); };
+    if (t256 < 4 * ctx().sm_count && eff(t128) > eff(t256) * 1.15) p.bn = 128;
+  }
   const i64 tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + p.bn - 1) / p.bn;
   const i64 kblocks = (g.K + BK - 1) / BK;
   const size_t stage_bytes = 2 * (size_t)(BM + p.bn) * BK * 4;
@@ -424,13 +474,17 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.C = g.C; p.bias = g.bias; p.partial = (float*)part.p;
   p.M = g.M; p.N = g.N; p.K = g.K; p.c_rs = g.c_rs; p.c_b1 = g.c_b1; p.c_b2 = g.c_b2; p.nb1 = g.nb1; p.nb2 = g.nb2;
   p.a_bcast1 = oa.bc1; p.a_bcast2 = oa.bc2; p.b_bcast1 = ob.bc1; p.b_bcast2 = ob.bc2;
+  p.a_mn = oa.mn; p.b_mn = ob.mn;
   p.alpha = g.alpha; p.beta = g.beta; p.err = ctx().d_err;
 
+  static int raw_hi_env = -1;
+  if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
+  p.raw_hi = raw_hi_env;
   size_t smem = (size_t)p.stages * stage_bytes + (3 * p.stages + 1) * sizeof(uint64_t) + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) { VB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr_set = true; }
   {
-    ProfScope prof("gemm_tc", 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
+    ProfScope prof(nb > 1 ? "gemm_tc_batched" : "gemm_tc", 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
     dim3 grid((unsigned)tiles_n, (unsigned)tiles_m, (unsigned)(nb * splits));
     k_gemm_tc<<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, p);
     VB_LAUNCH_CHECK();
