@@ -285,6 +285,17 @@ def sync(): vb_check(lib().vb_sync(), "vb_sync")
 def check_errors(): vb_check(lib().vb_check_errors(), "vb_check_errors")
 
 
+def plan_buckets(numels, target_elems):
+    """The data-parallel gradient-bucket plan for parameters of the given sizes (host arithmetic, no GPU needed).
+    Returns dict(param_offset, bucket_of, buckets=[(offset, numel), ...], total)."""
+    n = len(numels)
+    arr = (C.c_int64 * max(1, n))(*numels)
+    po = (C.c_int64 * max(1, n))(); bo = (C.c_int * max(1, n))()
+    boff = (C.c_int64 * max(1, n))(); bnum = (C.c_int64 * max(1, n))(); total = C.c_int64(0)
+    nb = _chk(lib().vh_plan_buckets(arr, n, C.c_int64(target_elems), po, bo, boff, bnum, max(1, n), C.byref(total)))
+    return dict(param_offset=list(po)[:n], bucket_of=list(bo)[:n], buckets=[(boff[i], bnum[i]) for i in range(nb)], total=total.value)
+
+
 def memory_stats():
     v = [C.c_int64(0) for _ in range(4)]
     vb_check(lib().vb_memory_stats(*[C.byref(x) for x in v]))

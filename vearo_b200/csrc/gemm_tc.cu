@@ -29,6 +29,7 @@
 // error word, drains what it has in flight, frees its tensor memory and returns.
 #include "common.h"
 #include <cuda.h>
+#include <cstdio>
 #include <cstdlib>
 
 namespace vb {
@@ -47,8 +48,9 @@ struct TcParams {
   i64 c_rs, c_b1, c_b2;
   i64 nb1, nb2;
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
-  int bn, stages, splits, kblocks_per_split;
+  int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
   int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
+  int debug;                                      // timing experiments only (results are wrong): 1 skip the split, 2 issue one MMA of three
   int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
   float alpha, beta;
   int* err;
@@ -147,13 +149,16 @@ __device__ __forceinline__ float tf32_rna(float x) {
 __global__ void __launch_bounds__(kThreads, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // carve: [stages][ A_hi | B_hi | A_lo | B_lo ], then barriers
+  // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ], barriers.
+  // The raw ring is deep (it has to cover the latency of TMA loads from HBM); the lo ring only spans convert -> MMA.
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment in the shared window
-  const int bn = p.bn, stages = p.stages;
-  const uint32_t a_bytes = BM * BK * 4, b_bytes = (uint32_t)bn * BK * 4, raw_bytes = a_bytes + b_bytes, stage_bytes = 2 * raw_bytes;
-  uint64_t* bars = (uint64_t*)(smem + (size_t)stages * stage_bytes);
-  uint64_t* full = bars; uint64_t* conv = bars + stages; uint64_t* empty = bars + 2 * stages; uint64_t* tmem_full = bars + 3 * stages;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 3 * stages + 1);
+  const int bn = p.bn, stages = p.stages, lstages = p.lstages;
+  const uint32_t a_bytes = BM * BK * 4, b_bytes = (uint32_t)bn * BK * 4, raw_bytes = a_bytes + b_bytes;
+  uint8_t* lo_ring = smem + (size_t)stages * raw_bytes;
+  uint64_t* bars = (uint64_t*)(lo_ring + (size_t)lstages * raw_bytes);
+  uint64_t* full = bars; uint64_t* empty = bars + stages; uint64_t* conv = bars + 2 * stages; uint64_t* lo_empty = conv + lstages;
+  uint64_t* tmem_full = lo_empty + lstages;
+  uint32_t* tmem_slot = (uint32_t*)(tmem_full + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -167,7 +172,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   const int nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&conv[s], kConvWarps); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], kConvWarps); mbar_init(&lo_empty[s], 1); }
     mbar_init(tmem_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -188,7 +194,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       for (int kb = 0; kb < nkb; ++kb) {
         int s = kb % stages; uint32_t ph = (uint32_t)(kb / stages) & 1;
         if (kb >= stages && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        uint8_t* st = smem + (size_t)s * stage_bytes;
+        uint8_t* st = smem + (size_t)s * raw_bytes;
         mbar_arrive_expect_tx(&full[s], raw_bytes);
         int k = (int)((kb0 + kb) * BK);
         const int ab2 = p.a_bcast2 ? 0 : b2, ab1 = p.a_bcast1 ? 0 : b1, bb2 = p.b_bcast2 ? 0 : b2, bb1 = p.b_bcast1 ? 0 : b1;
@@ -212,22 +218,24 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       const uint32_t idesc = make_idesc(bn, p.a_mn, p.b_mn);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
-        int s = kb % stages; uint32_t ph = (uint32_t)(kb / stages) & 1;
-        ok = mbar_wait(&conv[s], ph, abort_flag);
+        int s = kb % stages, l = kb % lstages; uint32_t lph = (uint32_t)(kb / lstages) & 1;
+        ok = mbar_wait(&conv[l], lph, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
-        uint32_t a_hi = st, b_hi = st + a_bytes, a_lo = st + raw_bytes, b_lo = st + raw_bytes + a_bytes;
+        uint32_t st = smem_u32(smem + (size_t)s * raw_bytes), lt = smem_u32(lo_ring + (size_t)l * raw_bytes);
+        uint32_t a_hi = st, b_hi = st + a_bytes, a_lo = lt, b_lo = lt + a_bytes;
 #pragma unroll
         for (int ks = 0; ks < BK / 8; ++ks) {
           // one MMA covers 8 k: 32 bytes along a K-major row, or one 1024-byte k group of an MN-major tile
           uint64_t da_hi = make_desc(a_hi, ks, p.a_mn), db_hi = make_desc(b_hi, ks, p.b_mn);
           uint64_t da_lo = make_desc(a_lo, ks, p.a_mn), db_lo = make_desc(b_lo, ks, p.b_mn);
+          if (p.debug & 2) { mma_tf32(tmem_base, da_hi, db_hi, idesc, (kb | ks) ? 1u : 0u); continue; }
           mma_tf32(tmem_base, da_lo, db_hi, idesc, (kb | ks) ? 1u : 0u);
           mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
           mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
         }
-        mma_commit(&empty[s]);          // frees the stage once these MMAs have read it
+        mma_commit(&empty[s]);          // frees the raw stage once these MMAs have read it
+        mma_commit(&lo_empty[l]);       // ... and the lo stage
       }
       if (ok) mma_commit(tmem_full);    // accumulator complete
     }
@@ -237,13 +245,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     constexpr int kConvThreads = 32 * kConvWarps;
     bool ok = true;
     for (int kb = 0; kb < nkb && ok; ++kb) {
-      int s = kb % stages; uint32_t ph = (uint32_t)(kb / stages) & 1;
-      ok = mbar_wait(&full[s], ph, abort_flag);
+      int s = kb % stages, l = kb % lstages; uint32_t ph = (uint32_t)(kb / stages) & 1, lph = (uint32_t)(kb / lstages) & 1;
+      if (kb >= lstages) ok = mbar_wait(&lo_empty[l], lph ^ 1, abort_flag);
+      if (ok) ok = mbar_wait(&full[s], ph, abort_flag);
       if (!ok) break;
-      float4* hi = (float4*)(smem + (size_t)s * stage_bytes);
-      float4* lo = (float4*)(smem + (size_t)s * stage_bytes + raw_bytes);
+      float4* hi = (float4*)(smem + (size_t)s * raw_bytes);
+      float4* lo = (float4*)(lo_ring + (size_t)l * raw_bytes);
       const int n4 = (int)(raw_bytes / 16);      // 768, 1024 or 1536: a multiple of kConvThreads
-      if (p.raw_hi) {
+      if (p.debug & 1) {
+      } else if (p.raw_hi) {
 #pragma unroll 3
         for (int i = ct; i < n4; i += kConvThreads) {
           float4 x = hi[i], l;
@@ -264,7 +274,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
       __syncwarp();
-      if (lane == 0) mbar_arrive(&conv[s]);
+      if (lane == 0) mbar_arrive(&conv[l]);
     }
     // epilogue: TMEM lane quarter of this warp is (warp % 4)
     if (nkb == 0) ok = true;
@@ -451,8 +461,9 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   }
   const i64 tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + p.bn - 1) / p.bn;
   const i64 kblocks = (g.K + BK - 1) / BK;
-  const size_t stage_bytes = 2 * (size_t)(BM + p.bn) * BK * 4;
-  p.stages = (int)((200 * 1024) / stage_bytes); if (p.stages > 8) p.stages = 8;
+  const size_t raw_bytes = (size_t)(BM + p.bn) * BK * 4;
+  p.lstages = p.bn == 256 ? 2 : 3;
+  p.stages = (int)((204 * 1024) / raw_bytes) - p.lstages; if (p.stages > 10) p.stages = 10;
   // split-K when the tile count cannot fill the machine
   i64 ctas = tiles_m * tiles_n * nb;
   int splits = 1;
@@ -480,7 +491,9 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
   p.raw_hi = raw_hi_env;
-  size_t smem = (size_t)p.stages * stage_bytes + (3 * p.stages + 1) * sizeof(uint64_t) + 16 + 1024;
+  { static int dbg = -1; if (dbg < 0) { const char* e = getenv("VB200_TC_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
+  { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 204 * 1024) { p.stages = r; p.lstages = l; } } }
+  size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 1) * sizeof(uint64_t) + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) { VB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr_set = true; }
   {

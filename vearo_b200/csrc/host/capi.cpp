@@ -119,6 +119,18 @@ int vh_clip_grad_norm(const int* params, int n, float max_norm, float* norm) {
 }
 float vh_cosine_lr(float base, float min_lr, uint32_t warmup, uint32_t total, uint32_t step) { return optim::cosine_lr(base, min_lr, warmup, total, step); }
 
+// Gradient-bucket plan (host arithmetic only, usable without a device): fills param_offset[n], bucket_of[n],
+// and up to `max_buckets` entries of bucket_offset / bucket_numel; returns the number of buckets.
+int vh_plan_buckets(const int64_t* numels, int n, int64_t target_elems, int64_t* param_offset, int* bucket_of,
+                    int64_t* bucket_offset, int64_t* bucket_numel, int max_buckets, int64_t* total) {
+  VH_TRY(optim::BucketPlan bp = optim::plan_buckets(std::vector<i64>(numels, numels + n), target_elems);
+         if ((int)bp.bucket_offset.size() > max_buckets) throw Error("too many buckets for the caller's arrays");
+         for (int i = 0; i < n; ++i) { param_offset[i] = bp.param_offset[i]; bucket_of[i] = bp.bucket_of[i]; }
+         for (size_t b = 0; b < bp.bucket_offset.size(); ++b) { bucket_offset[b] = bp.bucket_offset[b]; bucket_numel[b] = bp.bucket_numel[b]; }
+         if (total) *total = bp.total;
+         return (int)bp.bucket_offset.size());
+}
+
 // One whole training step from HOST buffers: upload inputs, zero_gradients, reset tape, forward,
 // backward (gradient exchange overlapped when data parallel), clip + optimizer step, read the loss.
 // x / y are flat f32 arrays with the given shapes.  max_norm <= 0: no clipping.

@@ -130,14 +130,32 @@ Tensor FusedOpBench::loss(const Tensor& x, const Tensor& labels) { return head.f
 
 namespace optim {
 
+BucketPlan plan_buckets(const std::vector<i64>& numels, i64 target_elems) {
+  BucketPlan bp;
+  for (i64 n : numels) { bp.param_offset.push_back(bp.total); bp.total += (n + 3) & ~i64(3); }
+  bp.bucket_of.assign(numels.size(), 0);
+  i64 end = bp.total; int cnt = 0;
+  for (int i = (int)numels.size() - 1; i >= 0; --i) {
+    i64 acc = end - bp.param_offset[i]; ++cnt;
+    bp.bucket_of[i] = (int)bp.bucket_offset.size();
+    if (acc >= target_elems || i == 0) {
+      bp.bucket_offset.push_back(bp.param_offset[i]); bp.bucket_numel.push_back(acc); bp.bucket_nparams.push_back(cnt);
+      end = bp.param_offset[i]; cnt = 0;
+    }
+  }
+  return bp;
+}
+
 Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params, bool data_parallel) : cfg_(cfg), params_(params), dp_(data_parallel) {
   // one flat gradient arena, parameters in registration order, every view 16-byte aligned
-  i64 total = 0;
-  std::vector<i64> offs;
+  std::vector<i64> numels;
   for (const Tensor& p : params_) {
     if (!p.is_contiguous()) throw Error("optimizer parameters must be contiguous");
-    offs.push_back(total); total += (p.numel() + 3) & ~i64(3);
+    numels.push_back(p.numel());
   }
+  BucketPlan bp = plan_buckets(numels, (32ll << 20) / 4);
+  const i64 total = bp.total;
+  const std::vector<i64>& offs = bp.param_offset;
   arena_ = Tensor::zeros({total > 0 ? total : 1});
   std::vector<vb_tensor> pd, gd;
   for (size_t i = 0; i < params_.size(); ++i) {
@@ -150,18 +168,9 @@ Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params
   int rank = 0;
   check(vb_dp_world(&rank, &world_), "dp_world");
   if (!dp_) world_ = 1;
-  // buckets: contiguous arena ranges of >= 32 MiB, cut from the END of the arena backwards, because
-  // gradients become final in roughly reverse parameter order during the backward walk
-  bucket_of_.assign(params_.size(), 0);
-  const i64 target = (32ll << 20) / 4;
-  i64 end = total; int cnt = 0; i64 acc = 0;
-  std::vector<Bucket> rev;
-  for (int i = (int)params_.size() - 1; i >= 0; --i) {
-    acc = end - offs[i]; ++cnt;
-    bucket_of_[i] = (int)rev.size();
-    if (acc >= target || i == 0) { rev.push_back(Bucket{offs[i], acc, cnt, cnt}); end = offs[i]; cnt = 0; }
-  }
-  buckets_ = rev;
+  // buckets: contiguous arena ranges of >= 32 MiB (see plan_buckets)
+  bucket_of_ = bp.bucket_of;
+  for (size_t b = 0; b < bp.bucket_offset.size(); ++b) buckets_.push_back(Bucket{bp.bucket_offset[b], bp.bucket_numel[b], bp.bucket_nparams[b], bp.bucket_nparams[b]});
   ready_.assign(params_.size(), 0);
   autograd::register_grad_sinks(params_, sinks_, &Optimizer::on_ready, this);
 }

@@ -126,6 +126,12 @@ class Optimizer {
   std::vector<uint8_t> ready_;
   int world_ = 1;
 };
+// Gradient-bucket plan for data parallel: parameters are laid out in a flat arena in registration order
+// (each rounded up to 4 floats); buckets are contiguous arena ranges of at least `target_elems`, cut from
+// the END of the arena backwards, because gradients become final in roughly reverse parameter order.
+// Pure host arithmetic (no device needed); every rank computes the same plan from the same shapes.
+struct BucketPlan { std::vector<i64> param_offset, bucket_offset, bucket_numel; std::vector<int> bucket_of, bucket_nparams; i64 total = 0; };
+BucketPlan plan_buckets(const std::vector<i64>& numels, i64 target_elems);
 // Reference-shaped free function: clip_grad_norm(params, max_norm) -> pre-clip norm (lib.rs:360-383).
 float clip_grad_norm(const std::vector<Tensor>& params, float max_norm);
 float cosine_lr(float base_lr, float min_lr, uint32_t warmup, uint32_t total, uint32_t step);   // lib.rs:336-348

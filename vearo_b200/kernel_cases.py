@@ -1,0 +1,88 @@
+"""Small single-kernel cases of the library's hot kernels, for profiling with ncu and quick timing.
+
+  python -m vearo_b200.kernel_cases gemm_fc1      x[8192,768] . W[3072,768]^T   (Linear forward)
+  python -m vearo_b200.kernel_cases gemm_dx       g[8192,3072] . W[3072,768]    (B consumed as a transposed view)
+  python -m vearo_b200.kernel_cases gemm_dw       g[8192,3072]^T . x[8192,768]  (both operands transposed views, split-K)
+  python -m vearo_b200.kernel_cases gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
+  python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
+  python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
+  python -m vearo_b200.kernel_cases adamw         64 Mi parameters
+A second argument gives the repetition count (default 3); `time` instead prints the average device
+time per repetition over 20 repetitions (CUDA events through the library's profiling hooks are not
+used here: the loop is synchronised on both sides and timed on the host).
+Each case holds well under 2 GB on the device.
+"""
+import sys
+import time
+
+import numpy as np
+
+import vearo_b200 as vb
+
+
+def build(case):
+    r = np.random.default_rng(0)
+    f = lambda *s: (r.standard_normal(s) * 0.05).astype(np.float32)
+    T = vb.Tensor.from_numpy
+    if case == "gemm_fc1":
+        x, w = T(f(8192, 768)), T(f(3072, 768))
+        return lambda: x.linear(w)
+    if case == "gemm_dx":
+        g, w = T(f(8192, 3072)), T(f(3072, 768))
+        return lambda: g.matmul(w)
+    if case == "gemm_dw":
+        g, x = T(f(8192, 3072)), T(f(8192, 768))
+        gt = g.transpose(0, 1)
+        return lambda: gt.matmul(x)
+    if case == "gemm_qk":
+        q, k = T(f(8, 12, 1024, 64)), T(f(8, 12, 1024, 64))
+        kt = k.transpose(2, 3)
+        return lambda: q.matmul(kt)
+    if case == "layernorm_bwd":
+        x, w, b, g = T(f(8192, 768), True), T(f(768), True), T(f(768), True), T(f(8192, 768))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            x.layernorm(w, b, 1e-5).mul(g).sum(1, False).sum(0, False).backward()
+        return run
+    if case == "ce_bwd":
+        l, t = T(f(2048, 50304), True), T(r.integers(0, 50304, 2048).astype(np.float32))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            l.cross_entropy(t).backward()
+        return run
+    if case == "adamw":
+        w = T(f(64 << 20), True)
+        opt = vb.AdamW([w], 1e-3)
+        g = T(f(64 << 20))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            w.mul(g).sum(0, False).backward()
+            opt.clip_and_step(1.0)
+        return run
+    raise SystemExit("unknown case " + case)
+
+
+def main(case, mode):
+    vb.init()
+    fn = build(case)
+    if mode == "time":
+        for _ in range(3):
+            fn()
+        vb.sync(); t0 = time.perf_counter()
+        for _ in range(20):
+            fn()
+        vb.sync()
+        print("%s: %.1f us per call" % (case, (time.perf_counter() - t0) / 20 * 1e6))
+    else:
+        for _ in range(int(mode)):
+            fn()
+        vb.sync()
+    vb.check_errors()
+    print("ok", case)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) > 2 else "3")
