@@ -146,7 +146,7 @@ __device__ __forceinline__ float tf32_rna(float x) {
   return __uint_as_float(u);
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ], barriers.
@@ -178,8 +178,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // tensor memory: 256 columns hold a 128 x 256 f32 accumulator
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+  if (warp == 1) {   // tensor memory: bn columns hold the 128 x bn f32 accumulator (so that several CTAs can share an SM's 512 columns)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)bn) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -328,7 +328,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)bn) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.err, ERRBIT_WAIT_TIMEOUT);
 }
@@ -462,8 +462,10 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   const i64 tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + p.bn - 1) / p.bn;
   const i64 kblocks = (g.K + BK - 1) / BK;
   const size_t raw_bytes = (size_t)(BM + p.bn) * BK * 4;
-  p.lstages = p.bn == 256 ? 2 : 3;
-  p.stages = (int)((204 * 1024) / raw_bytes) - p.lstages; if (p.stages > 10) p.stages = 10;
+  // Small rings on purpose: two (BN 256) to four (BN 64) CTAs then share an SM, and one CTA's epilogue and pipeline
+  // bubbles are covered by the others' main loops; measured faster than one CTA per SM with a deep ring.
+  p.lstages = 2;
+  p.stages = p.bn == 256 ? 2 : 3;
   // split-K when the tile count cannot fill the machine
   i64 ctas = tiles_m * tiles_n * nb;
   int splits = 1;
