@@ -127,7 +127,9 @@ int vb_batchnorm_backward(const vb_tensor* x, const vb_tensor* gamma, const vb_t
  * [B,H,S,S] with size-1 dims broadcast; softmax uses 1/(sum + 1e-9) as vearo-backend-cpu
  * lib.rs:2455.  The reference's CUDA backend runs this on the CPU (lib.rs:1594-1636); here it
  * runs on the device.  `probs` (may be NULL) receives the [B,H,S,S] probabilities so that the
- * backward pass need not recompute them. */
+ * backward pass need not recompute them.  The results of both calls (out; dq, dk, dv) are the one exception
+ * to "outputs are contiguous": they are [B,H,S,dk] views (strides S*H*dk, dk, H*dk, 1) of fresh [B,S,H,dk]
+ * buffers, which makes the layer's following transpose(1,2).reshape a view instead of a copy. */
 int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,
                        vb_tensor* out, vb_tensor* probs);
 int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,

@@ -395,13 +395,24 @@ static void qk_gemm_operand(const vb_tensor* t, i64* rs, i64* cs, i64* b1, i64* 
   *b1 = t->strides[0]; *b2 = t->strides[1]; *rs = t->strides[2]; *cs = t->strides[3];
 }
 
+// Attention results are laid out in memory as [B,S,H,dk] and returned as the [B,H,S,dk] view of that buffer: the
+// `transpose(1,2).reshape([B,S,D])` that follows in MultiHeadAttention::forward (and its mirror image in the
+// backward walk) is then a pure view, with no copy.
+static int new_output_bshd(vb_tensor* out, i64 B, i64 H, i64 S, i64 dk) {
+  i64 mem[4] = {B, S, H, dk};
+  VB_TRY(new_output(out, 4, mem));
+  out->dims[0] = B; out->dims[1] = H; out->dims[2] = S; out->dims[3] = dk;
+  out->strides[0] = S * H * dk; out->strides[1] = dk; out->strides[2] = H * dk; out->strides[3] = 1;
+  return VB_OK;
+}
+
 int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask,
                        vb_tensor* out, vb_tensor* probs) {
   VB_CHECK(q->rank == 4 && same_shape(*q, *k) && same_shape(*q, *v), "fused_attention expects q, k, v of equal shape [B,H,S,dk]");
   i64 B = q->dims[0], H = q->dims[1], S = q->dims[2], dk = q->dims[3];
   float *pq, *pk, *pv; VB_TRY(tensor_ptr(q, &pq)); VB_TRY(tensor_ptr(k, &pk)); VB_TRY(tensor_ptr(v, &pv));
   const float* pm; i64 ms[4]; VB_TRY(mask_strides(mask, B, H, S, S, &pm, ms));
-  VB_TRY(new_output(out, 4, q->dims));
+  VB_TRY(new_output_bshd(out, B, H, S, dk));
   if (numel(*q) == 0) { if (probs) { i64 pd[4] = {B, H, S, S}; VB_TRY(new_output(probs, 4, pd)); } return VB_OK; }
   float* po; VB_TRY(slot_ptr(out->slot, &po));
   // scores / probabilities
@@ -421,7 +432,7 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
     o.M = S; o.N = dk; o.K = S; o.nb1 = B; o.nb2 = H;
     o.A = pp; o.a_rs = S; o.a_cs = 1; o.a_b1 = H * S * S; o.a_b2 = S * S;
     o.B = pv; qk_gemm_operand(v, &o.b_rs, &o.b_cs, &o.b_b1, &o.b_b2);
-    o.C = po; o.c_rs = dk; o.c_cs = 1; o.c_b1 = H * S * dk; o.c_b2 = S * dk;
+    o.C = po; o.c_rs = H * dk; o.c_cs = 1; o.c_b1 = S * H * dk; o.c_b2 = dk;
     rc = launch_gemm(o);
   }
   if (rc == VB_OK && probs) *probs = ptmp; else slot_release(ptmp.slot, nullptr);
@@ -434,7 +445,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
   i64 B = q->dims[0], H = q->dims[1], S = q->dims[2], dk = q->dims[3];
   float *pq, *pk, *pv, *pg;
   VB_TRY(tensor_ptr(q, &pq)); VB_TRY(tensor_ptr(k, &pk)); VB_TRY(tensor_ptr(v, &pv)); VB_TRY(tensor_ptr(gout, &pg));
-  VB_TRY(new_output(dq, 4, q->dims)); VB_TRY(new_output(dk_, 4, q->dims)); VB_TRY(new_output(dv, 4, q->dims));
+  VB_TRY(new_output_bshd(dq, B, H, S, dk)); VB_TRY(new_output_bshd(dk_, B, H, S, dk)); VB_TRY(new_output_bshd(dv, B, H, S, dk));
   if (numel(*q) == 0) return VB_OK;
   float *pdq, *pdk, *pdv;
   VB_TRY(slot_ptr(dq->slot, &pdq)); VB_TRY(slot_ptr(dk_->slot, &pdk)); VB_TRY(slot_ptr(dv->slot, &pdv));
@@ -468,7 +479,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H;
     g.A = pp; g.a_rs = 1; g.a_cs = S; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pg; qk_gemm_operand(gout, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
-    g.C = pdv; g.c_rs = dk; g.c_cs = 1; g.c_b1 = H * S * dk; g.c_b2 = S * dk;
+    g.C = pdv; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
   if (rc == VB_OK) {   // dP = dO . V^T
@@ -485,7 +496,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H;
     g.A = pdp; g.a_rs = S; g.a_cs = 1; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pk; qk_gemm_operand(k, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
-    g.C = pdq; g.c_rs = dk; g.c_cs = 1; g.c_b1 = H * S * dk; g.c_b2 = S * dk;
+    g.C = pdq; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
   if (rc == VB_OK) {   // dK = dS^T . Q
@@ -493,7 +504,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H;
     g.A = pdp; g.a_rs = 1; g.a_cs = S; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pq; qk_gemm_operand(q, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
-    g.C = pdk; g.c_rs = dk; g.c_cs = 1; g.c_b1 = H * S * dk; g.c_b2 = S * dk;
+    g.C = pdk; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
   if (dpv) scratch_free(dpv);

@@ -97,6 +97,77 @@ __global__ void __launch_bounds__(256) k_attn_softmax_long(float* __restrict__ s
   for (i64 j = threadIdx.x; j < sk; j += blockDim.x) r[j] *= inv;
 }
 
+// Warp-per-row variants for rows of up to 1024 columns (a multiple of 4): 128-bit loads and stores, the row lives
+// in registers, reductions are warp shuffles only (no block barrier).  V = float4 per lane.
+template <int V>
+__global__ void __launch_bounds__(128) k_attn_softmax_warp(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
+                                                           i64 H, i64 sq, i64 sk, i64 rows) {
+  const int lane = threadIdx.x & 31;
+  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
+  for (i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; row < rows; row += nwarps) {
+    i64 i = row % sq, bh = row / sq, h = bh % H, b = bh / H;
+    float4* r4 = reinterpret_cast<float4*>(s + row * sk);
+    const float4* m4 = mask ? reinterpret_cast<const float4*>(mask + b * ms.b + h * ms.h + i * ms.q) : nullptr;
+    float4 v[V];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      int j4 = e * 32 + lane;
+      if (j4 * 4 < sk) {
+        float4 x = r4[j4];
+        if (m4) { float4 m = m4[j4]; x.x += m.x; x.y += m.y; x.z += m.z; x.w += m.w; }
+        v[e] = x;
+        mx = fmaxf(mx, fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w)));
+      } else v[e] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    mx = a_wmax(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+      if ((e * 32 + lane) * 4 < sk) {
+        v[e].x = expf(v[e].x - mx); v[e].y = expf(v[e].y - mx); v[e].z = expf(v[e].z - mx); v[e].w = expf(v[e].w - mx);
+        sum += (v[e].x + v[e].y) + (v[e].z + v[e].w);
+      }
+    sum = a_wsum(sum);
+    float inv = 1.0f / (sum + 1e-9f);
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+      if ((e * 32 + lane) * 4 < sk) r4[e * 32 + lane] = make_float4(v[e].x * inv, v[e].y * inv, v[e].z * inv, v[e].w * inv);
+  }
+}
+template <int V>
+__global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __restrict__ p, float* __restrict__ dp, i64 sk, float scale, i64 rows) {
+  const int lane = threadIdx.x & 31;
+  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
+  for (i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; row < rows; row += nwarps) {
+    const float4* p4 = reinterpret_cast<const float4*>(p + row * sk);
+    float4* d4 = reinterpret_cast<float4*>(dp + row * sk);
+    float4 pv[V], dv[V];
+    float dot = 0.0f;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      int j4 = e * 32 + lane;
+      if (j4 * 4 < sk) {
+        pv[e] = p4[j4]; dv[e] = d4[j4];
+        dot = fmaf(dv[e].x, pv[e].x, dot); dot = fmaf(dv[e].y, pv[e].y, dot); dot = fmaf(dv[e].z, pv[e].z, dot); dot = fmaf(dv[e].w, pv[e].w, dot);
+      }
+    }
+    dot = a_wsum(dot);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      int j4 = e * 32 + lane;
+      if (j4 * 4 < sk)
+        d4[j4] = make_float4((pv[e].x * (dv[e].x - dot)) * scale, (pv[e].y * (dv[e].y - dot)) * scale,
+                             (pv[e].z * (dv[e].z - dot)) * scale, (pv[e].w * (dv[e].w - dot)) * scale);
+    }
+  }
+}
+static inline bool al16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static inline unsigned warp_grid(i64 rows) {
+  i64 blocks = (rows + 3) / 4, cap = (i64)ctx().sm_count * 16;
+  return (unsigned)(blocks > cap ? cap : blocks);
+}
+
 int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale) {
   (void)causal; (void)scale;
   i64 rows = b * h * sq;
@@ -105,6 +176,16 @@ int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool cau
   MaskStrides ms{0, 0, 0, 0};
   if (mask) ms = MaskStrides{mstr[0], mstr[1], mstr[2], mstr[3]};
   cudaStream_t st = ctx().stream;
+  bool mask_vec = !mask || (ms.k == 1 && al16p(mask) && !(ms.b & 3) && !(ms.h & 3) && !(ms.q & 3));
+  if ((sk & 3) == 0 && sk <= 1024 && al16p(s) && mask_vec) {
+    unsigned wg = warp_grid(rows);
+    if (sk <= 128) k_attn_softmax_warp<1><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
+    else if (sk <= 256) k_attn_softmax_warp<2><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
+    else if (sk <= 512) k_attn_softmax_warp<4><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
+    else k_attn_softmax_warp<8><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
+    VB_LAUNCH_CHECK();
+    return VB_OK;
+  }
   unsigned g = (unsigned)rows;
   if (sk <= 128) k_attn_softmax<1><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
   else if (sk <= 256) k_attn_softmax<2><<<g, 128, 0, st>>>(s, mask, ms, h, sq, sk);
@@ -151,6 +232,15 @@ int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, fl
   if (rows <= 0 || sk <= 0) return VB_OK;
   ProfScope prof("attn_softmax_bwd", 3.0 * (double)rows * (double)sk * 4.0);
   cudaStream_t st = ctx().stream;
+  if ((sk & 3) == 0 && sk <= 1024 && al16p(p) && al16p(dp)) {
+    unsigned wg = warp_grid(rows);
+    if (sk <= 128) k_attn_softmax_bwd_warp<1><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
+    else if (sk <= 256) k_attn_softmax_bwd_warp<2><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
+    else if (sk <= 512) k_attn_softmax_bwd_warp<4><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
+    else k_attn_softmax_bwd_warp<8><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
+    VB_LAUNCH_CHECK();
+    return VB_OK;
+  }
   unsigned g = (unsigned)rows;
   if (sk <= 128) k_attn_softmax_bwd<1><<<g, 128, 0, st>>>(p, dp, sk, scale);
   else if (sk <= 256) k_attn_softmax_bwd<2><<<g, 128, 0, st>>>(p, dp, sk, scale);

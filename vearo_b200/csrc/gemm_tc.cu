@@ -453,27 +453,36 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   VB_TRY(prepare(g.B, g.N, g.b_cs, g.b_rs, g.b_b1, g.b_b2, hold_b, &ob));   // B^T rows are the columns of B
 
   TcParams p{};
+  // Tile width and split-K factor: minimise an estimate of the run time in units of one 256-wide k-block.
+  // A k-block of a 128-wide tile costs ~0.62 of a 256-wide one (same A traffic for half the flops); the epilogue of a
+  // tile costs about 10 (256) / 6 (128) k-blocks; split-K adds a pass over the partial tiles.
+  const i64 kblocks = (g.K + BK - 1) / BK;
+  const i64 slots = (i64)ctx().sm_count * 2;          // two resident CTAs per SM
   p.bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
-  if (p.bn == 256) {   // wave quantisation: with few 256-wide tiles, 128-wide ones fill the SMs better
-    i64 t256 = ((g.M + BM - 1) / BM) * ((g.N + 255) / 256) * nb, t128 = ((g.M + BM - 1) / BM) * ((g.N + 127) / 128) * nb;
-    auto eff = [&](i64 t) { i64 waves = (t + ctx().sm_count - 1) / ctx().sm_count; return (double)t / (double)(waves * ctx().sm_count); };
-    if (t256 < 4 * ctx().sm_count && eff(t128) > eff(t256) * 1.15) p.bn = 128;
+  int splits = 1;
+  if (p.bn == 256) {
+    double best = 1e300;
+    for (int bn : {256, 128}) {
+      i64 tiles = ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * nb;
+      for (int sk : {1, 2, 3, 4, 6, 8, 12, 16}) {
+        if (sk > 1 && kblocks / sk < 24) break;
+        i64 units = tiles * sk, waves = (units + slots - 1) / slots;
+        double kb_cost = bn == 256 ? 1.0 : 0.62, epi = bn == 256 ? 10.0 : 6.0;
+        double t = (double)waves * ((double)((kblocks + sk - 1) / sk) * kb_cost + epi);
+        if (sk > 1) t += (double)tiles * (double)sk * epi * 0.5 / (double)slots + epi;      // partial tiles written, then summed
+        if (t < best * 0.97) { best = t; p.bn = bn; splits = sk; }
+      }
+    }
+  } else {
+    i64 tiles = ((g.M + BM - 1) / BM) * nb;
+    if (tiles < slots && kblocks >= 48) { splits = (int)((slots + tiles - 1) / tiles); if (splits > kblocks / 24) splits = (int)(kblocks / 24); if (splits < 1) splits = 1; }
   }
   const i64 tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + p.bn - 1) / p.bn;
-  const i64 kblocks = (g.K + BK - 1) / BK;
   const size_t raw_bytes = (size_t)(BM + p.bn) * BK * 4;
-  // Small rings on purpose: two (BN 256) to four (BN 64) CTAs then share an SM, and one CTA's epilogue and pipeline
-  // bubbles are covered by the others' main loops; measured faster than one CTA per SM with a deep ring.
+  // Small rings on purpose: two CTAs then share an SM, and one CTA's epilogue and pipeline bubbles are covered by
+  // the other's main loop; measured faster than one CTA per SM with a deep ring.
   p.lstages = 2;
   p.stages = p.bn == 256 ? 2 : 3;
-  // split-K when the tile count cannot fill the machine
-  i64 ctas = tiles_m * tiles_n * nb;
-  int splits = 1;
-  if (ctas < ctx().sm_count && kblocks >= 32) {
-    splits = (int)((ctx().sm_count + ctas - 1) / ctas);
-    i64 max_splits = kblocks / 16; if (splits > max_splits) splits = (int)max_splits;
-    if (splits < 1) splits = 1;
-  }
   p.kblocks_per_split = (int)((kblocks + splits - 1) / splits);
   splits = (int)((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
   p.splits = splits;
@@ -499,7 +508,12 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   static bool attr_set = false;
   if (!attr_set) { VB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr_set = true; }
   {
-    ProfScope prof(nb > 1 ? "gemm_tc_batched" : "gemm_tc", 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
+    static int shapes = -1;
+    if (shapes < 0) { const char* e = getenv("VB200_PROF_SHAPES"); shapes = (e && e[0] == '1') ? 1 : 0; }
+    char fam[96];
+    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits);
+    else snprintf(fam, sizeof fam, "%s", nb > 1 ? "gemm_tc_batched" : "gemm_tc");
+    ProfScope prof(fam, 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
     dim3 grid((unsigned)tiles_n, (unsigned)tiles_m, (unsigned)(nb * splits));
     k_gemm_tc<<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, p);
     VB_LAUNCH_CHECK();

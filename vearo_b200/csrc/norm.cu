@@ -148,6 +148,24 @@ __global__ void __launch_bounds__(256) k_ln_bwd_warp(const float* __restrict__ x
   }
 }
 
+// Second stage of the fast path: add the per-CTA partial rows of dw and db in CTA order.  A 32 x 8 block owns
+// 32 columns; its 8 row lanes each add every 8th partial row, then lane 0 adds the 8 sums in lane order.
+__global__ void __launch_bounds__(256) k_ln_partials_sum(const float* __restrict__ part_w, const float* __restrict__ part_b,
+                                                          float* __restrict__ gw, float* __restrict__ gb, int ctas, int C) {
+  __shared__ float sw[8][33], sb[8][33];
+  int c = blockIdx.x * 32 + threadIdx.x;
+  float a = 0.0f, b = 0.0f;
+  if (c < C) for (int i = threadIdx.y; i < ctas; i += 8) { a += part_w[(i64)i * C + c]; b += part_b[(i64)i * C + c]; }
+  sw[threadIdx.y][threadIdx.x] = a; sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < C) {
+    float ta = 0.0f, tb = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { ta += sw[i][threadIdx.x]; tb += sb[i][threadIdx.x]; }
+    gw[c] = ta; gb[c] = tb;
+  }
+}
+
 // ---- LayerNorm, generic path (any C): one block per row, rows re-read from L1/L2 ------------
 __global__ void k_ln_fwd_block(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                float* __restrict__ out, float* __restrict__ stats, i64 C, float eps) {
@@ -226,10 +244,8 @@ int launch_layernorm_backward(const float* x, const float* w, const float* g, fl
       k_ln_bwd_warp<V><<<(unsigned)blocks, warps * 32, smem, st>>>(x, w, g, gx, pw, pb, rows, (int)c, eps); break;
     switch (vpt) { LN_BWD(1) LN_BWD(2) LN_BWD(3) LN_BWD(4) LN_BWD(5) LN_BWD(6) LN_BWD(7) LN_BWD(8) }
 #undef LN_BWD
-    int rc = launch_colsum(pw, gw, blocks, c, false);
-    if (rc == VB_OK) rc = launch_colsum(pb, gb, blocks, c, false);
+    k_ln_partials_sum<<<(unsigned)((c + 31) / 32), dim3(32, 8), 0, st>>>(pw, pb, gw, gb, (int)blocks, (int)c);
     scratch_free(part);
-    VB_TRY(rc);
   } else {
     void* stats = nullptr;
     VB_TRY(scratch_alloc((size_t)(2 * rows) * sizeof(float), &stats));

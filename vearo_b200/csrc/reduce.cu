@@ -99,9 +99,50 @@ __global__ void k_colsum_final(const float* __restrict__ part, float* __restrict
   for (int i = 0; i < splits; ++i) s += part[(i64)i * cols + c];
   out[c] = accumulate ? out[c] + s : s;
 }
+// 128-bit variant: a 32 x 8 block owns 128 columns (one float4 per thread and row), four rows in flight per thread.
+__global__ void __launch_bounds__(256) k_colsum_partial_vec(const float4* __restrict__ x, float4* __restrict__ part, i64 rows, i64 cols4, i64 rows_per_split) {
+  __shared__ float4 sm[8][33];
+  i64 c = (i64)blockIdx.x * 32 + threadIdx.x;
+  i64 r0 = (i64)blockIdx.y * rows_per_split;
+  i64 r1 = r0 + rows_per_split; if (r1 > rows) r1 = rows;
+  float4 s = make_float4(0, 0, 0, 0);
+  if (c < cols4) {
+    i64 r = r0 + threadIdx.y;
+    for (; r + 24 < r1; r += 32) {
+      float4 a = x[r * cols4 + c], b = x[(r + 8) * cols4 + c], d = x[(r + 16) * cols4 + c], e = x[(r + 24) * cols4 + c];
+      s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w;
+      s.x += b.x; s.y += b.y; s.z += b.z; s.w += b.w;
+      s.x += d.x; s.y += d.y; s.z += d.z; s.w += d.w;
+      s.x += e.x; s.y += e.y; s.z += e.z; s.w += e.w;
+    }
+    for (; r < r1; r += 8) { float4 a = x[r * cols4 + c]; s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+  }
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols4) {
+    float4 t = make_float4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { float4 a = sm[i][threadIdx.x]; t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w; }
+    part[(i64)blockIdx.y * cols4 + c] = t;
+  }
+}
 int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulate) {
   if (cols <= 0) return VB_OK;
   ProfScope prof("colsum", (double)rows * (double)cols * 4.0);
+  if ((cols & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && rows >= 64) {
+    i64 cols4 = cols / 4, col_blocks = (cols4 + 31) / 32;
+    i64 want = ((i64)ctx().sm_count * 4 + col_blocks - 1) / col_blocks;
+    i64 splits = rows / 64; if (splits < 1) splits = 1; if (splits > want) splits = want; if (splits > 65535) splits = 65535;
+    i64 rps = (rows + splits - 1) / splits;
+    splits = (rows + rps - 1) / rps;
+    void* part = nullptr;
+    VB_TRY(scratch_alloc((size_t)(splits * cols) * sizeof(float), &part));
+    k_colsum_partial_vec<<<dim3((unsigned)col_blocks, (unsigned)splits), dim3(32, 8), 0, ctx().stream>>>((const float4*)x, (float4*)part, rows, cols4, rps);
+    k_colsum_final<<<(unsigned)((cols + 255) / 256), 256, 0, ctx().stream>>>((const float*)part, out, cols, (int)splits, accumulate);
+    scratch_free(part);
+    VB_LAUNCH_CHECK();
+    return VB_OK;
+  }
   i64 col_blocks = (cols + 31) / 32;
   i64 want = ((i64)ctx().sm_count * 8 + col_blocks - 1) / col_blocks;
   i64 splits = rows / 64; if (splits < 1) splits = 1; if (splits > want) splits = want; if (splits > 65535) splits = 65535;
