@@ -129,7 +129,10 @@ int vb_batchnorm_backward(const vb_tensor* x, const vb_tensor* gamma, const vb_t
  * runs on the device.  `probs` (may be NULL) receives the [B,H,S,S] probabilities so that the
  * backward pass need not recompute them.  The results of both calls (out; dq, dk, dv) are the one exception
  * to "outputs are contiguous": they are [B,H,S,dk] views (strides S*H*dk, dk, H*dk, 1) of fresh [B,S,H,dk]
- * buffers, which makes the layer's following transpose(1,2).reshape a view instead of a copy. */
+ * buffers, which makes the layer's following transpose(1,2).reshape a view instead of a copy.
+ * When the mask is a [S,S] causal mask (0 on/below the diagonal, <= -1e9 above; S a multiple of 128, <= 1024) the
+ * triangular structure is exploited; `probs` is then only defined up to the end of each row's 128-wide diagonal tile
+ * and must be handed to the backward call together with the same mask. */
 int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,
                        vb_tensor* out, vb_tensor* probs);
 int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,

@@ -87,7 +87,9 @@ def test_gpt_loss_curve_100_steps(vb):
         loss, norm = gm.train_step(gopt, ids, tg, max_norm=1.0)
         gloss.append(loss); gn.append(norm)
     np.testing.assert_allclose(gloss, closs, rtol=1e-3, atol=1e-4)
-    np.testing.assert_allclose(gn, cn, rtol=2e-3, atol=1e-4)
+    # the reference adds g*g sequentially in f32 (about 1e-5 relative error at this size); late steps also carry the drift of 100 updates
+    np.testing.assert_allclose(gn, cn, rtol=5e-3, atol=1e-4)
+    np.testing.assert_allclose(gn[:10], cn[:10], rtol=2e-4, atol=1e-5)
     assert closs[-1] < closs[0]
     for cp, gp in zip(cm.parameters(), gm.parameters()):
         np.testing.assert_allclose(gp.numpy(), cp.numpy(), rtol=5e-3, atol=5e-4)
@@ -172,6 +174,6 @@ def test_gpt_small_full_size_properties(vb):
     assert abs(loss - (np.log(V) + 0.5 * 0.02 ** 2 * 768)) < 0.1, loss
     assert np.isfinite(norm) and norm > 0
     assert loss2 < loss
-    # everything except the embedding scatter-add is order-fixed; the loss after one step must agree closely
-    assert abs(runs[0][2] - runs[1][2]) < 1e-4
-    np.testing.assert_allclose(runs[0][3], runs[1][3], rtol=1e-4, atol=1e-6)
+    # no kernel on the step uses atomics on values: two runs from the same state are bit-identical
+    assert runs[0][0] == runs[1][0] and runs[0][2] == runs[1][2]
+    assert (runs[0][3].view(np.uint32) == runs[1][3].view(np.uint32)).all()

@@ -327,12 +327,15 @@ def test_batchnorm(vb, training):
 
 
 # ---- attention (crates/vearo/tests/fused_attention_parity.rs) ------------------------------------------------
-@pytest.mark.parametrize("B,H,S,dk,masked", [(2, 3, 6, 4, True), (1, 2, 33, 16, True), (2, 2, 130, 64, True), (1, 1, 7, 8, False)])
+@pytest.mark.parametrize("B,H,S,dk,masked", [(2, 3, 6, 4, True), (1, 2, 33, 16, True), (2, 2, 130, 64, True), (1, 1, 7, 8, False),
+                                                (1, 2, 256, 64, True), (2, 1, 128, 32, True), (1, 2, 384, 64, True), (1, 2, 256, 64, "random")])
 def test_fused_attention(vb, B, H, S, dk, masked):
     idx = np.arange(B * H * S * dk, dtype=np.float32)
     fill = lambda ph: (np.sin(0.37 * idx + ph) / 2 + np.cos(0.11 * idx + ph) / 4).reshape(B, H, S, dk).astype(np.float32)
     q0, k0, v0, go = fill(0.0), fill(1.0), fill(2.0), fill(3.0)
-    mask0 = np.triu(np.full((S, S), -1e9, np.float32), 1)
+    mask0 = np.triu(np.full((S, S), -1e9, np.float32), 1)      # S a multiple of 128 takes the triangular (causal) fast path
+    if masked == "random":
+        mask0 = (np.random.default_rng(5).standard_normal((S, S)) * 2).astype(np.float32)
 
     def case(T, m):
         q, k, v = T.from_numpy(q0, True), T.from_numpy(k0, True), T.from_numpy(v0, True)

@@ -4,6 +4,7 @@
 // (crates/vearo-autograd/src/lib.rs:316-403); include/vearo_b200.h carries the per-function citations.
 #include "common.h"
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 using namespace vb;
@@ -391,6 +392,32 @@ static int mask_strides(const vb_tensor* mask, i64 B, i64 H, i64 Sq, i64 Sk, con
   *pm = p;
   return VB_OK;
 }
+// Causal fast path.  A [S,S] additive mask that is 0 on/below the diagonal and <= -1e9 above it makes every
+// probability above the diagonal exactly 0, so score tiles there need not be computed and the products with P / dS
+// are triangular.  The pattern is checked on the device once per mask (slot contents are versioned) and the answer
+// cached; shapes outside the tensor-core kernel's rules keep the general path.
+static bool attention_is_causal(const vb_tensor* mask, const vb_tensor* q, i64 S, i64 dk) {
+  static int disabled = -1;
+  if (disabled < 0) { const char* e = getenv("VB200_NO_CAUSAL"); disabled = (e && e[0] == '1') ? 1 : 0; }
+  if (disabled || !mask || S % 128 != 0 || S > 1024 || dk % 4 != 0 || dk < 32) return false;
+  for (int i = 0; i < mask->rank - 2; ++i) if (mask->dims[i] != 1) return false;
+  if (mask->rank < 2 || mask->dims[mask->rank - 1] != S || mask->dims[mask->rank - 2] != S || mask->strides[mask->rank - 1] != 1) return false;
+  for (int i = 0; i < 4; ++i) if (q->strides[i] % 4 != 0 && i != 3) return false;
+  struct Cache { vb_slot slot = 0; uint64_t serial = 0; i64 offset = -1, S = 0, rs = 0; bool causal = false; };
+  static Cache c;
+  i64 rs = mask->strides[mask->rank - 2];
+  if (c.slot == mask->slot && c.serial == slot_serial(mask->slot) && c.offset == mask->offset && c.S == S && c.rs == rs) return c.causal;
+  float* pm;
+  if (tensor_ptr(mask, &pm) != VB_OK) return false;
+  int* d_flag = reinterpret_cast<int*>(ctx().d_scalars + 8);
+  int one = 1, h = 0;
+  if (cudaMemcpyAsync(d_flag, &one, sizeof(int), cudaMemcpyHostToDevice, ctx().stream) != cudaSuccess) return false;
+  if (launch_mask_is_causal(pm, S, rs, d_flag) != VB_OK) return false;
+  if (cudaMemcpyAsync(&h, d_flag, sizeof(int), cudaMemcpyDeviceToHost, ctx().stream) != cudaSuccess) return false;
+  if (cudaStreamSynchronize(ctx().stream) != cudaSuccess) return false;
+  c.slot = mask->slot; c.serial = slot_serial(mask->slot); c.offset = mask->offset; c.S = S; c.rs = rs; c.causal = h == 1;
+  return c.causal;
+}
 static void qk_gemm_operand(const vb_tensor* t, i64* rs, i64* cs, i64* b1, i64* b2) {
   *b1 = t->strides[0]; *b2 = t->strides[1]; *rs = t->strides[2]; *cs = t->strides[3];
 }
@@ -420,16 +447,17 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
   VB_TRY(new_output(&ptmp, 4, pd));
   float* pp; VB_TRY(slot_ptr(ptmp.slot, &pp));
   float scale = 1.0f / sqrtf((float)dk);
+  const bool causal = attention_is_causal(mask, q, S, dk);
   GemmArgs g = gemm_args();
-  g.M = S; g.N = S; g.K = dk; g.alpha = scale; g.nb1 = B; g.nb2 = H;
+  g.M = S; g.N = S; g.K = dk; g.alpha = scale; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
   g.A = pq; qk_gemm_operand(q, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);
   g.B = pk; { i64 rs, cs; qk_gemm_operand(k, &rs, &cs, &g.b_b1, &g.b_b2); g.b_rs = cs; g.b_cs = rs; }   // K^T
   g.C = pp; g.c_rs = S; g.c_cs = 1; g.c_b1 = H * S * S; g.c_b2 = S * S;
   int rc = launch_gemm(g);
-  if (rc == VB_OK) rc = launch_attn_softmax(pp, pm, ms, false, B, H, S, S, scale);
+  if (rc == VB_OK) rc = launch_attn_softmax(pp, pm, ms, causal, B, H, S, S, scale);
   if (rc == VB_OK) {
     GemmArgs o = gemm_args();
-    o.M = S; o.N = dk; o.K = S; o.nb1 = B; o.nb2 = H;
+    o.M = S; o.N = dk; o.K = S; o.nb1 = B; o.nb2 = H; o.causal = causal ? 2 : 0;
     o.A = pp; o.a_rs = S; o.a_cs = 1; o.a_b1 = H * S * S; o.a_b2 = S * S;
     o.B = pv; qk_gemm_operand(v, &o.b_rs, &o.b_cs, &o.b_b1, &o.b_b2);
     o.C = po; o.c_rs = H * dk; o.c_cs = 1; o.c_b1 = S * H * dk; o.c_b2 = dk;
@@ -450,6 +478,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
   float *pdq, *pdk, *pdv;
   VB_TRY(slot_ptr(dq->slot, &pdq)); VB_TRY(slot_ptr(dk_->slot, &pdk)); VB_TRY(slot_ptr(dv->slot, &pdv));
   float scale = 1.0f / sqrtf((float)dk);
+  const bool causal = attention_is_causal(mask, q, S, dk);
   i64 SS = S * S;
   // probabilities: reuse the saved ones or recompute them
   vb_tensor ptmp; ptmp.slot = 0;
@@ -463,12 +492,12 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     VB_TRY(new_output(&ptmp, 4, pd));
     float* t; VB_TRY(slot_ptr(ptmp.slot, &t));
     GemmArgs g = gemm_args();
-    g.M = S; g.N = S; g.K = dk; g.alpha = scale; g.nb1 = B; g.nb2 = H;
+    g.M = S; g.N = S; g.K = dk; g.alpha = scale; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
     g.A = pq; qk_gemm_operand(q, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);
     g.B = pk; { i64 rs, cs; qk_gemm_operand(k, &rs, &cs, &g.b_b1, &g.b_b2); g.b_rs = cs; g.b_cs = rs; }
     g.C = t; g.c_rs = S; g.c_cs = 1; g.c_b1 = H * SS; g.c_b2 = SS;
     VB_TRY(launch_gemm(g));
-    VB_TRY(launch_attn_softmax(t, pm, ms, false, B, H, S, S, scale));
+    VB_TRY(launch_attn_softmax(t, pm, ms, causal, B, H, S, S, scale));
     pp = t;
   }
   void* dpv = nullptr;
@@ -476,7 +505,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
   float* pdp = (float*)dpv;
   if (rc == VB_OK) {   // dV = P^T . dO
     GemmArgs g = gemm_args();
-    g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H;
+    g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 3 : 0;
     g.A = pp; g.a_rs = 1; g.a_cs = S; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pg; qk_gemm_operand(gout, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
     g.C = pdv; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
@@ -484,16 +513,16 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
   }
   if (rc == VB_OK) {   // dP = dO . V^T
     GemmArgs g = gemm_args();
-    g.M = S; g.N = S; g.K = dk; g.nb1 = B; g.nb2 = H;
+    g.M = S; g.N = S; g.K = dk; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
     g.A = pg; qk_gemm_operand(gout, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);
     g.B = pv; { i64 rs, cs; qk_gemm_operand(v, &rs, &cs, &g.b_b1, &g.b_b2); g.b_rs = cs; g.b_cs = rs; }
     g.C = pdp; g.c_rs = S; g.c_cs = 1; g.c_b1 = H * SS; g.c_b2 = SS;
     rc = launch_gemm(g);
   }
-  if (rc == VB_OK) rc = launch_attn_softmax_backward(pp, pdp, B * H * S, S, scale, false, S);   // dS * scale, in place
+  if (rc == VB_OK) rc = launch_attn_softmax_backward(pp, pdp, B * H * S, S, scale, causal, S);   // dS * scale, in place
   if (rc == VB_OK) {   // dQ = dS . K
     GemmArgs g = gemm_args();
-    g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H;
+    g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 2 : 0;
     g.A = pdp; g.a_rs = S; g.a_cs = 1; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pk; qk_gemm_operand(k, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
     g.C = pdq; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
@@ -501,7 +530,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
   }
   if (rc == VB_OK) {   // dK = dS^T . Q
     GemmArgs g = gemm_args();
-    g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H;
+    g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 3 : 0;
     g.A = pdp; g.a_rs = 1; g.a_cs = S; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pq; qk_gemm_operand(q, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
     g.C = pdk; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
@@ -547,6 +576,7 @@ int vb_reduce_to(const vb_tensor* grad, const int64_t* tdims, int trank, vb_tens
 }
 
 int vb_accumulate(const vb_tensor* dst, const vb_tensor* src) {
+  slot_touch(dst->slot);
   VB_CHECK(is_contiguous(*dst), "accumulate destination must be contiguous");
   VB_CHECK(numel(*dst) == numel(*src), "accumulate sizes differ");
   float* pd; VB_TRY(tensor_ptr(dst, &pd));
@@ -554,6 +584,7 @@ int vb_accumulate(const vb_tensor* dst, const vb_tensor* src) {
   return launch_axpy(pd, ps, numel(*dst));
 }
 int vb_copy(const vb_tensor* dst, const vb_tensor* src) {
+  slot_touch(dst->slot);
   VB_CHECK(is_contiguous(*dst), "copy destination must be contiguous");
   VB_CHECK(numel(*dst) == numel(*src), "copy sizes differ");
   float *pd, *ps; VB_TRY(tensor_ptr(dst, &pd)); VB_TRY(tensor_ptr(src, &ps));
@@ -575,6 +606,7 @@ int vb_contiguous(const vb_tensor* x, vb_tensor* out) {
   return vb_copy(out, x);
 }
 int vb_fill(const vb_tensor* dst, float value) {
+  slot_touch(dst->slot);
   VB_CHECK(is_contiguous(*dst), "fill destination must be contiguous");
   float* pd; VB_TRY(tensor_ptr(dst, &pd));
   return launch_fill(pd, value, numel(*dst));

@@ -101,21 +101,31 @@ __global__ void __launch_bounds__(256) k_attn_softmax_long(float* __restrict__ s
 // in registers, reductions are warp shuffles only (no block barrier).  V = float4 per lane.
 template <int V>
 __global__ void __launch_bounds__(128) k_attn_softmax_warp(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
-                                                           i64 H, i64 sq, i64 sk, i64 rows) {
+                                                           i64 H, i64 sq, i64 sk, i64 rows, int causal) {
   const int lane = threadIdx.x & 31;
   const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
   for (i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; row < rows; row += nwarps) {
     i64 i = row % sq, bh = row / sq, h = bh % H, b = bh / H;
     float4* r4 = reinterpret_cast<float4*>(s + row * sk);
-    const float4* m4 = mask ? reinterpret_cast<const float4*>(mask + b * ms.b + h * ms.h + i * ms.q) : nullptr;
+    const float4* m4 = (mask && !causal) ? reinterpret_cast<const float4*>(mask + b * ms.b + h * ms.h + i * ms.q) : nullptr;
+    // causal: columns j > i hold probability 0; they are not read, and zeros are written only up to the end of the
+    // 128-row tile that contains row i (what the triangular products that follow can touch)
+    const i64 live = causal ? i + 1 : sk;                       // columns [0, live) take part
+    const i64 zero_to = causal ? (((i >> 7) + 1) << 7 < sk ? ((i >> 7) + 1) << 7 : sk) : sk;
     float4 v[V];
     float mx = -INFINITY;
 #pragma unroll
     for (int e = 0; e < V; ++e) {
       int j4 = e * 32 + lane;
-      if (j4 * 4 < sk) {
+      if (j4 * 4 < live) {
         float4 x = r4[j4];
         if (m4) { float4 m = m4[j4]; x.x += m.x; x.y += m.y; x.z += m.z; x.w += m.w; }
+        if (causal) {   // the chunk that straddles the diagonal
+          i64 j = (i64)j4 * 4;
+          if (j + 1 >= live) x.y = -INFINITY;
+          if (j + 2 >= live) x.z = -INFINITY;
+          if (j + 3 >= live) x.w = -INFINITY;
+        }
         v[e] = x;
         mx = fmaxf(mx, fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w)));
       } else v[e] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
@@ -124,31 +134,46 @@ __global__ void __launch_bounds__(128) k_attn_softmax_warp(float* __restrict__ s
     float sum = 0.0f;
 #pragma unroll
     for (int e = 0; e < V; ++e)
-      if ((e * 32 + lane) * 4 < sk) {
+      if ((e * 32 + lane) * 4 < live) {
         v[e].x = expf(v[e].x - mx); v[e].y = expf(v[e].y - mx); v[e].z = expf(v[e].z - mx); v[e].w = expf(v[e].w - mx);
         sum += (v[e].x + v[e].y) + (v[e].z + v[e].w);
       }
     sum = a_wsum(sum);
     float inv = 1.0f / (sum + 1e-9f);
 #pragma unroll
-    for (int e = 0; e < V; ++e)
-      if ((e * 32 + lane) * 4 < sk) r4[e * 32 + lane] = make_float4(v[e].x * inv, v[e].y * inv, v[e].z * inv, v[e].w * inv);
+    for (int e = 0; e < V; ++e) {
+      i64 j = (i64)(e * 32 + lane) * 4;
+      if (j < live) r4[e * 32 + lane] = make_float4(v[e].x * inv, v[e].y * inv, v[e].z * inv, v[e].w * inv);
+      else if (j < zero_to) r4[e * 32 + lane] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
   }
 }
 template <int V>
-__global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __restrict__ p, float* __restrict__ dp, i64 sk, float scale, i64 rows) {
+__global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __restrict__ p, float* __restrict__ dp, i64 sk, float scale, i64 rows,
+                                                               int causal, i64 sq) {
   const int lane = threadIdx.x & 31;
   const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
   for (i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; row < rows; row += nwarps) {
     const float4* p4 = reinterpret_cast<const float4*>(p + row * sk);
     float4* d4 = reinterpret_cast<float4*>(dp + row * sk);
+    const i64 i = row % sq;
+    // causal: p is exactly 0 for columns j > i (the forward wrote those zeros inside the diagonal tile), so chunks
+    // past the diagonal contribute nothing; dp there was never computed and is overwritten with zeros up to the tile end
+    const i64 live = causal ? i + 1 : sk;
+    const i64 zero_to = causal ? (((i >> 7) + 1) << 7 < sk ? ((i >> 7) + 1) << 7 : sk) : sk;
     float4 pv[V], dv[V];
     float dot = 0.0f;
 #pragma unroll
     for (int e = 0; e < V; ++e) {
       int j4 = e * 32 + lane;
-      if (j4 * 4 < sk) {
+      if (j4 * 4 < live) {
         pv[e] = p4[j4]; dv[e] = d4[j4];
+        if (causal) {   // dp entries beyond the diagonal inside this chunk may be unwritten memory: mask them (p is 0 there)
+          i64 j = (i64)j4 * 4;
+          if (j + 1 >= live) dv[e].y = 0.0f;
+          if (j + 2 >= live) dv[e].z = 0.0f;
+          if (j + 3 >= live) dv[e].w = 0.0f;
+        }
         dot = fmaf(dv[e].x, pv[e].x, dot); dot = fmaf(dv[e].y, pv[e].y, dot); dot = fmaf(dv[e].z, pv[e].z, dot); dot = fmaf(dv[e].w, pv[e].w, dot);
       }
     }
@@ -156,9 +181,10 @@ __global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __re
 #pragma unroll
     for (int e = 0; e < V; ++e) {
       int j4 = e * 32 + lane;
-      if (j4 * 4 < sk)
+      if (j4 * 4 < live)
         d4[j4] = make_float4((pv[e].x * (dv[e].x - dot)) * scale, (pv[e].y * (dv[e].y - dot)) * scale,
                              (pv[e].z * (dv[e].z - dot)) * scale, (pv[e].w * (dv[e].w - dot)) * scale);
+      else if ((i64)j4 * 4 < zero_to) d4[j4] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
   }
 }
@@ -169,7 +195,7 @@ static inline unsigned warp_grid(i64 rows) {
 }
 
 int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale) {
-  (void)causal; (void)scale;
+  (void)scale;
   i64 rows = b * h * sq;
   if (rows <= 0 || sk <= 0) return VB_OK;
   ProfScope prof("attn_softmax", 2.0 * (double)rows * (double)sk * 4.0);
@@ -177,12 +203,14 @@ int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool cau
   if (mask) ms = MaskStrides{mstr[0], mstr[1], mstr[2], mstr[3]};
   cudaStream_t st = ctx().stream;
   bool mask_vec = !mask || (ms.k == 1 && al16p(mask) && !(ms.b & 3) && !(ms.h & 3) && !(ms.q & 3));
-  if ((sk & 3) == 0 && sk <= 1024 && al16p(s) && mask_vec) {
+  if (causal && !((sk & 3) == 0 && sk <= 1024 && al16p(s) && sq == sk)) return set_error(VB_ERR_UNSUPPORTED, "causal attention softmax needs square S <= 1024, a multiple of 4");
+  if ((sk & 3) == 0 && sk <= 1024 && al16p(s) && (mask_vec || causal)) {
     unsigned wg = warp_grid(rows);
-    if (sk <= 128) k_attn_softmax_warp<1><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
-    else if (sk <= 256) k_attn_softmax_warp<2><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
-    else if (sk <= 512) k_attn_softmax_warp<4><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
-    else k_attn_softmax_warp<8><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows);
+    const int cz = causal ? 1 : 0;
+    if (sk <= 128) k_attn_softmax_warp<1><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
+    else if (sk <= 256) k_attn_softmax_warp<2><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
+    else if (sk <= 512) k_attn_softmax_warp<4><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
+    else k_attn_softmax_warp<8><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
     VB_LAUNCH_CHECK();
     return VB_OK;
   }
@@ -228,16 +256,16 @@ __global__ void __launch_bounds__(256) k_attn_softmax_bwd_long(const float* __re
   for (i64 j = threadIdx.x; j < sk; j += blockDim.x) dr[j] = (pr[j] * (dr[j] - dot)) * scale;
 }
 int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, float scale, bool causal, i64 sq) {
-  (void)causal; (void)sq;
   if (rows <= 0 || sk <= 0) return VB_OK;
+  if (causal && !((sk & 3) == 0 && sk <= 1024 && al16p(p) && al16p(dp) && sq == sk)) return set_error(VB_ERR_UNSUPPORTED, "causal attention softmax needs square S <= 1024, a multiple of 4");
   ProfScope prof("attn_softmax_bwd", 3.0 * (double)rows * (double)sk * 4.0);
   cudaStream_t st = ctx().stream;
   if ((sk & 3) == 0 && sk <= 1024 && al16p(p) && al16p(dp)) {
     unsigned wg = warp_grid(rows);
-    if (sk <= 128) k_attn_softmax_bwd_warp<1><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
-    else if (sk <= 256) k_attn_softmax_bwd_warp<2><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
-    else if (sk <= 512) k_attn_softmax_bwd_warp<4><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
-    else k_attn_softmax_bwd_warp<8><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows);
+    if (sk <= 128) k_attn_softmax_bwd_warp<1><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
+    else if (sk <= 256) k_attn_softmax_bwd_warp<2><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
+    else if (sk <= 512) k_attn_softmax_bwd_warp<4><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
+    else k_attn_softmax_bwd_warp<8><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
     VB_LAUNCH_CHECK();
     return VB_OK;
   }
@@ -249,6 +277,24 @@ int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, fl
   else if (sk <= 2048) k_attn_softmax_bwd<16><<<g, 128, 0, st>>>(p, dp, sk, scale);
   else if (sk <= 4096) k_attn_softmax_bwd<32><<<g, 128, 0, st>>>(p, dp, sk, scale);
   else k_attn_softmax_bwd_long<<<g, 256, 0, st>>>(p, dp, sk, scale);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
+// Does a [S,S] additive mask have the causal pattern for which skipping is exact: 0 on and below the diagonal and
+// <= -1e9 above it (exp(score - 1e9 - max) is exactly 0 in f32)?  Clears *d_flag when an entry breaks it.
+__global__ void k_mask_is_causal(const float* __restrict__ mask, i64 s, i64 row_stride, int* d_flag) {
+  i64 total = s * s;
+  for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    i64 i = idx / s, j = idx % s;
+    float m = mask[i * row_stride + j];
+    bool ok = j <= i ? (m == 0.0f) : (m <= -1e9f);
+    if (!ok) *d_flag = 0;
+  }
+}
+int launch_mask_is_causal(const float* mask, i64 s, i64 row_stride, int* d_flag) {
+  i64 blocks = (s * s + 255) / 256, cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
+  k_mask_is_causal<<<(unsigned)blocks, 256, 0, ctx().stream>>>(mask, s, row_stride, d_flag);
   VB_LAUNCH_CHECK();
   return VB_OK;
 }

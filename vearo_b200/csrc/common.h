@@ -40,6 +40,8 @@ int slot_alloc(i64 numel, bool zero, vb_slot* out);
 int slot_ptr(vb_slot s, float** p, i64* numel = nullptr);
 int slot_release(vb_slot s, int* freed);
 int slot_retain(vb_slot s);
+uint64_t slot_serial(vb_slot s);          // changes every time the slot id is handed out again or its contents are overwritten through the ABI
+void slot_touch(vb_slot s);               // note that the contents of a slot were overwritten
 // Raw cached device scratch, stream-ordered reuse; never shows up in the slot table.
 int scratch_alloc(size_t bytes, void** p);
 void scratch_free(void* p);
@@ -134,12 +136,19 @@ struct GemmArgs {
   i64 nb1, nb2;     // batch counts (>= 1)
   i64 a_b1, a_b2, b_b1, b_b2, c_b1, c_b2;   // batch strides (0 = broadcast)
   float alpha, beta;
+  // Triangular structure of attention with a causal mask (square S x S problems, exact zeros above the diagonal):
+  //   1  C tiles strictly above the diagonal are neither computed nor written (scores, dP)
+  //   2  A[m, k] == 0 for k > m: the k range of a tile stops at its last row (P.V, dS.K)
+  //   3  A[m, k] == 0 for k < m (A is a transposed view of such a matrix): the k range starts at the tile's first row (P^T.dO, dS^T.Q)
+  // Kernels that do not exploit it compute the full product, which gives the same values.
+  int causal;
 };
 int launch_gemm(const GemmArgs& g);
 inline GemmArgs gemm_args() { GemmArgs g{}; g.nb1 = g.nb2 = 1; g.alpha = 1.0f; g.beta = 0.0f; return g; }
 
 // attention.cu
 int launch_attn_softmax(float* s, const float* mask, const i64 mask_strides[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale);
+int launch_mask_is_causal(const float* mask, i64 s, i64 row_stride, int* d_flag);   // d_flag <- 0 when some entry breaks the causal pattern
 int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 sk, float scale, bool causal, i64 sq);
 
 // optim.cu

@@ -100,6 +100,8 @@ int launch_gemm(const GemmArgs& g) {
   bool handled = false;
   VB_TRY(launch_gemm_tc(g, &handled));
   if (handled) return VB_OK;
+  // a caller that relies on triangular structure leaves parts of its operands unwritten: only the tensor-core kernel honours that
+  if (g.causal) return set_error(VB_ERR_UNSUPPORTED, "triangular (causal) product outside the tensor-core kernel's shape rules");
   return launch_gemm_simt(g);
 }
 

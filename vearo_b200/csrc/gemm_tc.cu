@@ -50,6 +50,7 @@ struct TcParams {
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
   int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
+  int causal;                                     // see GemmArgs::causal
   int debug;                                      // timing experiments only (results are wrong): 1 skip the split, 2 issue one MMA of three
   int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
   float alpha, beta;
@@ -167,8 +168,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   const i64 bz = blockIdx.z % nbatch; const int split = (int)(blockIdx.z / nbatch);
   const int b1 = (int)(bz / p.nb2), b2 = (int)(bz % p.nb2);
   const i64 kblocks_total = (p.K + BK - 1) / BK;
-  const i64 kb0 = (i64)split * p.kblocks_per_split;
+  i64 kb0 = (i64)split * p.kblocks_per_split;
   i64 kb1 = kb0 + p.kblocks_per_split; if (kb1 > kblocks_total) kb1 = kblocks_total;
+  if (p.causal == 1 && tile_n * p.bn >= (tile_m + 1) * BM) return;                       // whole tile above the diagonal (uniform exit, nothing allocated yet)
+  if (p.causal == 2) { i64 lim = ((tile_m + 1) * BM + BK - 1) / BK; if (kb1 > lim) kb1 = lim; }
+  if (p.causal == 3) { i64 lo = (tile_m * BM) / BK; if (kb0 < lo) kb0 = lo; }
   const int nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0);
 
   if (threadIdx.x == 0) {
@@ -421,7 +425,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   if (g.c_cs != 1) return VB_OK;
   const i64 nb = g.nb1 * g.nb2;
   // worth a tensor-core launch?  (tiny products stay on the CUDA cores: exact and launch-bound anyway)
-  if (g.M < 32 || g.N < 32 || g.K < 8 || (double)g.M * (double)g.N * (double)g.K * (double)nb < 4.0e6) return VB_OK;
+  if (g.M < 32 || g.N < 32 || g.K < 8) return VB_OK;
+  if (!g.causal && (double)g.M * (double)g.N * (double)g.K * (double)nb < 4.0e6) return VB_OK;
   if (g.M > 0x7fffffffLL || g.N > 0x7fffffffLL || g.K > 0x7fffffffLL || nb > 60000) return VB_OK;
   if (g.nb1 > 1 && g.c_b1 <= 0) return VB_OK;
   if (g.nb2 > 1 && g.c_b2 <= 0) return VB_OK;
@@ -498,6 +503,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.a_bcast1 = oa.bc1; p.a_bcast2 = oa.bc2; p.b_bcast1 = ob.bc1; p.b_bcast2 = ob.bc2;
   p.a_mn = oa.mn; p.b_mn = ob.mn;
   p.alpha = g.alpha; p.beta = g.beta; p.err = ctx().d_err;
+  p.causal = (splits == 1 && g.M == (g.causal == 1 ? g.N : g.K)) ? g.causal : 0;
 
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }

@@ -50,8 +50,8 @@ int launch_embedding(const float* ids, const float* w, float* out, i64 n, i64 vo
   VB_LAUNCH_CHECK();
   return VB_OK;
 }
-// Backward: gw[id] += g[i].  Rows that share an id are added with float atomics (red.add), so the
-// order of those additions is not fixed; gw must be zero on entry.
+// Fallback backward (D > 1024 or unaligned): gw[id] += g[i] with float atomics; the order of additions into one row
+// is then not fixed.  gw must be zero on entry (both paths are given a zeroed buffer).
 __global__ void k_embedding_backward(const float* __restrict__ ids, const float* __restrict__ g, float* __restrict__ gw,
                                      i64 n, i64 vocab, i64 d, int* err) {
   int lane = threadIdx.x & 31;
@@ -65,8 +65,66 @@ __global__ void k_embedding_backward(const float* __restrict__ ids, const float*
     for (i64 j = lane; j < d; j += 32) atomicAdd(dst + j, src[j]);
   }
 }
+// Deterministic backward for D <= 1024 (a multiple of 4): one warp owns a row of the table, scans the token ids
+// (staged in shared memory, 8192 at a time) and adds the gradient rows that hit it in increasing token position —
+// the order of the CPU backend (lib.rs:948-976) — keeping the row in registers; every row is written exactly once
+// (zeros where no token hit), so no pre-zeroing and no atomics: bit-reproducible, and bit-identical to a sequential sum.
+constexpr int kEmbChunk = 8192;
+template <int V4>
+__global__ void __launch_bounds__(256) k_embedding_backward_rows(const float* __restrict__ ids, const float* __restrict__ g, float* __restrict__ gw,
+                                                                 i64 n, i64 vocab, int d, int* err) {
+  __shared__ int sids[kEmbChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const i64 rows_per_pass = (i64)gridDim.x * 8;
+  for (i64 row0 = (i64)blockIdx.x * 8; row0 < vocab; row0 += rows_per_pass) {     // uniform per block: barriers below are safe
+    const i64 row = row0 + warp;
+    float4 acc[V4];
+#pragma unroll
+    for (int v = 0; v < V4; ++v) acc[v] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (i64 c0 = 0; c0 < n; c0 += kEmbChunk) {
+      int cn = (int)(n - c0 < kEmbChunk ? n - c0 : kEmbChunk);
+      __syncthreads();
+      for (int i = threadIdx.x; i < cn; i += blockDim.x) {
+        float v = ids[c0 + i];
+        int id = -1;
+        if (!(v >= 0.0f)) { if (row0 == 0) atomicOr(err, ERRBIT_NEG_ID); }
+        else { i64 t = (i64)roundf(v); if (t >= vocab) { if (row0 == 0) atomicOr(err, ERRBIT_OOB_ID); } else id = (int)t; }
+        sids[i] = id;
+      }
+      __syncthreads();
+      if (row < vocab) {
+        for (int base = 0; base < cn; base += 32) {
+          int id = base + lane < cn ? sids[base + lane] : -1;
+          unsigned hit = __ballot_sync(0xffffffffu, id == (int)row);
+          while (hit) {
+            int b = __ffs(hit) - 1; hit &= hit - 1;
+            const float4* src = reinterpret_cast<const float4*>(g + (c0 + base + b) * d);
+#pragma unroll
+            for (int v = 0; v < V4; ++v)
+              if ((v * 32 + lane) * 4 < d) { float4 x = src[v * 32 + lane]; acc[v].x += x.x; acc[v].y += x.y; acc[v].z += x.z; acc[v].w += x.w; }
+          }
+        }
+      }
+    }
+    if (row < vocab) {
+      float4* dst = reinterpret_cast<float4*>(gw + row * d);
+#pragma unroll
+      for (int v = 0; v < V4; ++v) if ((v * 32 + lane) * 4 < d) dst[v * 32 + lane] = acc[v];
+    }
+  }
+}
 int launch_embedding_backward(const float* ids, const float* g, float* gw, i64 n, i64 vocab, i64 d) {
   if (n <= 0 || d <= 0) return VB_OK;
+  if ((d & 3) == 0 && d <= 1024 && vocab < 0x7fffffff && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gw)) & 15) == 0) {
+    ProfScope prof("embedding_bwd", ((double)n * (double)d + (double)vocab * (double)d) * 4.0);
+    i64 blocks = (vocab + 7) / 8, cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
+    int v4 = (int)((d + 127) / 128);
+#define EMB(V) case V: k_embedding_backward_rows<V><<<(unsigned)blocks, 256, 0, ctx().stream>>>(ids, g, gw, n, vocab, (int)d, ctx().d_err); break;
+    switch (v4) { EMB(1) EMB(2) EMB(3) EMB(4) EMB(5) EMB(6) EMB(7) EMB(8) }
+#undef EMB
+    VB_LAUNCH_CHECK();
+    return VB_OK;
+  }
   ProfScope prof("embedding_bwd", 2.0 * (double)n * (double)d * 4.0);
   i64 blocks = (n + 7) / 8, cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
   k_embedding_backward<<<(unsigned)blocks, 256, 0, ctx().stream>>>(ids, g, gw, n, vocab, d, ctx().d_err);

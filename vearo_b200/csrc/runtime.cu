@@ -73,7 +73,8 @@ int scratch_alloc(size_t bytes, void** p) { return arena_alloc(bytes ? bytes : 4
 void scratch_free(void* p) { arena_free(p); }
 
 // ---- slots --------------------------------------------------------------------------------
-struct Slot { float* ptr = nullptr; i64 numel = 0; int refs = 0; };
+struct Slot { float* ptr = nullptr; i64 numel = 0; int refs = 0; uint64_t serial = 0; };
+static uint64_t g_serial = 0;
 static std::vector<Slot>& g_slots = *new std::vector<Slot>(1);       // slot 0 = none
 static std::vector<vb_slot>& g_free_ids = *new std::vector<vb_slot>();
 static i64 g_live_slots = 0;
@@ -87,7 +88,7 @@ int slot_alloc(i64 n, bool zero, vb_slot* out) {
   vb_slot id;
   if (!g_free_ids.empty()) { id = g_free_ids.back(); g_free_ids.pop_back(); }
   else { id = (vb_slot)g_slots.size(); g_slots.emplace_back(); }
-  g_slots[id].ptr = (float*)p; g_slots[id].numel = n; g_slots[id].refs = 1;
+  g_slots[id].ptr = (float*)p; g_slots[id].numel = n; g_slots[id].refs = 1; g_slots[id].serial = ++g_serial;
   ++g_live_slots;
   *out = id;
   return VB_OK;
@@ -102,6 +103,8 @@ int slot_ptr(vb_slot s, float** p, i64* n) {
   *p = sl->ptr; if (n) *n = sl->numel;
   return VB_OK;
 }
+uint64_t slot_serial(vb_slot s) { return (s == 0 || s >= g_slots.size()) ? 0 : g_slots[s].serial; }
+void slot_touch(vb_slot s) { if (s != 0 && s < g_slots.size()) g_slots[s].serial = ++g_serial; }
 int slot_retain(vb_slot s) { Slot* sl; VB_TRY(slot_get(s, &sl)); ++sl->refs; return VB_OK; }
 int slot_release(vb_slot s, int* freed) {
   Slot* sl; VB_TRY(slot_get(s, &sl));
@@ -242,6 +245,7 @@ int vb_write(vb_slot s, int64_t offset, const float* host, int64_t n) {
   float* p; i64 cap; VB_TRY(slot_ptr(s, &p, &cap));
   VB_CHECK(offset >= 0 && n >= 0 && offset + n <= cap, "range exceeds the slot");
   if (n) VB_CUDA(cudaMemcpyAsync(p + offset, host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, g_ctx.stream));
+  slot_touch(s);
   return VB_OK;
 }
 int vb_read(vb_slot s, int64_t offset, float* host, int64_t n) {
