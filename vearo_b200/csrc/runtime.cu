@@ -225,6 +225,7 @@ int vb_check_errors(void) {
   VB_CUDA(cudaStreamSynchronize(g_ctx.stream));
   if (h) {
     VB_CUDA(cudaMemsetAsync(g_ctx.d_err, 0, sizeof(int), g_ctx.stream));
+    if (h & ERRBIT_WAIT_TIMEOUT) VB_TRY(gemm_tc_reset_state());
     std::string m;
     if (h & ERRBIT_NEG_ID) m += "Token ID / target class cannot be negative; ";
     if (h & ERRBIT_OOB_ID) m += "Token ID / target class out of bounds; ";

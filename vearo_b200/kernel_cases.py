@@ -75,7 +75,21 @@ def main(case, mode):
         for _ in range(20):
             fn()
         vb.sync()
-        print("%s: %.1f us per call" % (case, (time.perf_counter() - t0) / 20 * 1e6))
+        print("%s: %.1f us per call (host clock)" % (case, (time.perf_counter() - t0) / 20 * 1e6))
+        # device time of every kernel family (CUDA events around each launcher)
+        import ctypes as C
+        L = vb.lib()
+        vb.vb_check(L.vb_profile_reset()); vb.vb_check(L.vb_profile_enable(1))
+        for _ in range(20):
+            fn()
+        vb.sync(); vb.vb_check(L.vb_profile_enable(0))
+        buf = C.create_string_buffer(4096)
+        vb.vb_check(L.vb_profile_families(buf, 4096))
+        for fam in [f for f in buf.value.decode().split(",") if f]:
+            t, n, u = C.c_double(0), C.c_int64(0), C.c_double(0)
+            vb.vb_check(L.vb_profile_read(fam.encode(), C.byref(t), C.byref(n), C.byref(u)))
+            if n.value:
+                print("  %-28s %4d launches  %9.1f us each (device)" % (fam, n.value, 1e3 * t.value / n.value))
     else:
         for _ in range(int(mode)):
             fn()
