@@ -237,6 +237,32 @@ def test_embedding_forward_backward(vb):
     both(vb, case)
 
 
+@pytest.mark.parametrize("vocab,d,shape", [(300, 128, (2, 100)), (4000, 768, (3, 700)), (64, 8, (2, 40))])
+def test_embedding_backward_owner_scan(vb, vocab, d, shape):
+    """Fewer positions than table rows: the warp of the first position naming a row sums all its duplicates in order
+    (bit-identical to the sequential sum of the CPU backend), untouched rows are exact zeros."""
+    w0 = rnd(34, vocab, d); go = rnd(36, *shape, d)
+    ids = np.random.default_rng(35).integers(0, vocab, shape).astype(np.float32)
+    ids[0, :9] = 5; ids[-1, -3:] = 5; ids[0, 20:24] = vocab - 1
+
+    def run(T):
+        w = T.from_numpy(w0, True)
+        y = T.from_numpy(ids).embedding(w)
+        n = go.size
+        y.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return w.grad().numpy()
+    orc.reset_all()
+    ref = run(orc.Tensor)
+    vb.zero_gradients(); vb.reset_active_tape()
+    got = run(vb.Tensor)
+    want = np.zeros((vocab, d), np.float32)
+    for pos, i in enumerate(ids.reshape(-1).astype(np.int64)):      # sequential f32 sum in position order
+        want[i] += go.reshape(-1, d)[pos]
+    assert np.array_equal(got, want)
+    assert_close(got, ref, "embedding backward")
+    vb.check_errors()
+
+
 @pytest.mark.parametrize("ids,msg", [([-1.0, 0.0], "negative"), ([2.0, 0.0], "out of")])
 def test_invalid_ids_are_reported_not_skipped(vb, ids, msg):
     """CPU contract (crates/vearo-backend-cpu/src/lib.rs:2865-2899): invalid ids are an error."""

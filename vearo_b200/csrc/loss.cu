@@ -65,11 +65,68 @@ __global__ void k_embedding_backward(const float* __restrict__ ids, const float*
     for (i64 j = lane; j < d; j += 32) atomicAdd(dst + j, src[j]);
   }
 }
-// Deterministic backward for D <= 1024 (a multiple of 4): one warp owns a row of the table, scans the token ids
+// Deterministic backward for D <= 1024 (a multiple of 4).  The table gradient is zero-filled first; then one warp per
+// token position scans the token ids (staged in shared memory, 8192 at a time).  The warp of the FIRST position that
+// names a row owns that row: it adds the gradient rows of all positions naming it in increasing position — the order of
+// the CPU backend (lib.rs:948-976) — in registers and writes the row once.  Warps of later duplicates stop at their first
+// earlier hit.  No atomics: bit-reproducible, and bit-identical to a sequential sum.
+constexpr int kEmbChunk = 8192;
+template <int V4>
+__global__ void __launch_bounds__(256) k_embedding_backward_tokens(const float* __restrict__ ids, const float* __restrict__ g, float* __restrict__ gw,
+                                                                   i64 n, i64 vocab, int d, int* err) {
+  __shared__ int sids[kEmbChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const i64 tok = (i64)blockIdx.x * 8 + warp;
+  int my = -1;
+  if (tok < n) {
+    float v = ids[tok];
+    if (!(v >= 0.0f)) { if (lane == 0) atomicOr(err, ERRBIT_NEG_ID); }
+    else { i64 t = (i64)roundf(v); if (t >= vocab) { if (lane == 0) atomicOr(err, ERRBIT_OOB_ID); } else my = (int)t; }
+  }
+  bool owner = my >= 0;
+  float4 acc[V4];
+#pragma unroll
+  for (int v = 0; v < V4; ++v) acc[v] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  for (i64 c0 = 0; c0 < n; c0 += kEmbChunk) {      // uniform per block: the barriers are safe
+    int cn = (int)(n - c0 < kEmbChunk ? n - c0 : kEmbChunk);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn; i += blockDim.x) {
+      float v = ids[c0 + i];
+      int id = -1;
+      if (v >= 0.0f) { i64 t = (i64)roundf(v); if (t < vocab) id = (int)t; }
+      sids[i] = id;
+    }
+    __syncthreads();
+    if (!owner) continue;
+    for (int base = 0; base < cn; base += 32) {
+      int id = base + lane < cn ? sids[base + lane] : -1;
+      unsigned hit = __ballot_sync(0xffffffffu, id == my);
+      if (!hit) continue;
+      const i64 j0 = c0 + base;
+      if (j0 < tok) {       // positions before this one in the word
+        unsigned before = tok - j0 >= 32 ? 0xffffffffu : ((1u << (unsigned)(tok - j0)) - 1u);
+        if (hit & before) { owner = false; break; }
+      }
+      while (hit) {
+        int b = __ffs(hit) - 1; hit &= hit - 1;
+        const float4* src = reinterpret_cast<const float4*>(g + (j0 + b) * d);
+#pragma unroll
+        for (int v = 0; v < V4; ++v)
+          if ((v * 32 + lane) * 4 < d) { float4 x = src[v * 32 + lane]; acc[v].x += x.x; acc[v].y += x.y; acc[v].z += x.z; acc[v].w += x.w; }
+      }
+    }
+  }
+  if (owner) {
+    float4* dst = reinterpret_cast<float4*>(gw + (i64)my * d);
+#pragma unroll
+    for (int v = 0; v < V4; ++v) if ((v * 32 + lane) * 4 < d) dst[v * 32 + lane] = acc[v];
+  }
+}
+// The same result when there are more token positions than table rows (the scan above is quadratic in the positions):
+// one warp owns a row of the table, scans the token ids
 // (staged in shared memory, 8192 at a time) and adds the gradient rows that hit it in increasing token position —
 // the order of the CPU backend (lib.rs:948-976) — keeping the row in registers; every row is written exactly once
 // (zeros where no token hit), so no pre-zeroing and no atomics: bit-reproducible, and bit-identical to a sequential sum.
-constexpr int kEmbChunk = 8192;
 template <int V4>
 __global__ void __launch_bounds__(256) k_embedding_backward_rows(const float* __restrict__ ids, const float* __restrict__ g, float* __restrict__ gw,
                                                                  i64 n, i64 vocab, int d, int* err) {
@@ -117,11 +174,19 @@ int launch_embedding_backward(const float* ids, const float* g, float* gw, i64 n
   if (n <= 0 || d <= 0) return VB_OK;
   if ((d & 3) == 0 && d <= 1024 && vocab < 0x7fffffff && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(gw)) & 15) == 0) {
     ProfScope prof("embedding_bwd", ((double)n * (double)d + (double)vocab * (double)d) * 4.0);
-    i64 blocks = (vocab + 7) / 8, cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
     int v4 = (int)((d + 127) / 128);
-#define EMB(V) case V: k_embedding_backward_rows<V><<<(unsigned)blocks, 256, 0, ctx().stream>>>(ids, g, gw, n, vocab, (int)d, ctx().d_err); break;
-    switch (v4) { EMB(1) EMB(2) EMB(3) EMB(4) EMB(5) EMB(6) EMB(7) EMB(8) }
+    if (n <= vocab) {
+      VB_CUDA(cudaMemsetAsync(gw, 0, (size_t)(vocab * d) * sizeof(float), ctx().stream));
+      i64 blocks = (n + 7) / 8;
+#define EMB(V) case V: k_embedding_backward_tokens<V><<<(unsigned)blocks, 256, 0, ctx().stream>>>(ids, g, gw, n, vocab, (int)d, ctx().d_err); break;
+      switch (v4) { EMB(1) EMB(2) EMB(3) EMB(4) EMB(5) EMB(6) EMB(7) EMB(8) }
 #undef EMB
+    } else {
+      i64 blocks = (vocab + 7) / 8, cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
+#define EMB(V) case V: k_embedding_backward_rows<V><<<(unsigned)blocks, 256, 0, ctx().stream>>>(ids, g, gw, n, vocab, (int)d, ctx().d_err); break;
+      switch (v4) { EMB(1) EMB(2) EMB(3) EMB(4) EMB(5) EMB(6) EMB(7) EMB(8) }
+#undef EMB
+    }
     VB_LAUNCH_CHECK();
     return VB_OK;
   }

@@ -148,20 +148,30 @@ __global__ void __launch_bounds__(256) k_ln_bwd_warp(const float* __restrict__ x
   }
 }
 
-// Second stage of the fast path: add the per-CTA partial rows of dw and db in CTA order.  A 32 x 8 block owns
-// 32 columns; its 8 row lanes each add every 8th partial row, then lane 0 adds the 8 sums in lane order.
-__global__ void __launch_bounds__(256) k_ln_partials_sum(const float* __restrict__ part_w, const float* __restrict__ part_b,
-                                                          float* __restrict__ gw, float* __restrict__ gb, int ctas, int C) {
-  __shared__ float sw[8][33], sb[8][33];
+// Second stage of the fast path: add the per-CTA partial rows of dw and db in a fixed order.  A 32 x 32 block owns
+// 32 columns; its 32 row lanes each add every 32nd partial row (four loads in flight), then lane 0 adds the 32 sums
+// in lane order.
+__global__ void __launch_bounds__(1024) k_ln_partials_sum(const float* __restrict__ part_w, const float* __restrict__ part_b,
+                                                           float* __restrict__ gw, float* __restrict__ gb, int ctas, int C) {
+  __shared__ float sw[32][33], sb[32][33];
   int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.0f, b = 0.0f;
-  if (c < C) for (int i = threadIdx.y; i < ctas; i += 8) { a += part_w[(i64)i * C + c]; b += part_b[(i64)i * C + c]; }
+  if (c < C) {
+    int i = threadIdx.y;
+    for (; i + 96 < ctas; i += 128) {
+      float a0 = part_w[(i64)i * C + c], a1 = part_w[(i64)(i + 32) * C + c], a2 = part_w[(i64)(i + 64) * C + c], a3 = part_w[(i64)(i + 96) * C + c];
+      float b0 = part_b[(i64)i * C + c], b1 = part_b[(i64)(i + 32) * C + c], b2 = part_b[(i64)(i + 64) * C + c], b3 = part_b[(i64)(i + 96) * C + c];
+      a += a0; a += a1; a += a2; a += a3;
+      b += b0; b += b1; b += b2; b += b3;
+    }
+    for (; i < ctas; i += 32) { a += part_w[(i64)i * C + c]; b += part_b[(i64)i * C + c]; }
+  }
   sw[threadIdx.y][threadIdx.x] = a; sb[threadIdx.y][threadIdx.x] = b;
   __syncthreads();
   if (threadIdx.y == 0 && c < C) {
     float ta = 0.0f, tb = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { ta += sw[i][threadIdx.x]; tb += sb[i][threadIdx.x]; }
+    for (int i = 0; i < 32; ++i) { ta += sw[i][threadIdx.x]; tb += sb[i][threadIdx.x]; }
     gw[c] = ta; gb[c] = tb;
   }
 }
@@ -244,7 +254,7 @@ int launch_layernorm_backward(const float* x, const float* w, const float* g, fl
       k_ln_bwd_warp<V><<<(unsigned)blocks, warps * 32, smem, st>>>(x, w, g, gx, pw, pb, rows, (int)c, eps); break;
     switch (vpt) { LN_BWD(1) LN_BWD(2) LN_BWD(3) LN_BWD(4) LN_BWD(5) LN_BWD(6) LN_BWD(7) LN_BWD(8) }
 #undef LN_BWD
-    k_ln_partials_sum<<<(unsigned)((c + 31) / 32), dim3(32, 8), 0, st>>>(pw, pb, gw, gb, (int)blocks, (int)c);
+    k_ln_partials_sum<<<(unsigned)((c + 31) / 32), dim3(32, 32), 0, st>>>(pw, pb, gw, gb, (int)blocks, (int)c);
     scratch_free(part);
   } else {
     void* stats = nullptr;

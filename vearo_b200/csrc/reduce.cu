@@ -92,12 +92,28 @@ __global__ void k_colsum_partial(const float* __restrict__ x, float* __restrict_
     part[(i64)blockIdx.y * cols + c] = t;
   }
 }
-__global__ void k_colsum_final(const float* __restrict__ part, float* __restrict__ out, i64 cols, int splits, bool accumulate) {
-  i64 c = blockIdx.x * (i64)blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// Adds the partial rows in a fixed order: a 32 x 32 block owns 32 columns, row lane y adds partial rows y, y + 32, ...
+// (four loads in flight), then lane 0 adds the 32 sums in lane order.
+__global__ void __launch_bounds__(1024) k_colsum_final(const float* __restrict__ part, float* __restrict__ out, i64 cols, int splits, bool accumulate) {
+  __shared__ float sm[32][33];
+  i64 c = (i64)blockIdx.x * 32 + threadIdx.x;
   float s = 0.0f;
-  for (int i = 0; i < splits; ++i) s += part[(i64)i * cols + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < cols) {
+    int i = threadIdx.y;
+    for (; i + 96 < splits; i += 128) {
+      float a0 = part[(i64)i * cols + c], a1 = part[(i64)(i + 32) * cols + c], a2 = part[(i64)(i + 64) * cols + c], a3 = part[(i64)(i + 96) * cols + c];
+      s += a0; s += a1; s += a2; s += a3;
+    }
+    for (; i < splits; i += 32) s += part[(i64)i * cols + c];
+  }
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += sm[i][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 // 128-bit variant: a 32 x 8 block owns 128 columns (one float4 per thread and row), four rows in flight per thread.
 __global__ void __launch_bounds__(256) k_colsum_partial_vec(const float4* __restrict__ x, float4* __restrict__ part, i64 rows, i64 cols4, i64 rows_per_split) {
@@ -138,7 +154,7 @@ int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulat
     void* part = nullptr;
     VB_TRY(scratch_alloc((size_t)(splits * cols) * sizeof(float), &part));
     k_colsum_partial_vec<<<dim3((unsigned)col_blocks, (unsigned)splits), dim3(32, 8), 0, ctx().stream>>>((const float4*)x, (float4*)part, rows, cols4, rps);
-    k_colsum_final<<<(unsigned)((cols + 255) / 256), 256, 0, ctx().stream>>>((const float*)part, out, cols, (int)splits, accumulate);
+    k_colsum_final<<<(unsigned)((cols + 31) / 32), dim3(32, 32), 0, ctx().stream>>>((const float*)part, out, cols, (int)splits, accumulate);
     scratch_free(part);
     VB_LAUNCH_CHECK();
     return VB_OK;
@@ -152,7 +168,7 @@ int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulat
   VB_TRY(scratch_alloc((size_t)(splits * cols) * sizeof(float), &part));
   dim3 grid((unsigned)col_blocks, (unsigned)splits), block(32, 8);
   k_colsum_partial<<<grid, block, 0, ctx().stream>>>(x, (float*)part, rows, cols, rps);
-  k_colsum_final<<<(unsigned)((cols + 255) / 256), 256, 0, ctx().stream>>>((const float*)part, out, cols, (int)splits, accumulate);
+  k_colsum_final<<<(unsigned)((cols + 31) / 32), dim3(32, 32), 0, ctx().stream>>>((const float*)part, out, cols, (int)splits, accumulate);
   scratch_free(part);
   VB_LAUNCH_CHECK();
   return VB_OK;
