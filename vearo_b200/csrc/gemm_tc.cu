@@ -3,30 +3,37 @@
 //
 //   C[b] = alpha * A[b] . B[b] (+ beta * C[b]) (+ bias),  A [M,K] and B^T [N,K] both K-contiguous.
 //
-// Every f32 operand value x is split as x = hi + lo with hi = tf32(x) (round to nearest) and
-// lo = tf32(x - hi); the product is accumulated as lo_a*hi_b + hi_a*lo_b + hi_a*hi_b (small terms
-// first) in one FP32 accumulator, which leaves a relative error of about 2^-22 per product instead
-// of TF32's 2^-11.  The tensor pipe therefore issues three TF32 MMAs per useful multiply-add: the
+// Every f32 operand value x is split as x = hi + lo with hi = x cut to TF32's 10 mantissa bits (what the
+// tensor core reads of a raw f32 operand) and lo = tf32(x - hi), exact remainder rounded to nearest; the
+// product is accumulated as lo_a*hi_b + hi_a*lo_b + hi_a*hi_b (small terms first) in one FP32
+// accumulator, which leaves a relative error of about 2^-20 per product instead of TF32's 2^-10.  The tensor pipe therefore issues three TF32 MMAs per useful multiply-add: the
 // useful-flop ceiling of this kernel is one third of the TF32 peak.
 //
-// CTA = 192 threads, one 128 x BN output tile (BN = 64, 128 or 256 chosen per call):
-//   warp 0      TMA producer: raw f32 tiles of A and B (BK = 16 columns, 64-byte swizzle) into a
-//               4..6-stage ring, completion signalled on `full[s]` by transaction bytes.
-//   warps 2-5   converters: wait `full[s]`, rewrite the stage in place as `hi` and write `lo` to a
-//               twin buffer at the same offsets (the split is elementwise, so the swizzle pattern is
-//               irrelevant), fence the generic-proxy writes towards the async proxy, arrive `conv[s]`.
-//               After the main loop the same warps run the epilogue (tcgen05.ld -> registers -> global).
-//   warp 1      allocates tensor memory, waits `conv[s]`, issues the 3 x (BK/8) MMAs of the stage from
-//               one thread, and releases the stage with tcgen05.commit -> `empty[s]`.
-// Split-K (grid.z) spreads long-K, few-tile problems (weight gradients) over all 148 SMs; partial
-// tiles go to scratch and a second kernel adds them in a fixed order.
+// CTA = 320 threads, one 128 x BN output tile (BN = 64, 128 or 256 chosen per call), two CTAs per SM:
+//   warp 0      TMA producer: raw f32 tiles of A and B (BK = 16 k per stage) into a ring of 2-4 stages; one TMA box per
+//               operand tile; completion signalled on `full[s]` by transaction bytes.
+//   warps 2-9   converters: wait `full[s]`, write the `lo` parts of the stage into a second (2-3 stage) ring at the same
+//               offsets (the split is elementwise, so the swizzle pattern is irrelevant); the raw tile itself serves as
+//               `hi`, because the tensor core ignores the low 13 mantissa bits of a TF32 operand.  Then fence the
+//               generic-proxy writes towards the async proxy and arrive `conv[l]`.  After the main loop the same warps
+//               run the epilogue (tcgen05.ld -> registers -> transposed through the idle lo ring -> coalesced stores).
+//   warp 1      allocates tensor memory, waits `conv[l]`, issues the 3 x (BK/8) MMAs of the stage from one thread, and
+//               releases the stages with tcgen05.commit -> `empty[s]`, `lo_empty[l]`.
+// Shared memory bandwidth is what bounds the main loop (operand reads of three MMAs + the converters' read and write
+// + the TMA writes); everything per k-block in the two single-thread roles is kept to a handful of instructions.
 //
-// Operands that are not K-contiguous (transposed views) are first repacked by a tiled transpose
-// kernel into K-contiguous scratch; shapes that break TMA's alignment rules (row stride not a
-// multiple of 16 bytes, unaligned base) fall back to the CUDA-core kernel in gemm_simt.cu.
+// Few-tile, long-K products (weight gradients) are split along K: either tiled split-K (grid.z; partial tiles go to
+// scratch and a second kernel adds them in a fixed order) or, where a tile would have two or three parts at most,
+// stream-K: the k-blocks of all tiles are dealt evenly to one CTA per slot and the CTA that completes a shared tile last
+// adds the parts in k order inside the kernel.
 //
-// Every wait on an mbarrier is bounded: when a wait runs out the CTA raises a flag in the device
-// error word, drains what it has in flight, frees its tensor memory and returns.
+// Operands: K-contiguous rows go through 64-byte-swizzle boxes; transposed views (MN-contiguous) are consumed in place
+// through 32-float boxes in the 128-byte swizzle with a 32-byte base, the only MN-major layout the tensor core takes
+// for 32-bit data.  Anything else (neither axis contiguous, strides that break TMA's 16-byte rules) is first repacked
+// into K-contiguous scratch; shapes the tensor-core path declines fall back to the CUDA-core kernel in gemm_simt.cu.
+//
+// Every wait on an mbarrier is bounded: when a wait runs out the CTA raises a flag in the device error word, drains
+// what it has in flight, frees its tensor memory and returns.
 #include "common.h"
 #include <cuda.h>
 #include <cstdio>
