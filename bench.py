@@ -28,6 +28,8 @@ WORKLOADS = {
     "gpt-small": dict(vocab=50304, T=1024, d=768, heads=12, layers=12, ff=3072, micro_batch=8, lr=6e-4, wd=0.1, clip=1.0),
     # configs[4]
     "gpt-medium": dict(vocab=50304, T=1024, d=1024, heads=16, layers=24, ff=4096, micro_batch=4, lr=6e-4, wd=0.1, clip=1.0),
+    # configs[3]: 3 x [conv3x3 -> BatchNorm -> ReLU -> MaxPool] -> AvgPool -> Linear -> cross-entropy, SGD momentum; images/s
+    "convnet": dict(kind="convnet", channels=(3, 64, 128, 256), classes=10, hw=32, micro_batch=256, lr=0.1, momentum=0.9, clip=0.0),
     # a seconds-long case for plumbing checks
     "gpt-tiny": dict(vocab=512, T=64, d=128, heads=4, layers=2, ff=512, micro_batch=4, lr=6e-4, wd=0.1, clip=1.0),
 }
@@ -126,11 +128,52 @@ def cpu_baseline_sample(cfg, T=None, threads=0):
     return T / full, desc, orc.get_threads(), times[1], block
 
 
+def cpu_convnet_step_time(cfg, images=16, steps=1, warmup=0, threads=0):
+    """Seconds per step of the CPU oracle on a batch of `images` images of the ConvNet workload (SGD step included)."""
+    from oracle import oracle as orc
+    from oracle import models as om
+    from tests import modelspec as ms
+    orc.set_threads(threads); orc.reset_all()
+    m = om.ConvNet(ms.convnet_params(cfg["channels"], cfg["classes"]))
+    opt = orc.SGD(m.parameters(), cfg["lr"], cfg["momentum"], 0.0)
+    x, y = ms.convnet_batch(images, cfg["hw"], cfg["classes"])
+    durs = []
+    for s in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.zero_gradients(); orc.reset_active_tape()
+        loss = m.forward(orc.Tensor.from_numpy(x), orc.Tensor.from_numpy(y))
+        loss.backward(); opt.step()
+        if s >= warmup:
+            durs.append(time.perf_counter() - t0)
+    cores = orc.get_threads()
+    orc.reset_all()
+    return durs, cores
+
+
+def run_reference_convnet(args, cfg):
+    from oracle import build as ob
+    ob.build()
+    images = 16
+    durs, cores = cpu_convnet_step_time(cfg, images, args.steps, args.warmup)
+    step_s = float(np.mean(durs)); value = images / step_s
+    sample = "each step = fwd + bwd + SGD on %d images of 3x%dx%d (the workload's batch is %d; cost is linear in images)" % (images, cfg["hw"], cfg["hw"], cfg["micro_batch"])
+    out = {"impl": "reference", "metric": "ConvNet fwd+bwd+SGD images/s", "value": value, "unit": "images/s", "n_gpus": args.gpus,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": args.workload, "channels": list(cfg["channels"]), "classes": cfg["classes"], "hw": cfg["hw"], "micro_batch": images},
+           "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
+           "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    print(json.dumps(out), flush=True)
+
+
 def run_reference(args, cfg, rank):
     """The reference arm: the CPU restatement of the reference's implementation (the Rust crate cannot be
     built here: no cargo/rustc), all host threads the reference itself would use."""
     if rank != 0:
         return
+    if cfg.get("kind") == "convnet":
+        return run_reference_convnet(args, cfg)
     from oracle import build as ob
     ob.build()
     from oracle import oracle as orc
@@ -216,12 +259,23 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    B, T, V = cfg["micro_batch"], cfg["T"], cfg["vocab"]
-    model = vb.SimpleGPT(V, T, cfg["d"], cfg["heads"], cfg["layers"], cfg["ff"])
-    model.load(ms.gpt_params(V, T, cfg["d"], cfg["layers"], cfg["ff"], seed=0))          # identical on every rank
+    convnet = cfg.get("kind") == "convnet"
+    B = cfg["micro_batch"]
+    if convnet:
+        T = V = 0
+        model = vb.ConvNet(list(cfg["channels"]), cfg["classes"])
+        model.load(ms.convnet_params(cfg["channels"], cfg["classes"]))                  # identical on every rank
+        opt = vb.SGD(model.parameters(), cfg["lr"], cfg["momentum"], 0.0, data_parallel=world > 1)
+        batches = [ms.convnet_batch(B, cfg["hw"], cfg["classes"], seed=1000 * rank + i) for i in range(4)]
+        units_per_rank, unit = B, "images/s"
+    else:
+        T, V = cfg["T"], cfg["vocab"]
+        model = vb.SimpleGPT(V, T, cfg["d"], cfg["heads"], cfg["layers"], cfg["ff"])
+        model.load(ms.gpt_params(V, T, cfg["d"], cfg["layers"], cfg["ff"], seed=0))      # identical on every rank
+        opt = vb.AdamW(model.parameters(), cfg["lr"], 0.9, 0.999, 1e-8, cfg["wd"], data_parallel=world > 1)
+        batches = [ms.gpt_batch(V, B, T, seed=1000 * rank + i) for i in range(4)]      # per-rank data
+        units_per_rank, unit = B * T, "tokens/s"
     n_params = sum(int(np.prod(p.shape)) for p in model.parameters())
-    opt = vb.AdamW(model.parameters(), cfg["lr"], 0.9, 0.999, 1e-8, cfg["wd"], data_parallel=world > 1)
-    batches = [ms.gpt_batch(V, B, T, seed=1000 * rank + i) for i in range(4)]          # per-rank data
     resident = [(vb.Tensor.from_numpy(a), vb.Tensor.from_numpy(b)) for a, b in batches]
     pinned = []
     for a, b in batches:
@@ -265,7 +319,7 @@ def main():
         total_ms = timed(step_resident, args.steps)
     launches1 = C.c_int64(0); L.vb_launch_count(C.byref(launches1))
     vb.check_errors()
-    tokens = world * B * T
+    tokens = world * units_per_rank
     ms_per_step = total_ms / args.steps
     value = tokens / (ms_per_step * 1e-3)
 
@@ -313,20 +367,35 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         from oracle import build as ob
         ob.build()
-        tps, desc, cores, _, _ = cpu_baseline_sample(cfg)
-        cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
+        if convnet:
+            durs, cores = cpu_convnet_step_time(cfg, 16, 1, 0)
+            cpu = {"value": 16 / durs[0], "unit": unit, "cores": cores, "kind": "port",
+                   "sample": "one fwd + bwd + SGD step on 16 images (%.1f s); cost is linear in images" % durs[0]}
+        else:
+            tps, desc, cores, _, _ = cpu_baseline_sample(cfg)
+            cpu = {"value": tps, "unit": unit, "cores": cores, "kind": "port", "sample": desc}
+    if convnet:
+        config = {"workload": args.workload, "channels": list(cfg["channels"]), "classes": cfg["classes"], "image": [3, cfg["hw"], cfg["hw"]],
+                  "micro_batch_per_gpu": B, "global_batch": world * B, "params": n_params,
+                  "optimizer": "SGD lr %g momentum %g" % (cfg["lr"], cfg["momentum"]), "parallelism": "dp%d" % world,
+                  "matmul_precision": "fp32 (convolutions unfolded onto the 3xTF32 tensor-core GEMM)",
+                  "l2": "activations of one step (about 1 GB) exceed the 126 MB L2"}
+        h2d = int(world * (B * 3 * cfg["hw"] * cfg["hw"] + B) * 4)
+    else:
+        config = {"workload": args.workload, "n_layer": cfg["layers"], "n_head": cfg["heads"], "d_model": cfg["d"], "d_ff": cfg["ff"],
+                  "vocab": V, "seq_len": T, "micro_batch_per_gpu": B, "global_batch": world * B, "params": n_params,
+                  "optimizer": "AdamW lr %g wd %g, clip %g" % (cfg["lr"], cfg["wd"], cfg["clip"]), "parallelism": "dp%d" % world,
+                  "matmul_precision": "fp32 (3xTF32 on tensor cores where the tensor-core kernel applies, exact fp32 FMA otherwise)",
+                  "l2": "working set per step (weights, activations, optimizer state: several GB) exceeds the 126 MB L2 many times over"}
+        h2d = int(world * 2 * B * T * 4)
     out = {
-        "metric": "GPT-small fwd+bwd+AdamW tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": "ConvNet fwd+bwd+SGD images/s" if convnet else "GPT-small fwd+bwd+AdamW tokens/s", "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "n_layer": cfg["layers"], "n_head": cfg["heads"], "d_model": cfg["d"], "d_ff": cfg["ff"],
-                   "vocab": V, "seq_len": T, "micro_batch_per_gpu": B, "global_batch": world * B, "params": n_params,
-                   "optimizer": "AdamW lr %g wd %g, clip %g" % (cfg["lr"], cfg["wd"], cfg["clip"]), "parallelism": "dp%d" % world,
-                   "matmul_precision": "fp32 (3xTF32 on tensor cores where the tensor-core kernel applies, exact fp32 FMA otherwise)",
-                   "l2": "working set per step (weights, activations, optimizer state: several GB) exceeds the 126 MB L2 many times over"},
-        "useful_tflops": flops_per_token(cfg) * tokens / (ms_per_step * 1e-3) / 1e12,
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(world * 2 * B * T * 4), "d2h_bytes_per_step": int(world * 8)},
+        "config": config,
+        "useful_tflops": None if convnet else flops_per_token(cfg) * tokens / (ms_per_step * 1e-3) / 1e12,
+        "e2e": {"value": e2e_value, "unit": unit, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(world * 8)},
         "gpu_launches": int(launches1.value - launches0.value),
         "clocks": clocks.summary(),
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,

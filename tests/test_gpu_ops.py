@@ -319,6 +319,26 @@ def test_conv2d_forward_backward(vb, stride, pad, k):
     both(vb, case)
 
 
+@pytest.mark.parametrize("n,cin,cout,hw,stride,pad,k", [
+    (6, 16, 32, (14, 12), 1, 1, 3),     # the ConvNet layer shape in small: unfolded rows, MN-major operands
+    (4, 3, 64, (32, 32), 1, 1, 3),      # first layer: 27 taps (row length padded to 28), input gradient still asked for
+    (5, 24, 40, (13, 11), 2, 0, 3),     # stride 2, no padding, ragged tiles everywhere
+    (3, 8, 48, (10, 10), 1, 0, 2),      # even kernel
+])
+def test_conv2d_tensor_core_path(vb, n, cin, cout, hw, stride, pad, k):
+    """Convolutions with enough work are unfolded and run as tensor-core GEMMs; same results as the direct sum."""
+    x0, w0, b0 = rnd(80, n, cin, *hw, scale=0.5), rnd(81, cout, cin, k, k, scale=0.2), rnd(82, cout)
+
+    def case(T, m):
+        x, w, b = T.from_numpy(x0, True), T.from_numpy(w0, True), T.from_numpy(b0, True)
+        y = x.conv2d(w, b, stride, pad)
+        go = (np.sin(np.arange(int(np.prod(y.shape)), dtype=np.float32) * 0.37 + 1) * 0.05).reshape(y.shape)
+        cnt = go.size
+        y.mul(T.from_numpy(go)).reshape([1, cnt]).matmul(T.from_numpy(np.ones((cnt, 1), np.float32))).reshape([1]).backward()
+        return [y, x.grad(), w.grad(), b.grad()]
+    both(vb, case)
+
+
 @pytest.mark.parametrize("k,s,p", [(2, 2, 0), (3, 2, 1), (3, 1, 1), (2, 1, 0)])
 def test_pools_forward_backward(vb, k, s, p):
     x0 = rnd(39, 2, 3, 9, 7)

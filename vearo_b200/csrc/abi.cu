@@ -312,9 +312,11 @@ int vb_conv2d_backward(const vb_tensor* x, const vb_tensor* w, const vb_tensor* 
   VB_CHECK(g->dims[0] == n && g->dims[1] == cout, "grad_out shape mismatch");
   Temp hx, hw, hg; const float *px, *pw, *pg;
   VB_TRY(contiguous_ptr(x, &px, hx)); VB_TRY(contiguous_ptr(w, &pw, hw)); VB_TRY(contiguous_ptr(g, &pg, hg));
-  VB_TRY(new_output(gx, 4, x->dims)); VB_TRY(new_output(gw, 4, w->dims)); VB_TRY(new_output(gb, 1, &cout));
-  float *pgx, *pgw, *pgb;
-  VB_TRY(slot_ptr(gx->slot, &pgx)); VB_TRY(slot_ptr(gw->slot, &pgw)); VB_TRY(slot_ptr(gb->slot, &pgb));
+  if (gx) VB_TRY(new_output(gx, 4, x->dims));
+  VB_TRY(new_output(gw, 4, w->dims)); VB_TRY(new_output(gb, 1, &cout));
+  float *pgx = nullptr, *pgw, *pgb;
+  if (gx) VB_TRY(slot_ptr(gx->slot, &pgx));
+  VB_TRY(slot_ptr(gw->slot, &pgw)); VB_TRY(slot_ptr(gb->slot, &pgb));
   return launch_conv2d_backward(px, pw, pg, pgx, pgw, pgb, n, cin, h, wd, cout, kh, kw, oh, ow, stride, padding);
 }
 

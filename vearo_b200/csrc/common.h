@@ -129,6 +129,7 @@ int launch_avgpool2d_backward(const float* g, float* gx, i64 nc, i64 h, i64 w, i
 // every operand addressed through element strides, two batch levels (b = b1 * nb2 + b2).
 struct GemmArgs {
   const float* A; const float* B; float* C; const float* bias;   // bias: length N or null
+  const float* bias_m;                                            // per-row bias: length M or null (output channels of a convolution)
   i64 M, N, K;
   i64 a_rs, a_cs;   // A[m,k] = A[m*a_rs + k*a_cs]
   i64 b_rs, b_cs;   // B[k,n] = B[k*b_rs + n*b_cs]

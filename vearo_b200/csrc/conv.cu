@@ -5,7 +5,15 @@
 // backend; padded taps contribute nothing.  Max-pool keeps the FIRST maximum in (i, j) scan order
 // (strict >) and never selects a padded tap; average-pool divides by the number of valid taps.
 // All kernels are gather formulations: no atomics, bit-reproducible.
+//
+// Convolutions with enough work run on the tensor cores instead: the padded input windows are unfolded into a
+// [N*OH*OW, Cin*KH*KW] matrix (rows padded to a multiple of 4 floats) and the three products become GEMMs of the
+// FP32-accurate tcgen05 kernel -- forward  out[n] = W . cols[n]^T + b  (batched over images, written straight in
+// NCHW with a per-row bias), input gradient  dcols[n] = g[n]^T . W  folded back by a gather, weight gradient
+// dW = g^T . cols  as one long-K product over all images (g transposed to [N*OH*OW, Cout] first).  Summation order
+// differs from the direct kernels; results agree with them to FP32 rounding.
 #include "common.h"
+#include <cstdlib>
 
 namespace vb {
 
@@ -28,10 +36,102 @@ __global__ void k_conv2d_fwd(const float* __restrict__ x, const float* __restric
     out[idx] = acc;
   }
 }
+// ---- unfold / fold and the GEMM formulation ---------------------------------------------------------------------
+// cols[(n, y, x), (c, i, j)] = x_pad[n, c, y*s + i - p, x*s + j - p]; row length kp >= cin*kh*kw, the tail is zero.
+__global__ void k_im2col(const float* __restrict__ x, float* __restrict__ cols, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw,
+                         i64 oh, i64 ow, i64 stride, i64 pad, i64 kc, i64 kp) {
+  i64 total = n * oh * ow * kp;
+  for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    i64 k = idx % kp, r = idx / kp;
+    float v = 0.0f;
+    if (k < kc) {
+      i64 j = k % kw, i = (k / kw) % kh, c = k / (kw * kh);
+      i64 xo = r % ow, y = (r / ow) % oh, nn = r / (ow * oh);
+      i64 ih = y * stride + i - pad, iw = xo * stride + j - pad;
+      if (ih >= 0 && ih < h && iw >= 0 && iw < wd) v = x[((nn * cin + c) * h + ih) * wd + iw];
+    }
+    cols[idx] = v;
+  }
+}
+// dX[n, c, ih, iw] = sum over taps (i, j), in that order, of dcols[(n, y, x), (c, i, j)] with y*s + i - p = ih, x*s + j - p = iw.
+__global__ void k_col2im(const float* __restrict__ dcols, float* __restrict__ gx, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw,
+                         i64 oh, i64 ow, i64 stride, i64 pad, i64 kp) {
+  i64 total = n * cin * h * wd;
+  for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
+    i64 iw = idx % wd, ih = (idx / wd) % h, c = (idx / (wd * h)) % cin, nn = idx / (wd * h * cin);
+    float acc = 0.0f;
+    for (i64 i = 0; i < kh; ++i) {
+      i64 ty = ih + pad - i;
+      if (ty < 0 || ty % stride) continue;
+      i64 y = ty / stride; if (y >= oh) continue;
+      for (i64 j = 0; j < kw; ++j) {
+        i64 tx = iw + pad - j;
+        if (tx < 0 || tx % stride) continue;
+        i64 xo = tx / stride; if (xo >= ow) continue;
+        acc += dcols[((nn * oh + y) * ow + xo) * kp + (c * kh + i) * kw + j];
+      }
+    }
+    gx[idx] = acc;
+  }
+}
+// g [n, cout, ohw] -> gt [n*ohw, cout] (32 x 32 tiles through shared memory)
+__global__ void k_nchw_to_rows(const float* __restrict__ g, float* __restrict__ gt, i64 cout, i64 ohw) {
+  __shared__ float tile[32][33];
+  const float* src = g + (i64)blockIdx.z * cout * ohw;
+  float* dst = gt + (i64)blockIdx.z * ohw * cout;
+  i64 p0 = (i64)blockIdx.x * 32, c0 = (i64)blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    i64 c = c0 + i, pp = p0 + threadIdx.x;
+    tile[i][threadIdx.x] = (c < cout && pp < ohw) ? src[c * ohw + pp] : 0.0f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += 8) {
+    i64 pp = p0 + i, c = c0 + threadIdx.x;
+    if (pp < ohw && c < cout) dst[pp * cout + c] = tile[threadIdx.x][i];
+  }
+}
+// dst [rows, cols] <- src [rows, ld] (the first `cols` entries of every row)
+__global__ void k_copy_cols(const float* __restrict__ src, float* __restrict__ dst, i64 rows, i64 cols, i64 ld) {
+  i64 total = rows * cols;
+  for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x)
+    dst[idx] = src[(idx / cols) * ld + idx % cols];
+}
+// Row length of the unfolded matrix: the taps rounded up to 4 floats, and to 32 when there are fewer than 32 taps
+// (the tensor-core GEMM wants at least 32 columns on either side of a product).
+static i64 unfolded_row(i64 kc) { return kc < 32 ? 32 : ((kc + 3) & ~i64(3)); }
+static bool conv_as_gemm(i64 n, i64 cin, i64 cout, i64 kh, i64 kw, i64 oh, i64 ow) {
+  static int off = -1;
+  if (off < 0) { const char* e = getenv("VB200_CONV_DIRECT"); off = (e && e[0] == '1') ? 1 : 0; }
+  if (off) return false;
+  double macs = (double)n * (double)oh * (double)ow * (double)cin * (double)kh * (double)kw * (double)cout;
+  return macs >= 2.0e6 && n <= 60000 && (i64)oh * ow < 0x7fffffffLL;
+}
+static int unfold(const float* x, float* cols, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad, i64 kc, i64 kp) {
+  ProfScope prof("conv_unfold", ((double)n * cin * h * wd + (double)n * oh * ow * kp) * 4.0);
+  i64 total = n * oh * ow * kp;
+  i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 32; if (blocks > cap) blocks = cap;
+  k_im2col<<<(unsigned)blocks, 256, 0, ctx().stream>>>(x, cols, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kc, kp);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
 int launch_conv2d(const float* x, const float* w, const float* b, float* out, i64 n, i64 cin, i64 h, i64 wd,
                   i64 cout, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad) {
   i64 total = n * cout * oh * ow;
   if (total <= 0) return VB_OK;
+  if (conv_as_gemm(n, cin, cout, kh, kw, oh, ow)) {
+    const i64 kc = cin * kh * kw, kp = unfolded_row(kc), ohw = oh * ow;
+    Temp cols;
+    VB_TRY(scratch_alloc((size_t)(n * ohw * kp) * sizeof(float), &cols.p));
+    VB_TRY(unfold(x, (float*)cols.p, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kc, kp));
+    GemmArgs g = gemm_args();            // out[img] [cout, ohw] = W [cout, kc] . cols[img]^T [kc, ohw] + b[cout]
+    g.A = w; g.M = cout; g.K = kc; g.a_rs = kc; g.a_cs = 1;
+    g.B = (const float*)cols.p; g.N = ohw; g.b_rs = 1; g.b_cs = kp;
+    g.C = out; g.c_rs = ohw; g.c_cs = 1;
+    g.nb1 = 1; g.nb2 = n; g.a_b2 = 0; g.b_b2 = ohw * kp; g.c_b2 = cout * ohw;
+    g.bias_m = b;
+    return launch_gemm(g);
+  }
   i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 32; if (blocks > cap) blocks = cap;
   k_conv2d_fwd<<<(unsigned)blocks, 256, 0, ctx().stream>>>(x, w, b, out, n, cin, h, wd, cout, kh, kw, oh, ow, stride, pad);
   VB_LAUNCH_CHECK();
@@ -101,11 +201,55 @@ __global__ void k_conv2d_bwd_input(const float* __restrict__ w, const float* __r
 int launch_conv2d_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb,
                            i64 n, i64 cin, i64 h, i64 wd, i64 cout, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad) {
   cudaStream_t st = ctx().stream;
+  if (n * cout * oh * ow > 0 && cin > 0 && conv_as_gemm(n, cin, cout, kh, kw, oh, ow)) {
+    const i64 kc = cin * kh * kw, kp = unfolded_row(kc), ohw = oh * ow, rows = n * ohw;
+    Temp cols, gt;
+    VB_TRY(scratch_alloc((size_t)(rows * kp) * sizeof(float), &cols.p));
+    VB_TRY(scratch_alloc((size_t)(rows * cout) * sizeof(float), &gt.p));
+    {
+      ProfScope prof("conv_unfold", 2.0 * (double)rows * cout * 4.0);
+      dim3 grid((unsigned)((ohw + 31) / 32), (unsigned)((cout + 31) / 32), (unsigned)n), block(32, 8);
+      k_nchw_to_rows<<<grid, block, 0, st>>>(g, (float*)gt.p, cout, ohw);
+      VB_LAUNCH_CHECK();
+    }
+    // db = column sums of g^T; dW [cout, kc] = g^T^T [cout, rows] . cols [rows, kc]
+    VB_TRY(launch_colsum((const float*)gt.p, gb, rows, cout, false));
+    VB_TRY(unfold(x, (float*)cols.p, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kc, kp));
+    GemmArgs a = gemm_args();
+    a.A = (const float*)gt.p; a.M = cout; a.K = rows; a.a_rs = 1; a.a_cs = cout;
+    a.B = (const float*)cols.p; a.N = kc; a.b_rs = kp; a.b_cs = 1;
+    a.C = gw; a.c_rs = kc; a.c_cs = 1;
+    if (kc < 32) {          // all 32 (zero-padded) columns into scratch, then the real ones out
+      Temp wide;
+      VB_TRY(scratch_alloc((size_t)(cout * kp) * sizeof(float), &wide.p));
+      a.N = kp; a.C = (float*)wide.p; a.c_rs = kp;
+      VB_TRY(launch_gemm(a));
+      k_copy_cols<<<(unsigned)((cout * kc + 255) / 256), 256, 0, st>>>((const float*)wide.p, gw, cout, kc, kp);
+      VB_LAUNCH_CHECK();
+    } else {
+      VB_TRY(launch_gemm(a));
+    }
+    if (gx) {
+      // dcols[img] [ohw, kc] = g[img]^T [ohw, cout] . W [cout, kc], over the same scratch as cols; then folded back
+      GemmArgs d = gemm_args();
+      d.A = g; d.M = ohw; d.K = cout; d.a_rs = 1; d.a_cs = ohw;
+      d.B = w; d.N = kc; d.b_rs = kc; d.b_cs = 1;
+      d.C = (float*)cols.p; d.c_rs = kp; d.c_cs = 1;
+      d.nb1 = 1; d.nb2 = n; d.a_b2 = cout * ohw; d.b_b2 = 0; d.c_b2 = ohw * kp;
+      VB_TRY(launch_gemm(d));
+      ProfScope prof("conv_fold", ((double)rows * kc + (double)n * cin * h * wd) * 4.0);
+      i64 total = n * cin * h * wd;
+      i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 32; if (blocks > cap) blocks = cap;
+      k_col2im<<<(unsigned)blocks, 256, 0, st>>>((const float*)cols.p, gx, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kp);
+      VB_LAUNCH_CHECK();
+    }
+    return VB_OK;
+  }
   if (cout > 0) k_conv2d_bwd_bias<<<(unsigned)cout, 256, 0, st>>>(g, gb, n, cout, oh * ow);
   i64 nw = cout * cin * kh * kw;
   if (nw > 0) k_conv2d_bwd_weight<<<(unsigned)nw, 256, 0, st>>>(x, g, gw, n, cin, h, wd, cout, kh, kw, oh, ow, stride, pad);
   i64 total = n * cin * h * wd;
-  if (total > 0) {
+  if (total > 0 && gx) {
     i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 32; if (blocks > cap) blocks = cap;
     k_conv2d_bwd_input<<<(unsigned)blocks, 256, 0, st>>>(w, g, gx, n, cin, h, wd, cout, kh, kw, oh, ow, stride, pad);
   }

@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(256) k_gemm_simt(GemmArgs g) {
         float* c = C + m * g.c_rs + n * g.c_cs;
         if (g.beta != 0.0f) v += g.beta * *c;
         if (g.bias) v += g.bias[n];
+        if (g.bias_m) v += g.bias_m[m];
         *c = v;
       }
     }

@@ -55,7 +55,7 @@ constexpr bool kTiming = false;
 constexpr uint32_t kSpinLimit = 1u << 20; // polls of try_wait (each waits a bounded time) before giving up
 
 struct TcParams {
-  float* C; const float* bias; float* partial;   // partial: [splits][nbatch][M][N] when splits > 1
+  float* C; const float* bias; const float* bias_m; float* partial;   // partial: [splits][nbatch][M][N] when splits > 1
   i64 M, N, K;
   i64 c_rs, c_b1, c_b2;
   i64 nb1, nb2;
@@ -291,12 +291,14 @@ __device__ __forceinline__ void store_block(const TcParams& p, const uint32_t* v
     float* out = base + row * rs + col;
     float e[4] = {x.x, x.y, x.z, x.w};
     if (fin) {
+      const float bm = p.bias_m ? p.bias_m[row] : 0.0f;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         e[t] *= p.alpha;
         if (col + t < p.N) {
           if (p.beta != 0.0f) e[t] += p.beta * out[t];
           if (p.bias) e[t] += p.bias[col + t];
+          e[t] += bm;
         }
       }
     }
@@ -653,7 +655,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 }
 
 // Sum the split-K partial tiles in split order, then apply alpha / beta / bias.
-__global__ void k_splitk_reduce(const float* __restrict__ partial, float* __restrict__ C, const float* __restrict__ bias,
+__global__ void k_splitk_reduce(const float* __restrict__ partial, float* __restrict__ C, const float* __restrict__ bias, const float* __restrict__ bias_m,
                                 i64 M, i64 N, i64 nb2, i64 nbatch, int splits, i64 c_rs, i64 c_b1, i64 c_b2, float alpha, float beta) {
   i64 total = nbatch * M * N;
   for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
@@ -664,6 +666,7 @@ __global__ void k_splitk_reduce(const float* __restrict__ partial, float* __rest
     float v = alpha * s;
     if (beta != 0.0f) v += beta * *c;
     if (bias) v += bias[n];
+    if (bias_m) v += bias_m[m];
     *c = v;
   }
 }
@@ -889,7 +892,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (e && (atoi(e) & 128)) { VB_TRY(scratch_alloc(8 * 256 * 8, &ws.p)); p.ws = (float*)ws.p; VB_CUDA(cudaMemsetAsync(ws.p, 0, 8 * 256 * 8, ctx().stream)); }
     else if (e && (atoi(e) & 64)) { VB_TRY(scratch_alloc((size_t)tiles_n * CG * tiles_m * nb * splits * 24 + 1024, &ws.p)); p.ws = (float*)ws.p; }
   }
-  p.C = g.C; p.bias = g.bias; p.partial = (float*)part.p;
+  p.C = g.C; p.bias = g.bias; p.bias_m = g.bias_m; p.partial = (float*)part.p;
   p.M = g.M; p.N = g.N; p.K = g.K; p.c_rs = g.c_rs; p.c_b1 = g.c_b1; p.c_b2 = g.c_b2; p.nb1 = g.nb1; p.nb2 = g.nb2;
   p.a_bcast1 = oa.bc1; p.a_bcast2 = oa.bc2; p.b_bcast1 = ob.bc1; p.b_bcast2 = ob.bc2;
   p.a_mn = oa.mn; p.b_mn = ob.mn;
@@ -987,7 +990,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (splits > 1) {
       i64 total = nb * g.M * g.N;
       i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 16; if (blocks > cap) blocks = cap;
-      k_splitk_reduce<<<(unsigned)blocks, 256, 0, ctx().stream>>>((const float*)part.p, g.C, g.bias, g.M, g.N, g.nb2, nb, splits,
+      k_splitk_reduce<<<(unsigned)blocks, 256, 0, ctx().stream>>>((const float*)part.p, g.C, g.bias, g.bias_m, g.M, g.N, g.nb2, nb, splits,
                                                                    g.c_rs, g.c_b1, g.c_b2, g.alpha, g.beta);
       VB_LAUNCH_CHECK();
     }

@@ -357,8 +357,9 @@ void Tensor::backward() const {
       }
       case Op::Conv2d: {
         vb_tensor gi, gw, gb;
-        check(vb_conv2d_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), (int)node.a0, (int)node.a1, &gi, &gw, &gb), "conv2d_backward");
-        gin = {Tensor::adopt(gi), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
+        const bool need_x = node.inputs[0] >= 0;       // the first layer's input takes no gradient
+        check(vb_conv2d_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), (int)node.a0, (int)node.a1, need_x ? &gi : nullptr, &gw, &gb), "conv2d_backward");
+        gin = {need_x ? Tensor::adopt(gi) : Tensor(), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
       }
       case Op::MaxPool2d: { vb_tensor o; check(vb_maxpool2d_backward(&sv[0].desc(), &go.desc(), (int)node.a0, (int)node.a1, (int)node.a2, &o), "maxpool2d_backward"); gin = {Tensor::adopt(o)}; break; }
       case Op::AvgPool2d: { vb_tensor o; check(vb_avgpool2d_backward(&sv[0].desc(), &go.desc(), (int)node.a0, (int)node.a1, (int)node.a2, &o), "avgpool2d_backward"); gin = {Tensor::adopt(o)}; break; }
