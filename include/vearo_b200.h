@@ -123,6 +123,15 @@ int vb_batchnorm(const vb_tensor* x, const vb_tensor* gamma, const vb_tensor* be
 int vb_batchnorm_backward(const vb_tensor* x, const vb_tensor* gamma, const vb_tensor* beta, const vb_tensor* running_mean,
                           const vb_tensor* running_var, const vb_tensor* grad_out, int training, float eps,
                           vb_tensor* gx, vb_tensor* ggamma, vb_tensor* gbeta);                           /* lib.rs:722-830 */
+/* Fused BatchNorm2d -> ReLU -> MaxPool(2, 2, 0): the composition of vb_batchnorm, vb_relu and vb_maxpool2d(2, 2, 0) and of
+ * their backward functions, without the two intermediate tensors.  No single reference function corresponds to it (the
+ * reference runs the three ops of vearo-nn's conv blocks one after another; autograd arms lib.rs:537-541, 562-587,
+ * 619-627): an extra export for callers that know the pattern.  `stats` ([2, C]: the mean and 1/sqrt(var + eps) the forward
+ * normalised with) is produced by the forward and consumed by the backward. */
+int vb_bn_relu_maxpool(const vb_tensor* x, const vb_tensor* gamma, const vb_tensor* beta, const vb_tensor* running_mean,
+                       const vb_tensor* running_var, int training, float momentum, float eps, vb_tensor* out, vb_tensor* stats);
+int vb_bn_relu_maxpool_backward(const vb_tensor* x, const vb_tensor* gamma, const vb_tensor* beta, const vb_tensor* stats,
+                                const vb_tensor* grad_out, int training, vb_tensor* gx, vb_tensor* ggamma, vb_tensor* gbeta);
 /* q,k,v: [B,H,S,dk] (strided views accepted); mask: NULL or an additive tensor right-aligned to
  * [B,H,S,S] with size-1 dims broadcast; softmax uses 1/(sum + 1e-9) as vearo-backend-cpu
  * lib.rs:2455.  The reference's CUDA backend runs this on the CPU (lib.rs:1594-1636); here it

@@ -372,6 +372,34 @@ def test_batchnorm(vb, training):
     both(vb, case)
 
 
+@pytest.mark.parametrize("shape,training", [((6, 5, 8, 12), True), ((3, 7, 9, 7), True), ((4, 3, 6, 6), False), ((40, 16, 16, 16), True)])
+def test_bn_relu_maxpool_fused(vb, shape, training):
+    """The fused op against the reference's three separate ops (and their three backward arms) on the CPU oracle;
+    odd heights / widths leave elements outside every pooling window, exact ties and all-negative windows included."""
+    n, c, h, w = shape
+    x0 = rnd(44, *shape) * 1.5 + 0.2
+    x0[0, 0, :2, :2] = 0.7            # a window of four equal values: the first tap takes the gradient
+    x0[0, 1, :2, :2] = -5.0           # a window the rectifier zeroes entirely
+    g0, b0 = (rnd(45, c) * 0.3 + 1).astype(np.float32), rnd(46, c) * 0.2
+    go = rnd(47, n, c, h // 2, w // 2)
+    rm0 = np.linspace(-0.5, 0.5, c).astype(np.float32); rv0 = np.linspace(0.5, 1.5, c).astype(np.float32)
+
+    def run(T, fused):
+        x, g, b = T.from_numpy(x0, True), T.from_numpy(g0, True), T.from_numpy(b0, True)
+        rm, rv = T.from_numpy(rm0), T.from_numpy(rv0)
+        y = x.bn_relu_maxpool(g, b, rm, rv, training, 0.1, 1e-5) if fused else x.batchnorm(g, b, rm, rv, training, 0.1, 1e-5).relu().maxpool2d(2, 2, 0)
+        cnt = go.size
+        y.mul(T.from_numpy(go)).reshape([1, cnt]).matmul(T.from_numpy(np.ones((cnt, 1), np.float32))).reshape([1]).backward()
+        return [t.numpy() for t in (y, rm, rv, x.grad(), g.grad(), b.grad())]
+    orc.reset_all()
+    cpu = run(orc.Tensor, False)
+    vb.zero_gradients(); vb.reset_active_tape()
+    got = run(vb.Tensor, True)
+    for a, b_, name in zip(got, cpu, "y running_mean running_var dx dgamma dbeta".split()):
+        assert_close(a, b_, "bn_relu_maxpool " + name)
+    vb.check_errors()
+
+
 # ---- attention (crates/vearo/tests/fused_attention_parity.rs) ------------------------------------------------
 @pytest.mark.parametrize("B,H,S,dk,masked", [(2, 3, 6, 4, True), (1, 2, 33, 16, True), (2, 2, 130, 64, True), (1, 1, 7, 8, False),
                                                 (1, 2, 256, 64, True), (2, 1, 128, 32, True), (1, 2, 384, 64, True), (1, 2, 256, 64, "random")])

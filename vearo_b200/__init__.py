@@ -66,6 +66,7 @@ def lib():
         L.vh_cosine_lr.argtypes = [C.c_float, C.c_float, C.c_uint32, C.c_uint32, C.c_uint32]
         L.vh_layernorm.argtypes = [C.c_int, C.c_int, C.c_int, C.c_float]
         L.vh_batchnorm.argtypes = [C.c_int] * 6 + [C.c_float, C.c_float]
+        L.vh_bn_relu_maxpool.argtypes = [C.c_int] * 6 + [C.c_float, C.c_float]
         L.vh_adamw_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 5 + [C.c_int]
         L.vh_sgd_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 3 + [C.c_int]
         L.vh_opt_set_lr.argtypes = [C.c_int, C.c_float]
@@ -198,6 +199,10 @@ class Tensor:
 
     def batchnorm(self, g, b, rm, rv, training, momentum, eps):
         return Tensor(lib().vh_batchnorm(self.h, g.h, b.h, rm.h, rv.h, int(training), momentum, eps))
+
+    def bn_relu_maxpool(self, g, b, rm, rv, training, momentum, eps):
+        """batchnorm -> relu -> maxpool2d(2, 2, 0) in one fused op."""
+        return Tensor(lib().vh_bn_relu_maxpool(self.h, g.h, b.h, rm.h, rv.h, int(training), momentum, eps))
 
     def fused_attention(self, k, v, mask=None):
         return Tensor(lib().vh_fused_attention(self.h, k.h, v.h, -1 if mask is None else mask.h))

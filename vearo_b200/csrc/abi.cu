@@ -379,6 +379,37 @@ int vb_batchnorm_backward(const vb_tensor* x, const vb_tensor* gamma, const vb_t
   return launch_batchnorm_backward(px, pg, prm, prv, pgo, pgx, pgw, pgb, x->dims[0], c, x->dims[2] * x->dims[3], training != 0, eps);
 }
 
+int vb_bn_relu_maxpool(const vb_tensor* x, const vb_tensor* gamma, const vb_tensor* beta, const vb_tensor* rm, const vb_tensor* rv,
+                       int training, float momentum, float eps, vb_tensor* out, vb_tensor* stats) {
+  VB_CHECK(x->rank == 4, "BatchNorm2d input must be rank 4 (N, C, H, W)");
+  VB_CHECK(stats != nullptr, "vb_bn_relu_maxpool needs the stats output");
+  i64 c = x->dims[1];
+  VB_CHECK(gamma->rank == 1 && beta->rank == 1 && gamma->dims[0] == c && beta->dims[0] == c, "Gamma/Beta dim must match channels C");
+  VB_CHECK(numel(*rm) == c && numel(*rv) == c && is_contiguous(*rm) && is_contiguous(*rv), "running stats must be contiguous [C]");
+  VB_CHECK(x->dims[2] >= 2 && x->dims[3] >= 2, "pooling window larger than the input");
+  Temp hx, hg, hb; const float *px, *pg, *pb;
+  VB_TRY(contiguous_ptr(x, &px, hx)); VB_TRY(contiguous_ptr(gamma, &pg, hg)); VB_TRY(contiguous_ptr(beta, &pb, hb));
+  float *prm, *prv; VB_TRY(tensor_ptr(rm, &prm)); VB_TRY(tensor_ptr(rv, &prv));
+  i64 od[4] = {x->dims[0], c, x->dims[2] / 2, x->dims[3] / 2}, sd[2] = {2, c};
+  VB_TRY(new_output(out, 4, od)); VB_TRY(new_output(stats, 2, sd));
+  float *po, *ps; VB_TRY(slot_ptr(out->slot, &po)); VB_TRY(slot_ptr(stats->slot, &ps));
+  return launch_bn_relu_maxpool(px, pg, pb, prm, prv, ps, po, x->dims[0], c, x->dims[2], x->dims[3], training != 0, momentum, eps);
+}
+int vb_bn_relu_maxpool_backward(const vb_tensor* x, const vb_tensor* gamma, const vb_tensor* beta, const vb_tensor* stats,
+                                const vb_tensor* g, int training, vb_tensor* gx, vb_tensor* gw, vb_tensor* gb) {
+  VB_CHECK(x->rank == 4 && g->rank == 4, "BatchNorm2d tensors must be rank 4");
+  i64 c = x->dims[1];
+  VB_CHECK(g->dims[0] == x->dims[0] && g->dims[1] == c && g->dims[2] == x->dims[2] / 2 && g->dims[3] == x->dims[3] / 2, "grad_out shape mismatch");
+  VB_CHECK(numel(*stats) == 2 * c, "stats must be [2, C]");
+  Temp hx, hg, hb, hs, hgo; const float *px, *pg, *pb, *ps, *pgo;
+  VB_TRY(contiguous_ptr(x, &px, hx)); VB_TRY(contiguous_ptr(gamma, &pg, hg)); VB_TRY(contiguous_ptr(beta, &pb, hb));
+  VB_TRY(contiguous_ptr(stats, &ps, hs)); VB_TRY(contiguous_ptr(g, &pgo, hgo));
+  VB_TRY(new_output(gx, 4, x->dims)); VB_TRY(new_output(gw, 1, &c)); VB_TRY(new_output(gb, 1, &c));
+  float *pgx, *pgw, *pgb;
+  VB_TRY(slot_ptr(gx->slot, &pgx)); VB_TRY(slot_ptr(gw->slot, &pgw)); VB_TRY(slot_ptr(gb->slot, &pgb));
+  return launch_bn_relu_maxpool_backward(px, pg, pb, ps, pgo, pgx, pgw, pgb, x->dims[0], c, x->dims[2], x->dims[3], training != 0);
+}
+
 // ---- attention -------------------------------------------------------------------------------
 static int mask_strides(const vb_tensor* mask, i64 B, i64 H, i64 Sq, i64 Sk, const float** pm, i64 ms[4]) {
   *pm = nullptr; ms[0] = ms[1] = ms[2] = ms[3] = 0;

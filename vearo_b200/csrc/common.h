@@ -110,6 +110,10 @@ int launch_batchnorm(const float* x, const float* gamma, const float* beta, floa
 int launch_batchnorm_backward(const float* x, const float* gamma, const float* rm, const float* rv, const float* g,
                               float* gx, float* gw, float* gb, i64 n, i64 c, i64 hw, bool training, float eps);
 // loss.cu
+int launch_bn_relu_maxpool(const float* x, const float* gamma, const float* beta, float* rm, float* rv, float* stats, float* out,
+                           i64 n, i64 c, i64 h, i64 w, bool training, float momentum, float eps);                       // bn_fused.cu
+int launch_bn_relu_maxpool_backward(const float* x, const float* gamma, const float* beta, const float* stats, const float* g,
+                                    float* gx, float* gw, float* gb, i64 n, i64 c, i64 h, i64 w, bool training);
 int launch_embedding(const float* ids, const float* w, float* out, i64 n, i64 vocab, i64 d);
 int launch_embedding_backward(const float* ids, const float* g, float* gw, i64 n, i64 vocab, i64 d);   // gw pre-zeroed
 int launch_cross_entropy(const float* logits, const float* targets, float* loss, float* stats, i64 rows, i64 v);

@@ -74,7 +74,7 @@ void Tensor::write_f32(const float* data) const {
 // ---- tape ------------------------------------------------------------------------------------
 namespace {
 enum class Op { Add, Sub, Mul, Div, Matmul, Reshape, Transpose, Permute, Relu, Gelu, Softmax, LayerNorm, Embedding,
-                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, Leaf };
+                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, BnReluPool, Leaf };
 struct Node {
   int id = 0; Op op = Op::Leaf;
   std::vector<int> inputs;
@@ -210,6 +210,13 @@ Tensor Tensor::batchnorm(const Tensor& gamma, const Tensor& beta, const Tensor& 
   if (Node* n = record(Op::BatchNorm, {this, &gamma, &beta, &rm, &rv}, out)) { n->a0 = training; n->f0 = eps; }
   return out;
 }
+Tensor Tensor::bn_relu_maxpool(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const {
+  vb_tensor o_, s_;
+  check(vb_bn_relu_maxpool(&d_, &gamma.d_, &beta.d_, &rm.d_, &rv.d_, training, momentum, eps, &o_, &s_), "bn_relu_maxpool");
+  Tensor out = Tensor::adopt(o_), stats = Tensor::adopt(s_);
+  if (Node* n = record(Op::BnReluPool, {this, &gamma, &beta}, out)) { n->a0 = training; n->extra = stats; }
+  return out;
+}
 Tensor Tensor::fused_attention(const Tensor& k, const Tensor& v, const Tensor* mask) const {
   std::vector<const Tensor*> ins = {this, &k, &v};
   if (mask) ins.push_back(mask);
@@ -340,6 +347,11 @@ void Tensor::backward() const {
         check(vb_batchnorm_backward(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), &sv[3].desc(), &sv[4].desc(), &go.desc(),
                                     (int)node.a0, node.f0, &gx, &gw, &gb), "batchnorm_backward");
         gin = {Tensor::adopt(gx), Tensor::adopt(gw), Tensor::adopt(gb), Tensor(), Tensor()}; break;
+      }
+      case Op::BnReluPool: {
+        vb_tensor gx, gw, gb;
+        check(vb_bn_relu_maxpool_backward(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), &node.extra.desc(), &go.desc(), (int)node.a0, &gx, &gw, &gb), "bn_relu_maxpool_backward");
+        gin = {Tensor::adopt(gx), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
       }
       case Op::Embedding: { vb_tensor o; check(vb_embedding_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), &o), "embedding_backward"); gin = {Tensor(), Tensor::adopt(o)}; break; }
       case Op::CrossEntropy: {

@@ -116,7 +116,7 @@ std::vector<Tensor> ConvNet::parameters() const {
 Tensor ConvNet::loss(const Tensor& x, const Tensor& labels) {
   Tensor h = x;
   for (const auto& s : stages)
-    h = h.conv2d(s.w, s.b, 1, 1).batchnorm(s.gamma, s.beta, s.rm, s.rv, autograd::is_training(), momentum, eps).relu().maxpool2d(2, 2, 0);
+    h = h.conv2d(s.w, s.b, 1, 1).bn_relu_maxpool(s.gamma, s.beta, s.rm, s.rv, autograd::is_training(), momentum, eps);   // = batchnorm -> relu -> maxpool2d(2, 2, 0)
   std::vector<i64> sh = h.shape();
   h = h.avgpool2d((int)sh[2], (int)sh[2], 0).reshape({sh[0], sh[1]});
   return fc.forward(h).cross_entropy(labels);

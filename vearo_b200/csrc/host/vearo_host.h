@@ -67,6 +67,8 @@ class Tensor {
   Tensor conv2d(const Tensor& w, const Tensor& b, int stride, int padding) const;
   Tensor maxpool2d(int k, int s, int p) const; Tensor avgpool2d(int k, int s, int p) const;
   Tensor batchnorm(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const;
+  // batchnorm -> relu -> maxpool2d(2, 2, 0) as one op (one tape node, one fused backward)
+  Tensor bn_relu_maxpool(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const;
   Tensor fused_attention(const Tensor& k, const Tensor& v, const Tensor* mask) const;
   Tensor linear(const Tensor& weight, const Tensor* bias) const;   // fused x.W^T + b
   Tensor reshape(const std::vector<i64>& shape) const;
