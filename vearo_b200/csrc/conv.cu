@@ -37,38 +37,49 @@ __global__ void k_conv2d_fwd(const float* __restrict__ x, const float* __restric
   }
 }
 // ---- unfold / fold and the GEMM formulation ---------------------------------------------------------------------
-// cols[(n, y, x), (c, i, j)] = x_pad[n, c, y*s + i - p, x*s + j - p]; row length kp >= cin*kh*kw, the tail is zero.
-__global__ void k_im2col(const float* __restrict__ x, float* __restrict__ cols, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw,
-                         i64 oh, i64 ow, i64 stride, i64 pad, i64 kc, i64 kp) {
-  i64 total = n * oh * ow * kp;
+// cols[(n, y, x), (c, i, j)] = x_pad[n, c, y*s + i - p, x*s + j - p]; row length kp >= cin*kh*kw (a multiple of 4), the tail
+// is zero.  One thread writes four consecutive taps of a row (one 16-byte store); index arithmetic in 32 bits.
+__global__ void k_im2col(const float* __restrict__ x, float* __restrict__ cols, int n, int cin, int h, int wd, int kh, int kw,
+                         int oh, int ow, int stride, int pad, int kc, int kp) {
+  const int kq = kp >> 2, khw = kh * kw;
+  const i64 total = (i64)n * oh * ow * kq;
   for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
-    i64 k = idx % kp, r = idx / kp;
-    float v = 0.0f;
-    if (k < kc) {
-      i64 j = k % kw, i = (k / kw) % kh, c = k / (kw * kh);
-      i64 xo = r % ow, y = (r / ow) % oh, nn = r / (ow * oh);
-      i64 ih = y * stride + i - pad, iw = xo * stride + j - pad;
-      if (ih >= 0 && ih < h && iw >= 0 && iw < wd) v = x[((nn * cin + c) * h + ih) * wd + iw];
+    const int q = (int)(idx % kq); const i64 r = idx / kq;
+    const int xo = (int)(r % ow); const i64 r2 = r / ow;
+    const int y = (int)(r2 % oh), nn = (int)(r2 / oh);
+    float v[4];
+    int k = q * 4, c = k / khw, rem = k - c * khw, i = rem / kw, j = rem - i * kw;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float e = 0.0f;
+      if (k < kc) {
+        int ih = y * stride + i - pad, iw = xo * stride + j - pad;
+        if (ih >= 0 && ih < h && iw >= 0 && iw < wd) e = x[(((i64)nn * cin + c) * h + ih) * wd + iw];
+      }
+      v[t] = e;
+      ++k; if (++j == kw) { j = 0; if (++i == kh) { i = 0; ++c; } }
     }
-    cols[idx] = v;
+    reinterpret_cast<float4*>(cols)[idx] = make_float4(v[0], v[1], v[2], v[3]);
   }
 }
 // dX[n, c, ih, iw] = sum over taps (i, j), in that order, of dcols[(n, y, x), (c, i, j)] with y*s + i - p = ih, x*s + j - p = iw.
-__global__ void k_col2im(const float* __restrict__ dcols, float* __restrict__ gx, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw,
-                         i64 oh, i64 ow, i64 stride, i64 pad, i64 kp) {
-  i64 total = n * cin * h * wd;
+__global__ void k_col2im(const float* __restrict__ dcols, float* __restrict__ gx, int n, int cin, int h, int wd, int kh, int kw,
+                         int oh, int ow, int stride, int pad, int kp) {
+  const i64 total = (i64)n * cin * h * wd;
   for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
-    i64 iw = idx % wd, ih = (idx / wd) % h, c = (idx / (wd * h)) % cin, nn = idx / (wd * h * cin);
+    const int iw = (int)(idx % wd); const i64 r1 = idx / wd;
+    const int ih = (int)(r1 % h); const i64 r2 = r1 / h;
+    const int c = (int)(r2 % cin), nn = (int)(r2 / cin);
     float acc = 0.0f;
-    for (i64 i = 0; i < kh; ++i) {
-      i64 ty = ih + pad - i;
+    for (int i = 0; i < kh; ++i) {
+      int ty = ih + pad - i;
       if (ty < 0 || ty % stride) continue;
-      i64 y = ty / stride; if (y >= oh) continue;
-      for (i64 j = 0; j < kw; ++j) {
-        i64 tx = iw + pad - j;
+      int y = ty / stride; if (y >= oh) continue;
+      for (int j = 0; j < kw; ++j) {
+        int tx = iw + pad - j;
         if (tx < 0 || tx % stride) continue;
-        i64 xo = tx / stride; if (xo >= ow) continue;
-        acc += dcols[((nn * oh + y) * ow + xo) * kp + (c * kh + i) * kw + j];
+        int xo = tx / stride; if (xo >= ow) continue;
+        acc += dcols[(((i64)nn * oh + y) * ow + xo) * kp + (c * kh + i) * kw + j];
       }
     }
     gx[idx] = acc;
@@ -104,13 +115,13 @@ static bool conv_as_gemm(i64 n, i64 cin, i64 cout, i64 kh, i64 kw, i64 oh, i64 o
   if (off < 0) { const char* e = getenv("VB200_CONV_DIRECT"); off = (e && e[0] == '1') ? 1 : 0; }
   if (off) return false;
   double macs = (double)n * (double)oh * (double)ow * (double)cin * (double)kh * (double)kw * (double)cout;
-  return macs >= 2.0e6 && n <= 60000 && (i64)oh * ow < 0x7fffffffLL;
+  return macs >= 2.0e6 && n <= 60000 && (i64)oh * ow < 0x7fffffffLL && cin * kh * kw < (1 << 24);
 }
 static int unfold(const float* x, float* cols, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad, i64 kc, i64 kp) {
   ProfScope prof("conv_unfold", ((double)n * cin * h * wd + (double)n * oh * ow * kp) * 4.0);
-  i64 total = n * oh * ow * kp;
+  i64 total = n * oh * ow * (kp / 4);
   i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 32; if (blocks > cap) blocks = cap;
-  k_im2col<<<(unsigned)blocks, 256, 0, ctx().stream>>>(x, cols, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kc, kp);
+  k_im2col<<<(unsigned)blocks, 256, 0, ctx().stream>>>(x, cols, (int)n, (int)cin, (int)h, (int)wd, (int)kh, (int)kw, (int)oh, (int)ow, (int)stride, (int)pad, (int)kc, (int)kp);
   VB_LAUNCH_CHECK();
   return VB_OK;
 }
@@ -240,7 +251,7 @@ int launch_conv2d_backward(const float* x, const float* w, const float* g, float
       ProfScope prof("conv_fold", ((double)rows * kc + (double)n * cin * h * wd) * 4.0);
       i64 total = n * cin * h * wd;
       i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 32; if (blocks > cap) blocks = cap;
-      k_col2im<<<(unsigned)blocks, 256, 0, st>>>((const float*)cols.p, gx, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kp);
+      k_col2im<<<(unsigned)blocks, 256, 0, st>>>((const float*)cols.p, gx, (int)n, (int)cin, (int)h, (int)wd, (int)kh, (int)kw, (int)oh, (int)ow, (int)stride, (int)pad, (int)kp);
       VB_LAUNCH_CHECK();
     }
     return VB_OK;
