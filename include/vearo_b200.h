@@ -147,6 +147,13 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
 int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,
                                 const vb_tensor* grad_out, const vb_tensor* probs_or_null,
                                 vb_tensor* dq, vb_tensor* dk, vb_tensor* dv);
+/* The same attention over a packed projection: qkv is a contiguous [B, S, 3*D] tensor whose three column blocks are q, k and
+ * v (heads side by side), as one Linear over the stacked q/k/v weights of vearo-nn's MultiHeadAttention (lib.rs:584-621)
+ * produces; `out` is the [B, S, D] context and the backward returns a single [B, S, 3*D] gradient.  No reference function
+ * corresponds to it: an extra export that saves the three head-split copies and the gradient concatenation. */
+int vb_fused_attention_packed(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, vb_tensor* out, vb_tensor* probs_or_null);
+int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, const vb_tensor* grad_out,
+                                       const vb_tensor* probs_or_null, vb_tensor* dqkv);
 
 /* ---- backward arms the reference computes on the host for CUDA tensors -------------------
  * (vearo-autograd/src/lib.rs: reduce_to 316-361, relu/gelu masks 364-403, softmax arm 547-553,

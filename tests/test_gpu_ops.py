@@ -372,6 +372,32 @@ def test_batchnorm(vb, training):
     both(vb, case)
 
 
+@pytest.mark.parametrize("B,S,H,dk,masked", [(2, 40, 3, 8, True), (1, 256, 2, 64, True), (2, 64, 4, 16, False)])
+def test_fused_attention_packed(vb, B, S, H, dk, masked):
+    """Attention over the packed [B, S, 3*D] projection (q | k | v column blocks) against the oracle fed with the three
+    head-split tensors; the single packed gradient must be the three gradients side by side."""
+    D = H * dk
+    qkv0 = (rnd(90, B, S, 3 * D) * 0.5).astype(np.float32); go = rnd(91, B, S, D)
+    mask0 = np.triu(np.full((S, S), -1e9, np.float32), 1)
+
+    orc.reset_all()
+    parts = [orc.Tensor.from_numpy(np.ascontiguousarray(qkv0[:, :, i * D:(i + 1) * D].reshape(B, S, H, dk).transpose(0, 2, 1, 3)), True) for i in range(3)]
+    o = parts[0].fused_attention(parts[1], parts[2], orc.Tensor.from_numpy(mask0) if masked else None)
+    o = o.transpose(1, 2).reshape([B, S, D])
+    n = go.size
+    o.mul(orc.Tensor.from_numpy(go)).reshape([1, n]).matmul(orc.Tensor.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+    want_o = o.numpy()
+    want_g = np.concatenate([p.grad().numpy().transpose(0, 2, 1, 3).reshape(B, S, D) for p in parts], axis=2)
+
+    vb.zero_gradients(); vb.reset_active_tape()
+    x = vb.Tensor.from_numpy(qkv0, True)
+    y = x.fused_attention_packed(H, vb.Tensor.from_numpy(mask0) if masked else None)
+    y.mul(vb.Tensor.from_numpy(go)).reshape([1, n]).matmul(vb.Tensor.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+    assert_close(y.numpy(), want_o, "packed attention out")
+    assert_close(x.grad().numpy(), want_g, "packed attention dqkv")
+    vb.check_errors()
+
+
 @pytest.mark.parametrize("shape,training", [((6, 5, 8, 12), True), ((3, 7, 9, 7), True), ((4, 3, 6, 6), False), ((40, 16, 16, 16), True)])
 def test_bn_relu_maxpool_fused(vb, shape, training):
     """The fused op against the reference's three separate ops (and their three backward arms) on the CPU oracle;

@@ -207,6 +207,10 @@ class Tensor:
     def fused_attention(self, k, v, mask=None):
         return Tensor(lib().vh_fused_attention(self.h, k.h, v.h, -1 if mask is None else mask.h))
 
+    def fused_attention_packed(self, n_head, mask=None):
+        """self = [B, S, 3*D] with column blocks q | k | v; returns the [B, S, D] context."""
+        return Tensor(lib().vh_fused_attention_packed(self.h, int(n_head), -1 if mask is None else mask.h))
+
     def linear(self, w, b=None): return Tensor(lib().vh_linear(self.h, w.h, -1 if b is None else b.h))
 
     def reshape(self, shape):

@@ -500,16 +500,13 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
   return rc;
 }
 
-int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask,
-                                const vb_tensor* gout, const vb_tensor* probs, vb_tensor* dq, vb_tensor* dk_, vb_tensor* dv) {
-  VB_CHECK(q->rank == 4 && same_shape(*q, *k) && same_shape(*q, *v) && same_shape(*q, *gout), "fused_attention_backward expects [B,H,S,dk] tensors");
+// The backward products; gradients are written as [B,S,H,dk]-ordered rows of length `ld` floats (ld = H*dk for separate
+// buffers, 3*H*dk when dq, dk and dv are the three column blocks of one packed [B,S,3*H*dk] buffer).
+static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask,
+                                   const vb_tensor* gout, const vb_tensor* probs, float* pdq, float* pdk, float* pdv, i64 ld) {
   i64 B = q->dims[0], H = q->dims[1], S = q->dims[2], dk = q->dims[3];
   float *pq, *pk, *pv, *pg;
   VB_TRY(tensor_ptr(q, &pq)); VB_TRY(tensor_ptr(k, &pk)); VB_TRY(tensor_ptr(v, &pv)); VB_TRY(tensor_ptr(gout, &pg));
-  VB_TRY(new_output_bshd(dq, B, H, S, dk)); VB_TRY(new_output_bshd(dk_, B, H, S, dk)); VB_TRY(new_output_bshd(dv, B, H, S, dk));
-  if (numel(*q) == 0) return VB_OK;
-  float *pdq, *pdk, *pdv;
-  VB_TRY(slot_ptr(dq->slot, &pdq)); VB_TRY(slot_ptr(dk_->slot, &pdk)); VB_TRY(slot_ptr(dv->slot, &pdv));
   float scale = 1.0f / sqrtf((float)dk);
   const bool causal = attention_is_causal(mask, q, S, dk);
   i64 SS = S * S;
@@ -541,7 +538,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 3 : 0;
     g.A = pp; g.a_rs = 1; g.a_cs = S; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pg; qk_gemm_operand(gout, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
-    g.C = pdv; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
+    g.C = pdv; g.c_rs = ld; g.c_cs = 1; g.c_b1 = S * ld; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
   if (rc == VB_OK) {   // dP = dO . V^T
@@ -558,7 +555,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 2 : 0;
     g.A = pdp; g.a_rs = S; g.a_cs = 1; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pk; qk_gemm_operand(k, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
-    g.C = pdq; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
+    g.C = pdq; g.c_rs = ld; g.c_cs = 1; g.c_b1 = S * ld; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
   if (rc == VB_OK) {   // dK = dS^T . Q
@@ -566,11 +563,68 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 3 : 0;
     g.A = pdp; g.a_rs = 1; g.a_cs = S; g.a_b1 = H * SS; g.a_b2 = SS;
     g.B = pq; qk_gemm_operand(q, &g.b_rs, &g.b_cs, &g.b_b1, &g.b_b2);
-    g.C = pdk; g.c_rs = H * dk; g.c_cs = 1; g.c_b1 = S * H * dk; g.c_b2 = dk;
+    g.C = pdk; g.c_rs = ld; g.c_cs = 1; g.c_b1 = S * ld; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
   if (dpv) scratch_free(dpv);
   if (ptmp.slot) slot_release(ptmp.slot, nullptr);
+  return rc;
+}
+int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask,
+                                const vb_tensor* gout, const vb_tensor* probs, vb_tensor* dq, vb_tensor* dk_, vb_tensor* dv) {
+  VB_CHECK(q->rank == 4 && same_shape(*q, *k) && same_shape(*q, *v) && same_shape(*q, *gout), "fused_attention_backward expects [B,H,S,dk] tensors");
+  i64 B = q->dims[0], H = q->dims[1], S = q->dims[2], dk = q->dims[3];
+  VB_TRY(new_output_bshd(dq, B, H, S, dk)); VB_TRY(new_output_bshd(dk_, B, H, S, dk)); VB_TRY(new_output_bshd(dv, B, H, S, dk));
+  if (numel(*q) == 0) return VB_OK;
+  float *pdq, *pdk, *pdv;
+  VB_TRY(slot_ptr(dq->slot, &pdq)); VB_TRY(slot_ptr(dk_->slot, &pdk)); VB_TRY(slot_ptr(dv->slot, &pdv));
+  return attention_backward_core(q, k, v, mask, gout, probs, pdq, pdk, pdv, H * dk);
+}
+
+// Attention over a packed projection: qkv is a contiguous [B, S, 3*D] tensor whose column blocks [0,D), [D,2D), [2D,3D) are
+// q, k and v with heads side by side (what one Linear with the three weight matrices stacked produces).  The result is
+// the [B, S, D] context; the backward returns one [B, S, 3*D] gradient with the same column blocks, written by the
+// products themselves.
+static int packed_views(const vb_tensor* qkv, int n_head, vb_tensor* q, vb_tensor* k, vb_tensor* v) {
+  VB_CHECK(qkv->rank == 3 && is_contiguous(*qkv) && qkv->dims[2] % 3 == 0, "packed qkv must be a contiguous [B, S, 3*D] tensor");
+  i64 B = qkv->dims[0], S = qkv->dims[1], D = qkv->dims[2] / 3;
+  VB_CHECK(n_head > 0 && D % n_head == 0, "D must be divisible by the number of heads");
+  i64 dk = D / n_head;
+  vb_tensor t = *qkv;
+  t.rank = 4; t.dims[0] = B; t.dims[1] = n_head; t.dims[2] = S; t.dims[3] = dk;
+  t.strides[0] = S * 3 * D; t.strides[1] = dk; t.strides[2] = 3 * D; t.strides[3] = 1;
+  *q = t; *k = t; *v = t;
+  k->offset += D; v->offset += 2 * D;
+  return VB_OK;
+}
+int vb_fused_attention_packed(const vb_tensor* qkv, int n_head, const vb_tensor* mask, vb_tensor* out, vb_tensor* probs) {
+  vb_tensor q, k, v;
+  VB_TRY(packed_views(qkv, n_head, &q, &k, &v));
+  VB_TRY(vb_fused_attention(&q, &k, &v, mask, out, probs));
+  // the [B,H,S,dk] view of the [B,S,H,dk] buffer, seen as [B,S,D]
+  i64 B = qkv->dims[0], S = qkv->dims[1], D = qkv->dims[2] / 3;
+  out->rank = 3; out->dims[0] = B; out->dims[1] = S; out->dims[2] = D;
+  out->strides[0] = S * D; out->strides[1] = D; out->strides[2] = 1;
+  return VB_OK;
+}
+int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask, const vb_tensor* gout,
+                                       const vb_tensor* probs, vb_tensor* dqkv) {
+  vb_tensor q, k, v;
+  VB_TRY(packed_views(qkv, n_head, &q, &k, &v));
+  i64 B = qkv->dims[0], S = qkv->dims[1], D = qkv->dims[2] / 3, dk = D / n_head;
+  VB_CHECK(gout->rank == 3 && gout->dims[0] == B && gout->dims[1] == S && gout->dims[2] == D, "grad_out must be [B, S, D]");
+  Temp hg; const float* pg;
+  VB_TRY(contiguous_ptr(gout, &pg, hg));
+  vb_tensor g4 = *gout;                      // [B,S,D] rows seen as [B,H,S,dk]
+  vb_tensor gc; gc.slot = 0;
+  if (!is_contiguous(*gout)) { VB_TRY(vb_contiguous(gout, &gc)); g4 = gc; }
+  g4.rank = 4; g4.dims[0] = B; g4.dims[1] = n_head; g4.dims[2] = S; g4.dims[3] = dk;
+  g4.strides[0] = S * D; g4.strides[1] = dk; g4.strides[2] = D; g4.strides[3] = 1;
+  int rc = new_output(dqkv, 3, qkv->dims);
+  float* pd = nullptr;
+  if (rc == VB_OK && numel(*qkv) > 0) rc = slot_ptr(dqkv->slot, &pd);
+  if (rc == VB_OK && numel(*qkv) > 0) rc = attention_backward_core(&q, &k, &v, mask, &g4, probs, pd, pd + D, pd + 2 * D, 3 * D);
+  if (gc.slot) slot_release(gc.slot, nullptr);
   return rc;
 }
 

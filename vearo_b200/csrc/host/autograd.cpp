@@ -74,7 +74,7 @@ void Tensor::write_f32(const float* data) const {
 // ---- tape ------------------------------------------------------------------------------------
 namespace {
 enum class Op { Add, Sub, Mul, Div, Matmul, Reshape, Transpose, Permute, Relu, Gelu, Softmax, LayerNorm, Embedding,
-                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, BnReluPool, Leaf };
+                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, BnReluPool, PackRows, FusedAttentionPacked, Leaf };
 struct Node {
   int id = 0; Op op = Op::Leaf;
   std::vector<int> inputs;
@@ -87,10 +87,13 @@ struct Node {
 struct Tape { std::vector<Node> nodes; uint32_t generation = 0; };
 thread_local Tape t_tape;
 thread_local bool t_enabled = true, t_training = true;
-thread_local std::unordered_map<vb_slot, Tensor> t_grads;
+// A leaf is identified by where it lives: slot and offset (several parameters may be views of one slot).
+using LeafKey = uint64_t;
+inline LeafKey leaf_key(const Tensor& t) { return ((uint64_t)t.slot() << 40) ^ (uint64_t)t.desc().offset; }
+thread_local std::unordered_map<LeafKey, Tensor> t_grads;
 
 struct Sinks {
-  std::unordered_map<vb_slot, int> index;
+  std::unordered_map<uint64_t, int> index;      // leaf_key -> parameter index
   std::vector<Tensor> sinks;
   void (*on_ready)(int, void*) = nullptr; void* user = nullptr;
 };
@@ -141,7 +144,7 @@ void zero_gradients() { t_grads.clear(); }
 size_t tape_len() { return t_tape.nodes.size(); }
 void register_grad_sinks(const std::vector<Tensor>& params, const std::vector<Tensor>& sinks, void (*on_ready)(int, void*), void* user) {
   t_sinks = Sinks();
-  for (size_t i = 0; i < params.size(); ++i) t_sinks.index[params[i].slot()] = (int)i;
+  for (size_t i = 0; i < params.size(); ++i) t_sinks.index[leaf_key(params[i])] = (int)i;
   t_sinks.sinks = sinks; t_sinks.on_ready = on_ready; t_sinks.user = user;
 }
 void clear_grad_sinks(void* user) { if (t_sinks.user == user) t_sinks = Sinks(); }
@@ -229,6 +232,29 @@ Tensor Tensor::fused_attention(const Tensor& k, const Tensor& v, const Tensor* m
   if (Node* n = record(Op::FusedAttention, ins, out)) n->extra = probs;
   return out;
 }
+Tensor Tensor::fused_attention_packed(i64 n_head, const Tensor* mask) const {
+  std::vector<const Tensor*> ins = {this};
+  if (mask) ins.push_back(mask);
+  const bool rec = t_enabled && requires_grad();
+  vb_tensor o_, p_;
+  check(vb_fused_attention_packed(&d_, (int)n_head, mask ? &mask->d_ : nullptr, &o_, rec ? &p_ : nullptr), "fused_attention_packed");
+  Tensor out = Tensor::adopt(o_);
+  Tensor probs; if (rec) probs = Tensor::adopt(p_);
+  if (Node* n = record(Op::FusedAttentionPacked, ins, out)) { n->extra = probs; n->a0 = n_head; }
+  return out;
+}
+Tensor Tensor::pack_rows(const Tensor& a, const Tensor& b, const Tensor& c) {
+  const vb_tensor &da = a.d_, &db = b.d_, &dc = c.d_;
+  bool ok = a.defined() && da.rank >= 1 && da.slot == db.slot && da.slot == dc.slot && a.is_contiguous() && b.is_contiguous() && c.is_contiguous() &&
+            da.rank == db.rank && da.rank == dc.rank && db.offset == da.offset + a.numel() && dc.offset == db.offset + b.numel();
+  for (int i = 1; ok && i < da.rank; ++i) ok = da.dims[i] == db.dims[i] && da.dims[i] == dc.dims[i];
+  if (!ok) throw Error("pack_rows needs three contiguous views that follow one another in one storage");
+  vb_tensor d = da;
+  d.dims[0] = da.dims[0] + db.dims[0] + dc.dims[0];
+  Tensor out = view_of(a, d);
+  if (Node* n = record(Op::PackRows, {&a, &b, &c}, out)) { n->a0 = da.dims[0]; n->a1 = db.dims[0]; n->a2 = dc.dims[0]; }
+  return out;
+}
 Tensor Tensor::linear(const Tensor& weight, const Tensor* bias) const {
   VB_OUT1(vb_linear(&d_, &weight.d_, bias ? &bias->d_ : nullptr, &o_), "linear");
   std::vector<const Tensor*> ins = {this, &weight};
@@ -283,7 +309,7 @@ Tensor expand_reduce_grad(const Tensor& go, const std::vector<i64>& in_shape, in
 struct Restore { ~Restore() { t_enabled = true; } };
 
 void publish_leaf(const Node& leaf, Tensor& grad) {
-  vb_slot key = leaf.leaf.slot();
+  LeafKey key = leaf_key(leaf.leaf);
   auto it = t_sinks.index.find(key);
   if (it != t_sinks.index.end()) {
     const Tensor& sink = t_sinks.sinks[it->second];
@@ -367,6 +393,24 @@ void Tensor::backward() const {
         if (sv.size() > 3) gin.push_back(Tensor());
         break;
       }
+      case Op::FusedAttentionPacked: {
+        vb_tensor dqkv;
+        check(vb_fused_attention_packed_backward(&sv[0].desc(), (int)node.a0, sv.size() > 1 ? &sv[1].desc() : nullptr, &go.desc(),
+                                                 node.extra.defined() ? &node.extra.desc() : nullptr, &dqkv), "fused_attention_packed_backward");
+        gin = {Tensor::adopt(dqkv)};
+        if (sv.size() > 1) gin.push_back(Tensor());
+        break;
+      }
+      case Op::PackRows: {      // row blocks of the gradient, as views
+        i64 rows[3] = {node.a0, node.a1, node.a2}, at = 0;
+        for (int i = 0; i < 3; ++i) {
+          vb_tensor d = go.desc();
+          d.dims[0] = rows[i]; d.offset += at * d.strides[0];
+          gin.push_back(Tensor::view_of(go, d));
+          at += rows[i];
+        }
+        break;
+      }
       case Op::Conv2d: {
         vb_tensor gi, gw, gb;
         const bool need_x = node.inputs[0] >= 0;       // the first layer's input takes no gradient
@@ -409,7 +453,7 @@ void Tensor::backward() const {
 }
 
 bool Tensor::grad(Tensor* out) const {
-  auto it = t_grads.find(d_.slot);
+  auto it = t_grads.find(leaf_key(*this));
   if (it == t_grads.end()) return false;
   *out = it->second;
   return true;

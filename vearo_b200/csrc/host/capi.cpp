@@ -61,6 +61,7 @@ int vh_cross_entropy(int l, int t) { VH_TRY(return put(at(l).cross_entropy(at(t)
 int vh_conv2d(int x, int w, int b, int stride, int pad) { VH_TRY(return put(at(x).conv2d(at(w), at(b), stride, pad))); }
 int vh_maxpool2d(int x, int k, int s, int p) { VH_TRY(return put(at(x).maxpool2d(k, s, p))); }
 int vh_avgpool2d(int x, int k, int s, int p) { VH_TRY(return put(at(x).avgpool2d(k, s, p))); }
+int vh_fused_attention_packed(int qkv, int n_head, int mask) { VH_TRY(return put(at(qkv).fused_attention_packed(n_head, mask >= 0 ? &at(mask) : nullptr))); }
 int vh_bn_relu_maxpool(int x, int g, int b, int rm, int rv, int training, float mom, float eps) {
   VH_TRY(return put(at(x).bn_relu_maxpool(at(g), at(b), at(rm), at(rv), training != 0, mom, eps)));
 }

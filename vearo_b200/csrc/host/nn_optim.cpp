@@ -36,17 +36,26 @@ void Linear::parameters(std::vector<Tensor>& out) const { out.push_back(weight);
 
 LayerNorm::LayerNorm(i64 dim, float e) : eps(e) { weight = filled({dim}, 1.0f); bias = filled({dim}, 0.0f); }
 
-MultiHeadAttention::MultiHeadAttention(i64 d, i64 h) : q(d, d, true), k(d, d, true), v(d, d, true), o(d, d, true), n_head(h), n_embd(d) {
-  if (d % h != 0) throw Error("n_embd must be divisible by n_head");
+static Tensor row_block(const Tensor& base, i64 first, i64 rows) {     // rows [first, first + rows) of a contiguous tensor, as a parameter view
+  vb_tensor d = base.desc();
+  d.dims[0] = rows; d.offset += first * d.strides[0];
+  Tensor t = Tensor::view_of(base, d);
+  t.set_requires_grad(true);
+  return t;
 }
+MultiHeadAttention::MultiHeadAttention(i64 d, i64 h) : o(d, d, true), n_head(h), n_embd(d) {
+  if (d % h != 0) throw Error("n_embd must be divisible by n_head");
+  w_qkv = Tensor::zeros({3 * d, d}); b_qkv = Tensor::zeros({3 * d});
+  Linear* proj[3] = {&q, &k, &v};
+  for (int i = 0; i < 3; ++i) { proj[i]->has_bias = true; proj[i]->weight = row_block(w_qkv, i * d, d); proj[i]->bias = row_block(b_qkv, i * d, d); }
+}
+// MultiHeadAttention::forward (lib.rs:584-621): q, k, v projections, head split, attention, head merge, output
+// projection -- with the three projections as one GEMM over the stacked weights.
 Tensor MultiHeadAttention::forward(const Tensor& x, const Tensor* mask) const {
-  std::vector<i64> s = x.shape();
-  i64 b = s[0], t = s[1], d = n_embd, h = n_head, dk = d / h;
-  Tensor qq = q.forward(x).reshape({b, t, h, dk}).transpose(1, 2);
-  Tensor kk = k.forward(x).reshape({b, t, h, dk}).transpose(1, 2);
-  Tensor vv = v.forward(x).reshape({b, t, h, dk}).transpose(1, 2);
-  Tensor a = qq.fused_attention(kk, vv, mask);
-  return o.forward(a.transpose(1, 2).reshape({b, t, d}));
+  if (x.rank() != 3) throw Error("MultiHeadAttention expects [B, T, D]");
+  Tensor w = Tensor::pack_rows(q.weight, k.weight, v.weight), bias = Tensor::pack_rows(q.bias, k.bias, v.bias);
+  Tensor qkv = x.linear(w, &bias);                               // [B, T, 3*D]
+  return o.forward(qkv.fused_attention_packed(n_head, mask));
 }
 void MultiHeadAttention::parameters(std::vector<Tensor>& out) const { q.parameters(out); k.parameters(out); v.parameters(out); o.parameters(out); }
 

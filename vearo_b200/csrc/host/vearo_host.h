@@ -70,6 +70,11 @@ class Tensor {
   // batchnorm -> relu -> maxpool2d(2, 2, 0) as one op (one tape node, one fused backward)
   Tensor bn_relu_maxpool(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const;
   Tensor fused_attention(const Tensor& k, const Tensor& v, const Tensor* mask) const;
+  // self = packed projection [B, S, 3*D] (column blocks q | k | v): context [B, S, D]; one backward node returning [B, S, 3*D]
+  Tensor fused_attention_packed(i64 n_head, const Tensor* mask) const;
+  // a, b, c: views that lie one after another along dim 0 of one storage (same trailing shape); the view that spans the three.
+  // Recorded on the tape: its gradient is handed back to a, b and c as row blocks.
+  static Tensor pack_rows(const Tensor& a, const Tensor& b, const Tensor& c);
   Tensor linear(const Tensor& weight, const Tensor* bias) const;   // fused x.W^T + b
   Tensor reshape(const std::vector<i64>& shape) const;
   Tensor transpose(int d0, int d1) const;
@@ -155,8 +160,12 @@ struct LayerNorm {
   Tensor forward(const Tensor& x) const { return x.layernorm(weight, bias, eps); }
   void parameters(std::vector<Tensor>& out) const { out.push_back(weight); out.push_back(bias); }
 };
+// The q, k and v projections are separate parameters, as in the reference, but their storage is one [3*D, D] weight
+// block and one [3*D] bias block: the forward runs ONE GEMM for the three projections and the attention op reads its
+// packed output in place; the backward mirrors it (one GEMM for dX over K = 3*D, one for the stacked weight gradient).
 struct MultiHeadAttention {
   Linear q, k, v, o; i64 n_head = 1, n_embd = 1;
+  Tensor w_qkv, b_qkv;        // the blocks that q/k/v .weight and .bias are views of
   MultiHeadAttention() = default;
   MultiHeadAttention(i64 n_embd, i64 n_head);
   Tensor forward(const Tensor& x, const Tensor* mask) const;
