@@ -35,6 +35,12 @@ WORKLOADS = {
 }
 
 
+# ncu, one launch of k_gemm_tc on 8192x768 . 768x3072 (dram__bytes_read.sum + dram__bytes_write.sum); the operands and the
+# result of that launch are 25.2 + 9.4 + 100.7 MB: every operand byte is read once, part of the result is still in L2 at exit
+NCU_TRAFFIC_GEMM_FC1 = {"traffic": 84.1e6, "traffic_unit": "bytes per launch", "traffic_launch": "M8192 N3072 K768 (GPT-small fc1 forward)",
+                        "traffic_algorithmic": 135.3e6}
+
+
 def flops_per_token(c):
     """Useful fwd+bwd flops per token: 6 per weight of every matmul + full (non-causal) attention,
     as the reference computes it."""
@@ -234,6 +240,7 @@ def main():
     import vearo_b200 as vb
     from tests import modelspec as ms
 
+    os.environ.setdefault("VB200_PROF_SHAPES", "1")      # the profiling pass keeps GEMM launches apart by shape
     torch.cuda.set_device(local)
     vb.init(local)
     L = vb.lib()
@@ -335,17 +342,27 @@ def main():
         for i in range(args.profile_steps):
             step_resident(i)
         vb.sync(); vb.vb_check(L.vb_profile_enable(0))
+    gemm_shapes = {}
     if rank == 0 and args.profile_steps > 0:
-        buf = C.create_string_buffer(4096)
-        vb.vb_check(L.vb_profile_families(buf, 4096))
-        for fam in [f for f in buf.value.decode().split(",") if f]:
+        buf = C.create_string_buffer(1 << 16)
+        vb.vb_check(L.vb_profile_families(buf, 1 << 16))
+        acc = {}                                         # family -> [ms, launches, units]
+        for name in [f for f in buf.value.decode().split(",") if f]:
             t, n, u = C.c_double(0), C.c_int64(0), C.c_double(0)
-            vb.vb_check(L.vb_profile_read(fam.encode(), C.byref(t), C.byref(n), C.byref(u)))
+            vb.vb_check(L.vb_profile_read(name.encode(), C.byref(t), C.byref(n), C.byref(u)))
             if n.value == 0:
                 continue
+            fam = name
+            if name.startswith("gemm_tc M"):             # "gemm_tc M.. N.. K.. nb.. a. b. bn.. sk.. [streamk]": one family, shapes kept aside
+                fam = "gemm_tc" if " nb1 " in name else "gemm_tc_batched"
+                gemm_shapes[name[len("gemm_tc "):]] = {"launches_per_step": n.value / args.profile_steps, "us_per_launch": 1e3 * t.value / n.value,
+                                                       "tflops": u.value / (t.value * 1e-3) / 1e12 if t.value > 0 else 0.0}
+            a = acc.setdefault(fam, [0.0, 0, 0.0])
+            a[0] += t.value; a[1] += n.value; a[2] += u.value
+        for fam, (t, n, u) in acc.items():
             is_gemm = fam.startswith("gemm")
-            rate = u.value / (t.value * 1e-3) if t.value > 0 else 0.0
-            kernels[fam] = {"launches_per_step": n.value / args.profile_steps, "ms_per_step": t.value / args.profile_steps,
+            rate = u / (t * 1e-3) if t > 0 else 0.0
+            kernels[fam] = {"launches_per_step": n / args.profile_steps, "ms_per_step": t / args.profile_steps,
                             "bound": "tensor" if is_gemm else "hbm",
                             "achieved": rate / 1e12 if is_gemm else rate / 1e9, "unit": "TFLOP/s" if is_gemm else "GB/s",
                             "frac": (rate / 1e12 / pk["bf16_tflops_sustained"]) if is_gemm else (rate / 1e9 / pk["hbm_gbs"])}
@@ -360,6 +377,10 @@ def main():
                 # 3xTF32: three TF32 MMAs per useful product and TF32 runs at half the bf16 rate
                 roofline["peak_3xtf32_useful"] = pk["bf16_tflops_sustained"] / 6.0
                 roofline["frac_of_3xtf32_peak"] = k["achieved"] / roofline["peak_3xtf32_useful"]
+            if dom == "gemm_tc" and not convnet:
+                # DRAM bytes of ONE launch, from the ncu capture of the fc1-shaped product (profiles/gemm_tc_fc1_and_dw.md);
+                # `achieved` above averages all launches of the kernel, whose shapes differ
+                roofline.update(NCU_TRAFFIC_GEMM_FC1)
 
     if rank != 0:
         return
@@ -398,7 +419,7 @@ def main():
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(world * 8)},
         "gpu_launches": int(launches1.value - launches0.value),
         "clocks": clocks.summary(),
-        "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
+        "roofline": roofline, "kernels": kernels, "gemm_shapes": gemm_shapes, "cpu_baseline": cpu,
         "last_loss": losses[-1] if losses else None,
     }
     print(json.dumps(out), flush=True)
