@@ -152,8 +152,10 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
  * produces; `out` is the [B, S, D] context and the backward returns a single [B, S, 3*D] gradient.  No reference function
  * corresponds to it: an extra export that saves the three head-split copies and the gradient concatenation. */
 int vb_fused_attention_packed(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, vb_tensor* out, vb_tensor* probs_or_null);
-int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, const vb_tensor* grad_out,
-                                       const vb_tensor* probs_or_null, vb_tensor* dqkv);
+/* `out_or_null`: the forward's result; when given, the softmax backward is folded into the dP product (dS = scale * P o
+ * (dO.V^T - rowsum(dO o O))) instead of running as a pass of its own. */
+int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, const vb_tensor* out_or_null,
+                                       const vb_tensor* grad_out, const vb_tensor* probs_or_null, vb_tensor* dqkv);
 
 /* ---- backward arms the reference computes on the host for CUDA tensors -------------------
  * (vearo-autograd/src/lib.rs: reduce_to 316-361, relu/gelu masks 364-403, softmax arm 547-553,
@@ -220,6 +222,11 @@ typedef struct vb_opt_config {
 int vb_opt_create(const vb_opt_config* cfg, const vb_tensor* params, const vb_tensor* grads, int n, int* opt);
 int vb_opt_destroy(int opt);
 int vb_opt_set_lr(int opt, float lr);
+/* Optimizer state for checkpoints: the slot that holds m then v (AdamW) or the velocity (SGD), one flat array in parameter
+ * order with every parameter's share rounded up to 4 floats; and the step counter t of AdamW's bias correction
+ * (vearo-optim/src/lib.rs:68-70, 105-123 keep them in host Vecs). */
+int vb_opt_state(int opt, vb_slot* state, int64_t* state_numel, uint32_t* step);
+int vb_opt_set_step(int opt, uint32_t step);
 /* active[i] == 0 skips parameter i (no gradient this step; vearo-optim/src/lib.rs:106-108); NULL = all.
  * max_norm <= 0 disables clipping.  grad_scale multiplies every gradient first (1/world for data
  * parallel sums).  *total_norm (may be NULL) receives the pre-clip norm; reading it synchronises. */

@@ -70,6 +70,8 @@ def lib():
         L.vh_adamw_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 5 + [C.c_int]
         L.vh_sgd_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 3 + [C.c_int]
         L.vh_opt_set_lr.argtypes = [C.c_int, C.c_float]
+        for fn in (L.vh_opt_save_state, L.vh_opt_load_state, L.vh_save_checkpoint, L.vh_load_checkpoint):
+            fn.argtypes = [C.c_int, C.c_char_p]
         L.vh_opt_clip_and_step.argtypes = [C.c_int, C.c_float, c_f32p]
         L.vh_clip_grad_norm.argtypes = [c_intp, C.c_int, C.c_float, c_f32p]
         L.vh_gpt_new.argtypes = [C.c_int64] * 6
@@ -254,6 +256,12 @@ class _Opt:
 
     def set_lr(self, lr): _chk(lib().vh_opt_set_lr(self.o, lr))
 
+    def save_state(self, path):
+        """m, v (or the velocity) and the step counter, as a `.ve` container."""
+        _chk(lib().vh_opt_save_state(self.o, str(path).encode()))
+
+    def load_state(self, path): _chk(lib().vh_opt_load_state(self.o, str(path).encode()))
+
     def close(self):
         if self.o >= 0:
             lib().vh_opt_free(self.o)
@@ -327,6 +335,12 @@ class Model:
             p.write(a)
 
     def loss(self, x, y): return Tensor(lib().vh_model_loss(self.m, x.h, y.h))
+
+    def save_checkpoint(self, path):
+        """vearo::checkpoint::save_checkpoint(&params, path): the reference's `.ve` weight file."""
+        _chk(lib().vh_save_checkpoint(self.m, str(path).encode()))
+
+    def load_checkpoint(self, path): _chk(lib().vh_load_checkpoint(self.m, str(path).encode()))
 
     def train_step(self, opt, x, y, max_norm=0.0, x_requires_grad=False):
         """One full step from HOST arrays (H2D of inputs and D2H of the loss included)."""

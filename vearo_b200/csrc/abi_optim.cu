@@ -147,6 +147,14 @@ int vb_opt_destroy(int id) {
   g_opts[id].reset();
   return VB_OK;
 }
+int vb_opt_state(int id, vb_slot* state, int64_t* state_numel, uint32_t* step) {
+  Opt* o; VB_TRY(get_opt(id, &o));
+  if (state) *state = o->state;
+  if (state_numel) { float* p; VB_TRY(slot_ptr(o->state, &p, state_numel)); }
+  if (step) *step = o->t;
+  return VB_OK;
+}
+int vb_opt_set_step(int id, uint32_t step) { Opt* o; VB_TRY(get_opt(id, &o)); o->t = step; return VB_OK; }
 int vb_opt_set_lr(int id, float lr) { Opt* o; VB_TRY(get_opt(id, &o)); o->cfg.lr = lr; return VB_OK; }
 
 int vb_opt_step(int id, const uint8_t* active, float max_norm, float grad_scale, float* total_norm) {

@@ -117,6 +117,10 @@ int vh_sgd_new(const int* params, int n, float lr, float momentum, float wd, int
 int vh_opt_free(int o) { VH_TRY(opt(o); g_opts[o].reset(); return 0); }
 int vh_opt_step(int o) { VH_TRY(opt(o).step(); return 0); }
 int vh_opt_clip_and_step(int o, float max_norm, float* norm) { VH_TRY(float n = opt(o).clip_and_step(max_norm); if (norm) *norm = n; return 0); }
+int vh_opt_save_state(int o, const char* path) { VH_TRY(opt(o).save_state(path); return 0); }
+int vh_opt_load_state(int o, const char* path) { VH_TRY(opt(o).load_state(path); return 0); }
+int vh_save_checkpoint(int m, const char* path) { VH_TRY(checkpoint::save_checkpoint(model(m).parameters(), path); return 0); }
+int vh_load_checkpoint(int m, const char* path) { VH_TRY(checkpoint::load_checkpoint(model(m).parameters(), path); return 0); }
 int vh_opt_set_lr(int o, float lr) { VH_TRY(opt(o).set_lr(lr); return 0); }
 int vh_clip_grad_norm(const int* params, int n, float max_norm, float* norm) {
   VH_TRY(std::vector<Tensor> ps; for (int i = 0; i < n; ++i) ps.push_back(at(params[i])); *norm = optim::clip_grad_norm(ps, max_norm); return 0);

@@ -13,6 +13,8 @@
 // fused launch for all parameters.
 #include "vearo_host.h"
 #include <cmath>
+#include <cstdio>
+#include <cstring>
 
 namespace vearo {
 namespace nn {
@@ -246,4 +248,81 @@ float cosine_lr(float base, float min_lr, uint32_t warmup, uint32_t total, uint3
 }
 
 }  // namespace optim
+// ---- `.ve` checkpoints ----------------------------------------------------------------------------------------
+namespace checkpoint {
+namespace {
+struct File {
+  FILE* f;
+  File(const std::string& path, const char* mode) : f(std::fopen(path.c_str(), mode)) { if (!f) throw Error("cannot open " + path); }
+  ~File() { if (f) std::fclose(f); }
+};
+void put_u32(FILE* f, uint64_t v) {
+  if (v > 0xffffffffull) throw Error("value does not fit the checkpoint format's u32 field");
+  uint32_t x = (uint32_t)v; unsigned char b[4] = {(unsigned char)x, (unsigned char)(x >> 8), (unsigned char)(x >> 16), (unsigned char)(x >> 24)};
+  if (std::fwrite(b, 1, 4, f) != 4) throw Error("checkpoint write failed");
+}
+uint32_t get_u32(FILE* f) {
+  unsigned char b[4];
+  if (std::fread(b, 1, 4, f) != 4) throw Error("failed to fill whole buffer");       // std::io::ErrorKind::UnexpectedEof
+  return (uint32_t)b[0] | ((uint32_t)b[1] << 8) | ((uint32_t)b[2] << 16) | ((uint32_t)b[3] << 24);
+}
+}  // namespace
+void write_container(const std::vector<HostTensor>& ts, const std::string& path) {
+  File fl(path, "wb");
+  put_u32(fl.f, ts.size());
+  for (const HostTensor& t : ts) {
+    put_u32(fl.f, t.dims.size());
+    for (i64 d : t.dims) put_u32(fl.f, (uint64_t)d);
+    put_u32(fl.f, t.data.size());
+    // f32 little endian: the byte order of every machine this library runs on
+    if (!t.data.empty() && std::fwrite(t.data.data(), sizeof(float), t.data.size(), fl.f) != t.data.size()) throw Error("checkpoint write failed");
+  }
+  if (std::fflush(fl.f) != 0) throw Error("checkpoint write failed");
+}
+std::vector<HostTensor> read_container(const std::string& path) {
+  File fl(path, "rb");
+  std::vector<HostTensor> ts(get_u32(fl.f));
+  for (HostTensor& t : ts) {
+    t.dims.resize(get_u32(fl.f));
+    for (i64& d : t.dims) d = get_u32(fl.f);
+    t.data.resize(get_u32(fl.f));
+    if (!t.data.empty() && std::fread(t.data.data(), sizeof(float), t.data.size(), fl.f) != t.data.size()) throw Error("failed to fill whole buffer");
+  }
+  return ts;
+}
+void save_checkpoint(const std::vector<Tensor>& params, const std::string& path) {
+  std::vector<HostTensor> ts;
+  for (const Tensor& p : params) ts.push_back(HostTensor{p.shape(), p.to_vec_f32()});
+  write_container(ts, path);
+}
+void load_checkpoint(const std::vector<Tensor>& params, const std::string& path) {
+  std::vector<HostTensor> ts = read_container(path);
+  if (ts.size() != params.size()) throw Error("Checkpoint tensor count does not match model parameter count");
+  for (size_t i = 0; i < ts.size(); ++i)
+    if (ts[i].dims != params[i].shape()) throw Error("Checkpoint shape does not match parameter shape");
+  for (size_t i = 0; i < ts.size(); ++i) {
+    if ((i64)ts[i].data.size() != params[i].numel()) throw Error("Checkpoint shape does not match parameter shape");
+    params[i].write_f32(ts[i].data.data());
+  }
+}
+}  // namespace checkpoint
+
+namespace optim {
+void Optimizer::save_state(const std::string& path) const {
+  vb_slot st; int64_t n = 0; uint32_t t = 0;
+  check(vb_opt_state(opt_, &st, &n, &t), "opt_state");
+  checkpoint::HostTensor step{{1}, {(float)t}}, state{{n}, std::vector<float>((size_t)n)};
+  if (n) check(vb_read(st, 0, state.data.data(), n), "read optimizer state");
+  checkpoint::write_container({step, state}, path);
+}
+void Optimizer::load_state(const std::string& path) {
+  std::vector<checkpoint::HostTensor> ts = checkpoint::read_container(path);
+  vb_slot st; int64_t n = 0;
+  check(vb_opt_state(opt_, &st, &n, nullptr), "opt_state");
+  if (ts.size() != 2 || ts[0].data.size() != 1 || (int64_t)ts[1].data.size() != n) throw Error("optimizer state file does not match this optimizer");
+  if (n) check(vb_write(st, 0, ts[1].data.data(), n), "write optimizer state");
+  check(vb_opt_set_step(opt_, (uint32_t)ts[0].data[0]), "opt_set_step");
+}
+}  // namespace optim
+
 }  // namespace vearo

@@ -118,6 +118,10 @@ class Optimizer {
   void set_lr(float lr); float lr() const { return cfg_.lr; }
   const std::vector<Tensor>& params() const { return params_; }
   const std::vector<Tensor>& grads() const { return sinks_; }
+  // Optimizer state as a `.ve` container (see checkpoint::): tensor 0 = [t] (the AdamW step counter as f32), tensor 1 =
+  // the flat state array (m then v, or the velocity).  The reference's optimizers have no save of their own.
+  void save_state(const std::string& path) const;
+  void load_state(const std::string& path);
  private:
   void finish_reduce();
   static void on_ready(int idx, void* self);
@@ -143,6 +147,17 @@ BucketPlan plan_buckets(const std::vector<i64>& numels, i64 target_elems);
 float clip_grad_norm(const std::vector<Tensor>& params, float max_norm);
 float cosine_lr(float base_lr, float min_lr, uint32_t warmup, uint32_t total, uint32_t step);   // lib.rs:336-348
 }  // namespace optim
+
+// ---- `.ve` weight checkpoints (crates/vearo/src/checkpoint.rs:10-88) ---------------------------
+// File: u32 tensor count; per tensor u32 rank, u32 dims..., u32 element count, f32 data; little endian.
+namespace checkpoint {
+void save_checkpoint(const std::vector<Tensor>& params, const std::string& path);
+void load_checkpoint(const std::vector<Tensor>& params, const std::string& path);   // count / shape mismatches throw with the reference's messages
+// the container itself, on host arrays
+struct HostTensor { std::vector<i64> dims; std::vector<float> data; };
+void write_container(const std::vector<HostTensor>& ts, const std::string& path);
+std::vector<HostTensor> read_container(const std::string& path);
+}  // namespace checkpoint
 
 // ---- layers and the five workload graphs (vearo-nn/src/lib.rs) -------------------------------
 namespace nn {
