@@ -152,8 +152,9 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
  * produces; `out` is the [B, S, D] context and the backward returns a single [B, S, 3*D] gradient.  No reference function
  * corresponds to it: an extra export that saves the three head-split copies and the gradient concatenation. */
 int vb_fused_attention_packed(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, vb_tensor* out, vb_tensor* probs_or_null);
-/* `out_or_null`: the forward's result; when given, the softmax backward is folded into the dP product (dS = scale * P o
- * (dO.V^T - rowsum(dO o O))) instead of running as a pass of its own. */
+/* `out_or_null`: the forward's result; with it and VB200_ATTN_FUSED_DS=1 in the environment the softmax backward is folded into
+ * the dP product (dS = scale * P o (dO.V^T - rowsum(dO o O))) instead of running as a pass of its own (off by default:
+ * measured slower). */
 int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, const vb_tensor* out_or_null,
                                        const vb_tensor* grad_out, const vb_tensor* probs_or_null, vb_tensor* dqkv);
 
@@ -198,6 +199,10 @@ int vb_layernorm_backward_noalloc(const float* x, const float* w, const float* g
 int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias_or_null, vb_tensor* out);
 int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* grad_out,
                        vb_tensor* gx, vb_tensor* gw, vb_tensor* gb);
+/* The same with the weight and bias gradients written into existing tensors (NULL: not wanted) -- a parameter's slice of a flat
+ * gradient buffer -- so that no copy follows the GEMM.  No reference counterpart (the reference allocates every gradient). */
+int vb_linear_backward_into(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* grad_out, vb_tensor* gx_or_null,
+                            const vb_tensor* gw_into_or_null, const vb_tensor* gb_into_or_null);
 
 /* ---- optimizer ---------------------------------------------------------------------------
  * Single-tensor steps replace the CUDA branches of Tensor::adamw_step / sgd_step

@@ -545,9 +545,10 @@ static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const
     rc = launch_gemm(g);
   }
   Temp rowsum;
-  static int fuse_env = -1;
-  if (fuse_env < 0) { const char* e = getenv("VB200_ATTN_UNFUSED_DS"); fuse_env = (e && e[0] == '1') ? 0 : 1; }
-  const bool fuse_ds = out != nullptr && fuse_env && out->strides[3] == 1 && gout->strides[3] == 1;
+  // Opt-in (VB200_ATTN_FUSED_DS=1, read at every call): as measured on GPT-small the P reads in the product's epilogue
+  // cost more than the separate pass over P and dP they replace (13.1 ms against 11.5 + 1.7 ms per step).
+  const char* fuse_env = getenv("VB200_ATTN_FUSED_DS");
+  const bool fuse_ds = out != nullptr && fuse_env && fuse_env[0] == '1' && out->strides[3] == 1 && gout->strides[3] == 1;
   if (rc == VB_OK && fuse_ds) {   // D[b,h,s] = sum_d dO o O
     float* po; rc = tensor_ptr(out, &po);
     if (rc == VB_OK) rc = scratch_alloc((size_t)(B * H * S) * sizeof(float), &rowsum.p);
@@ -740,11 +741,16 @@ int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias
   g.C = po; g.c_rs = g.N; g.c_cs = 1; g.bias = pb;
   return launch_gemm(g);
 }
-int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* gout, vb_tensor* gx, vb_tensor* gw, vb_tensor* gb) {
+// gw_into / gb_into: existing contiguous tensors the weight and bias gradients are written into (a parameter's slice of
+// the flat gradient arena) instead of fresh outputs.
+static int linear_backward_impl(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* gout, vb_tensor* gx, vb_tensor* gw, vb_tensor* gb,
+                                const vb_tensor* gw_into, const vb_tensor* gb_into) {
   VB_CHECK(weight->rank == 2 && x->rank >= 1 && gout->rank == x->rank, "linear_backward shape mismatch");
   i64 rows, in; VB_TRY(rows_of(x, &rows, &in));
   i64 outf = weight->dims[0];
   VB_CHECK(in == weight->dims[1] && gout->dims[gout->rank - 1] == outf && numel(*gout) == rows * outf, "linear_backward shape mismatch");
+  if (gw_into) VB_CHECK(is_contiguous(*gw_into) && numel(*gw_into) == outf * in, "weight-gradient destination must be a contiguous [out, in] tensor");
+  if (gb_into) VB_CHECK(is_contiguous(*gb_into) && numel(*gb_into) == outf, "bias-gradient destination must be a contiguous [out] tensor");
   Temp hx, hg; const float *px, *pg;
   VB_TRY(contiguous_ptr(x, &px, hx)); VB_TRY(contiguous_ptr(gout, &pg, hg));
   float* pw; VB_TRY(tensor_ptr(weight, &pw));
@@ -760,10 +766,10 @@ int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_ten
       VB_TRY(launch_gemm(g));
     }
   }
-  if (gw) {   // gw[out, in] = gy^T . x
-    i64 wd[2] = {outf, in};
-    VB_TRY(new_output(gw, 2, wd));
-    float* p; VB_TRY(slot_ptr(gw->slot, &p));
+  if (gw || gw_into) {   // gw[out, in] = gy^T . x
+    float* p;
+    if (gw_into) VB_TRY(tensor_ptr(gw_into, &p));
+    else { i64 wd[2] = {outf, in}; VB_TRY(new_output(gw, 2, wd)); VB_TRY(slot_ptr(gw->slot, &p)); }
     if (rows == 0) VB_TRY(launch_fill(p, 0.0f, outf * in));
     else {
       GemmArgs g = gemm_args();
@@ -774,12 +780,21 @@ int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_ten
       VB_TRY(launch_gemm(g));
     }
   }
-  if (gb) {
-    VB_TRY(new_output(gb, 1, &outf, true));
-    float* p; VB_TRY(slot_ptr(gb->slot, &p));
+  if (gb || gb_into) {
+    float* p;
+    if (gb_into) VB_TRY(tensor_ptr(gb_into, &p));
+    else { VB_TRY(new_output(gb, 1, &outf, true)); VB_TRY(slot_ptr(gb->slot, &p)); }
     if (rows > 0) VB_TRY(launch_colsum(pg, p, rows, outf, false));
+    else if (gb_into) VB_TRY(launch_fill(p, 0.0f, outf));
   }
   return VB_OK;
+}
+int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* gout, vb_tensor* gx, vb_tensor* gw, vb_tensor* gb) {
+  return linear_backward_impl(x, weight, gout, gx, gw, gb, nullptr, nullptr);
+}
+int vb_linear_backward_into(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* gout, vb_tensor* gx,
+                            const vb_tensor* gw_into, const vb_tensor* gb_into) {
+  return linear_backward_impl(x, weight, gout, gx, nullptr, nullptr, gw_into, gb_into);
 }
 
 }  // extern "C"

@@ -315,7 +315,8 @@ void publish_leaf(const Node& leaf, Tensor& grad) {
   if (it != t_sinks.index.end()) {
     const Tensor& sink = t_sinks.sinks[it->second];
     if (sink.numel() != grad.numel()) throw Error("gradient sink size mismatch");
-    check(vb_copy(&sink.desc(), &grad.desc()), "copy into gradient buffer");
+    const bool in_place = grad.slot() == sink.slot() && grad.desc().offset == sink.desc().offset;      // the producer wrote into the sink
+    if (!in_place) check(vb_copy(&sink.desc(), &grad.desc()), "copy into gradient buffer");
     t_grads[key] = sink;
     if (t_sinks.on_ready) t_sinks.on_ready(it->second, t_sinks.user);
   } else t_grads[key] = grad;
@@ -428,10 +429,27 @@ void Tensor::backward() const {
       }
       case Op::Linear: {
         bool need_x = node.inputs[0] >= 0, need_w = node.inputs[1] >= 0, need_b = sv.size() > 2 && node.inputs[2] >= 0;
+        // A parameter that gets its whole gradient from this node and owns a slice of the flat gradient buffer: the products
+        // write straight into the slice (no fresh tensor, no copy when the leaf is published).
+        auto sink_of = [&](int id) -> const Tensor* {
+          if (id < 0 || nodes[id].op != Op::Leaf || first_use[id] != ni || gm[id].defined()) return nullptr;
+          auto it = t_sinks.index.find(leaf_key(nodes[id].leaf));
+          if (it == t_sinks.index.end()) return nullptr;
+          const Tensor& s = t_sinks.sinks[it->second];
+          return (s.is_contiguous() && s.numel() == nodes[id].leaf.numel()) ? &s : nullptr;
+        };
+        const Tensor* ws = need_w ? sink_of(node.inputs[1]) : nullptr;
+        const Tensor* bs = need_b ? sink_of(node.inputs[2]) : nullptr;
         vb_tensor gx, gw, gb;
-        check(vb_linear_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), need_x ? &gx : nullptr, need_w ? &gw : nullptr, need_b ? &gb : nullptr), "linear_backward");
-        gin = {need_x ? Tensor::adopt(gx) : Tensor(), need_w ? Tensor::adopt(gw) : Tensor()};
-        if (sv.size() > 2) gin.push_back(need_b ? Tensor::adopt(gb) : Tensor());
+        if (ws || bs) {
+          check(vb_linear_backward_into(&sv[0].desc(), &sv[1].desc(), &go.desc(), need_x ? &gx : nullptr, ws ? &ws->desc() : nullptr, bs ? &bs->desc() : nullptr), "linear_backward");
+          if ((need_w && !ws) || (need_b && !bs))      // the other gradient the ordinary way
+            check(vb_linear_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), nullptr, (need_w && !ws) ? &gw : nullptr, (need_b && !bs) ? &gb : nullptr), "linear_backward");
+        } else {
+          check(vb_linear_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), need_x ? &gx : nullptr, need_w ? &gw : nullptr, need_b ? &gb : nullptr), "linear_backward");
+        }
+        gin = {need_x ? Tensor::adopt(gx) : Tensor(), !need_w ? Tensor() : (ws ? *ws : Tensor::adopt(gw))};
+        if (sv.size() > 2) gin.push_back(!need_b ? Tensor() : (bs ? *bs : Tensor::adopt(gb)));
         break;
       }
       case Op::Leaf: break;
