@@ -152,11 +152,8 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
  * produces; `out` is the [B, S, D] context and the backward returns a single [B, S, 3*D] gradient.  No reference function
  * corresponds to it: an extra export that saves the three head-split copies and the gradient concatenation. */
 int vb_fused_attention_packed(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, vb_tensor* out, vb_tensor* probs_or_null);
-/* `out_or_null`: the forward's result; with it and VB200_ATTN_FUSED_DS=1 in the environment the softmax backward is folded into
- * the dP product (dS = scale * P o (dO.V^T - rowsum(dO o O))) instead of running as a pass of its own (off by default:
- * measured slower). */
-int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, const vb_tensor* out_or_null,
-                                       const vb_tensor* grad_out, const vb_tensor* probs_or_null, vb_tensor* dqkv);
+int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask_or_null, const vb_tensor* grad_out,
+                                       const vb_tensor* probs_or_null, vb_tensor* dqkv);
 
 /* ---- backward arms the reference computes on the host for CUDA tensors -------------------
  * (vearo-autograd/src/lib.rs: reduce_to 316-361, relu/gelu masks 364-403, softmax arm 547-553,

@@ -372,12 +372,10 @@ def test_batchnorm(vb, training):
     both(vb, case)
 
 
-@pytest.mark.parametrize("fused_ds", ["0", "1"])
 @pytest.mark.parametrize("B,S,H,dk,masked", [(2, 40, 3, 8, True), (1, 256, 2, 64, True), (2, 64, 4, 16, False)])
-def test_fused_attention_packed(vb, monkeypatch, B, S, H, dk, masked, fused_ds):
+def test_fused_attention_packed(vb, B, S, H, dk, masked):
     """Attention over the packed [B, S, 3*D] projection (q | k | v column blocks) against the oracle fed with the three
     head-split tensors; the single packed gradient must be the three gradients side by side."""
-    monkeypatch.setenv("VB200_ATTN_FUSED_DS", fused_ds)       # "1": softmax backward in the epilogue of the dP product
     D = H * dk
     qkv0 = (rnd(90, B, S, 3 * D) * 0.5).astype(np.float32); go = rnd(91, B, S, D)
     mask0 = np.triu(np.full((S, S), -1e9, np.float32), 1)

@@ -502,11 +502,8 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
 
 // The backward products; gradients are written as [B,S,H,dk]-ordered rows of length `ld` floats (ld = H*dk for separate
 // buffers, 3*H*dk when dq, dk and dv are the three column blocks of one packed [B,S,3*H*dk] buffer).
-// `out` (the forward's result as a [B,H,S,dk] view, may be null): with it the softmax backward is folded into the
-// epilogue of the dP product, dS = scale * P o (dO.V^T - rowsum(dO o O)), and neither dP nor a separate pass over
-// P and dP exists.
 static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask,
-                                   const vb_tensor* gout, const vb_tensor* probs, const vb_tensor* out, float* pdq, float* pdk, float* pdv, i64 ld) {
+                                   const vb_tensor* gout, const vb_tensor* probs, float* pdq, float* pdk, float* pdv, i64 ld) {
   i64 B = q->dims[0], H = q->dims[1], S = q->dims[2], dk = q->dims[3];
   float *pq, *pk, *pv, *pg;
   VB_TRY(tensor_ptr(q, &pq)); VB_TRY(tensor_ptr(k, &pk)); VB_TRY(tensor_ptr(v, &pv)); VB_TRY(tensor_ptr(gout, &pg));
@@ -544,26 +541,15 @@ static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const
     g.C = pdv; g.c_rs = ld; g.c_cs = 1; g.c_b1 = S * ld; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
-  Temp rowsum;
-  // Opt-in (VB200_ATTN_FUSED_DS=1, read at every call): as measured on GPT-small the P reads in the product's epilogue
-  // cost more than the separate pass over P and dP they replace (13.1 ms against 11.5 + 1.7 ms per step).
-  const char* fuse_env = getenv("VB200_ATTN_FUSED_DS");
-  const bool fuse_ds = out != nullptr && fuse_env && fuse_env[0] == '1' && out->strides[3] == 1 && gout->strides[3] == 1;
-  if (rc == VB_OK && fuse_ds) {   // D[b,h,s] = sum_d dO o O
-    float* po; rc = tensor_ptr(out, &po);
-    if (rc == VB_OK) rc = scratch_alloc((size_t)(B * H * S) * sizeof(float), &rowsum.p);
-    if (rc == VB_OK) rc = launch_rowdot_bhsd(pg, gout->strides, po, out->strides, (float*)rowsum.p, B, H, S, dk);
-  }
-  if (rc == VB_OK) {   // dP = dO . V^T  (dS directly when the softmax backward rides in the epilogue)
+  if (rc == VB_OK) {   // dP = dO . V^T
     GemmArgs g = gemm_args();
     g.M = S; g.N = S; g.K = dk; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
     g.A = pg; qk_gemm_operand(gout, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);
     g.B = pv; { i64 rs, cs; qk_gemm_operand(v, &rs, &cs, &g.b_b1, &g.b_b2); g.b_rs = cs; g.b_cs = rs; }
     g.C = pdp; g.c_rs = S; g.c_cs = 1; g.c_b1 = H * SS; g.c_b2 = SS;
-    if (fuse_ds) { g.alpha = scale; g.epi_mul = pp; g.epi_rowsub = (const float*)rowsum.p; }
     rc = launch_gemm(g);
   }
-  if (rc == VB_OK && !fuse_ds) rc = launch_attn_softmax_backward(pp, pdp, B * H * S, S, scale, causal, S);   // dS * scale, in place
+  if (rc == VB_OK) rc = launch_attn_softmax_backward(pp, pdp, B * H * S, S, scale, causal, S);   // dS * scale, in place
   if (rc == VB_OK) {   // dQ = dS . K
     GemmArgs g = gemm_args();
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 2 : 0;
@@ -592,7 +578,7 @@ int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb
   if (numel(*q) == 0) return VB_OK;
   float *pdq, *pdk, *pdv;
   VB_TRY(slot_ptr(dq->slot, &pdq)); VB_TRY(slot_ptr(dk_->slot, &pdk)); VB_TRY(slot_ptr(dv->slot, &pdv));
-  return attention_backward_core(q, k, v, mask, gout, probs, nullptr, pdq, pdk, pdv, H * dk);
+  return attention_backward_core(q, k, v, mask, gout, probs, pdq, pdk, pdv, H * dk);
 }
 
 // Attention over a packed projection: qkv is a contiguous [B, S, 3*D] tensor whose column blocks [0,D), [D,2D), [2D,3D) are
@@ -621,7 +607,7 @@ int vb_fused_attention_packed(const vb_tensor* qkv, int n_head, const vb_tensor*
   out->strides[0] = S * D; out->strides[1] = D; out->strides[2] = 1;
   return VB_OK;
 }
-int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask, const vb_tensor* out, const vb_tensor* gout,
+int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const vb_tensor* mask, const vb_tensor* gout,
                                        const vb_tensor* probs, vb_tensor* dqkv) {
   vb_tensor q, k, v;
   VB_TRY(packed_views(qkv, n_head, &q, &k, &v));
@@ -634,16 +620,10 @@ int vb_fused_attention_packed_backward(const vb_tensor* qkv, int n_head, const v
   if (!is_contiguous(*gout)) { VB_TRY(vb_contiguous(gout, &gc)); g4 = gc; }
   g4.rank = 4; g4.dims[0] = B; g4.dims[1] = n_head; g4.dims[2] = S; g4.dims[3] = dk;
   g4.strides[0] = S * D; g4.strides[1] = dk; g4.strides[2] = D; g4.strides[3] = 1;
-  vb_tensor o4; const vb_tensor* po4 = nullptr;
-  if (out && out->rank == 3 && is_contiguous(*out) && out->dims[0] == B && out->dims[1] == S && out->dims[2] == D) {
-    o4 = *out; o4.rank = 4; o4.dims[0] = B; o4.dims[1] = n_head; o4.dims[2] = S; o4.dims[3] = dk;
-    o4.strides[0] = S * D; o4.strides[1] = dk; o4.strides[2] = D; o4.strides[3] = 1;
-    po4 = &o4;
-  }
   int rc = new_output(dqkv, 3, qkv->dims);
   float* pd = nullptr;
   if (rc == VB_OK && numel(*qkv) > 0) rc = slot_ptr(dqkv->slot, &pd);
-  if (rc == VB_OK && numel(*qkv) > 0) rc = attention_backward_core(&q, &k, &v, mask, &g4, probs, po4, pd, pd + D, pd + 2 * D, 3 * D);
+  if (rc == VB_OK && numel(*qkv) > 0) rc = attention_backward_core(&q, &k, &v, mask, &g4, probs, pd, pd + D, pd + 2 * D, 3 * D);
   if (gc.slot) slot_release(gc.slot, nullptr);
   return rc;
 }

@@ -281,34 +281,6 @@ int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, fl
   return VB_OK;
 }
 
-// out[b, h, s] = sum_d a[b,h,s,d] * b[b,h,s,d] for two strided [B,H,S,dk] views (last stride 1): one warp per row.
-// With a = dO and b = O this is the row sum of P o dP that the softmax backward subtracts (P.V = O).
-__global__ void k_rowdot_bhsd(const float* __restrict__ a, i64 a0, i64 a1, i64 a2, const float* __restrict__ b, i64 b0, i64 b1, i64 b2,
-                              float* __restrict__ out, i64 B, i64 H, i64 S, i64 dk) {
-  const i64 rows = B * H * S;
-  const int lane = threadIdx.x & 31;
-  for (i64 r = (i64)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += (i64)gridDim.x * (blockDim.x >> 5)) {
-    const i64 s = r % S, h = (r / S) % H, bb = r / (S * H);
-    const float* pa = a + bb * a0 + h * a1 + s * a2;
-    const float* pb = b + bb * b0 + h * b1 + s * b2;
-    float acc = 0.0f;
-    for (i64 d = lane; d < dk; d += 32) acc = fmaf(pa[d], pb[d], acc);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) out[r] = acc;
-  }
-}
-int launch_rowdot_bhsd(const float* a, const i64 sa[4], const float* b, const i64 sb[4], float* out, i64 B, i64 H, i64 S, i64 dk) {
-  const i64 rows = B * H * S;
-  if (rows <= 0) return VB_OK;
-  if (sa[3] != 1 || sb[3] != 1) return set_error(VB_ERR_UNSUPPORTED, "rowdot needs a unit last stride");
-  ProfScope prof("attn_rowdot", 2.0 * (double)rows * (double)dk * 4.0);
-  i64 blocks = (rows + 7) / 8, cap = (i64)ctx().sm_count * 16; if (blocks > cap) blocks = cap;
-  k_rowdot_bhsd<<<(unsigned)blocks, 256, 0, ctx().stream>>>(a, sa[0], sa[1], sa[2], b, sb[0], sb[1], sb[2], out, B, H, S, dk);
-  VB_LAUNCH_CHECK();
-  return VB_OK;
-}
-
 // Does a [S,S] additive mask have the causal pattern for which skipping is exact: 0 on and below the diagonal and
 // <= -1e9 above it (exp(score - 1e9 - max) is exactly 0 in f32)?  Clears *d_flag when an entry breaks it.
 __global__ void k_mask_is_causal(const float* __restrict__ mask, i64 s, i64 row_stride, int* d_flag) {

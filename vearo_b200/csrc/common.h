@@ -134,9 +134,6 @@ int launch_avgpool2d_backward(const float* g, float* gx, i64 nc, i64 h, i64 w, i
 struct GemmArgs {
   const float* A; const float* B; float* C; const float* bias;   // bias: length N or null
   const float* bias_m;                                            // per-row bias: length M or null (output channels of a convolution)
-  // Softmax-backward epilogue (attention): C = alpha * epi_mul[m, n] * (A.B - epi_rowsub[batch, m]), epi_mul laid out like C
-  // (same strides) and epi_rowsub a dense [batches, M] array; beta and the biases are not applied in this mode.
-  const float* epi_mul; const float* epi_rowsub;
   i64 M, N, K;
   i64 a_rs, a_cs;   // A[m,k] = A[m*a_rs + k*a_cs]
   i64 b_rs, b_cs;   // B[k,n] = B[k*b_rs + n*b_cs]
@@ -158,7 +155,6 @@ inline GemmArgs gemm_args() { GemmArgs g{}; g.nb1 = g.nb2 = 1; g.alpha = 1.0f; g
 // attention.cu
 int launch_attn_softmax(float* s, const float* mask, const i64 mask_strides[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale);
 int launch_mask_is_causal(const float* mask, i64 s, i64 row_stride, int* d_flag);   // d_flag <- 0 when some entry breaks the causal pattern
-int launch_rowdot_bhsd(const float* a, const i64 sa[4], const float* b, const i64 sb[4], float* out, i64 B, i64 H, i64 S, i64 dk);   // out[b,h,s] = sum_d a*b
 int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 sk, float scale, bool causal, i64 sq);
 
 // optim.cu

@@ -76,7 +76,6 @@ __global__ void __launch_bounds__(256) k_gemm_simt(GemmArgs g) {
         if (n >= g.N) continue;
         float v = g.alpha * acc[i][j];
         float* c = C + m * g.c_rs + n * g.c_cs;
-        if (g.epi_mul) { *c = g.alpha * g.epi_mul[c - g.C] * (acc[i][j] - g.epi_rowsub[bz * g.M + m]); continue; }
         if (g.beta != 0.0f) v += g.beta * *c;
         if (g.bias) v += g.bias[n];
         if (g.bias_m) v += g.bias_m[m];

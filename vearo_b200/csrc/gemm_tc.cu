@@ -55,7 +55,7 @@ constexpr bool kTiming = false;
 constexpr uint32_t kSpinLimit = 1u << 20; // polls of try_wait (each waits a bounded time) before giving up
 
 struct TcParams {
-  float* C; const float* bias; const float* bias_m; const float* epi_mul; const float* epi_rowsub; float* partial;   // partial: [splits][nbatch][M][N] when splits > 1
+  float* C; const float* bias; const float* bias_m; float* partial;   // partial: [splits][nbatch][M][N] when splits > 1
   i64 M, N, K;
   i64 c_rs, c_b1, c_b2;
   i64 nb1, nb2;
@@ -274,12 +274,17 @@ struct WorkIter {
 // transposed through a 4 KB per-warp staging area (XOR-swizzled 16-byte units, conflict-free both ways) so that every store
 // instruction writes four full 128-byte row segments instead of 32 scattered ones.
 //   fin: apply alpha, beta * C and bias (final result); otherwise the raw sums are stored.
-//   rowsub: softmax-backward epilogue (GemmArgs::epi_mul / epi_rowsub), already offset to this batch; null otherwise.
+__device__ __forceinline__ void stage_put(float4* stg, int lane, int j4, float4 x) { stg[lane * 8 + (j4 ^ (lane & 7))] = x; }
+__device__ __forceinline__ void stage_write_out(const TcParams& p, float4* stg, int lane, float* base, i64 rs, i64 row0, i64 col0, bool fin, bool vec_ok);
 __device__ __forceinline__ void store_block(const TcParams& p, const uint32_t* v, float4* stg, int lane, float* base, i64 rs, i64 row0, i64 col0,
-                                            bool fin, bool vec_ok, const float* rowsub) {
+                                            bool fin, bool vec_ok) {
 #pragma unroll
   for (int j4 = 0; j4 < 8; ++j4)
-    stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(__uint_as_float(v[4 * j4]), __uint_as_float(v[4 * j4 + 1]), __uint_as_float(v[4 * j4 + 2]), __uint_as_float(v[4 * j4 + 3]));
+    stage_put(stg, lane, j4, make_float4(__uint_as_float(v[4 * j4]), __uint_as_float(v[4 * j4 + 1]), __uint_as_float(v[4 * j4 + 2]), __uint_as_float(v[4 * j4 + 3])));
+  stage_write_out(p, stg, lane, base, rs, row0, col0, fin, vec_ok);
+}
+// Second half: read the staged block back one row segment per 8 lanes and store it (apply alpha / beta / biases when `fin`).
+__device__ __forceinline__ void stage_write_out(const TcParams& p, float4* stg, int lane, float* base, i64 rs, i64 row0, i64 col0, bool fin, bool vec_ok) {
   __syncwarp();
   const int c4 = lane & 7;
   const i64 col = col0 + 4 * c4;
@@ -291,12 +296,7 @@ __device__ __forceinline__ void store_block(const TcParams& p, const uint32_t* v
     if (row >= p.M || col >= p.N) continue;
     float* out = base + row * rs + col;
     float e[4] = {x.x, x.y, x.z, x.w};
-    if (fin && rowsub) {
-      const float d = rowsub[row];
-      const float* mul = p.epi_mul + (out - p.C);
-#pragma unroll
-      for (int t = 0; t < 4; ++t) if (col + t < p.N) e[t] = p.alpha * mul[t] * (e[t] - d);
-    } else if (fin) {
+    if (fin) {
       const float bm = p.bias_m ? p.bias_m[row] : 0.0f;
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -547,7 +547,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       const i64 row0 = ((i64)wk.tile_m * CG + rank) * BM + q * 32;
       const bool streamk_part = p.persistent && !wk.whole;
       float* cbase = p.C + (i64)wk.b1 * p.c_b1 + (i64)wk.b2 * p.c_b2;
-      const float* rowsub = p.epi_rowsub ? p.epi_rowsub + (i64)wk.bz * p.M : nullptr;
       const bool c_vec = (p.c_rs & 3) == 0 && (((uintptr_t)p.C | (uintptr_t)(p.c_b1 * 4) | (uintptr_t)(p.c_b2 * 4)) & 15) == 0;
       float* pbase = p.partial + ((i64)wk.split * (p.nb1 * p.nb2) + wk.bz) * p.M * p.N;       // split-K scratch of the tiled mode
       const i64 slot_floats = (i64)BM * bn;
@@ -573,9 +572,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             for (int j4 = 0; j4 < 8; ++j4)
               dst[j4 * 32] = make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]), __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
           } else if (wk.whole) {
-            store_block(p, r, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec, rowsub);
+            store_block(p, r, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
           } else {
-            store_block(p, r, stg, lane, pbase, p.N, row0, col0, false, (p.N & 3) == 0, nullptr);
+            store_block(p, r, stg, lane, pbase, p.N, row0, col0, false, (p.N & 3) == 0);
           }
         }
       }
@@ -618,19 +617,29 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
             i64 col0 = (i64)wk.tile_n * bn + c0;
             if (col0 >= p.N) break;
-            float acc[32];
+            // part by part, accumulating in the staging block itself (every thread re-reads only what it wrote): eight loads in
+            // flight per thread, and no accumulator registers beyond the eight values just loaded
+            const i64 unit = ((c0 >> 5) * 4 + q) * 256 + lane;
             for (int i = 0; i < np; ++i) {
               const i64 c = cf + i;
               const int which = ((c * W) / G >= x0) ? 0 : 1;
-              const float4* src = (const float4*)p.ws + (((2 * c + which) * CG + rank) * slot_floats) / 4 + ((c0 >> 5) * 4 + q) * 256 + lane;
+              const float4* src = (const float4*)p.ws + (((2 * c + which) * CG + rank) * slot_floats) / 4 + unit;
+              float4 x[8];
 #pragma unroll
-              for (int j4 = 0; j4 < 8; ++j4) {
-                float4 x = __ldcg(src + j4 * 32);
-                if (i == 0) { acc[4 * j4] = x.x; acc[4 * j4 + 1] = x.y; acc[4 * j4 + 2] = x.z; acc[4 * j4 + 3] = x.w; }
-                else { acc[4 * j4] += x.x; acc[4 * j4 + 1] += x.y; acc[4 * j4 + 2] += x.z; acc[4 * j4 + 3] += x.w; }
+              for (int j4 = 0; j4 < 8; ++j4) x[j4] = __ldcg(src + j4 * 32);
+              if (i == 0) {
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) stage_put(stg, lane, j4, x[j4]);
+              } else {
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                  float4 a = stg[lane * 8 + (j4 ^ (lane & 7))];
+                  a.x += x[j4].x; a.y += x[j4].y; a.z += x[j4].z; a.w += x[j4].w;
+                  stage_put(stg, lane, j4, a);
+                }
               }
             }
-            store_block(p, reinterpret_cast<const uint32_t*>(acc), stg, lane, cbase, p.c_rs, row0, col0, true, c_vec, rowsub);
+            stage_write_out(p, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
           }
         }
       }
@@ -663,14 +672,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
 // Sum the split-K partial tiles in split order, then apply alpha / beta / bias.
 __global__ void k_splitk_reduce(const float* __restrict__ partial, float* __restrict__ C, const float* __restrict__ bias, const float* __restrict__ bias_m,
-                                const float* __restrict__ epi_mul, const float* __restrict__ epi_rowsub, i64 M, i64 N, i64 nb2, i64 nbatch, int splits, i64 c_rs, i64 c_b1, i64 c_b2, float alpha, float beta) {
+                                i64 M, i64 N, i64 nb2, i64 nbatch, int splits, i64 c_rs, i64 c_b1, i64 c_b2, float alpha, float beta) {
   i64 total = nbatch * M * N;
   for (i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x; idx < total; idx += (i64)gridDim.x * blockDim.x) {
     i64 n = idx % N, m = (idx / N) % M, bz = idx / (N * M);
     float s = 0.0f;
     for (int k = 0; k < splits; ++k) s += partial[(i64)k * total + idx];
     float* c = C + (bz / nb2) * c_b1 + (bz % nb2) * c_b2 + m * c_rs + n;
-    if (epi_mul) { *c = alpha * epi_mul[c - C] * (s - epi_rowsub[bz * M + m]); continue; }
     float v = alpha * s;
     if (beta != 0.0f) v += beta * *c;
     if (bias) v += bias[n];
@@ -854,7 +862,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     i64 W = tiles * kblocks, G = slots;
     if (G > W / 8) G = W / 8;                          // at least 8 k-blocks per group
     if (G < 1) G = 1;
-    if (tiles * CG <= 4096 && (persist_env == 2 || W / G >= kblocks / 2)) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
+    // (very long K: plain split-K measured faster, 2.74 ms against 2.90 ms for 8192 x 50304 . 50304 x 768)
+    if (tiles * CG <= 4096 && (persist_env == 2 || (W / G >= kblocks / 2 && kblocks <= 1024))) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
   }
   { const char* e = getenv("VB200_TC_BN"); if (e && !persistent && p.bn == 256 && atoi(e) == 192) p.bn = 192; }
   p.tmem_cols = p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256);
@@ -900,7 +909,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (e && (atoi(e) & 128)) { VB_TRY(scratch_alloc(8 * 256 * 8, &ws.p)); p.ws = (float*)ws.p; VB_CUDA(cudaMemsetAsync(ws.p, 0, 8 * 256 * 8, ctx().stream)); }
     else if (e && (atoi(e) & 64)) { VB_TRY(scratch_alloc((size_t)tiles_n * CG * tiles_m * nb * splits * 24 + 1024, &ws.p)); p.ws = (float*)ws.p; }
   }
-  p.C = g.C; p.bias = g.bias; p.bias_m = g.bias_m; p.epi_mul = g.epi_mul; p.epi_rowsub = g.epi_rowsub; p.partial = (float*)part.p;
+  p.C = g.C; p.bias = g.bias; p.bias_m = g.bias_m; p.partial = (float*)part.p;
   p.M = g.M; p.N = g.N; p.K = g.K; p.c_rs = g.c_rs; p.c_b1 = g.c_b1; p.c_b2 = g.c_b2; p.nb1 = g.nb1; p.nb2 = g.nb2;
   p.a_bcast1 = oa.bc1; p.a_bcast2 = oa.bc2; p.b_bcast1 = ob.bc1; p.b_bcast2 = ob.bc2;
   p.a_mn = oa.mn; p.b_mn = ob.mn;
@@ -998,7 +1007,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (splits > 1) {
       i64 total = nb * g.M * g.N;
       i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 16; if (blocks > cap) blocks = cap;
-      k_splitk_reduce<<<(unsigned)blocks, 256, 0, ctx().stream>>>((const float*)part.p, g.C, g.bias, g.bias_m, g.epi_mul, g.epi_rowsub, g.M, g.N, g.nb2, nb, splits,
+      k_splitk_reduce<<<(unsigned)blocks, 256, 0, ctx().stream>>>((const float*)part.p, g.C, g.bias, g.bias_m, g.M, g.N, g.nb2, nb, splits,
                                                                    g.c_rs, g.c_b1, g.c_b2, g.alpha, g.beta);
       VB_LAUNCH_CHECK();
     }

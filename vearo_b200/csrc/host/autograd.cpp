@@ -82,7 +82,6 @@ struct Node {
   i64 a0 = 0, a1 = 0, a2 = 0; float f0 = 0.0f;
   std::vector<i64> axes;
   Tensor extra;             // attention probabilities / cross-entropy row statistics
-  Tensor extra2;            // packed attention: the forward's result
   Tensor leaf;              // for Leaf nodes: the tensor itself
 };
 struct Tape { std::vector<Node> nodes; uint32_t generation = 0; };
@@ -241,7 +240,7 @@ Tensor Tensor::fused_attention_packed(i64 n_head, const Tensor* mask) const {
   check(vb_fused_attention_packed(&d_, (int)n_head, mask ? &mask->d_ : nullptr, &o_, rec ? &p_ : nullptr), "fused_attention_packed");
   Tensor out = Tensor::adopt(o_);
   Tensor probs; if (rec) probs = Tensor::adopt(p_);
-  if (Node* n = record(Op::FusedAttentionPacked, ins, out)) { n->extra = probs; n->extra2 = out; n->a0 = n_head; }
+  if (Node* n = record(Op::FusedAttentionPacked, ins, out)) { n->extra = probs; n->a0 = n_head; }
   return out;
 }
 Tensor Tensor::pack_rows(const Tensor& a, const Tensor& b, const Tensor& c) {
@@ -340,7 +339,7 @@ void Tensor::backward() const {
   t_grads.clear();
   for (int ni = N - 1; ni >= 0; --ni) {
     Node& node = nodes[ni];
-    if (!gm[ni].defined()) { node.saved.clear(); node.extra = Tensor(); node.extra2 = Tensor(); continue; }
+    if (!gm[ni].defined()) { node.saved.clear(); node.extra = Tensor(); continue; }
     if (node.op == Op::Leaf) continue;
     Tensor go = std::move(gm[ni]); gm[ni] = Tensor();
     const std::vector<Tensor>& sv = node.saved;
@@ -397,8 +396,7 @@ void Tensor::backward() const {
       }
       case Op::FusedAttentionPacked: {
         vb_tensor dqkv;
-        check(vb_fused_attention_packed_backward(&sv[0].desc(), (int)node.a0, sv.size() > 1 ? &sv[1].desc() : nullptr,
-                                                 node.extra2.defined() ? &node.extra2.desc() : nullptr, &go.desc(),
+        check(vb_fused_attention_packed_backward(&sv[0].desc(), (int)node.a0, sv.size() > 1 ? &sv[1].desc() : nullptr, &go.desc(),
                                                  node.extra.defined() ? &node.extra.desc() : nullptr, &dqkv), "fused_attention_packed_backward");
         gin = {Tensor::adopt(dqkv)};
         if (sv.size() > 1) gin.push_back(Tensor());
@@ -467,7 +465,7 @@ void Tensor::backward() const {
     // leaves whose last contribution this was: publish now
     for (int id : node.inputs)
       if (id >= 0 && nodes[id].op == Op::Leaf && first_use[id] == ni && gm[id].defined()) { publish_leaf(nodes[id], gm[id]); gm[id] = Tensor(); }
-    node.saved.clear(); node.extra = Tensor(); node.extra2 = Tensor();
+    node.saved.clear(); node.extra = Tensor();
   }
   t_tape.generation++;
 }
