@@ -69,8 +69,9 @@ struct TcParams {
   int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
   float alpha, beta;
   int* err;
-  int persistent;                                 // 1: stream-K launch (see WorkIter)
+  int persistent;                                 // 1: stream-K launch, 2: whole tiles dealt round-robin to resident CTAs (see WorkIter)
   i64 total_kb, tiles_m, tiles_n;                 // stream-K: k-blocks of all tiles; tile grid
+  i64 live_tiles, live_per_batch;                 // round-robin: tiles that are computed (all, or those on and below the diagonal)
   float* ws;                                      // stream-K: partial sums, two 128 x bn slots per CTA
   int* counters;                                  // stream-K: arrivals per tile (all zero between launches)
 };
@@ -235,6 +236,7 @@ struct WorkIter {
   int done;
   __device__ __forceinline__ void init(const TcParams& p) {
     done = 0;
+    if (p.persistent == 2) { w = blockIdx.x / CG; return; }
     if (p.persistent) {
       const i64 G = gridDim.x / CG, c = blockIdx.x / CG;
       w0 = (c * p.total_kb) / G; w1 = ((c + 1) * p.total_kb) / G; w = w0;
@@ -242,6 +244,26 @@ struct WorkIter {
   }
   __device__ __forceinline__ bool next(const TcParams& p, Work& o) {
     const i64 kblocks_total = (p.K + BK - 1) / BK;
+    if (p.persistent == 2) {
+      // whole tiles, the u-th computed tile to group u mod G: no launch / allocation / barrier set-up per tile, and the producer
+      // runs ahead into the next tile while this one is stored.  With tiles skipped above the diagonal (causal 1) only the
+      // computed ones are counted, so that every group gets the same number of them.
+      if (w >= p.live_tiles) return false;
+      const i64 u = w; w += gridDim.x / CG;
+      o.bz = (int)(u / p.live_per_batch);
+      int j = (int)(u - (i64)o.bz * p.live_per_batch), m = 0;
+      if (p.causal == 1) {
+        for (;; ++m) {
+          i64 c = (((i64)m + 1) * (BM * CG) + p.bn - 1) / p.bn; if (c > p.tiles_n) c = p.tiles_n;      // computed tiles of tile row m
+          if (j < c) break;
+          j -= (int)c;
+        }
+      } else { m = j / (int)p.tiles_n; j -= m * (int)p.tiles_n; }
+      o.tile_m = m; o.tile_n = j; o.tile = 0; o.which = 0; o.split = 0;
+      o.b1 = o.bz / (int)p.nb2; o.b2 = o.bz % (int)p.nb2;
+      o.kb0 = 0; o.nkb = (int)kblocks_total; o.whole = 1;
+      return true;
+    }
     if (p.persistent) {
       if (w >= w1) return false;
       o.tile = (int)(w / kblocks_total);
@@ -358,7 +380,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;    // 0: the CTA that issues the MMAs
-  if (p.causal == 1 && (i64)(blockIdx.x / CG) * p.bn >= ((i64)blockIdx.y + 1) * (BM * CG)) return;   // whole tile above the diagonal (uniform over the group, nothing allocated yet)
+  if (p.causal == 1 && !p.persistent && (i64)(blockIdx.x / CG) * p.bn >= ((i64)blockIdx.y + 1) * (BM * CG)) return;   // whole tile above the diagonal (uniform over the group, nothing allocated yet)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -868,6 +890,17 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   { const char* e = getenv("VB200_TC_BN"); if (e && !persistent && p.bn == 256 && atoi(e) == 192) p.bn = 192; }
   p.tmem_cols = p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256);
   const i64 tiles_m = (g.M + BMT - 1) / BMT, tiles_n = (g.N + p.bn - 1) / p.bn;
+  // Short-K products with many tiles per slot (attention scores, the vocabulary projection): resident CTAs take whole tiles
+  // round-robin instead of one launch slot per tile.
+  const int causal_eff = (splits == 1 && !persistent && g.M == (g.causal == 1 ? g.N : g.K)) ? g.causal : 0;
+  i64 live_per_batch = tiles_m * tiles_n;
+  if (causal_eff == 1) {
+    live_per_batch = 0;
+    for (i64 m = 0; m < tiles_m; ++m) { i64 c = ((m + 1) * BMT + p.bn - 1) / p.bn; live_per_batch += c < tiles_n ? c : tiles_n; }
+  }
+  static int rr_env = -1;
+  if (rr_env < 0) { const char* e = getenv("VB200_TC_ROUNDROBIN"); rr_env = (e && e[0] == '0') ? 0 : 1; }
+  const bool round_robin = rr_env && !persistent && splits == 1 && kblocks <= 64 && causal_eff <= 1 && live_per_batch * nb >= 4 * slots;
   const size_t raw_bytes = (size_t)(BM + p.bn / CG) * BK * 4;
   // Small rings on purpose: two CTAs then share an SM, and one CTA's epilogue and pipeline bubbles are covered by
   // the other's main loop; measured faster than one CTA per SM with a deep ring.  The lo ring is at least 32 KB
@@ -881,7 +914,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.kblocks_per_split = (int)((kblocks + splits - 1) / splits);
   splits = (int)((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
   p.splits = splits;
-  if (!persistent && (tiles_m > 65535 || nb * splits > 65535)) return VB_OK;
+  if (!persistent && !round_robin && (tiles_m > 65535 || nb * splits > 65535)) return VB_OK;
 
   CUtensorMap map_a, map_b;
   bool fold_a = false, fold_b = false;
@@ -914,7 +947,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.a_bcast1 = oa.bc1; p.a_bcast2 = oa.bc2; p.b_bcast1 = ob.bc1; p.b_bcast2 = ob.bc2;
   p.a_mn = oa.mn; p.b_mn = ob.mn;
   p.alpha = g.alpha; p.beta = g.beta; p.err = ctx().d_err;
-  p.causal = (splits == 1 && !persistent && g.M == (g.causal == 1 ? g.N : g.K)) ? g.causal : 0;
+  p.causal = causal_eff;
+  if (round_robin) { p.persistent = 2; p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.live_per_batch = live_per_batch; p.live_tiles = live_per_batch * nb; }
 
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
@@ -934,11 +968,12 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     static int shapes = -1;
     if (shapes < 0) { const char* e = getenv("VB200_PROF_SHAPES"); shapes = (e && e[0] == '1') ? 1 : 0; }
     char fam[96];
-    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d%s", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits, persistent ? " streamk" : (CG == 2 ? " pair" : ""));
+    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d%s", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits, persistent ? " streamk" : (round_robin ? " roundrobin" : (CG == 2 ? " pair" : "")));
     else snprintf(fam, sizeof fam, "%s", nb > 1 ? "gemm_tc_batched" : "gemm_tc");
     ProfScope prof(fam, 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
     dim3 grid((unsigned)(tiles_n * CG), (unsigned)tiles_m, (unsigned)(nb * splits));
     if (persistent) grid = dim3((unsigned)(streamk_groups * CG), 1, 1);
+    if (round_robin) grid = dim3((unsigned)(slots * CG), 1, 1);
     if (CG == 2) {
       cudaLaunchConfig_t cfg{};
       cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * CW, 1, 1); cfg.dynamicSmemBytes = smem; cfg.stream = ctx().stream;
