@@ -61,6 +61,7 @@ struct TcParams {
   i64 nb1, nb2;
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
   int tmem_cols;                                  // tensor-memory columns allocated: bn rounded up to a power of two
+  int bk;                                         // k per stage: 16, or 32 for the narrow (64-wide) tiles whose per-stage hand-offs dominate
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
   int a_fold, b_fold;                             // 1: MN-contiguous operand whose tensor map is folded into 32-wide blocks (one TMA box per tile)
   int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
@@ -142,36 +143,37 @@ __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m
 //   K-major            dims {K, rows, 1, b2, b1}        one box BK x rows
 //   MN-major, folded   dims {32, K, rows/32, b2, b1}    one box 32 x BK x rows/32 (the 32-wide blocks of the tile land one after another)
 //   MN-major, plain    dims {rows, K, 1, b2, b1}        one box 32 x BK per 32-wide block (row counts that are not multiples of 32)
-__device__ __forceinline__ void tma_load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int mode, int rows, int r0, int k, int b2, int b1) {
+__device__ __forceinline__ void tma_load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int mode, int rows, int r0, int k, int b2, int b1, int bk) {
   if (mode == 0) tma_load_5d(dst, map, bar, k, r0, 0, b2, b1);
   else if (mode == 2) tma_load_5d(dst, map, bar, 0, k, r0 >> 5, b2, b1);
-  else for (int j = 0; j < rows / 32; ++j) tma_load_5d(dst + j * (BK * 128), map, bar, r0 + 32 * j, k, 0, b2, b1);
+  else for (int j = 0; j < rows / 32; ++j) tma_load_5d(dst + j * (bk * 128), map, bar, r0 + 32 * j, k, 0, b2, b1);
 }
 
-// Shared-memory matrix descriptor, K-major, SWIZZLE_64B: rows of 64 bytes, 8-row groups 512 bytes apart.
-__device__ __forceinline__ uint64_t make_desc_k_sw64(uint32_t smem_addr) {
+// Shared-memory matrix descriptor, K-major: rows of bk floats -- 64 bytes with SWIZZLE_64B (bk = 16) or 128 bytes with
+// SWIZZLE_128B (bk = 32) -- and 8-row groups 512 / 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_k(uint32_t smem_addr, int bk) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address
   d |= (uint64_t)1 << 16;                              // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(512 >> 4) << 32;                     // stride byte offset: 8 rows * 64 B
+  d |= (uint64_t)((bk * 32) >> 4) << 32;               // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                              // descriptor version (Blackwell)
-  d |= (uint64_t)4 << 61;                              // layout type: SWIZZLE_64B
+  d |= (uint64_t)(bk == 32 ? 2 : 4) << 61;             // layout type: SWIZZLE_128B / SWIZZLE_64B
   return d;
 }
 // Shared-memory matrix descriptor, MN-major.  For 32-bit operands the only MN-major layout the tensor core accepts
 // is the 128-byte swizzle with a 32-byte base: the tile is a row of 32-float (128-byte) MN blocks, each block BK rows
 // (k) of 128 bytes; blocks are 2048 bytes apart (leading offset), groups of 4 k rows 512 bytes apart (stride offset).
-__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr) {
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, int bk) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)((BK * 128) >> 4) << 16;              // leading byte offset: next 32-wide MN block
+  d |= (uint64_t)((bk * 128) >> 4) << 16;              // leading byte offset: next 32-wide MN block
   d |= (uint64_t)(512 >> 4) << 32;                     // stride byte offset: next group of 4 k rows
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)1 << 61;                              // layout type: SWIZZLE_128B_BASE32B
   return d;
 }
-__device__ __forceinline__ uint64_t make_desc(uint32_t base, int ks, int mn_major) {
-  return mn_major ? make_desc_mn_sw128(base + ks * 1024) : make_desc_k_sw64(base + ks * 32);
+__device__ __forceinline__ uint64_t make_desc(uint32_t base, int ks, int mn_major, int bk) {
+  return mn_major ? make_desc_mn_sw128(base + ks * 1024, bk) : make_desc_k(base + ks * 32, bk);
 }
 // Instruction descriptor: D = F32, A = B = TF32, M = 128, N = bn, operand majors as given.
 __device__ __forceinline__ uint32_t make_idesc(int bm, int bn, int a_mn, int b_mn) {
@@ -243,7 +245,7 @@ struct WorkIter {
     }
   }
   __device__ __forceinline__ bool next(const TcParams& p, Work& o) {
-    const i64 kblocks_total = (p.K + BK - 1) / BK;
+    const i64 kblocks_total = (p.K + p.bk - 1) / p.bk;
     if (p.persistent == 2) {
       // whole tiles, the u-th computed tile to group u mod G: no launch / allocation / barrier set-up per tile, and the producer
       // runs ahead into the next tile while this one is stored.  With tiles skipped above the diagonal (causal 1) only the
@@ -285,8 +287,8 @@ struct WorkIter {
     o.b1 = o.bz / (int)p.nb2; o.b2 = o.bz % (int)p.nb2;
     i64 kb0 = (i64)o.split * p.kblocks_per_split, kb1 = kb0 + p.kblocks_per_split;
     if (kb1 > kblocks_total) kb1 = kblocks_total;
-    if (p.causal == 2) { i64 lim = (((i64)o.tile_m + 1) * (BM * CG) + BK - 1) / BK; if (kb1 > lim) kb1 = lim; }
-    if (p.causal == 3) { i64 lo = ((i64)o.tile_m * (BM * CG)) / BK; if (kb0 < lo) kb0 = lo; }
+    if (p.causal == 2) { i64 lim = (((i64)o.tile_m + 1) * (BM * CG) + p.bk - 1) / p.bk; if (kb1 > lim) kb1 = lim; }
+    if (p.causal == 3) { i64 lo = ((i64)o.tile_m * (BM * CG)) / p.bk; if (kb0 < lo) kb0 = lo; }
     o.kb0 = (int)kb0; o.nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0); o.whole = p.splits == 1;
     return true;
   }
@@ -368,7 +370,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment in the shared window
   const int bn = p.bn, stages = p.stages, lstages = p.lstages;
   const int bnc = bn / CG;                                   // B rows staged by this CTA
-  const uint32_t a_bytes = BM * BK * 4, b_bytes = (uint32_t)bnc * BK * 4, raw_bytes = a_bytes + b_bytes;
+  const int bk = p.bk;
+  const uint32_t a_bytes = BM * bk * 4, b_bytes = (uint32_t)bnc * bk * 4, raw_bytes = a_bytes + b_bytes;
   uint8_t* lo_ring = smem + (size_t)stages * raw_bytes;
   uint64_t* bars = (uint64_t*)(lo_ring + (size_t)lstages * raw_bytes);
   uint64_t* full = bars; uint64_t* empty = bars + stages; uint64_t* conv = bars + 2 * stages; uint64_t* lo_empty = conv + lstages;
@@ -424,15 +427,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       while (ok && wi.next(p, wk)) {
         const int ab2 = p.a_bcast2 ? 0 : wk.b2, ab1 = p.a_bcast1 ? 0 : wk.b1, bb2 = p.b_bcast2 ? 0 : wk.b2, bb1 = p.b_bcast1 ? 0 : wk.b1;
         const int m0 = (wk.tile_m * CG + (int)rank) * BM, n0 = wk.tile_n * bn + (int)rank * bnc;
-        int k = wk.kb0 * BK;
-        for (int kb = 0; kb < wk.nkb; ++kb, ++it, k += BK) {
+        int k = wk.kb0 * bk;
+        for (int kb = 0; kb < wk.nkb; ++kb, ++it, k += bk) {
           if (kTiming && (p.debug & 4)) continue;
           if (it >= stages && !mbar_wait(&empty[s], ph, abort_flag)) { ok = false; break; }
           trace_event(p, 0, it);
           uint8_t* st = smem + (size_t)s * raw_bytes;
           mbar_arrive_expect_tx(&full[s], raw_bytes);
-          tma_load_tile(st, &map_a, &full[s], amode, BM, m0, k, ab2, ab1);
-          tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bnc, n0, k, bb2, bb1);
+          tma_load_tile(st, &map_a, &full[s], amode, BM, m0, k, ab2, ab1, bk);
+          tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bnc, n0, k, bb2, bb1, bk);
           trace_event(p, 1, it);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
@@ -451,8 +454,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     // additions; nothing else is computed per k-block.
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = make_idesc(BM * CG, bn, p.a_mn, p.b_mn);
-      const uint64_t a_hi0 = make_desc(smem_u32(smem), 0, p.a_mn), b_hi0 = make_desc(smem_u32(smem) + a_bytes, 0, p.b_mn);
-      const uint64_t a_lo0 = make_desc(smem_u32(lo_ring), 0, p.a_mn), b_lo0 = make_desc(smem_u32(lo_ring) + a_bytes, 0, p.b_mn);
+      const uint64_t a_hi0 = make_desc(smem_u32(smem), 0, p.a_mn, bk), b_hi0 = make_desc(smem_u32(smem) + a_bytes, 0, p.b_mn, bk);
+      const uint64_t a_lo0 = make_desc(smem_u32(lo_ring), 0, p.a_mn, bk), b_lo0 = make_desc(smem_u32(lo_ring) + a_bytes, 0, p.b_mn, bk);
       const uint64_t a_ks = p.a_mn ? (1024 >> 4) : (32 >> 4), b_ks = p.b_mn ? (1024 >> 4) : (32 >> 4);   // second 8-wide k step of a k-block
       const uint64_t stage16 = raw_bytes >> 4;
       uint64_t a_hi = a_hi0, b_hi = b_hi0, a_lo = a_lo0, b_lo = b_lo0;
@@ -497,6 +500,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 mma_tf32(tmem_base, a_lo + a_ks, b_hi + b_ks, idesc, 1u);
                 mma_tf32(tmem_base, a_hi + a_ks, b_lo + b_ks, idesc, 1u);
                 mma_tf32(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u);
+                if (bk == 32) {         // two more 8-wide k steps
+                  mma_tf32(tmem_base, a_lo + 2 * a_ks, b_hi + 2 * b_ks, idesc, 1u);
+                  mma_tf32(tmem_base, a_hi + 2 * a_ks, b_lo + 2 * b_ks, idesc, 1u);
+                  mma_tf32(tmem_base, a_hi + 2 * a_ks, b_hi + 2 * b_ks, idesc, 1u);
+                  mma_tf32(tmem_base, a_lo + 3 * a_ks, b_hi + 3 * b_ks, idesc, 1u);
+                  mma_tf32(tmem_base, a_hi + 3 * a_ks, b_lo + 3 * b_ks, idesc, 1u);
+                  mma_tf32(tmem_base, a_hi + 3 * a_ks, b_hi + 3 * b_ks, idesc, 1u);
+                }
               }
             }
             acc = 1u;
@@ -613,7 +624,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         // the same whichever CTA happens to be last) and writes the result.  Nobody waits for anybody.
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
-        const i64 kblocks_total = (p.K + BK - 1) / BK;
+        const i64 kblocks_total = (p.K + p.bk - 1) / p.bk;
         const i64 x0 = (i64)wk.tile * kblocks_total, G = gridDim.x / CG, W = p.total_kb;
         // first and last group whose range meets [x0, x0 + kblocks_total): group c starts at floor(c*W/G)
         i64 cf = ((x0 + 1) * G + W - 1) / W - 1;
@@ -757,7 +768,7 @@ bool tma_ok(const Operand& o, i64 nb1, i64 nb2) {
   if (o.rs <= 0 || (!o.bc1 && nb1 > 1 && o.b1 <= 0) || (!o.bc2 && nb2 > 1 && o.b2 <= 0)) return false;
   return true;
 }
-int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int box_rows, bool* folded) {
+int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int box_rows, int bk, bool* folded) {
   i64 d2 = o.bc2 ? 1 : nb2, d3 = o.bc1 ? 1 : nb1;
   *folded = o.mn && (o.rows % 32) == 0;
   // a batch level of extent 1 never advances: any 16-byte-multiple stride is acceptable there
@@ -768,21 +779,22 @@ int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int bo
   if (!o.mn) {            // K-major: one box of BK x box_rows, 64-byte swizzle
     dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)o.rows; dims[2] = 1;
     strides[0] = (cuuint64_t)o.rs * 4; strides[1] = (cuuint64_t)plane * 4;
-    box[0] = BK; box[1] = (cuuint32_t)box_rows; box[2] = 1;
+    box[0] = (cuuint32_t)bk; box[1] = (cuuint32_t)box_rows; box[2] = 1;
   } else if (*folded) {   // MN-major, rows a multiple of 32: {32, K, rows/32}, one box of 32 x BK x box_rows/32, 128-byte swizzle on 32-byte units
     dims[0] = 32; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)(o.rows / 32);
     strides[0] = (cuuint64_t)o.rs * 4; strides[1] = 128;
-    box[0] = 32; box[1] = BK; box[2] = (cuuint32_t)(box_rows / 32);
+    box[0] = 32; box[1] = (cuuint32_t)bk; box[2] = (cuuint32_t)(box_rows / 32);
   } else {                // MN-major, any row count: boxes of 32 x BK
     dims[0] = (cuuint64_t)o.rows; dims[1] = (cuuint64_t)K; dims[2] = 1;
     strides[0] = (cuuint64_t)o.rs * 4; strides[1] = (cuuint64_t)plane * 4;
-    box[0] = 32; box[1] = BK; box[2] = 1;
+    box[0] = 32; box[1] = (cuuint32_t)bk; box[2] = 1;
   }
   dims[3] = (cuuint64_t)d2; dims[4] = (cuuint64_t)d3;
   strides[2] = (cuuint64_t)s2 * 4; strides[3] = (cuuint64_t)s3 * 4;
   box[3] = 1; box[4] = 1;
   CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, (void*)o.p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           o.mn ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           o.mn ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return set_error(VB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
   return VB_OK;
 }
@@ -836,12 +848,16 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   VB_TRY(prepare(g.B, g.N, g.b_cs, g.b_rs, g.b_b1, g.b_b2, hold_b, &ob));   // B^T rows are the columns of B
 
   TcParams p{};
-  const i64 kblocks = (g.K + BK - 1) / BK;
   // CTA pairs (256-row tiles, one MMA for two SMs) are opt-in: they move a third less through L2 and shared memory, but as
   // measured the cross-CTA hand-offs cost more than that saves (fc1 of GPT-small: 268 us against 224 us with single CTAs).
   static int cg_env = -1;
   if (cg_env < 0) { const char* e = getenv("VB200_TC_CG"); cg_env = e ? atoi(e) : 1; }
   const int CG = (cg_env == 2 && g.M > BM && !g.causal) ? 2 : 1;
+  // 64-wide tiles do a quarter of the work of 256-wide ones per k-block but pay the same hand-offs: twice the k per stage
+  static int bk32_env = -1;
+  if (bk32_env < 0) { const char* e = getenv("VB200_TC_BK32"); bk32_env = (e && e[0] == '0') ? 0 : 1; }
+  const int bk = (bk32_env && CG == 1 && g.N <= 64 && g.K >= 64) ? 32 : BK;
+  const i64 kblocks = (g.K + bk - 1) / bk;
   static int cw_env = -1;
   if (cw_env < 0) { const char* e = getenv("VB200_TC_CW"); cw_env = (e && atoi(e) == 16) ? 16 : 8; }
   const int CW = cw_env;
@@ -901,7 +917,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   static int rr_env = -1;
   if (rr_env < 0) { const char* e = getenv("VB200_TC_ROUNDROBIN"); rr_env = (e && e[0] == '0') ? 0 : 1; }
   const bool round_robin = rr_env && !persistent && splits == 1 && kblocks <= 64 && causal_eff <= 1 && live_per_batch * nb >= 4 * slots;
-  const size_t raw_bytes = (size_t)(BM + p.bn / CG) * BK * 4;
+  const size_t raw_bytes = (size_t)(BM + p.bn / CG) * bk * 4;
+  p.bk = bk;
   // Small rings on purpose: two CTAs then share an SM, and one CTA's epilogue and pipeline bubbles are covered by
   // the other's main loop; measured faster than one CTA per SM with a deep ring.  The lo ring is at least 32 KB
   // because the epilogue stages its stores there.
@@ -918,8 +935,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
 
   CUtensorMap map_a, map_b;
   bool fold_a = false, fold_b = false;
-  VB_TRY(make_map(&map_a, oa, g.K, g.nb1, g.nb2, BM, &fold_a));
-  VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn / CG, &fold_b));
+  VB_TRY(make_map(&map_a, oa, g.K, g.nb1, g.nb2, BM, bk, &fold_a));
+  VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn / CG, bk, &fold_b));
   p.a_fold = fold_a; p.b_fold = fold_b;
   Temp part, ws;
   if (splits > 1) VB_TRY(scratch_alloc((size_t)((i64)splits * nb * g.M * g.N) * sizeof(float), &part.p));

@@ -4,6 +4,7 @@
   python -m vearo_b200.kernel_cases gemm_dx       g[8192,3072] . W[3072,768]    (B consumed as a transposed view)
   python -m vearo_b200.kernel_cases gemm_dw       g[8192,3072]^T . x[8192,768]  (both operands transposed views, split-K)
   python -m vearo_b200.kernel_cases gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
+  python -m vearo_b200.kernel_cases gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
   python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
   python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
   python -m vearo_b200.kernel_cases adamw         64 Mi parameters
@@ -38,6 +39,9 @@ def build(case):
         q, k = T(f(8, 12, 1024, 64)), T(f(8, 12, 1024, 64))
         kt = k.transpose(2, 3)
         return lambda: q.matmul(kt)
+    if case == "gemm_pv":
+        pr, v = T(f(8, 12, 1024, 1024)), T(f(8, 12, 1024, 64))
+        return lambda: pr.matmul(v)
     if case == "layernorm_bwd":
         x, w, b, g = T(f(8192, 768), True), T(f(768), True), T(f(768), True), T(f(8192, 768))
 
