@@ -38,6 +38,7 @@
 #include <cuda.h>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <vector>
 
 namespace vb {
@@ -61,6 +62,7 @@ struct TcParams {
   i64 nb1, nb2;
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
   int tmem_cols;                                  // tensor-memory columns allocated: bn rounded up to a power of two
+  int tma_out;                                    // results leave through TMA stores of the staged 32 x 32 blocks (map_c)
   int bk;                                         // k per stage: 16, or 32 for the narrow (64-wide) tiles whose per-stage hand-offs dominate
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
   int a_fold, b_fold;                             // 1: MN-contiguous operand whose tensor map is folded into 32-wide blocks (one TMA box per tile)
@@ -148,6 +150,16 @@ __device__ __forceinline__ void tma_load_tile(uint8_t* dst, const CUtensorMap* m
   else if (mode == 2) tma_load_5d(dst, map, bar, 0, k, r0 >> 5, b2, b1);
   else for (int j = 0; j < rows / 32; ++j) tma_load_5d(dst + j * (bk * 128), map, bar, r0 + 32 * j, k, 0, b2, b1);
 }
+
+// One staged 32-row x 32-column block (128-byte rows, 128-byte swizzle: the layout stage_put writes) to global memory; rows and
+// columns beyond the tensor's extent are clipped by the copy engine.  Coordinates: column, row, inner batch, outer batch.
+__device__ __forceinline__ void tma_store_block(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// The issuing thread's earlier block stores have finished reading shared memory.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, K-major: rows of bk floats -- 64 bytes with SWIZZLE_64B (bk = 16) or 128 bytes with
 // SWIZZLE_128B (bk = 32) -- and 8-row groups 512 / 1024 bytes apart.
@@ -363,7 +375,7 @@ __device__ __forceinline__ void trace_event(const TcParams& p, int ev, int kb) {
 
 template <int CG, int CW>
 __global__ void __launch_bounds__(64 + 32 * CW, CW == 8 ? 2 : 1)
-k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ]
   // (doubles as the epilogue's staging area: nothing converts while a tile is being stored), barriers.
@@ -604,6 +616,29 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 #pragma unroll
             for (int j4 = 0; j4 < 8; ++j4)
               dst[j4 * 32] = make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]), __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
+          } else if (p.tma_out) {
+            // final values (or raw split-K sums) are formed in registers, staged, and stored by the copy engine: the store of
+            // one block overlaps the read of the next from tensor memory
+            if (wk.whole) {
+              const float bm = (p.bias_m && row0 + lane < p.M) ? p.bias_m[row0 + lane] : 0.0f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float e = __uint_as_float(r[j]) * p.alpha;
+                if (p.bias && col0 + j < p.N) e += __ldg(p.bias + col0 + j);
+                r[j] = __float_as_uint(e + bm);
+              }
+            }
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4)
+              stage_put(stg, lane, j4, make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]), __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3])));
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              if (wk.whole) tma_store_block(&map_c, stg, (int)col0, (int)row0, wk.b2, wk.b1);
+              else tma_store_block(&map_c, stg, (int)col0, (int)row0, (int)((i64)wk.split * (p.nb1 * p.nb2) + wk.bz), 0);
+            }
           } else if (wk.whole) {
             store_block(p, r, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
           } else {
@@ -611,6 +646,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           }
         }
       }
+      if (p.tma_out) { if (lane == 0) tma_store_wait_read(); __syncwarp(); }     // the staging area is the lo ring of the next unit
       if (ct == 0) trace_event(p, 6, 1);
       if (wk.nkb > 0) {                 // the accumulator has been read: the next unit's first MMA may overwrite it
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -653,6 +689,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             // part by part, accumulating in the staging block itself (every thread re-reads only what it wrote): eight loads in
             // flight per thread, and no accumulator registers beyond the eight values just loaded
             const i64 unit = ((c0 >> 5) * 4 + q) * 256 + lane;
+            if (p.tma_out) { if (lane == 0) tma_store_wait_read(); __syncwarp(); }
             for (int i = 0; i < np; ++i) {
               const i64 c = cf + i;
               const int which = ((c * W) / G >= x0) ? 0 : 1;
@@ -672,8 +709,28 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
                 }
               }
             }
-            stage_write_out(p, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
+            if (p.tma_out) {          // finish row `lane` of the staged block in place, then hand the block to the copy engine
+              const float bm = (p.bias_m && row0 + lane < p.M) ? p.bias_m[row0 + lane] : 0.0f;
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4) {
+                float4 a = stg[lane * 8 + (j4 ^ (lane & 7))];
+                float e[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  e[t] *= p.alpha;
+                  if (p.bias && col0 + 4 * j4 + t < p.N) e[t] += __ldg(p.bias + col0 + 4 * j4 + t);
+                  e[t] += bm;
+                }
+                stage_put(stg, lane, j4, make_float4(e[0], e[1], e[2], e[3]));
+              }
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0 && row0 < p.M) tma_store_block(&map_c, stg, (int)col0, (int)row0, wk.b2, wk.b1);
+            } else {
+              stage_write_out(p, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
+            }
           }
+          if (p.tma_out) { if (lane == 0) tma_store_wait_read(); __syncwarp(); }
         }
       }
       // the staging area is the lo ring, and last_flag is per unit: nobody starts converting the next unit before all have finished this one
@@ -799,6 +856,24 @@ int make_map(CUtensorMap* map, const Operand& o, i64 K, i64 nb1, i64 nb2, int bo
   return VB_OK;
 }
 
+// Map of the output (or of the split-K scratch) for the epilogue's block stores: {columns, rows, inner batch, outer batch}, boxes of
+// 32 x 32 with the 128-byte swizzle.  False when the layout cannot be described (unaligned base or strides): the kernel then
+// stores with ordinary instructions.
+bool make_out_map(CUtensorMap* map, float* base, i64 N, i64 M, i64 d2, i64 d3, i64 rs, i64 s2, i64 s3) {
+  if (((uintptr_t)base & 15) || (rs & 3) || rs <= 0 || N <= 0 || M <= 0) return false;
+  if (d2 <= 1) { d2 = 1; s2 = rs * M; }
+  if (d3 <= 1) { d3 = 1; s3 = s2 * d2; }
+  if ((s2 & 3) || (s3 & 3) || s2 <= 0 || s3 <= 0) return false;
+  const i64 lim = (i64)1 << 38;     // strides in bytes must stay below 2^40
+  if (rs >= lim || s2 >= lim || s3 >= lim || N > 0x7fffffff || M > 0x7fffffff || d2 > 0x7fffffff || d3 > 0x7fffffff) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)d2, (cuuint64_t)d3};
+  cuuint64_t strides[3] = {(cuuint64_t)rs * 4, (cuuint64_t)s2 * 4, (cuuint64_t)s3 * 4};
+  cuuint32_t box[4] = {32, 32, 1, 1}, estr[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int* g_tile_counters = nullptr;     // stream-K arrival counters (zero between launches)
 
 }  // namespace
@@ -872,7 +947,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     double best = 1e300;
     for (int bn : {256, 128}) {
       i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
-      for (int sk : {1, 2, 3, 4, 6, 8, 12, 16}) {
+      for (int sk : {1, 2, 3, 4, 5, 6, 8, 10, 12, 16}) {
         if (sk > 1 && kblocks / sk < 24) break;
         i64 units = tiles * sk, waves = (units + slots - 1) / slots;
         double kb_cost = bn == 256 ? 1.0 : 0.62, epi = bn == 256 ? 10.0 : 6.0;
@@ -967,6 +1042,16 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.causal = causal_eff;
   if (round_robin) { p.persistent = 2; p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.live_per_batch = live_per_batch; p.live_tiles = live_per_batch * nb; }
 
+  // Results leave through the copy engine when the layout allows and nothing has to be read back (beta = 0).
+  CUtensorMap map_c;
+  memset(&map_c, 0, sizeof map_c);
+  static int tma_out_env = -1;
+  if (tma_out_env < 0) { const char* e = getenv("VB200_TC_TMA_OUT"); tma_out_env = (e && e[0] == '0') ? 0 : 1; }
+  if (tma_out_env && g.beta == 0.0f && !(kTiming && getenv("VB200_TC_DEBUG"))) {
+    if (splits == 1) p.tma_out = make_out_map(&map_c, g.C, g.N, g.M, g.nb2, g.nb1, g.c_rs, g.c_b2, g.c_b1) ? 1 : 0;
+    else p.tma_out = make_out_map(&map_c, (float*)part.p, g.N, g.M, (i64)splits * nb, 1, g.N, g.M * g.N, 0) ? 1 : 0;
+  }
+
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
   p.raw_hi = raw_hi_env;
@@ -1000,12 +1085,12 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
       cfg.attrs = attr; cfg.numAttrs = 1;
       { static int occ = -1; if (occ < 0) { const char* e = getenv("VB200_TC_OCC"); occ = (e && e[0] == '1') ? 1 : 0; }
         if (occ) { int n = 0; cudaError_t r = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<2, 8>, &cfg); fprintf(stderr, "[gemm_tc] max active clusters %d (err %d), smem %zu, grid %u\n", n, (int)r, smem, grid.x * grid.y * grid.z); occ = 0; } }
-      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, p));
-      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, p));
+      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, map_c, p));
+      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, map_c, p));
     } else if (CW == 16) {
-      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, p);
+      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, map_c, p);
     } else {
-      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, p);
+      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, map_c, p);
     }
     VB_LAUNCH_CHECK();
     if (kTiming && (p.debug & 64)) {
