@@ -11,6 +11,7 @@
 // Both kernels are HBM-bound: one CTA of 128 threads per row, the row held in registers
 // (up to 4096 columns), one read and one write of the matrix.
 #include "common.h"
+#include <cstdlib>
 
 namespace vb {
 
@@ -99,15 +100,21 @@ __global__ void __launch_bounds__(256) k_attn_softmax_long(float* __restrict__ s
 
 // Warp-per-row variants for rows of up to 1024 columns (a multiple of 4): 128-bit loads and stores, the row lives
 // in registers, reductions are warp shuffles only (no block barrier).  V = float4 per lane.
+// i_lo, i_cnt: the rows [i_lo, i_lo + i_cnt) of every [sq, sk] matrix are handled by this launch (`rows` = number of matrices).
+// Causal launches go by bands of rows, each with the instance whose register array just covers the band's live columns.
 template <int V>
 __global__ void __launch_bounds__(128) k_attn_softmax_warp(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
-                                                           i64 H, i64 sq, i64 sk, i64 rows, int causal) {
+                                                           i64 H, i64 sq, i64 sk, i64 rows, int causal, i64 i_lo, i64 i_cnt) {
   const int lane = threadIdx.x & 31;
-  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
-  for (i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; row < rows; row += nwarps) {
-    i64 i = row % sq, bh = row / sq, h = bh % H, b = bh / H;
+  // grid: x = groups of four rows of the band, y = matrices (no division on the way to the row's address)
+  const i64 ii = (i64)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (ii >= i_cnt) return;
+  const i64 i = i_lo + ii;
+  for (i64 bh = blockIdx.y; bh < rows; bh += gridDim.y) {
+    const i64 row = bh * sq + i;
     float4* r4 = reinterpret_cast<float4*>(s + row * sk);
-    const float4* m4 = (mask && !causal) ? reinterpret_cast<const float4*>(mask + b * ms.b + h * ms.h + i * ms.q) : nullptr;
+    const float4* m4 = nullptr;
+    if (mask && !causal) { const i64 h = bh % H, b = bh / H; m4 = reinterpret_cast<const float4*>(mask + b * ms.b + h * ms.h + i * ms.q); }
     // causal: columns j > i hold probability 0; they are not read, and zeros are written only up to the end of the
     // 128-row tile that contains row i (what the triangular products that follow can touch)
     const i64 live = causal ? i + 1 : sk;                       // columns [0, live) take part
@@ -150,13 +157,15 @@ __global__ void __launch_bounds__(128) k_attn_softmax_warp(float* __restrict__ s
 }
 template <int V>
 __global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __restrict__ p, float* __restrict__ dp, i64 sk, float scale, i64 rows,
-                                                               int causal, i64 sq) {
+                                                               int causal, i64 sq, i64 i_lo, i64 i_cnt) {
   const int lane = threadIdx.x & 31;
-  const i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
-  for (i64 row = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5; row < rows; row += nwarps) {
+  const i64 ii = (i64)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (ii >= i_cnt) return;
+  const i64 i = i_lo + ii;
+  for (i64 bh = blockIdx.y; bh < rows; bh += gridDim.y) {
+    const i64 row = bh * sq + i;
     const float4* p4 = reinterpret_cast<const float4*>(p + row * sk);
     float4* d4 = reinterpret_cast<float4*>(dp + row * sk);
-    const i64 i = row % sq;
     // causal: p is exactly 0 for columns j > i (the forward wrote those zeros inside the diagonal tile), so chunks
     // past the diagonal contribute nothing; dp there was never computed and is overwritten with zeros up to the tile end
     const i64 live = causal ? i + 1 : sk;
@@ -188,11 +197,8 @@ __global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __re
     }
   }
 }
+static inline i64 causal_band() { static i64 b = 0; if (!b) { const char* e = getenv("VB200_SOFTMAX_BAND"); b = e ? atoll(e) : 512; if (b < 128) b = 128; } return b; }
 static inline bool al16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-static inline unsigned warp_grid(i64 rows) {
-  i64 blocks = (rows + 3) / 4, cap = (i64)ctx().sm_count * 16;
-  return (unsigned)(blocks > cap ? cap : blocks);
-}
 
 int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool causal, i64 b, i64 h, i64 sq, i64 sk, float scale) {
   (void)scale;
@@ -205,12 +211,20 @@ int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool cau
   bool mask_vec = !mask || (ms.k == 1 && al16p(mask) && !(ms.b & 3) && !(ms.h & 3) && !(ms.q & 3));
   if (causal && !((sk & 3) == 0 && sk <= 1024 && al16p(s) && sq == sk)) return set_error(VB_ERR_UNSUPPORTED, "causal attention softmax needs square S <= 1024, a multiple of 4");
   if ((sk & 3) == 0 && sk <= 1024 && al16p(s) && (mask_vec || causal)) {
-    unsigned wg = warp_grid(rows);
-    const int cz = causal ? 1 : 0;
-    if (sk <= 128) k_attn_softmax_warp<1><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
-    else if (sk <= 256) k_attn_softmax_warp<2><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
-    else if (sk <= 512) k_attn_softmax_warp<4><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
-    else k_attn_softmax_warp<8><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, rows, cz);
+    const i64 mats = b * h;
+    // causal: bands of 256 rows, band c with the instance covering its 256 (c + 1) live columns; otherwise one launch over all rows
+    const i64 band = causal ? causal_band() : sq;
+    for (i64 lo = 0; lo < sq; lo += band) {
+      const i64 cnt = sq - lo < band ? sq - lo : band;
+      const i64 width = causal ? (lo + cnt < sk ? lo + cnt : sk) : sk;
+      const dim3 wg((unsigned)((cnt + 3) / 4), (unsigned)(mats < 65535 ? mats : 65535));
+      const int cz = causal ? 1 : 0;
+      if (width <= 128) k_attn_softmax_warp<1><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, mats, cz, lo, cnt);
+      else if (width <= 256) k_attn_softmax_warp<2><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, mats, cz, lo, cnt);
+      else if (width <= 512) k_attn_softmax_warp<4><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, mats, cz, lo, cnt);
+      else if (width <= 768) k_attn_softmax_warp<6><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, mats, cz, lo, cnt);
+      else k_attn_softmax_warp<8><<<wg, 128, 0, st>>>(s, mask, ms, h, sq, sk, mats, cz, lo, cnt);
+    }
     VB_LAUNCH_CHECK();
     return VB_OK;
   }
@@ -261,11 +275,19 @@ int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, fl
   ProfScope prof("attn_softmax_bwd", 3.0 * (double)rows * (double)sk * 4.0);
   cudaStream_t st = ctx().stream;
   if ((sk & 3) == 0 && sk <= 1024 && al16p(p) && al16p(dp)) {
-    unsigned wg = warp_grid(rows);
-    if (sk <= 128) k_attn_softmax_bwd_warp<1><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
-    else if (sk <= 256) k_attn_softmax_bwd_warp<2><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
-    else if (sk <= 512) k_attn_softmax_bwd_warp<4><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
-    else k_attn_softmax_bwd_warp<8><<<wg, 128, 0, st>>>(p, dp, sk, scale, rows, causal ? 1 : 0, sq);
+    const i64 mats = causal ? rows / sq : 1, seq = causal ? sq : rows;      // without a causal mask all rows are alike: one band
+    const i64 band = causal ? causal_band() : seq;
+    const int cz = causal ? 1 : 0;
+    for (i64 lo = 0; lo < seq; lo += band) {
+      const i64 cnt = seq - lo < band ? seq - lo : band;
+      const i64 width = causal ? (lo + cnt < sk ? lo + cnt : sk) : sk;
+      const dim3 wg((unsigned)((cnt + 3) / 4), (unsigned)(mats < 65535 ? mats : 65535));
+      if (width <= 128) k_attn_softmax_bwd_warp<1><<<wg, 128, 0, st>>>(p, dp, sk, scale, mats, cz, seq, lo, cnt);
+      else if (width <= 256) k_attn_softmax_bwd_warp<2><<<wg, 128, 0, st>>>(p, dp, sk, scale, mats, cz, seq, lo, cnt);
+      else if (width <= 512) k_attn_softmax_bwd_warp<4><<<wg, 128, 0, st>>>(p, dp, sk, scale, mats, cz, seq, lo, cnt);
+      else if (width <= 768) k_attn_softmax_bwd_warp<6><<<wg, 128, 0, st>>>(p, dp, sk, scale, mats, cz, seq, lo, cnt);
+      else k_attn_softmax_bwd_warp<8><<<wg, 128, 0, st>>>(p, dp, sk, scale, mats, cz, seq, lo, cnt);
+    }
     VB_LAUNCH_CHECK();
     return VB_OK;
   }

@@ -5,6 +5,7 @@
   python -m vearo_b200.kernel_cases gemm_dw       g[8192,3072]^T . x[8192,768]  (both operands transposed views, split-K)
   python -m vearo_b200.kernel_cases gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
   python -m vearo_b200.kernel_cases gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
+  python -m vearo_b200.kernel_cases attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
   python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
   python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
   python -m vearo_b200.kernel_cases adamw         64 Mi parameters
@@ -42,6 +43,14 @@ def build(case):
     if case == "gemm_pv":
         pr, v = T(f(8, 12, 1024, 1024)), T(f(8, 12, 1024, 64))
         return lambda: pr.matmul(v)
+    if case == "attention":
+        qkv, go = T(f(8, 1024, 2304), True), T(f(8, 1024, 768))
+        mask = T(np.triu(np.full((1024, 1024), -1e9, np.float32), 1))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            qkv.fused_attention_packed(12, mask).mul(go).sum(2, False).sum(1, False).sum(0, False).backward()
+        return run
     if case == "layernorm_bwd":
         x, w, b, g = T(f(8192, 768), True), T(f(768), True), T(f(768), True), T(f(8192, 768))
 
