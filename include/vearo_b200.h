@@ -214,7 +214,9 @@ int vb_clip_grad_norm(const vb_tensor* grads, int n, float max_norm, float* tota
 
 /* Fused multi-tensor optimizer: one launch updates every parameter; global-norm clipping is
  * folded in (the scale is applied inside the update, the gradients are never rewritten). */
-enum vb_opt_kind { VB_OPT_ADAMW = 0, VB_OPT_SGD = 1 };
+/* VB_OPT_ADAMW8BIT is AdamW8bit (vearo-optim/src/lib.rs:211-303): the moments are held as int8 with one f32 scale per
+ * 256 elements of a parameter, dequantized before and requantized after every update (QuantizedState, lib.rs:137-209). */
+enum vb_opt_kind { VB_OPT_ADAMW = 0, VB_OPT_SGD = 1, VB_OPT_ADAMW8BIT = 2 };
 typedef struct vb_opt_config {
   int32_t kind;
   float lr, beta1, beta2, eps, weight_decay, momentum;
@@ -229,6 +231,11 @@ int vb_opt_set_lr(int opt, float lr);
  * (vearo-optim/src/lib.rs:68-70, 105-123 keep them in host Vecs). */
 int vb_opt_state(int opt, vb_slot* state, int64_t* state_numel, uint32_t* step);
 int vb_opt_set_step(int opt, uint32_t step);
+/* Quantized state of parameter `param` of a VB_OPT_ADAMW8BIT optimizer, copied to host memory: numel int8 values and
+ * (numel + 255) / 256 scales, for m and for v (the fields of QuantizedState, lib.rs:138-142).  Synchronises.
+ * (The slot vb_opt_state returns holds, for this kind, the same bytes: all m values, all v values, then all m scales and all
+ * v scales, every parameter's share starting on a 256-element boundary; checkpoints store it as it is.) */
+int vb_opt_state8(int opt, int param, int8_t* m8, float* m_scales, int8_t* v8, float* v_scales);
 /* active[i] == 0 skips parameter i (no gradient this step; vearo-optim/src/lib.rs:106-108); NULL = all.
  * max_norm <= 0 disables clipping.  grad_scale multiplies every gradient first (1/world for data
  * parallel sums).  *total_norm (may be NULL) receives the pre-clip norm; reading it synchronises. */

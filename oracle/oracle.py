@@ -39,6 +39,8 @@ def lib():
         _lib.orc_layernorm_backward.argtypes = [C.c_int] * 4 + [C.c_float, c_intp]
         _lib.orc_batchnorm_backward.argtypes = [C.c_int] * 6 + [C.c_float, c_intp]
         _lib.orc_adamw_create.argtypes = [c_intp, C.c_int] + [C.c_float] * 5
+        _lib.orc_adamw8bit_create.argtypes = [c_intp, C.c_int] + [C.c_float] * 5
+        _lib.orc_opt_state8.argtypes = [C.c_int, C.c_int, C.c_void_p, c_f32p, C.c_void_p, c_f32p]
         _lib.orc_sgd_create.argtypes = [c_intp, C.c_int] + [C.c_float] * 3
         _lib.orc_opt_set_lr.argtypes = [C.c_int, C.c_float]
         _lib.orc_clip_grad_norm.argtypes = [c_intp, C.c_int, C.c_float]
@@ -185,6 +187,27 @@ class AdamW:
 
     def step(self): _chk(lib().orc_opt_step(self.o))
     def set_lr(self, lr): _chk(lib().orc_opt_set_lr(self.o, lr))
+
+
+class AdamW8bit:
+    """vearo_optim::AdamW8bit (crates/vearo-optim/src/lib.rs:211-303): AdamW whose moments live as int8 with one
+    scale per 256 elements, dequantized before and requantized after every step."""
+
+    def __init__(self, params, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0):
+        hs, n = _handles(params)
+        self.sizes = [int(np.prod(p.shape)) if len(p.shape) else 1 for p in params]
+        self.o = _chk(lib().orc_adamw8bit_create(hs, n, lr, beta1, beta2, eps, weight_decay))
+
+    def step(self): _chk(lib().orc_opt_step(self.o))
+    def set_lr(self, lr): _chk(lib().orc_opt_set_lr(self.o, lr))
+
+    def state(self, i):
+        """(m int8, m scales, v int8, v scales) of parameter i."""
+        n = self.sizes[i]; nb = (n + 255) // 256
+        m8, v8 = np.zeros(n, np.int8), np.zeros(n, np.int8)
+        ms, vs = np.zeros(nb, np.float32), np.zeros(nb, np.float32)
+        _chk(lib().orc_opt_state8(self.o, i, m8.ctypes.data, ms.ctypes.data_as(c_f32p), v8.ctypes.data, vs.ctypes.data_as(c_f32p)))
+        return m8, ms, v8, vs
 
 
 class SGD:

@@ -1083,9 +1083,42 @@ static float powi(float a, int n) {  // f32::powi -> repeated squaring (compiler
   while (true) { if (n & 1) r *= a; n /= 2; if (n == 0) break; a *= a; }
   return recip ? 1.0f / r : r;
 }
+// QuantizedState, vearo-optim/src/lib.rs:137-209: int8 values with one f32 scale (block maximum / 127) per 256 elements.
+struct Quantized {
+  std::vector<int8_t> data; std::vector<float> scales; size_t block = 256;
+  explicit Quantized(size_t n = 0) : data(n, 0), scales((n + 255) / 256, 0.0f) {}
+  void quantize(const std::vector<float>& src) {           // lib.rs:157-194
+    const size_t n = src.size();
+    for (size_t b = 0; b < scales.size(); ++b) {
+      size_t start = b * block, end = std::min(start + block, n);
+      if (start >= end) continue;
+      float mx = 0.0f;
+      for (size_t i = start; i < end; ++i) { float a = std::fabs(src[i]); if (a > mx) mx = a; }
+      scales[b] = mx / 127.0f;
+      if (mx > 0.0f) {
+        float inv = 127.0f / mx;
+        for (size_t i = start; i < end; ++i) {
+          float q = std::round(src[i] * inv);                // f32::round: half away from zero
+          q = q < -127.0f ? -127.0f : (q > 127.0f ? 127.0f : q);
+          data[i] = (int8_t)q;
+        }
+      } else {
+        for (size_t i = start; i < end; ++i) data[i] = 0;
+      }
+    }
+  }
+  void dequantize(std::vector<float>& dst) const {           // lib.rs:197-208
+    const size_t n = dst.size();
+    for (size_t b = 0; b < scales.size(); ++b) {
+      size_t start = b * block, end = std::min(start + block, n);
+      for (size_t i = start; i < end; ++i) dst[i] = (float)data[i] * scales[b];
+    }
+  }
+};
 struct Optimizer {
   bool adam; std::vector<Tensor> params; float lr, b1, b2, eps, wd, momentum;
   std::vector<std::vector<float>> m, v; uint32_t t = 0;
+  bool eight_bit = false; std::vector<Quantized> qm, qv;    // AdamW8bit, lib.rs:211-303
 };
 static void opt_step(Optimizer& o) {
   if (o.adam) o.t += 1;   // AdamW::step, vearo-optim/src/lib.rs:105-123
@@ -1100,6 +1133,7 @@ static void opt_step(Optimizer& o) {
     i64 n = p.numel();
     if (o.adam) {   // adamw_step, tensor.rs:972-985
       float bc1 = 1.0f - powi(o.b1, (int)o.t), bc2 = 1.0f - powi(o.b2, (int)o.t);
+      if (o.eight_bit) { o.qm[pi].dequantize(o.m[pi]); o.qv[pi].dequantize(o.v[pi]); }    // AdamW8bit::step, lib.rs:268-275
       float* m = o.m[pi].data(); float* v = o.v[pi].data();
       for (i64 i = 0; i < n; ++i) {
         float gv = gd[i];
@@ -1109,6 +1143,7 @@ static void opt_step(Optimizer& o) {
         w[i] -= o.lr * o.wd * w[i];
         w[i] -= o.lr * mh / (std::sqrt(vh) + o.eps);
       }
+      if (o.eight_bit) { o.qm[pi].quantize(o.m[pi]); o.qv[pi].quantize(o.v[pi]); }        // lib.rs:290-292
     } else {        // sgd_step, tensor.rs:1062-1069
       float* vel = o.m[pi].data();
       for (i64 i = 0; i < n; ++i) {
@@ -1242,6 +1277,24 @@ int orc_adamw_create(const int* params, int n, float lr, float b1, float b2, flo
   ORC_TRY(auto o = std::make_unique<Optimizer>(); o->adam = true; o->lr = lr; o->b1 = b1; o->b2 = b2; o->eps = eps; o->wd = wd; o->momentum = 0;
           for (int i = 0; i < n; ++i) { o->params.push_back(at(params[i])); o->m.emplace_back((size_t)at(params[i]).numel(), 0.0f); o->v.emplace_back((size_t)at(params[i]).numel(), 0.0f); }
           g_opts.push_back(std::move(o)); return (int)g_opts.size() - 1);
+}
+int orc_adamw8bit_create(const int* params, int n, float lr, float b1, float b2, float eps, float wd) {
+  ORC_TRY(auto o = std::make_unique<Optimizer>(); o->adam = true; o->eight_bit = true; o->lr = lr; o->b1 = b1; o->b2 = b2; o->eps = eps; o->wd = wd; o->momentum = 0;
+          for (int i = 0; i < n; ++i) {
+            size_t cnt = (size_t)at(params[i]).numel();
+            o->params.push_back(at(params[i])); o->m.emplace_back(cnt, 0.0f); o->v.emplace_back(cnt, 0.0f);
+            o->qm.emplace_back(cnt); o->qv.emplace_back(cnt);
+          }
+          g_opts.push_back(std::move(o)); return (int)g_opts.size() - 1);
+}
+// Quantized state of parameter `param` of an 8-bit optimizer: int8 values (numel) and block scales ((numel + 255) / 256), m then v.
+int orc_opt_state8(int o, int param, int8_t* m8, float* ms, int8_t* v8, float* vs) {
+  ORC_TRY(if (o < 0 || o >= (int)g_opts.size() || !g_opts[o]->eight_bit) fail("not an 8-bit optimizer");
+          Optimizer& op = *g_opts[o];
+          if (param < 0 || param >= (int)op.qm.size()) fail("bad parameter index");
+          std::copy(op.qm[param].data.begin(), op.qm[param].data.end(), m8); std::copy(op.qm[param].scales.begin(), op.qm[param].scales.end(), ms);
+          std::copy(op.qv[param].data.begin(), op.qv[param].data.end(), v8); std::copy(op.qv[param].scales.begin(), op.qv[param].scales.end(), vs);
+          return 0);
 }
 int orc_sgd_create(const int* params, int n, float lr, float momentum, float wd) {
   ORC_TRY(auto o = std::make_unique<Optimizer>(); o->adam = false; o->lr = lr; o->momentum = momentum; o->wd = wd; o->b1 = o->b2 = o->eps = 0;

@@ -481,6 +481,50 @@ def test_optimizer_steps_match_oracle(vb, kind):
     both(vb, case)
 
 
+def test_adamw_8bit_matches_oracle_bit_for_bit(vb):
+    """AdamW8bit (crates/vearo-optim/src/lib.rs:211-303): after every step the int8 moments, their block scales and the
+    weights equal the CPU restatement's exactly -- the kernel uses single-rounding arithmetic in the reference's order,
+    so no update can fall on the other side of a quantizer boundary.  Sizes cover a partial last block, a tensor of
+    several chunks with an unaligned tail, a parameter skipped for one step, and a block of zero gradients."""
+    w0 = [rnd(148, 37), rnd(149, 5, 1031), rnd(150, 16384 * 2 + 259), rnd(151, 512)]
+    gs = [[rnd(200 + 10 * s + i, *w.shape) for i, w in enumerate(w0)] for s in range(4)]
+    for s in range(4):
+        gs[s][3][:256] = 0.0                     # m and v of that block stay zero: scale 0, zeros stored
+
+    def run(T, m):
+        ws = [T.from_numpy(w, True) for w in w0]
+        opt = m.AdamW8bit(ws, 1e-2, 0.9, 0.999, 1e-8, 0.1)
+        out = []
+        for s in range(4):
+            m.zero_gradients(); m.reset_active_tape()
+            loss = None
+            for w, g in zip(ws[:2] + ws[3:] if s == 1 else ws, gs[s][:2] + gs[s][3:] if s == 1 else gs[s]):
+                term = w.mul(T.from_numpy(g)).reshape([1, g.size]).sum(1, False).reshape([1])
+                loss = term if loss is None else loss.add(term)
+            loss.backward()
+            opt.step()
+            out.append([w.numpy().copy() for w in ws] + [a.copy() for i in range(len(ws)) for a in opt.state(i)])
+        return out
+    orc.reset_all()
+    want = run(orc.Tensor, orc)
+    vb.zero_gradients(); vb.reset_active_tape()
+    got = run(vb.Tensor, vb)
+    for s, (a, b) in enumerate(zip(got, want)):
+        for k, (x, y) in enumerate(zip(a, b)):
+            assert x.dtype == y.dtype and np.array_equal(x, y), "step %d item %d differs (max %g)" % (
+                s, k, np.abs(x.astype(np.float64) - y.astype(np.float64)).max())
+    # the reference's own test (lib.rs:461-505): 8-bit stays within 1e-2 of plain AdamW after five steps
+    wa, wb = vb.Tensor.from_numpy(np.array([1, 2, 3, 4], np.float32), True), vb.Tensor.from_numpy(np.array([1, 2, 3, 4], np.float32), True)
+    oa, ob = vb.AdamW([wa], 0.1, 0.9, 0.999, 1e-8, 0.01), vb.AdamW8bit([wb], 0.1, 0.9, 0.999, 1e-8, 0.01)
+    for _ in range(5):
+        vb.zero_gradients(); vb.reset_active_tape()
+        wa.mul(wa).sum(0, False).backward(); oa.step()
+        vb.zero_gradients(); vb.reset_active_tape()
+        wb.mul(wb).sum(0, False).backward(); ob.step()
+    assert np.abs(wa.numpy() - wb.numpy()).max() < 1e-2
+    vb.check_errors()
+
+
 def test_clip_grad_norm_known_answer_and_fused_clip(vb):
     """crates/vearo-optim/src/lib.rs:438-459: grads [6, 8] -> norm 10, clipped to [3, 4]."""
     x = vb.Tensor.from_numpy(np.array([3.0, 4.0], np.float32), True)

@@ -160,6 +160,38 @@ def test_optimizer_known_answers():
     np.testing.assert_allclose(x.grad().numpy(), [3, 4], atol=1e-3)
 
 
+def test_adamw_8bit_known_answers():
+    """crates/vearo-optim/src/lib.rs:461-505: five steps of loss = sum(w * w) from w = [1,2,3,4] with lr 0.1,
+    betas (0.9, 0.999), eps 1e-8, weight decay 0.01 -- the 8-bit optimizer must stay within 1e-2 of plain AdamW.
+    Plus the quantizer's definition (lib.rs:157-208) on a hand-checkable block: scale = max|x| / 127,
+    q = round-half-away(x * 127 / max|x|) clamped to [-127, 127], x' = q * scale."""
+    orc.reset_all()
+    w_std, w_8 = T.from_numpy(f32(1, 2, 3, 4), True), T.from_numpy(f32(1, 2, 3, 4), True)
+    o_std, o_8 = orc.AdamW([w_std], 0.1, 0.9, 0.999, 1e-8, 0.01), orc.AdamW8bit([w_8], 0.1, 0.9, 0.999, 1e-8, 0.01)
+    for _ in range(5):
+        orc.zero_gradients(); orc.reset_active_tape()
+        w_std.mul(w_std).sum(0).backward(); o_std.step()
+        orc.zero_gradients(); orc.reset_active_tape()
+        w_8.mul(w_8).sum(0).backward(); o_8.step()
+    assert np.abs(w_std.numpy() - w_8.numpy()).max() < 1e-2
+    # after the first step of a fresh optimizer m = 0.1 g and v = 0.001 g^2; with g = [2, -1, 0.5, 0.0078125]:
+    orc.reset_all()
+    w = T.from_numpy(f32(1, 1, 1, 1), True)
+    g = f32(2, -1, 0.5, 0.0078125)
+    w.mul(T.from_numpy(g)).sum(0).backward()
+    o = orc.AdamW8bit([w], 0.1, 0.9, 0.999, 1e-8, 0.0)
+    o.step()
+    m8, ms, v8, vs = o.state(0)
+    m = np.float32(0.1) * g                      # (1 - 0.9) * g in f32, as the reference forms it
+    m = (np.float32(1.0) - np.float32(0.9)) * g
+    assert ms[0] == np.float32(np.abs(m).max() / np.float32(127.0))
+    # 127 * [1, -0.5, 0.25, 0.00390625] -> 127, -63.5 -> -64 (half away from zero), 31.75 -> 32, 0.496 -> 0
+    assert m8.tolist() == [127, -64, 32, 0]
+    v = (np.float32(1.0) - np.float32(0.999)) * g * g
+    assert vs[0] == np.float32(v.max() / np.float32(127.0))
+    assert v8.tolist() == [127, 32, 8, 0]        # 127 * [1, 0.25, 0.0625, 1.5e-5] -> 127, 31.75 -> 32, 7.94 -> 8, 0
+
+
 def test_batchnorm_running_stats():
     """crates/vearo/tests/batchnorm_review.rs:119-174."""
     n, c, h, w = 2, 2, 2, 2

@@ -69,6 +69,8 @@ def lib():
         L.vh_bn_relu_maxpool.argtypes = [C.c_int] * 6 + [C.c_float, C.c_float]
         L.vh_adamw_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 5 + [C.c_int]
         L.vh_sgd_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 3 + [C.c_int]
+        L.vh_adamw8bit_new.argtypes = [c_intp, C.c_int] + [C.c_float] * 5 + [C.c_int]
+        L.vh_opt_state8.argtypes = [C.c_int, C.c_int, C.c_void_p, c_f32p, C.c_void_p, c_f32p]
         L.vh_opt_set_lr.argtypes = [C.c_int, C.c_float]
         for fn in (L.vh_opt_save_state, L.vh_opt_load_state, L.vh_save_checkpoint, L.vh_load_checkpoint):
             fn.argtypes = [C.c_int, C.c_char_p]
@@ -275,6 +277,25 @@ class AdamW(_Opt):
         hs, n = _handles(params)
         self.params = list(params)
         self.o = _chk(lib().vh_adamw_new(hs, n, lr, beta1, beta2, eps, weight_decay, int(data_parallel)))
+
+
+class AdamW8bit(_Opt):
+    """vearo_optim::AdamW8bit::new(params, lr, beta1, beta2, eps, weight_decay): AdamW whose moments are held as int8
+    with one scale per 256 elements (crates/vearo-optim/src/lib.rs:211-303)."""
+
+    def __init__(self, params, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, data_parallel=False):
+        hs, n = _handles(params)
+        self.params = list(params)
+        self.o = _chk(lib().vh_adamw8bit_new(hs, n, lr, beta1, beta2, eps, weight_decay, int(data_parallel)))
+
+    def state(self, i):
+        """(m int8, m scales, v int8, v scales) of parameter i, as QuantizedState holds them."""
+        n = int(np.prod(self.params[i].shape)) if len(self.params[i].shape) else 1
+        nb = (n + 255) // 256
+        m8, v8 = np.zeros(n, np.int8), np.zeros(n, np.int8)
+        ms, vs = np.zeros(nb, np.float32), np.zeros(nb, np.float32)
+        _chk(lib().vh_opt_state8(self.o, i, m8.ctypes.data, ms.ctypes.data_as(c_f32p), v8.ctypes.data, vs.ctypes.data_as(c_f32p)))
+        return m8, ms, v8, vs
 
 
 class SGD(_Opt):

@@ -28,6 +28,8 @@ struct Opt {
   void* d_partials = nullptr;  // float[nchunks]
   void* d_active = nullptr;    // uint8[nparams]
   std::vector<vb_slot> retained;
+  // 8-bit AdamW: byte offset of every parameter's share of the int8 planes, their common length, and the parameter sizes
+  std::vector<i64> off8, numel8; i64 total8 = 0;
 };
 std::vector<std::unique_ptr<Opt>>& g_opts = *new std::vector<std::unique_ptr<Opt>>();
 }  // namespace
@@ -98,29 +100,40 @@ int vb_clip_grad_norm(const vb_tensor* grads, int n, float max_norm, float* tota
 
 int vb_opt_create(const vb_opt_config* cfg, const vb_tensor* params, const vb_tensor* grads, int n, int* opt) {
   VB_CHECK(cfg && opt && n >= 0, "bad arguments");
-  VB_CHECK(cfg->kind == VB_OPT_ADAMW || cfg->kind == VB_OPT_SGD, "unknown optimizer kind");
+  VB_CHECK(cfg->kind == VB_OPT_ADAMW || cfg->kind == VB_OPT_SGD || cfg->kind == VB_OPT_ADAMW8BIT, "unknown optimizer kind");
+  const bool q8 = cfg->kind == VB_OPT_ADAMW8BIT;
   auto o = std::make_unique<Opt>();
   o->cfg = *cfg; o->nparams = n;
   i64 total = 0;
   for (int i = 0; i < n; ++i) {
     VB_CHECK(is_contiguous(params[i]) && is_contiguous(grads[i]), "optimizer tensors must be contiguous");
     VB_CHECK(numel(params[i]) == numel(grads[i]), "param / grad sizes differ");
-    total += (numel(params[i]) + 3) & ~i64(3);   // keep every tensor's state 16-byte aligned
+    if (q8) { o->off8.push_back(total); o->numel8.push_back(numel(params[i])); total += (numel(params[i]) + 255) & ~i64(255); }   // whole blocks of 256
+    else total += (numel(params[i]) + 3) & ~i64(3);   // keep every tensor's state 16-byte aligned
   }
-  int planes = cfg->kind == VB_OPT_ADAMW ? 2 : 1;
-  VB_TRY(slot_alloc(total * planes > 0 ? total * planes : 1, true, &o->state));
+  int planes = cfg->kind == VB_OPT_SGD ? 1 : 2;
+  // 8-bit: two planes of `total` bytes, then two planes of total / 256 scales -- counted in floats for the slot
+  const i64 state_floats = q8 ? total / 2 + 2 * (total / 256) : total * planes;
+  o->total8 = q8 ? total : 0;
+  VB_TRY(slot_alloc(state_floats > 0 ? state_floats : 1, true, &o->state));
   float* st; VB_TRY(slot_ptr(o->state, &st));
+  int8_t* st8 = reinterpret_cast<int8_t*>(st);
+  float* scales8 = st + total / 2;
   std::vector<OptChunk> chunks;
   i64 off = 0;
   for (int i = 0; i < n; ++i) {
     float *pw, *pg; VB_TRY(tensor_ptr(&params[i], &pw)); VB_TRY(tensor_ptr(&grads[i], &pg));
     i64 cnt = numel(params[i]);
     for (i64 c = 0; c < cnt; c += kChunk) {
-      OptChunk ch; ch.w = pw + c; ch.g = pg + c; ch.m = st + off + c; ch.v = planes == 2 ? st + total + off + c : nullptr;
+      OptChunk ch; ch.w = pw + c; ch.g = pg + c; ch.ms = ch.vs = nullptr;
+      if (q8) {
+        ch.m = reinterpret_cast<float*>(st8 + off + c); ch.v = reinterpret_cast<float*>(st8 + total + off + c);
+        ch.ms = scales8 + (off + c) / 256; ch.vs = scales8 + total / 256 + (off + c) / 256;
+      } else { ch.m = st + off + c; ch.v = planes == 2 ? st + total + off + c : nullptr; }
       ch.n = (int)(cnt - c < kChunk ? cnt - c : kChunk); ch.param = i;
       chunks.push_back(ch);
     }
-    off += (cnt + 3) & ~i64(3);
+    off += q8 ? ((cnt + 255) & ~i64(255)) : ((cnt + 3) & ~i64(3));
     VB_TRY(slot_retain(params[i].slot)); o->retained.push_back(params[i].slot);
     VB_TRY(slot_retain(grads[i].slot)); o->retained.push_back(grads[i].slot);
   }
@@ -154,13 +167,31 @@ int vb_opt_state(int id, vb_slot* state, int64_t* state_numel, uint32_t* step) {
   if (step) *step = o->t;
   return VB_OK;
 }
+int vb_opt_state8(int id, int param, int8_t* m8, float* m_scales, int8_t* v8, float* v_scales) {
+  Opt* o; VB_TRY(get_opt(id, &o));
+  VB_CHECK(o->cfg.kind == VB_OPT_ADAMW8BIT, "not an 8-bit optimizer");
+  VB_CHECK(param >= 0 && param < o->nparams && m8 && m_scales && v8 && v_scales, "bad arguments");
+  float* st; VB_TRY(slot_ptr(o->state, &st));
+  const int8_t* st8 = reinterpret_cast<const int8_t*>(st);
+  const float* sc = st + o->total8 / 2;
+  const i64 off = o->off8[param], n = o->numel8[param], nb = (n + 255) / 256;
+  cudaStream_t s = ctx().stream;
+  if (n > 0) {
+    VB_CUDA(cudaMemcpyAsync(m8, st8 + off, (size_t)n, cudaMemcpyDeviceToHost, s));
+    VB_CUDA(cudaMemcpyAsync(v8, st8 + o->total8 + off, (size_t)n, cudaMemcpyDeviceToHost, s));
+    VB_CUDA(cudaMemcpyAsync(m_scales, sc + off / 256, (size_t)nb * sizeof(float), cudaMemcpyDeviceToHost, s));
+    VB_CUDA(cudaMemcpyAsync(v_scales, sc + o->total8 / 256 + off / 256, (size_t)nb * sizeof(float), cudaMemcpyDeviceToHost, s));
+  }
+  VB_CUDA(cudaStreamSynchronize(s));
+  return VB_OK;
+}
 int vb_opt_set_step(int id, uint32_t step) { Opt* o; VB_TRY(get_opt(id, &o)); o->t = step; return VB_OK; }
 int vb_opt_set_lr(int id, float lr) { Opt* o; VB_TRY(get_opt(id, &o)); o->cfg.lr = lr; return VB_OK; }
 
 int vb_opt_step(int id, const uint8_t* active, float max_norm, float grad_scale, float* total_norm) {
   Opt* o; VB_TRY(get_opt(id, &o));
   const vb_opt_config& c = o->cfg;
-  if (c.kind == VB_OPT_ADAMW) o->t += 1;
+  if (c.kind != VB_OPT_SGD) o->t += 1;
   const uint8_t* d_active = nullptr;
   if (active && o->nparams > 0) {
     VB_CUDA(cudaMemcpyAsync(o->d_active, active, (size_t)o->nparams, cudaMemcpyHostToDevice, ctx().stream));
@@ -173,7 +204,7 @@ int vb_opt_step(int id, const uint8_t* active, float max_norm, float grad_scale,
     VB_TRY(launch_sum_partials((const float*)o->d_partials, o->nchunks, d_normsq));
   }
   float bc1 = 1.0f, bc2 = 1.0f;
-  if (c.kind == VB_OPT_ADAMW) { bc1 = 1.0f - powi(c.beta1, (int)o->t); bc2 = 1.0f - powi(c.beta2, (int)o->t); }
+  if (c.kind != VB_OPT_SGD) { bc1 = 1.0f - powi(c.beta1, (int)o->t); bc2 = 1.0f - powi(c.beta2, (int)o->t); }
   VB_TRY(launch_opt_multi((const OptChunk*)o->d_chunks, o->nchunks, d_active, c.kind, d_normsq, max_norm, grad_scale,
                           c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.momentum, bc1, bc2));
   if (total_norm) {

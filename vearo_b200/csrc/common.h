@@ -158,7 +158,8 @@ int launch_mask_is_causal(const float* mask, i64 s, i64 row_stride, int* d_flag)
 int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 sk, float scale, bool causal, i64 sq);
 
 // optim.cu
-struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param; };
+// (8-bit AdamW: m and v point at int8 values, ms and vs at the scales of the chunk's 256-element blocks)
+struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param; float* ms; float* vs; };
 int launch_adamw_single(float* w, const float* g, float* m, float* v, i64 n, float lr, float b1, float b2, float eps, float wd,
                         float bc1, float bc2);
 int launch_sgd_single(float* w, const float* g, float* vel, i64 n, float lr, float mu, float wd);

@@ -92,11 +92,10 @@ using LeafKey = uint64_t;
 inline LeafKey leaf_key(const Tensor& t) { return ((uint64_t)t.slot() << 40) ^ (uint64_t)t.desc().offset; }
 thread_local std::unordered_map<LeafKey, Tensor> t_grads;
 
-struct Sinks {
-  std::unordered_map<uint64_t, int> index;      // leaf_key -> parameter index
-  std::vector<Tensor> sinks;
-  void (*on_ready)(int, void*) = nullptr; void* user = nullptr;
-};
+// Gradient sinks of every live optimizer (several may coexist, each over its own parameters; a parameter given to two
+// optimizers belongs to the one registered last).
+struct SinkEntry { Tensor sink; int idx = 0; void (*on_ready)(int, void*) = nullptr; void* user = nullptr; };
+struct Sinks { std::unordered_map<uint64_t, SinkEntry> index; };      // leaf_key -> sink, index within its optimizer, callback
 thread_local Sinks t_sinks;
 
 i64 pack(uint32_t gen, uint32_t idx) { return ((i64)gen << 32) | idx; }
@@ -143,11 +142,11 @@ void reset_active_tape() { t_tape.nodes.clear(); t_tape.generation++; }
 void zero_gradients() { t_grads.clear(); }
 size_t tape_len() { return t_tape.nodes.size(); }
 void register_grad_sinks(const std::vector<Tensor>& params, const std::vector<Tensor>& sinks, void (*on_ready)(int, void*), void* user) {
-  t_sinks = Sinks();
-  for (size_t i = 0; i < params.size(); ++i) t_sinks.index[leaf_key(params[i])] = (int)i;
-  t_sinks.sinks = sinks; t_sinks.on_ready = on_ready; t_sinks.user = user;
+  for (size_t i = 0; i < params.size(); ++i) t_sinks.index[leaf_key(params[i])] = SinkEntry{sinks[i], (int)i, on_ready, user};
 }
-void clear_grad_sinks(void* user) { if (t_sinks.user == user) t_sinks = Sinks(); }
+void clear_grad_sinks(void* user) {
+  for (auto it = t_sinks.index.begin(); it != t_sinks.index.end();) { if (it->second.user == user) it = t_sinks.index.erase(it); else ++it; }
+}
 }  // namespace autograd
 
 // ---- ops ---------------------------------------------------------------------------------------
@@ -312,12 +311,12 @@ void publish_leaf(const Node& leaf, Tensor& grad) {
   LeafKey key = leaf_key(leaf.leaf);
   auto it = t_sinks.index.find(key);
   if (it != t_sinks.index.end()) {
-    const Tensor& sink = t_sinks.sinks[it->second];
+    const Tensor& sink = it->second.sink;
     if (sink.numel() != grad.numel()) throw Error("gradient sink size mismatch");
     const bool in_place = grad.slot() == sink.slot() && grad.desc().offset == sink.desc().offset;      // the producer wrote into the sink
     if (!in_place) check(vb_copy(&sink.desc(), &grad.desc()), "copy into gradient buffer");
     t_grads[key] = sink;
-    if (t_sinks.on_ready) t_sinks.on_ready(it->second, t_sinks.user);
+    if (it->second.on_ready) it->second.on_ready(it->second.idx, it->second.user);
   } else t_grads[key] = grad;
 }
 }  // namespace
@@ -433,7 +432,7 @@ void Tensor::backward() const {
           if (id < 0 || nodes[id].op != Op::Leaf || first_use[id] != ni || gm[id].defined()) return nullptr;
           auto it = t_sinks.index.find(leaf_key(nodes[id].leaf));
           if (it == t_sinks.index.end()) return nullptr;
-          const Tensor& s = t_sinks.sinks[it->second];
+          const Tensor& s = it->second.sink;
           return (s.is_contiguous() && s.numel() == nodes[id].leaf.numel()) ? &s : nullptr;
         };
         const Tensor* ws = need_w ? sink_of(node.inputs[1]) : nullptr;

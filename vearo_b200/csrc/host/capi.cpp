@@ -111,6 +111,13 @@ static int make_opt(const vb_opt_config& cfg, const int* params, int n, int dp) 
 int vh_adamw_new(const int* params, int n, float lr, float b1, float b2, float eps, float wd, int data_parallel) {
   VH_TRY(vb_opt_config c{VB_OPT_ADAMW, lr, b1, b2, eps, wd, 0.0f}; return make_opt(c, params, n, data_parallel));
 }
+// AdamW8bit::new (vearo-optim/src/lib.rs:225-253): block-wise int8 moments, blocks of 256
+int vh_adamw8bit_new(const int* params, int n, float lr, float b1, float b2, float eps, float wd, int data_parallel) {
+  VH_TRY(vb_opt_config c{VB_OPT_ADAMW8BIT, lr, b1, b2, eps, wd, 0.0f}; return make_opt(c, params, n, data_parallel));
+}
+int vh_opt_state8(int o, int param, int8_t* m8, float* ms, int8_t* v8, float* vs) {
+  VH_TRY(if (vb_opt_state8(opt(o).handle(), param, m8, ms, v8, vs) != 0) throw Error(vb_last_error()); return 0);
+}
 int vh_sgd_new(const int* params, int n, float lr, float momentum, float wd, int data_parallel) {
   VH_TRY(vb_opt_config c{VB_OPT_SGD, lr, 0.0f, 0.0f, 0.0f, wd, momentum}; return make_opt(c, params, n, data_parallel));
 }

@@ -102,7 +102,7 @@ size_t tape_len();
 // `on_ready(index)` fires — which is what lets the data-parallel reducer start a bucket's
 // allreduce while the backward pass is still running.
 void register_grad_sinks(const std::vector<Tensor>& params, const std::vector<Tensor>& sinks, void (*on_ready)(int, void*), void* user);
-void clear_grad_sinks(void* user);   // no-op unless `user` registered the current sinks
+void clear_grad_sinks(void* user);   // removes the sinks `user` registered
 }  // namespace autograd
 
 // ---- optimizers (vearo-optim/src/lib.rs) -----------------------------------------------------
@@ -122,6 +122,7 @@ class Optimizer {
   // the flat state array (m then v, or the velocity).  The reference's optimizers have no save of their own.
   void save_state(const std::string& path) const;
   void load_state(const std::string& path);
+  int handle() const { return opt_; }          // the library's optimizer handle (vb_opt_*)
  private:
   void finish_reduce();
   static void on_ready(int idx, void* self);

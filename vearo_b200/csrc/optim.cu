@@ -61,6 +61,100 @@ __device__ __forceinline__ void update_range(float* __restrict__ w, const float*
   }
 }
 
+// ---- AdamW with 8-bit block-wise state (crates/vearo-optim/src/lib.rs:137-303) ----------------------------------
+// m and v live as int8 with one f32 scale per 256 elements of a parameter (scale = block maximum / 127).  A step
+// dequantizes (q * scale), applies the AdamW update above, and requantizes: q = round-half-away(x * (127 / max)),
+// clamped to [-127, 127]; a block whose maximum is 0 stores zeros and scale 0.  One warp per block: lane l owns
+// elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum is a warp shuffle, nothing is staged.  Algorithmic bytes
+// per element: 16 (read g, w, m, v; write w, m, v) + 16 per block of scales, against 28 for the f32 state.
+// The arithmetic is written with explicit single-rounding intrinsics (no fused multiply-add): an update that differs
+// in the last bit from the reference's can land on the other side of a rounding boundary of the quantizer.
+__device__ __forceinline__ void adamw_elem_exact(float& w, float g, float& m, float& v, const Hyper& h) {
+  m = __fadd_rn(__fmul_rn(h.b1, m), __fmul_rn(__fsub_rn(1.0f, h.b1), g));
+  v = __fadd_rn(__fmul_rn(h.b2, v), __fmul_rn(__fmul_rn(__fsub_rn(1.0f, h.b2), g), g));
+  const float mh = __fdiv_rn(m, h.bc1), vh = __fdiv_rn(v, h.bc2);
+  w = __fsub_rn(w, __fmul_rn(__fmul_rn(h.lr, h.wd), w));
+  w = __fsub_rn(w, __fdiv_rn(__fmul_rn(h.lr, mh), __fadd_rn(__fsqrt_rn(vh), h.eps)));
+}
+__device__ __forceinline__ float wmax32(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+__device__ __forceinline__ int quant8(float x, float inv) {
+  float q = roundf(__fmul_rn(x, inv));
+  q = fminf(fmaxf(q, -127.0f), 127.0f);
+  return (int)q;
+}
+__global__ void __launch_bounds__(256, 4) k_opt_adamw8(const OptChunk* __restrict__ chunks, const uint8_t* __restrict__ active,
+                                                    const float* __restrict__ normsq, float max_norm, float grad_scale, Hyper h) {
+  const OptChunk c = chunks[blockIdx.x];
+  if (active && !active[c.param]) return;
+  const float gs = clip_scale(normsq, max_norm, grad_scale);
+  int8_t* __restrict__ m8 = reinterpret_cast<int8_t*>(c.m);
+  int8_t* __restrict__ v8 = reinterpret_cast<int8_t*>(c.v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = (c.n + 255) >> 8;
+  const bool vec = ((reinterpret_cast<uintptr_t>(c.w) | reinterpret_cast<uintptr_t>(c.g)) & 15) == 0;
+  for (int b = warp; b < nblk; b += 8) {
+    const int base = b << 8, cnt = c.n - base < 256 ? c.n - base : 256;
+    const float sm = c.ms[b], sv = c.vs[b];
+    float w[8], m[8], v[8];
+    bool ok[8];
+    if (vec && cnt == 256) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int e = base + hf * 128 + lane * 4;
+        const float4 ww = *reinterpret_cast<const float4*>(c.w + e), gg = *reinterpret_cast<const float4*>(c.g + e);
+        const char4 mq = *reinterpret_cast<const char4*>(m8 + e), vq = *reinterpret_cast<const char4*>(v8 + e);
+        const float wv[4] = {ww.x, ww.y, ww.z, ww.w}, gv[4] = {gg.x, gg.y, gg.z, gg.w};
+        const signed char mv[4] = {mq.x, mq.y, mq.z, mq.w}, vv[4] = {vq.x, vq.y, vq.z, vq.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int k = hf * 4 + t;
+          w[k] = wv[t]; m[k] = __fmul_rn((float)mv[t], sm); v[k] = __fmul_rn((float)vv[t], sv); ok[k] = true;
+          adamw_elem_exact(w[k], __fmul_rn(gv[t], gs), m[k], v[k], h);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int o = (k >> 2) * 128 + lane * 4 + (k & 3);
+        ok[k] = o < cnt;
+        w[k] = 0.0f; m[k] = 0.0f; v[k] = 0.0f;
+        if (ok[k]) {
+          w[k] = c.w[base + o]; m[k] = __fmul_rn((float)m8[base + o], sm); v[k] = __fmul_rn((float)v8[base + o], sv);
+          adamw_elem_exact(w[k], __fmul_rn(c.g[base + o], gs), m[k], v[k], h);
+        }
+      }
+    }
+    float mx_m = 0.0f, mx_v = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) if (ok[k]) { mx_m = fmaxf(mx_m, fabsf(m[k])); mx_v = fmaxf(mx_v, fabsf(v[k])); }
+    mx_m = wmax32(mx_m); mx_v = wmax32(mx_v);
+    const float inv_m = mx_m > 0.0f ? __fdiv_rn(127.0f, mx_m) : 0.0f, inv_v = mx_v > 0.0f ? __fdiv_rn(127.0f, mx_v) : 0.0f;
+    int qm[8], qv[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { qm[k] = mx_m > 0.0f ? quant8(m[k], inv_m) : 0; qv[k] = mx_v > 0.0f ? quant8(v[k], inv_v) : 0; }
+    if (vec && cnt == 256) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int e = base + hf * 128 + lane * 4;
+        *reinterpret_cast<float4*>(c.w + e) = make_float4(w[hf * 4], w[hf * 4 + 1], w[hf * 4 + 2], w[hf * 4 + 3]);
+        *reinterpret_cast<char4*>(m8 + e) = make_char4((signed char)qm[hf * 4], (signed char)qm[hf * 4 + 1], (signed char)qm[hf * 4 + 2], (signed char)qm[hf * 4 + 3]);
+        *reinterpret_cast<char4*>(v8 + e) = make_char4((signed char)qv[hf * 4], (signed char)qv[hf * 4 + 1], (signed char)qv[hf * 4 + 2], (signed char)qv[hf * 4 + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int o = (k >> 2) * 128 + lane * 4 + (k & 3);
+        if (ok[k]) { c.w[base + o] = w[k]; m8[base + o] = (int8_t)qm[k]; v8[base + o] = (int8_t)qv[k]; }
+      }
+    }
+    if (lane == 0) { c.ms[b] = __fdiv_rn(mx_m, 127.0f); c.vs[b] = __fdiv_rn(mx_v, 127.0f); }
+  }
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(256) k_opt_multi(const OptChunk* __restrict__ chunks, const uint8_t* __restrict__ active,
                                                    const float* __restrict__ normsq, float max_norm, float grad_scale, Hyper h) {
@@ -73,9 +167,11 @@ int launch_opt_multi(const OptChunk* chunks, int nchunks, const uint8_t* active,
                      float max_norm, float grad_scale, float lr, float b1, float b2, float eps, float wd, float mu,
                      float bc1, float bc2) {
   if (nchunks <= 0) return VB_OK;
-  ProfScope prof(kind == VB_OPT_ADAMW ? "adamw" : "sgd", (kind == VB_OPT_ADAMW ? 28.0 : 20.0) * 16384.0 * (double)nchunks);
+  ProfScope prof(kind == VB_OPT_ADAMW ? "adamw" : (kind == VB_OPT_ADAMW8BIT ? "adamw8bit" : "sgd"),
+                 (kind == VB_OPT_ADAMW ? 28.0 : (kind == VB_OPT_ADAMW8BIT ? 16.0625 : 20.0)) * 16384.0 * (double)nchunks);
   Hyper h{lr, b1, b2, eps, wd, mu, bc1, bc2};
-  if (kind == VB_OPT_ADAMW) k_opt_multi<0><<<nchunks, 256, 0, ctx().stream>>>(chunks, active, normsq, max_norm, grad_scale, h);
+  if (kind == VB_OPT_ADAMW8BIT) k_opt_adamw8<<<nchunks, 256, 0, ctx().stream>>>(chunks, active, normsq, max_norm, grad_scale, h);
+  else if (kind == VB_OPT_ADAMW) k_opt_multi<0><<<nchunks, 256, 0, ctx().stream>>>(chunks, active, normsq, max_norm, grad_scale, h);
   else k_opt_multi<1><<<nchunks, 256, 0, ctx().stream>>>(chunks, active, normsq, max_norm, grad_scale, h);
   VB_LAUNCH_CHECK();
   return VB_OK;

@@ -9,6 +9,7 @@
   python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
   python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
   python -m vearo_b200.kernel_cases adamw         64 Mi parameters
+  python -m vearo_b200.kernel_cases adamw8bit     64 Mi parameters, int8 block-wise moments
 A second argument gives the repetition count (default 3); `time` instead prints the average device
 time per repetition over 20 repetitions (CUDA events through the library's profiling hooks are not
 used here: the loop is synchronised on both sides and timed on the host).
@@ -65,9 +66,9 @@ def build(case):
             vb.zero_gradients(); vb.reset_active_tape()
             l.cross_entropy(t).backward()
         return run
-    if case == "adamw":
+    if case in ("adamw", "adamw8bit"):
         w = T(f(64 << 20), True)
-        opt = vb.AdamW([w], 1e-3)
+        opt = vb.AdamW([w], 1e-3) if case == "adamw" else vb.AdamW8bit([w], 1e-3)
         g = T(f(64 << 20))
 
         def run():
