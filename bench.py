@@ -225,6 +225,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt-small", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--checkpoint-blocks", action="store_true", help="GPT workloads: every transformer block under activation checkpointing")
+    ap.add_argument("--adamw8bit", action="store_true", help="GPT workloads: AdamW with block-wise int8 moments")
     ap.add_argument("--profile-steps", type=int, default=2)
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
@@ -279,7 +281,9 @@ def main():
         T, V = cfg["T"], cfg["vocab"]
         model = vb.SimpleGPT(V, T, cfg["d"], cfg["heads"], cfg["layers"], cfg["ff"])
         model.load(ms.gpt_params(V, T, cfg["d"], cfg["layers"], cfg["ff"], seed=0))      # identical on every rank
-        opt = vb.AdamW(model.parameters(), cfg["lr"], 0.9, 0.999, 1e-8, cfg["wd"], data_parallel=world > 1)
+        if args.checkpoint_blocks: model.set_checkpointing(True)
+        Opt = vb.AdamW8bit if args.adamw8bit else vb.AdamW
+        opt = Opt(model.parameters(), cfg["lr"], 0.9, 0.999, 1e-8, cfg["wd"], data_parallel=world > 1)
         batches = [ms.gpt_batch(V, B, T, seed=1000 * rank + i) for i in range(4)]      # per-rank data
         units_per_rank, unit = B * T, "tokens/s"
     n_params = sum(int(np.prod(p.shape)) for p in model.parameters())
@@ -405,7 +409,8 @@ def main():
     else:
         config = {"workload": args.workload, "n_layer": cfg["layers"], "n_head": cfg["heads"], "d_model": cfg["d"], "d_ff": cfg["ff"],
                   "vocab": V, "seq_len": T, "micro_batch_per_gpu": B, "global_batch": world * B, "params": n_params,
-                  "optimizer": "AdamW lr %g wd %g, clip %g" % (cfg["lr"], cfg["wd"], cfg["clip"]), "parallelism": "dp%d" % world,
+                  "optimizer": "%s lr %g wd %g, clip %g" % ("AdamW8bit" if args.adamw8bit else "AdamW", cfg["lr"], cfg["wd"], cfg["clip"]),
+                  "activation_checkpointing": bool(args.checkpoint_blocks), "parallelism": "dp%d" % world,
                   "matmul_precision": "fp32 (3xTF32 on tensor cores where the tensor-core kernel applies, exact fp32 FMA otherwise)",
                   "l2": "working set per step (weights, activations, optimizer state: several GB) exceeds the 126 MB L2 many times over"}
         h2d = int(world * 2 * B * T * 4)
@@ -418,6 +423,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(world * 8)},
         "gpu_launches": int(launches1.value - launches0.value),
+        "device_memory": vb.memory_stats(),
         "clocks": clocks.summary(),
         "roofline": roofline, "kernels": kernels, "gemm_shapes": gemm_shapes, "cpu_baseline": cpu,
         "last_loss": losses[-1] if losses else None,

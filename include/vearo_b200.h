@@ -85,6 +85,8 @@ int vb_slot_numel(vb_slot slot, int64_t* numel);
 /* Live slots and bytes held by them / cached by the arena (memory-regression tests, the
  * counterpart of PEAK_CUDA_MEM_BYTES, vearo-backend-cuda/src/lib.rs:35,73-82). */
 int vb_memory_stats(int64_t* live_slots, int64_t* live_bytes, int64_t* cached_bytes, int64_t* peak_bytes);
+/* Start a new peak measurement from the bytes live now (the reference's peak counter only ever grows). */
+int vb_memory_reset_peak(void);
 
 /* ---- forward ops: one per field of `BackendOps` (vearo-core/src/tensor.rs:1111-1175) ---- */
 int vb_add(const vb_tensor* a, const vb_tensor* b, vb_tensor* out);   /* vearo-backend-cuda lib.rs:832-899 */

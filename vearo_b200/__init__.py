@@ -316,7 +316,36 @@ def clip_grad_norm(params, max_norm):
 
 def cosine_lr(base, min_lr, warmup, total, step): return float(lib().vh_cosine_lr(base, min_lr, warmup, total, step))
 def zero_gradients(): lib().vh_zero_gradients()
-def reset_active_tape(): lib().vh_reset_active_tape()
+
+
+def reset_active_tape():
+    lib().vh_reset_active_tape()
+    del _ckpt_keep[:]          # blocks of tapes that are gone
+
+
+_CKPT_FN = C.CFUNCTYPE(C.c_int, C.c_int, C.c_void_p)
+_ckpt_keep = []
+
+
+def checkpoint(x, fn):
+    """vearo_autograd::checkpoint(x, f): f(x) runs now without recording (its activations are freed as it goes) and once
+    more, recorded, when backward reaches it.  `fn` maps a Tensor to a Tensor."""
+    def call(hin, _user):
+        try:
+            out = fn(Tensor(hin))
+            _ckpt_keep.append(out)      # the handle must outlive this call: the library copies the tensor after it returns
+            return out.h
+        except Exception:               # an exception may not cross the C boundary
+            import traceback
+            traceback.print_exc()
+            return -1
+    cb = _CKPT_FN(call)
+    _ckpt_keep.append(cb)
+    lib().vh_checkpoint.argtypes = [C.c_int, _CKPT_FN, C.c_void_p]
+    return Tensor(_chk(lib().vh_checkpoint(x.h, cb, None)))
+
+
+def is_recomputing(): return bool(lib().vh_is_recomputing())
 def set_training(t): lib().vh_set_training(int(t))
 def set_autograd_enabled(e): lib().vh_set_autograd_enabled(int(e))
 def sync(): vb_check(lib().vb_sync(), "vb_sync")
@@ -349,6 +378,10 @@ class Model:
         self._params = [Tensor(lib().vh_model_param(self.m, i)) for i in range(n)]
 
     def parameters(self): return list(self._params)
+
+    def set_checkpointing(self, on=True):
+        """SimpleGPT only: wrap every transformer block in activation checkpointing."""
+        _chk(lib().vh_gpt_set_checkpointing(self.m, int(on)))
 
     def load(self, arrays):
         assert len(arrays) == len(self._params), (len(arrays), len(self._params))

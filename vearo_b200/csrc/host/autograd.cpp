@@ -13,6 +13,7 @@
 // published the moment its last contribution has arrived (its earliest consumer on the tape),
 // which is what allows gradient exchange to overlap the rest of the walk.
 #include "vearo_host.h"
+#include <functional>
 #include <algorithm>
 #include <cmath>
 #include <unordered_map>
@@ -74,7 +75,7 @@ void Tensor::write_f32(const float* data) const {
 // ---- tape ------------------------------------------------------------------------------------
 namespace {
 enum class Op { Add, Sub, Mul, Div, Matmul, Reshape, Transpose, Permute, Relu, Gelu, Softmax, LayerNorm, Embedding,
-                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, BnReluPool, PackRows, FusedAttentionPacked, Leaf };
+                CrossEntropy, Sum, Mean, Conv2d, MaxPool2d, AvgPool2d, BatchNorm, FusedAttention, Linear, BnReluPool, PackRows, FusedAttentionPacked, Checkpoint, Leaf };
 struct Node {
   int id = 0; Op op = Op::Leaf;
   std::vector<int> inputs;
@@ -83,10 +84,11 @@ struct Node {
   std::vector<i64> axes;
   Tensor extra;             // attention probabilities / cross-entropy row statistics
   Tensor leaf;              // for Leaf nodes: the tensor itself
+  std::function<Tensor(const Tensor&)> fn;      // Checkpoint nodes: the block to run again during backward
 };
 struct Tape { std::vector<Node> nodes; uint32_t generation = 0; };
 thread_local Tape t_tape;
-thread_local bool t_enabled = true, t_training = true;
+thread_local bool t_enabled = true, t_training = true, t_recomputing = false;
 // A leaf is identified by where it lives: slot and offset (several parameters may be views of one slot).
 using LeafKey = uint64_t;
 inline LeafKey leaf_key(const Tensor& t) { return ((uint64_t)t.slot() << 40) ^ (uint64_t)t.desc().offset; }
@@ -208,12 +210,16 @@ Tensor Tensor::avgpool2d(int k, int s, int p) const {
   return out;
 }
 Tensor Tensor::batchnorm(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const {
+  // under recomputation (a checkpointed block run again during backward) the running statistics must not advance a second time
+  // (vearo-nn/src/lib.rs:437-454 passes detached copies); momentum 0 leaves them bit-for-bit as they are
+  if (t_recomputing) momentum = 0.0f;
   VB_OUT1(vb_batchnorm(&d_, &gamma.d_, &beta.d_, &rm.d_, &rv.d_, training, momentum, eps, &o_), "batchnorm");
   if (Node* n = record(Op::BatchNorm, {this, &gamma, &beta, &rm, &rv}, out)) { n->a0 = training; n->f0 = eps; }
   return out;
 }
 Tensor Tensor::bn_relu_maxpool(const Tensor& gamma, const Tensor& beta, const Tensor& rm, const Tensor& rv, bool training, float momentum, float eps) const {
   vb_tensor o_, s_;
+  if (t_recomputing) momentum = 0.0f;
   check(vb_bn_relu_maxpool(&d_, &gamma.d_, &beta.d_, &rm.d_, &rv.d_, training, momentum, eps, &o_, &s_), "bn_relu_maxpool");
   Tensor out = Tensor::adopt(o_), stats = Tensor::adopt(s_);
   if (Node* n = record(Op::BnReluPool, {this, &gamma, &beta}, out)) { n->a0 = training; n->extra = stats; }
@@ -307,9 +313,27 @@ Tensor expand_reduce_grad(const Tensor& go, const std::vector<i64>& in_shape, in
 }
 struct Restore { ~Restore() { t_enabled = true; } };
 
-void publish_leaf(const Node& leaf, Tensor& grad) {
+// Where a nested (checkpoint) backward delivers the gradient of the block's input instead of publishing it as a leaf gradient.
+struct NestedInput { bool active = false; LeafKey key = 0; Tensor* gx = nullptr; };
+
+void publish_leaf(const Node& leaf, Tensor& grad, const NestedInput& nested) {
   LeafKey key = leaf_key(leaf.leaf);
+  if (nested.active && key == nested.key) {
+    *nested.gx = nested.gx->defined() ? nested.gx->add(grad) : grad;
+    return;
+  }
   auto it = t_sinks.index.find(key);
+  auto have = t_grads.find(key);
+  if (have != t_grads.end()) {
+    // a second contribution within one backward pass (a parameter used by several checkpointed blocks, or inside and outside
+    // one): summed, as the reference merges its checkpoint gradients (lib.rs:717-726, 781-791)
+    Tensor& ex = have->second;
+    if (ex.is_contiguous() && ex.shape() == grad.shape() && (it != t_sinks.index.end() || ex.storage_unique()))
+      check(vb_accumulate(&ex.desc(), &grad.desc()), "accumulate");
+    else ex = ex.add(grad);
+    if (it != t_sinks.index.end() && it->second.on_ready) it->second.on_ready(-1 - it->second.idx, it->second.user);
+    return;
+  }
   if (it != t_sinks.index.end()) {
     const Tensor& sink = it->second.sink;
     if (sink.numel() != grad.numel()) throw Error("gradient sink size mismatch");
@@ -321,11 +345,25 @@ void publish_leaf(const Node& leaf, Tensor& grad) {
 }
 }  // namespace
 
+namespace { void run_backward(const Tensor& y, const Tensor& seed, const NestedInput& nested); }
+
 void Tensor::backward() const {
   if (numel() != 1) throw Error("backward can only be called on scalar tensors");
   t_enabled = false;
   Restore restore;
-  int out_idx = live_index(*this);
+  if (live_index(*this) < 0) return;
+  float one = 1.0f;
+  Tensor seed = Tensor::from_f32(&one, shape());
+  t_grads.clear();
+  run_backward(*this, seed, NestedInput{});
+  t_tape.generation++;
+}
+
+namespace {
+// backward_impl (vearo-autograd/src/lib.rs:429-792) over the nodes recorded since the last reset; `seed` is the gradient of y.
+// Called once per Tensor::backward, and once more, on a tape of its own, for every checkpointed block met on the way.
+void run_backward(const Tensor& y, const Tensor& seed, const NestedInput& nested) {
+  int out_idx = live_index(y);
   if (out_idx < 0) return;
   std::vector<Node> nodes = std::move(t_tape.nodes);
   t_tape.nodes.clear();
@@ -334,8 +372,7 @@ void Tensor::backward() const {
   std::vector<int> first_use(N, N);
   for (const Node& n : nodes) for (int in : n.inputs) if (in >= 0 && n.id < first_use[in]) first_use[in] = n.id;
   std::vector<Tensor> gm(N);
-  { float one = 1.0f; gm[out_idx] = Tensor::from_f32(&one, shape()); }
-  t_grads.clear();
+  gm[out_idx] = seed;
   for (int ni = N - 1; ni >= 0; --ni) {
     Node& node = nodes[ni];
     if (!gm[ni].defined()) { node.saved.clear(); node.extra = Tensor(); continue; }
@@ -432,6 +469,7 @@ void Tensor::backward() const {
           if (id < 0 || nodes[id].op != Op::Leaf || first_use[id] != ni || gm[id].defined()) return nullptr;
           auto it = t_sinks.index.find(leaf_key(nodes[id].leaf));
           if (it == t_sinks.index.end()) return nullptr;
+          if (t_grads.count(leaf_key(nodes[id].leaf))) return nullptr;      // already holds a contribution of this pass: must be added to
           const Tensor& s = it->second.sink;
           return (s.is_contiguous() && s.numel() == nodes[id].leaf.numel()) ? &s : nullptr;
         };
@@ -449,6 +487,25 @@ void Tensor::backward() const {
         if (sv.size() > 2) gin.push_back(!need_b ? Tensor() : (bs ? *bs : Tensor::adopt(gb)));
         break;
       }
+      case Op::Checkpoint: {
+        // Run the block again, recording this time, and walk its tape with `go` as the seed (lib.rs:649-730).  Stateful
+        // layers see is_recomputing() and leave their state alone; parameter gradients are published from the inner walk.
+        const Tensor x = sv[0];
+        const i64 x_token = x.node_id();
+        t_tape.nodes.clear(); t_tape.generation++;
+        t_enabled = true; t_recomputing = true;
+        Tensor y_new;
+        try { y_new = node.fn(x); } catch (...) { t_enabled = false; t_recomputing = false; throw; }
+        t_enabled = false; t_recomputing = false;
+        Tensor gx;
+        NestedInput inner; inner.active = true; inner.key = leaf_key(x); inner.gx = &gx;
+        run_backward(y_new, go, inner);
+        t_tape.nodes.clear(); t_tape.generation++;
+        x.set_node_id(x_token);
+        gin = {gx};
+        node.fn = nullptr;
+        break;
+      }
       case Op::Leaf: break;
     }
     go = Tensor();
@@ -463,11 +520,30 @@ void Tensor::backward() const {
     gin.clear();
     // leaves whose last contribution this was: publish now
     for (int id : node.inputs)
-      if (id >= 0 && nodes[id].op == Op::Leaf && first_use[id] == ni && gm[id].defined()) { publish_leaf(nodes[id], gm[id]); gm[id] = Tensor(); }
+      if (id >= 0 && nodes[id].op == Op::Leaf && first_use[id] == ni && gm[id].defined()) { publish_leaf(nodes[id], gm[id], nested); gm[id] = Tensor(); }
     node.saved.clear(); node.extra = Tensor();
   }
-  t_tape.generation++;
 }
+}  // namespace
+
+namespace autograd {
+// checkpoint (vearo-autograd/src/lib.rs:897-959): run the block without recording -- its activations are freed as it goes -- keep
+// only the input, and record one node that re-runs the block when the backward walk reaches it.
+Tensor checkpoint(const Tensor& x, std::function<Tensor(const Tensor&)> f) {
+  const bool was = t_enabled;
+  t_enabled = false;
+  Tensor out;
+  try { out = f(x); } catch (...) { t_enabled = was; throw; }
+  t_enabled = was;
+  if (was && (x.requires_grad() || out.requires_grad())) {
+    out.set_requires_grad(true);
+    Node& n = push(Op::Checkpoint, {&x}, out);
+    n.fn = std::move(f);
+  }
+  return out;
+}
+bool is_recomputing() { return t_recomputing; }
+}  // namespace autograd
 
 bool Tensor::grad(Tensor* out) const {
   auto it = t_grads.find(leaf_key(*this));

@@ -102,6 +102,22 @@ int vh_convnet_running(int m, int stage, int which) {
          return put(which == 0 ? c->stages[stage].rm : c->stages[stage].rv));
 }
 
+// Activation checkpointing.  vh_checkpoint: `fn(x_handle, user)` returns the handle of the block's output (or a negative value on
+// failure); it is called once now, without recording, and once more during backward.  The caller keeps `fn` and `user` alive until then.
+int vh_checkpoint(int x, int (*fn)(int, void*), void* user) {
+  VH_TRY(Tensor out = autograd::checkpoint(at(x), [fn, user](const Tensor& in) {
+           int hin = put(in);
+           int hout = fn(hin, user);
+           if (hout < 0) throw Error("checkpoint callback failed");
+           return at(hout);
+         });
+         return put(out));
+}
+int vh_is_recomputing() { return autograd::is_recomputing() ? 1 : 0; }
+int vh_gpt_set_checkpointing(int m, int on) {
+  VH_TRY(nn::SimpleGPT* g = dynamic_cast<nn::SimpleGPT*>(&model(m)); if (!g) throw Error("not a SimpleGPT"); g->checkpoint_blocks = on != 0; return 0);
+}
+
 // ---- optimizers ----
 static int make_opt(const vb_opt_config& cfg, const int* params, int n, int dp) {
   std::vector<Tensor> ps; for (int i = 0; i < n; ++i) ps.push_back(at(params[i]));

@@ -94,7 +94,10 @@ Tensor SimpleGPT::loss(const Tensor& ids, const Tensor& targets) {
     cached_b_ = b; cached_s_ = t;
   }
   Tensor h = ids.embedding(tok).add(pos_ids_.embedding(pos));
-  for (const auto& blk : blocks) h = blk.forward(h, &mask_);
+  for (const auto& blk : blocks) {
+    if (checkpoint_blocks) { const TransformerBlock* bp = &blk; Tensor m = mask_; h = autograd::checkpoint(h, [bp, m](const Tensor& in) { return bp->forward(in, &m); }); }
+    else h = blk.forward(h, &mask_);
+  }
   Tensor logits = lm_head.forward(ln_f.forward(h).reshape({b * t, n_embd}));
   return logits.cross_entropy(targets.reshape({b * t}));
 }
@@ -191,6 +194,10 @@ Optimizer::~Optimizer() {
 }
 void Optimizer::on_ready(int idx, void* self) {
   Optimizer* o = (Optimizer*)self;
+  if (idx < 0) {      // a further contribution to parameter -1 - idx was added to its sink after the first was published
+    if (o->world_ > 1) throw Error("a parameter that gets gradient from several checkpointed regions is not supported under data parallel: its bucket may already have been reduced");
+    return;
+  }
   if (o->ready_[idx]) return;
   o->ready_[idx] = 1;
   if (o->world_ <= 1) return;

@@ -6,6 +6,7 @@
 // the same text).  Everything below talks to the device only through include/vearo_b200.h.
 #pragma once
 #include <cstdint>
+#include <functional>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -97,6 +98,10 @@ void set_training(bool t); bool is_training();
 void reset_active_tape();      // lib.rs:831
 void zero_gradients();         // lib.rs:836
 size_t tape_len();
+// Activation checkpointing (lib.rs:897-959): runs f(x) without recording and keeps only x; the backward walk runs f again,
+// recording, and differentiates that.  While it does, is_recomputing() is true and stateful layers leave their state alone.
+Tensor checkpoint(const Tensor& x, std::function<Tensor(const Tensor&)> f);
+bool is_recomputing();
 // Persistent gradient buffers: when a leaf with a registered sink gets its final gradient, the
 // gradient is written into the sink (a view of a flat arena) instead of a fresh tensor, and
 // `on_ready(index)` fires — which is what lets the data-parallel reducer start a bucket's
@@ -203,6 +208,7 @@ struct Model {
 struct SimpleGPT : Model {
   Tensor tok, pos; std::vector<TransformerBlock> blocks; LayerNorm ln_f; Linear lm_head; i64 n_embd;
   Tensor pos_ids_, mask_; i64 cached_b_ = -1, cached_s_ = -1;     // built on the device once per shape
+  bool checkpoint_blocks = false;     // wrap every transformer block in autograd::checkpoint (activations of one block live at a time)
   SimpleGPT(i64 vocab, i64 max_seq, i64 n_embd, i64 n_head, i64 n_layer, i64 mlp_dim);
   std::vector<Tensor> parameters() const override;
   Tensor loss(const Tensor& ids, const Tensor& targets) override;

@@ -263,5 +263,6 @@ int vb_memory_stats(int64_t* live_slots, int64_t* live_bytes, int64_t* cached_by
   if (peak_bytes) *peak_bytes = (int64_t)g_arena.peak;
   return VB_OK;
 }
+int vb_memory_reset_peak(void) { g_arena.peak = g_arena.live; return VB_OK; }
 
 }  // extern "C"
