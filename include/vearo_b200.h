@@ -109,6 +109,10 @@ int vb_embedding_backward(const vb_tensor* ids, const vb_tensor* weight, const v
 /* loss is a shape-[1] tensor: mean over rows.  `row_stats` (may be NULL) receives a [B,2] tensor of
  * per-row (max, sum exp) that vb_cross_entropy_backward can reuse to skip its own first pass. */
 int vb_cross_entropy(const vb_tensor* logits, const vb_tensor* targets, vb_tensor* loss, vb_tensor* row_stats); /* lib.rs:1466-1534 */
+/* Forward and backward of the loss in one pass (no counterpart in the reference): returns the loss of vb_cross_entropy and
+ * overwrites the (contiguous) logits with what vb_cross_entropy_backward returns for an upstream gradient of 1.  For callers that
+ * are about to differentiate the loss and need the logits for nothing else; it moves 2 * B * V * 4 bytes instead of 3. */
+int vb_cross_entropy_fused(const vb_tensor* logits_inout, const vb_tensor* targets, vb_tensor* loss);
 int vb_cross_entropy_backward(const vb_tensor* logits, const vb_tensor* targets, const vb_tensor* grad_out,
                               const vb_tensor* row_stats_or_null, vb_tensor* glogits);                   /* lib.rs:1536-1592 */
 int vb_conv2d(const vb_tensor* x, const vb_tensor* w, const vb_tensor* bias, int stride, int padding, vb_tensor* out); /* lib.rs:245-301 */

@@ -288,6 +288,24 @@ def test_cross_entropy(vb, rows, v):
     both(vb, case, guard=False)
 
 
+@pytest.mark.parametrize("rows,v,scale", [(7, 1001, None), (64, 4096, None), (5, 50304, 0.5)])
+def test_cross_entropy_fused_forward_backward(vb, rows, v, scale):
+    """The one-pass form (loss out, logits overwritten with their gradient) against the oracle's two calls; with a loss that
+    is scaled afterwards the upstream gradient is not 1 and the stored gradient is multiplied by it."""
+    x0, w0 = rnd(232, rows, 24, scale=1.0), rnd(233, 24, v, scale=0.8)
+    t0 = np.random.default_rng(234).integers(0, v, rows).astype(np.float32)
+
+    def case(T, m):
+        x, w = T.from_numpy(x0, True), T.from_numpy(w0, True)
+        logits = x.matmul(w)
+        loss = logits.cross_entropy_consuming(T.from_numpy(t0)) if m is not orc else logits.cross_entropy(T.from_numpy(t0))
+        del logits
+        out = loss if scale is None else loss.mul(T.from_numpy(np.array([scale], np.float32)))
+        out.backward()
+        return [loss, x.grad(), w.grad().contiguous()]
+    both(vb, case, guard=False)
+
+
 def test_cross_entropy_stability_and_backward_without_stats(vb):
     import ctypes as C
     loss = vb.Tensor.from_numpy(np.array([[1000.0, -1000.0]], np.float32)).cross_entropy(vb.Tensor.from_numpy(np.array([0.0], np.float32)))

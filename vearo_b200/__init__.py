@@ -197,6 +197,11 @@ class Tensor:
     def layernorm(self, w, b, eps): return Tensor(lib().vh_layernorm(self.h, w.h, b.h, eps))
     def embedding(self, w): return Tensor(lib().vh_embedding(self.h, w.h))
     def cross_entropy(self, t): return Tensor(lib().vh_cross_entropy(self.h, t.h))
+
+    def cross_entropy_consuming(self, t):
+        """cross_entropy for logits that are needed for nothing else: when the loss will be differentiated, one pass returns
+        the loss and leaves the logits' gradient in their place."""
+        return Tensor(lib().vh_cross_entropy_consuming(self.h, t.h))
     def conv2d(self, w, b, stride, padding): return Tensor(lib().vh_conv2d(self.h, w.h, b.h, stride, padding))
     def maxpool2d(self, k, s, p): return Tensor(lib().vh_maxpool2d(self.h, k, s, p))
     def avgpool2d(self, k, s, p): return Tensor(lib().vh_avgpool2d(self.h, k, s, p))

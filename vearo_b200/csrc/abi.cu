@@ -272,6 +272,22 @@ int vb_cross_entropy(const vb_tensor* logits, const vb_tensor* targets, vb_tenso
   if (row_stats) { i64 sd[2] = {B, 2}; VB_TRY(new_output(row_stats, 2, sd)); VB_TRY(slot_ptr(row_stats->slot, &pst)); }
   return launch_cross_entropy(pl, pt, plo, pst, B, V);
 }
+int vb_cross_entropy_fused(const vb_tensor* logits_inout, const vb_tensor* targets, vb_tensor* loss) {
+  VB_CHECK(logits_inout->rank == 2, "Logits must be rank 2 (batch_size, vocab_size)");
+  VB_CHECK(targets->rank == 1, "Targets must be rank 1 (batch_size)");
+  i64 B = logits_inout->dims[0], V = logits_inout->dims[1];
+  VB_CHECK(B > 0, "Batch size must be greater than 0");
+  VB_CHECK(V > 0, "Vocabulary size must be greater than 0");
+  VB_CHECK(targets->dims[0] == B, "Targets shape must match batch size");
+  VB_CHECK(is_contiguous(*logits_inout), "cross_entropy_fused overwrites the logits: they must be contiguous");
+  float* pl; VB_TRY(tensor_ptr(logits_inout, &pl));
+  Temp ht; const float* pt;
+  VB_TRY(contiguous_ptr(targets, &pt, ht));
+  i64 one = 1;
+  VB_TRY(new_output(loss, 1, &one));
+  float* plo; VB_TRY(slot_ptr(loss->slot, &plo));
+  return launch_cross_entropy_fused(pl, pt, plo, B, V);
+}
 int vb_cross_entropy_backward(const vb_tensor* logits, const vb_tensor* targets, const vb_tensor* g,
                               const vb_tensor* row_stats, vb_tensor* gl) {
   VB_CHECK(logits->rank == 2, "Logits must be rank 2 (batch_size, vocab_size)");

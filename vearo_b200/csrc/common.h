@@ -117,6 +117,7 @@ int launch_bn_relu_maxpool_backward(const float* x, const float* gamma, const fl
 int launch_embedding(const float* ids, const float* w, float* out, i64 n, i64 vocab, i64 d);
 int launch_embedding_backward(const float* ids, const float* g, float* gw, i64 n, i64 vocab, i64 d);   // gw pre-zeroed
 int launch_cross_entropy(const float* logits, const float* targets, float* loss, float* stats, i64 rows, i64 v);
+int launch_cross_entropy_fused(float* logits, const float* targets, float* loss, i64 rows, i64 v);
 int launch_cross_entropy_backward(const float* logits, const float* targets, const float* gout, const float* stats,
                                   float* gl, i64 rows, i64 v);
 // conv.cu

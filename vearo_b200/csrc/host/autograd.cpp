@@ -194,6 +194,17 @@ Tensor Tensor::cross_entropy(const Tensor& targets) const {
   if (Node* n = record(Op::CrossEntropy, {this, &targets}, out)) n->extra = stats;
   return out;
 }
+// cross_entropy for a caller that gives the logits up: when the loss is going to be differentiated and nobody else holds the
+// logits, one pass computes the loss and leaves d loss / d logits (for a unit upstream gradient) in their place.
+Tensor Tensor::cross_entropy_consuming(const Tensor& targets) const {
+  const bool fuse = t_enabled && requires_grad() && !targets.requires_grad() && is_contiguous() && live_index(*this) >= 0;
+  if (!fuse) return cross_entropy(targets);
+  vb_tensor o_;
+  check(vb_cross_entropy_fused(&d_, &targets.d_, &o_), "cross_entropy_fused");
+  Tensor out = Tensor::adopt(o_);
+  if (Node* n = record(Op::CrossEntropy, {this, &targets}, out)) n->a1 = 1;      // saved[0] now holds the gradient
+  return out;
+}
 Tensor Tensor::conv2d(const Tensor& w, const Tensor& b, int stride, int padding) const {
   VB_OUT1(vb_conv2d(&d_, &w.d_, &b.d_, stride, padding, &o_), "conv2d");
   if (Node* n = record(Op::Conv2d, {this, &w, &b}, out)) { n->a0 = stride; n->a1 = padding; }
@@ -418,6 +429,11 @@ void run_backward(const Tensor& y, const Tensor& seed, const NestedInput& nested
       }
       case Op::Embedding: { vb_tensor o; check(vb_embedding_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), &o), "embedding_backward"); gin = {Tensor(), Tensor::adopt(o)}; break; }
       case Op::CrossEntropy: {
+        if (node.a1) {      // fused forward: the gradient for a unit seed is already in place of the logits
+          const bool unit_seed = !nested.active && ni == out_idx;
+          gin = {unit_seed ? sv[0] : sv[0].mul(go), Tensor()};
+          break;
+        }
         vb_tensor o;
         check(vb_cross_entropy_backward(&sv[0].desc(), &sv[1].desc(), &go.desc(), node.extra.defined() ? &node.extra.desc() : nullptr, &o), "cross_entropy_backward");
         gin = {Tensor::adopt(o), Tensor()}; break;

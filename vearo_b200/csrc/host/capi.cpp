@@ -58,6 +58,7 @@ int vh_mean(int a, int dim, int keep) { VH_TRY(return put(at(a).mean(dim, keep !
 int vh_layernorm(int x, int w, int b, float eps) { VH_TRY(return put(at(x).layernorm(at(w), at(b), eps))); }
 int vh_embedding(int ids, int w) { VH_TRY(return put(at(ids).embedding(at(w)))); }
 int vh_cross_entropy(int l, int t) { VH_TRY(return put(at(l).cross_entropy(at(t)))); }
+int vh_cross_entropy_consuming(int l, int t) { VH_TRY(return put(at(l).cross_entropy_consuming(at(t)))); }
 int vh_conv2d(int x, int w, int b, int stride, int pad) { VH_TRY(return put(at(x).conv2d(at(w), at(b), stride, pad))); }
 int vh_maxpool2d(int x, int k, int s, int p) { VH_TRY(return put(at(x).maxpool2d(k, s, p))); }
 int vh_avgpool2d(int x, int k, int s, int p) { VH_TRY(return put(at(x).avgpool2d(k, s, p))); }

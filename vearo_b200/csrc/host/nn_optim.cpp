@@ -99,7 +99,7 @@ Tensor SimpleGPT::loss(const Tensor& ids, const Tensor& targets) {
     else h = blk.forward(h, &mask_);
   }
   Tensor logits = lm_head.forward(ln_f.forward(h).reshape({b * t, n_embd}));
-  return logits.cross_entropy(targets.reshape({b * t}));
+  return logits.cross_entropy_consuming(targets.reshape({b * t}));
 }
 
 MLP::MLP(const std::vector<i64>& sizes) { for (size_t i = 0; i + 1 < sizes.size(); ++i) layers.emplace_back(sizes[i], sizes[i + 1], true); }

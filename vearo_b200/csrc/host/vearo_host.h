@@ -82,6 +82,8 @@ class Tensor {
   Tensor permute(const std::vector<i64>& axes) const;
   Tensor contiguous() const;
 
+  // cross_entropy that may overwrite the logits (self) with their gradient; use where the logits are needed for nothing else
+  Tensor cross_entropy_consuming(const Tensor& targets) const;
   void backward() const;                // tensor.rs:703-714
   bool grad(Tensor* out) const;         // tensor.rs:716-725; false when no gradient is held
 

@@ -305,6 +305,54 @@ __global__ void k_ce_backward(const float* __restrict__ logits, const float* __r
     for (i64 c = threadIdx.x; c < v; c += blockDim.x) orow[c] = g * (expf(row[c] - m) / s - (c == cls ? 1.0f : 0.0f)) / fb;
   }
 }
+// Forward and backward in one pass over the logits, in place: the row's (max, sum) pass is followed, while the row is still in
+// L2, by the pass that overwrites it with d loss / d logits for an upstream gradient of 1 (the value a loss gets from
+// backward()); the row's loss term comes out of the first pass.  Algorithmic bytes 2 * rows * V * 4 for both directions
+// together -- what the backward alone moves otherwise.
+__global__ void k_ce_fused(float* __restrict__ logits, const float* __restrict__ targets, float* __restrict__ row_loss, i64 rows, i64 v, int* err) {
+  __shared__ float red[64];
+  __shared__ i64 s_cls;
+  const i64 r = blockIdx.x;
+  float* row = logits + r * v;
+  float m, s;
+  row_max_sum(row, v, m, s, red);
+  if (threadIdx.x == 0) {
+    const i64 cls = checked_id(targets[r], v, err);
+    row_loss[r] = cls < 0 ? 0.0f : -(row[cls] - m - logf(s));
+    s_cls = cls;
+  }
+  __syncthreads();      // the loss term has read row[cls] before anyone overwrites it
+  const i64 cls = s_cls;
+  // (softmax - onehot) / rows with the two divisions as multiplications by reciprocals formed once per row: a correctly rounded
+  // division costs several times a multiplication and this pass is short of issue slots, not of bandwidth (results move by an ulp)
+  const float inv_s = 1.0f / s, inv_fb = 1.0f / (float)rows;
+  if ((v & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    float4* r4 = reinterpret_cast<float4*>(row);
+    const i64 cq = cls >= 0 ? cls / 4 : -1;
+    for (i64 i = threadIdx.x; i < v / 4; i += blockDim.x) {
+      const float4 x = r4[i];
+      float4 o;
+      o.x = expf(x.x - m) * inv_s; o.y = expf(x.y - m) * inv_s; o.z = expf(x.z - m) * inv_s; o.w = expf(x.w - m) * inv_s;
+      if (i == cq) reinterpret_cast<float*>(&o)[cls & 3] -= 1.0f;
+      o.x *= inv_fb; o.y *= inv_fb; o.z *= inv_fb; o.w *= inv_fb;
+      r4[i] = o;
+    }
+  } else {
+    for (i64 c = threadIdx.x; c < v; c += blockDim.x) row[c] = (expf(row[c] - m) * inv_s - (c == cls ? 1.0f : 0.0f)) * inv_fb;
+  }
+}
+int launch_cross_entropy_fused(float* logits, const float* targets, float* loss, i64 rows, i64 v) {
+  void* rl = nullptr;
+  VB_TRY(scratch_alloc((size_t)rows * sizeof(float), &rl));
+  ProfScope prof("cross_entropy_fused", 2.0 * (double)rows * (double)v * 4.0);
+  int threads = v >= 8192 ? 512 : (v >= 1024 ? 256 : 64);
+  k_ce_fused<<<(unsigned)rows, threads, 0, ctx().stream>>>(logits, targets, (float*)rl, rows, v, ctx().d_err);
+  k_ce_mean<<<1, 1024, 0, ctx().stream>>>((const float*)rl, loss, rows);
+  scratch_free(rl);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
 int launch_cross_entropy_backward(const float* logits, const float* targets, const float* gout, const float* stats,
                                   float* gl, i64 rows, i64 v) {
   if (rows <= 0 || v <= 0) return VB_OK;
