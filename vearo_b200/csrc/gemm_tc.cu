@@ -960,7 +960,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     i64 tiles = ((g.M + BMT - 1) / BMT) * nb;
     if (tiles < slots && kblocks >= 48) { splits = (int)((slots + tiles - 1) / tiles); if (splits > kblocks / 24) splits = (int)(kblocks / 24); if (splits < 1) splits = 1; }
   }
-  // Stream-K instead of split-K where a tile would be shared by two or three groups at most: the k-blocks of all tiles are
+  // Stream-K instead of split-K where a tile would be shared by three or four groups at most: the k-blocks of all tiles are
   // dealt evenly to one group per slot and shared tiles are finished inside the kernel (no pass over partial tiles).
   // Measured slower than plain tiles when nothing needs splitting (groups at different k positions stop sharing
   // operand lines in L2) and when a tile has many parts (the group finishing a tile adds them alone).
@@ -968,7 +968,11 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   if (persist_env < 0) { const char* e = getenv("VB200_TC_STREAMK"); persist_env = e ? atoi(e) : 1; }
   bool persistent = false;
   i64 streamk_groups = 0;
-  if (persist_env && !g.causal && p.bn >= 128 && (splits > 1 || persist_env == 2)) {
+  // ... and where whole 256-wide tiles would fill one wave and less than half of a second one (measured on 4096 x 1024 . 1024 x 3072:
+  // 384 tiles for 296 slots, 157 us against 187 us with 128-wide tiles)
+  const i64 tiles256 = ((g.M + BMT - 1) / BMT) * ((g.N + 255) / 256) * nb;
+  const bool ragged_wave = splits == 1 && g.N > 128 && tiles256 > slots && 2 * tiles256 <= 3 * slots && kblocks >= 32;
+  if (persist_env && !g.causal && p.bn >= 128 && (splits > 1 || ragged_wave || persist_env == 2)) {
     int bn = 256;
     if (g.N <= 128 || ((g.N + 127) / 128) * 128 * 5 <= ((g.N + 255) / 256) * 256 * 4) bn = 128;     // a 256-wide last tile would be mostly padding
     i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
@@ -976,7 +980,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (G > W / 8) G = W / 8;                          // at least 8 k-blocks per group
     if (G < 1) G = 1;
     // (very long K: plain split-K measured faster, 2.74 ms against 2.90 ms for 8192 x 50304 . 50304 x 768)
-    if (tiles * CG <= 4096 && (persist_env == 2 || (W / G >= kblocks / 2 && kblocks <= 1024))) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
+    if (tiles * CG <= 4096 && (persist_env == 2 || (W / G >= kblocks / 3 && kblocks <= 1024))) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
   }
   { const char* e = getenv("VB200_TC_BN"); if (e && !persistent && p.bn == 256 && atoi(e) == 192) p.bn = 192; }
   p.tmem_cols = p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256);
