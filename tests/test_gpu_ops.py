@@ -617,6 +617,7 @@ def test_slot_lifecycle(vb):
     (4096, 768, 768, False, True),    # stream-K: one CTA per slot, 3-4 parts per tile
     (768, 1536, 4096, True, False),   # stream-K on a weight-gradient shape (A transposed view, long K)
     (2048, 300, 520, False, False),   # stream-K with 128-wide tiles (a 256-wide last tile would be mostly padding)
+    (4096, 3072, 512, False, True),   # stream-K because whole tiles would fill one wave and a fraction of a second (384 tiles, 296 slots)
     (384, 64, 1000, False, False),    # 64-wide tiles take 32-wide k-blocks: K ragged against 32, B row-major (MN-major)
     (384, 48, 328, False, True),      # ... both operands K-contiguous (128-byte swizzled rows), ragged N and K
     (640, 64, 1064, True, False),     # ... both operands MN-major (attention dV = P^T . dO shape)

@@ -67,6 +67,7 @@ struct TcParams {
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
   int a_fold, b_fold;                             // 1: MN-contiguous operand whose tensor map is folded into 32-wide blocks (one TMA box per tile)
   int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
+  int long_first;                                 // triangular products (causal 2, 3), tiled mode: gridDim = (tiles_n, batch, tiles_m) and the tile rows with the longest k range are dispatched first
   int causal;                                     // see GemmArgs::causal
   int debug;                                      // timing experiments only (results are wrong): 1 skip the split, 2 issue one MMA of three, 4 MMAs only (no loads), 8 loads only (no MMAs)
   int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
@@ -293,9 +294,13 @@ struct WorkIter {
     }
     if (done) return false;
     done = 1;
-    o.tile_n = blockIdx.x / CG; o.tile_m = blockIdx.y; o.tile = 0; o.which = 0;
+    // blocks are dispatched x first, z last: with long_first the slowest index walks the tile rows from the longest k range to the
+    // shortest, over all batches, so that the launch does not end on a few long tiles
+    const unsigned gy = p.long_first ? (p.causal == 2 ? gridDim.z - 1 - blockIdx.z : blockIdx.z) : blockIdx.y;
+    const unsigned gz = p.long_first ? blockIdx.y : blockIdx.z;
+    o.tile_n = blockIdx.x / CG; o.tile_m = (int)gy; o.tile = 0; o.which = 0;
     const i64 nbatch = p.nb1 * p.nb2;
-    o.bz = (int)(blockIdx.z % nbatch); o.split = (int)(blockIdx.z / nbatch);
+    o.bz = (int)(gz % nbatch); o.split = (int)(gz / nbatch);
     o.b1 = o.bz / (int)p.nb2; o.b2 = o.bz % (int)p.nb2;
     i64 kb0 = (i64)o.split * p.kblocks_per_split, kb1 = kb0 + p.kblocks_per_split;
     if (kb1 > kblocks_total) kb1 = kblocks_total;
@@ -1044,6 +1049,9 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.a_mn = oa.mn; p.b_mn = ob.mn;
   p.alpha = g.alpha; p.beta = g.beta; p.err = ctx().d_err;
   p.causal = causal_eff;
+  static int lf_env = -1;
+  if (lf_env < 0) { const char* e = getenv("VB200_TC_LONG_FIRST"); lf_env = (e && e[0] == '0') ? 0 : 1; }
+  p.long_first = (lf_env && !persistent && !round_robin && causal_eff >= 2 && tiles_m <= 65535 && nb * splits <= 65535) ? 1 : 0;
   if (round_robin) { p.persistent = 2; p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.live_per_batch = live_per_batch; p.live_tiles = live_per_batch * nb; }
 
   // Results leave through the copy engine when the layout allows and nothing has to be read back (beta = 0).
@@ -1078,6 +1086,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     else snprintf(fam, sizeof fam, "%s", nb > 1 ? "gemm_tc_batched" : "gemm_tc");
     ProfScope prof(fam, 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
     dim3 grid((unsigned)(tiles_n * CG), (unsigned)tiles_m, (unsigned)(nb * splits));
+    if (p.long_first) grid = dim3((unsigned)(tiles_n * CG), (unsigned)(nb * splits), (unsigned)tiles_m);
     if (persistent) grid = dim3((unsigned)(streamk_groups * CG), 1, 1);
     if (round_robin) grid = dim3((unsigned)(slots * CG), 1, 1);
     if (CG == 2) {
