@@ -617,6 +617,8 @@ def test_slot_lifecycle(vb):
     (4096, 768, 768, False, True),    # stream-K: one CTA per slot, 3-4 parts per tile
     (768, 1536, 4096, True, False),   # stream-K on a weight-gradient shape (A transposed view, long K)
     (2048, 300, 520, False, False),   # stream-K with 128-wide tiles (a 256-wide last tile would be mostly padding)
+    (2048, 384, 300, False, True),    # 192-wide tiles (a single wave either way, less padding work than 256)
+    (1024, 500, 264, True, False),    # 192-wide tiles with a ragged last tile, A as a transposed view
     (4096, 3072, 512, False, True),   # stream-K because whole tiles would fill one wave and a fraction of a second (384 tiles, 296 slots)
     (384, 64, 1000, False, False),    # 64-wide tiles take 32-wide k-blocks: K ragged against 32, B row-major (MN-major)
     (384, 48, 328, False, True),      # ... both operands K-contiguous (128-byte swizzled rows), ragged N and K

@@ -950,12 +950,15 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     // A k-block of a 128-wide tile costs ~0.62 of a 256-wide one (same A traffic for half the flops); the epilogue of a
     // tile costs about 10 (256) / 6 (128) k-blocks; split-K adds a pass over the partial tiles.
     double best = 1e300;
-    for (int bn : {256, 128}) {
+    // 192-wide tiles only where they make a single wave fuller (8192 x 768 . 768 x 768: 256 tiles instead of 192 for 296 slots,
+    // 62.7 us against 74.7 us); on multi-wave products they measured no better than 256
+    for (int bn : {256, 192, 128}) {
       i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
       for (int sk : {1, 2, 3, 4, 5, 6, 8, 10, 12, 16}) {
         if (sk > 1 && kblocks / sk < 24) break;
+        if (bn == 192 && (sk > 1 || tiles > slots || CG != 1)) break;
         i64 units = tiles * sk, waves = (units + slots - 1) / slots;
-        double kb_cost = bn == 256 ? 1.0 : 0.62, epi = bn == 256 ? 10.0 : 6.0;
+        double kb_cost = bn == 256 ? 1.0 : (bn == 192 ? 0.81 : 0.62), epi = bn == 256 ? 10.0 : (bn == 192 ? 8.0 : 6.0);
         double t = (double)waves * ((double)((kblocks + sk - 1) / sk) * kb_cost + epi);
         if (sk > 1) t += (double)tiles * (double)sk * epi * 0.5 / (double)slots + epi;      // partial tiles written, then summed
         if (t < best * 0.97) { best = t; p.bn = bn; splits = sk; }

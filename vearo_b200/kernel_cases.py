@@ -1,6 +1,7 @@
 """Small single-kernel cases of the library's hot kernels, for profiling with ncu and quick timing.
 
   python -m vearo_b200.kernel_cases gemm_fc1      x[8192,768] . W[3072,768]^T   (Linear forward)
+  python -m vearo_b200.kernel_cases gemm_proj     x[8192,768] . W[768,768]^T    (192 tiles of 128 x 256 for 296 CTA slots)
   python -m vearo_b200.kernel_cases gemm_dx       g[8192,3072] . W[3072,768]    (B consumed as a transposed view)
   python -m vearo_b200.kernel_cases gemm_dw       g[8192,3072]^T . x[8192,768]  (both operands transposed views, split-K)
   python -m vearo_b200.kernel_cases gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
@@ -29,6 +30,9 @@ def build(case):
     T = vb.Tensor.from_numpy
     if case == "gemm_fc1":
         x, w = T(f(8192, 768)), T(f(3072, 768))
+        return lambda: x.linear(w)
+    if case == "gemm_proj":
+        x, w = T(f(8192, 768)), T(f(768, 768))
         return lambda: x.linear(w)
     if case == "gemm_dx":
         g, w = T(f(8192, 3072)), T(f(3072, 768))
