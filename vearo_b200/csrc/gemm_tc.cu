@@ -9,23 +9,28 @@
 // accumulator, which leaves a relative error of about 2^-20 per product instead of TF32's 2^-10.  The tensor pipe therefore issues three TF32 MMAs per useful multiply-add: the
 // useful-flop ceiling of this kernel is one third of the TF32 peak.
 //
-// CTA = 320 threads, one 128 x BN output tile (BN = 64, 128 or 256 chosen per call), two CTAs per SM:
-//   warp 0      TMA producer: raw f32 tiles of A and B (BK = 16 k per stage) into a ring of 2-4 stages; one TMA box per
-//               operand tile; completion signalled on `full[s]` by transaction bytes.
+// CTA = 320 threads, one 128 x BN output tile (BN = 64, 128, 192 or 256 chosen per call), two CTAs per SM:
+//   warp 0      TMA producer: raw f32 tiles of A and B (16 k per stage; 32 for the 64-wide tiles, whose cost is the per-stage
+//               hand-offs) into a ring of 2-4 stages; one TMA box per operand tile; completion signalled on `full[s]` by
+//               transaction bytes.
 //   warps 2-9   converters: wait `full[s]`, write the `lo` parts of the stage into a second (2-3 stage) ring at the same
 //               offsets (the split is elementwise, so the swizzle pattern is irrelevant); the raw tile itself serves as
 //               `hi`, because the tensor core ignores the low 13 mantissa bits of a TF32 operand.  Then fence the
 //               generic-proxy writes towards the async proxy and arrive `conv[l]`.  After the main loop the same warps
-//               run the epilogue (tcgen05.ld -> registers -> transposed through the idle lo ring -> coalesced stores).
+//               run the epilogue: tcgen05.ld -> registers (alpha, biases) -> staged in the idle lo ring in the 128-byte-swizzled
+//               layout -> one TMA store per 32 x 32 block, which overlaps the next block's read from tensor memory
+//               (ordinary coalesced stores when the output breaks TMA's alignment rules or beta != 0).
 //   warp 1      allocates tensor memory, waits `conv[l]`, issues the 3 x (BK/8) MMAs of the stage from one thread, and
 //               releases the stages with tcgen05.commit -> `empty[s]`, `lo_empty[l]`.
 // Shared memory bandwidth is what bounds the main loop (operand reads of three MMAs + the converters' read and write
 // + the TMA writes); everything per k-block in the two single-thread roles is kept to a handful of instructions.
 //
 // Few-tile, long-K products (weight gradients) are split along K: either tiled split-K (grid.z; partial tiles go to
-// scratch and a second kernel adds them in a fixed order) or, where a tile would have two or three parts at most,
+// scratch and a second kernel adds them in a fixed order) or, where a tile would have three or four parts at most,
 // stream-K: the k-blocks of all tiles are dealt evenly to one CTA per slot and the CTA that completes a shared tile last
-// adds the parts in k order inside the kernel.
+// adds the parts in k order inside the kernel.  Short-K products with many tiles (attention scores, the vocabulary
+// projection) deal whole tiles round-robin to resident CTAs; triangular products (attention under a causal mask) clamp
+// each tile row's k range and dispatch the longest rows first.
 //
 // Operands: K-contiguous rows go through 64-byte-swizzle boxes; transposed views (MN-contiguous) are consumed in place
 // through 32-float boxes in the 128-byte swizzle with a 32-byte base, the only MN-major layout the tensor core takes
