@@ -104,6 +104,11 @@ class Tensor:
     def add(self, o): return Tensor(lib().orc_binary(0, self.h, o.h))
     def sub(self, o): return Tensor(lib().orc_binary(1, self.h, o.h))
     def mul(self, o): return Tensor(lib().orc_binary(2, self.h, o.h))
+
+    def dropout(self, p, seed):
+        """vearo_nn::Dropout::new(p, seed).forward(self) (crates/vearo-nn/src/lib.rs:308-357)."""
+        lib().orc_dropout.argtypes = [C.c_int, C.c_float, C.c_uint64]
+        return Tensor(_chk(lib().orc_dropout(self.h, p, seed)))
     def div(self, o): return Tensor(lib().orc_binary(3, self.h, o.h))
     def matmul(self, o): return Tensor(lib().orc_matmul(self.h, o.h))
     def relu(self): return Tensor(lib().orc_relu(self.h))
@@ -237,6 +242,16 @@ def zero_gradients(): lib().orc_zero_gradients()
 def reset_active_tape(): lib().orc_reset_tape()
 def reset_all(): lib().orc_reset_all()
 def set_training(t): lib().orc_set_training(int(t))
+
+
+def rng_counter():
+    lib().orc_rng_counter.restype = C.c_uint64
+    return int(lib().orc_rng_counter())
+
+
+def set_rng_counter(v):
+    lib().orc_set_rng_counter.argtypes = [C.c_uint64]
+    lib().orc_set_rng_counter(int(v))
 def set_threads(n): lib().orc_set_threads(int(n))
 def get_threads(): return int(lib().orc_get_threads())
 def set_autograd_enabled(e): lib().orc_set_autograd(int(e))

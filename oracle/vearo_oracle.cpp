@@ -1212,8 +1212,28 @@ const char* orc_last_error() { return g_err.c_str(); }
 void orc_set_threads(int n) { g_threads = n; }
 int orc_get_threads() { return n_threads(); }
 void orc_set_training(int t) { g_training = t != 0; }
+// Dropout::forward (vearo-nn/src/lib.rs:333-357) with SimpleRng (lib.rs:14-50) and the per-call counter (vearo-core/src/tensor.rs:1240-1285)
+static uint64_t g_rng_counter = 0;
+uint64_t orc_rng_counter() { return g_rng_counter; }
+void orc_set_rng_counter(uint64_t v) { g_rng_counter = v; }
+int orc_dropout(int x, float p, uint64_t seed) {
+  ORC_TRY(Tensor& in = at(x);          // by reference: the tape token lives in the tensor
+          if (p <= 0.0f || !g_training) return put(in);
+          float scale = 1.0f / (1.0f - p);
+          uint64_t call = g_rng_counter++;
+          uint64_t st = seed ^ (call * 0x9E3779B97F4A7C15ull);
+          if (st == 0) st = 0x123456789ABCDEF0ull;
+          std::vector<float> mask((size_t)in.numel());
+          for (float& m : mask) {
+            st ^= st << 13; st ^= st >> 7; st ^= st << 17;
+            float u = (float)st / (float)UINT64_MAX;
+            m = u >= p ? scale : 0.0f;
+          }
+          Tensor mt = from_data(mask.data(), in.shape);
+          return put(op_binary((Op)2, in, mt)));   // input.mul(&mask_t), recorded on the tape like any product
+}
 void orc_set_autograd(int e) { g_autograd = e != 0; }
-void orc_reset_all() { g_tensors.clear(); g_opts.clear(); g_grads.clear(); g_tape.nodes.clear(); g_tape.generation++; g_autograd = true; g_training = true; }
+void orc_reset_all() { g_tensors.clear(); g_opts.clear(); g_grads.clear(); g_tape.nodes.clear(); g_tape.generation++; g_autograd = true; g_training = true; g_rng_counter = 0; }
 void orc_reset_tape() { g_tape.nodes.clear(); g_tape.generation++; }   // reset_active_tape, autograd lib.rs:831
 void orc_zero_gradients() { g_grads.clear(); }                          // zero_gradients, autograd lib.rs:836
 void orc_free(int h) { if (h >= 0 && h < (int)g_tensors.size()) g_tensors[h].reset(); }

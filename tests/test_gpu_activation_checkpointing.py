@@ -66,6 +66,37 @@ def test_shared_parameter_and_nested_blocks(vb):
     vb.check_errors()
 
 
+def test_dropout_matches_oracle_and_is_reproducible_under_checkpoint(vb):
+    """crates/vearo/tests/checkpoint_hazards.rs:30-82: a block containing dropout gives the same gradient with and without
+    checkpointing, because the recomputation rewinds the call counter and draws the same mask.  The mask itself is the
+    reference's (xorshift64 seeded with seed ^ call * 0x9E3779B97F4A7C15, keep where u >= p, scale 1 / (1 - p))."""
+    x0 = np.array([0.5, -1.5, 2.0, 0.25, 1.0, -0.75], np.float32).reshape(2, 3)
+    big = rnd(310, 37, 29)
+
+    def run(T, m, ckpt):
+        m.set_training(True); m.set_rng_counter(0)
+        x, y = T.from_numpy(x0, True), T.from_numpy(big, True)
+        m.zero_gradients(); m.reset_active_tape()
+        f = lambda t: t.dropout(0.25, 7)
+        out = (m.checkpoint(x, f) if ckpt else f(x))
+        z = y.dropout(0.5, 11).mul(y)                       # a second draw after the block: counter 1 in both variants
+        out.sum(0, False).sum(0, False).add(z.sum(0, False).sum(0, False)).backward()
+        return [out.numpy().copy(), x.grad().numpy().copy(), y.grad().numpy().copy()], m.rng_counter()
+    orc.reset_all()
+    ref, ref_ctr = run(orc.Tensor, orc, False)
+    plain, c1 = run(vb.Tensor, vb, False)
+    ck, c2 = run(vb.Tensor, vb, True)
+    assert ref_ctr == c1 == c2 == 2
+    for a, b, c in zip(ref, plain, ck):
+        assert np.array_equal(a, b) and np.array_equal(b, c)
+    assert (plain[0] == 0).sum() + (big.size - np.count_nonzero(plain[2])) > 0      # something was dropped
+    vb.set_training(False)
+    t = vb.Tensor.from_numpy(x0)
+    assert np.array_equal(t.dropout(0.25, 7).numpy(), x0)                              # identity outside training
+    vb.set_training(True)
+    vb.check_errors()
+
+
 def test_batchnorm_running_stats_advance_once(vb):
     """crates/vearo/tests/checkpoint_hazards.rs:84-140: the block runs twice, the running statistics move once."""
     T = vb.Tensor

@@ -192,6 +192,32 @@ def test_adamw_8bit_known_answers():
     assert v8.tolist() == [127, 32, 8, 0]        # 127 * [1, 0.25, 0.0625, 1.5e-5] -> 127, 31.75 -> 32, 7.94 -> 8, 0
 
 
+def test_dropout_definition():
+    """crates/vearo-nn/src/lib.rs:308-357 with SimpleRng (lib.rs:14-50): mask element i keeps (value 1 / (1 - p)) where the
+    i-th xorshift64 draw, as f32 / 2^64, is >= p; the generator is seeded with seed ^ call * 0x9E3779B97F4A7C15 and the call
+    counter advances once per forward; identity when p <= 0 or outside training.  Checked against a Python restatement."""
+    def mask(seed, call, p, n):
+        st = (seed ^ (call * 0x9E3779B97F4A7C15)) & 0xFFFFFFFFFFFFFFFF
+        if st == 0: st = 0x123456789ABCDEF0
+        out = []
+        for _ in range(n):
+            st ^= (st << 13) & 0xFFFFFFFFFFFFFFFF; st ^= st >> 7; st ^= (st << 17) & 0xFFFFFFFFFFFFFFFF
+            u = np.float32(st) / np.float32(2.0 ** 64)
+            out.append(np.float32(1.0) / (np.float32(1.0) - np.float32(p)) if u >= np.float32(p) else np.float32(0.0))
+        return np.array(out, np.float32)
+    orc.reset_all()
+    x = T.from_numpy(np.ones(64, np.float32))
+    a, b = x.dropout(0.25, 7).numpy(), x.dropout(0.25, 7).numpy()
+    assert np.array_equal(a, mask(7, 0, 0.25, 64)) and np.array_equal(b, mask(7, 1, 0.25, 64)) and orc.rng_counter() == 2
+    assert 0 < (a == 0).sum() < 64 and not np.array_equal(a, b)
+    orc.set_rng_counter(0)
+    assert np.array_equal(x.dropout(0.25, 7).numpy(), a)               # rewinding the counter reproduces the draw
+    assert np.array_equal(x.dropout(0.0, 7).numpy(), np.ones(64, np.float32)) and orc.rng_counter() == 1
+    orc.set_training(False)
+    assert np.array_equal(x.dropout(0.9, 7).numpy(), np.ones(64, np.float32))
+    orc.set_training(True)
+
+
 def test_batchnorm_running_stats():
     """crates/vearo/tests/batchnorm_review.rs:119-174."""
     n, c, h, w = 2, 2, 2, 2

@@ -198,6 +198,11 @@ class Tensor:
     def embedding(self, w): return Tensor(lib().vh_embedding(self.h, w.h))
     def cross_entropy(self, t): return Tensor(lib().vh_cross_entropy(self.h, t.h))
 
+    def dropout(self, p, seed):
+        """vearo_nn::Dropout::new(p, seed).forward(self): the reference's mask for (seed, call counter), identity when not training."""
+        lib().vh_dropout.argtypes = [C.c_int, C.c_float, C.c_uint64]
+        return Tensor(_chk(lib().vh_dropout(self.h, p, seed)))
+
     def cross_entropy_consuming(self, t):
         """cross_entropy for logits that are needed for nothing else: when the loss will be differentiated, one pass returns
         the loss and leaves the logits' gradient in their place."""
@@ -351,6 +356,16 @@ def checkpoint(x, fn):
 
 
 def is_recomputing(): return bool(lib().vh_is_recomputing())
+
+
+def rng_counter():
+    lib().vh_rng_counter.restype = C.c_uint64
+    return int(lib().vh_rng_counter())
+
+
+def set_rng_counter(v):
+    lib().vh_set_rng_counter.argtypes = [C.c_uint64]
+    lib().vh_set_rng_counter(int(v))
 def set_training(t): lib().vh_set_training(int(t))
 def set_autograd_enabled(e): lib().vh_set_autograd_enabled(int(e))
 def sync(): vb_check(lib().vb_sync(), "vb_sync")

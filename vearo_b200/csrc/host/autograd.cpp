@@ -85,10 +85,12 @@ struct Node {
   Tensor extra;             // attention probabilities / cross-entropy row statistics
   Tensor leaf;              // for Leaf nodes: the tensor itself
   std::function<Tensor(const Tensor&)> fn;      // Checkpoint nodes: the block to run again during backward
+  uint64_t rng = 0;                             // Checkpoint nodes: the per-call randomness counter when the block first ran
 };
 struct Tape { std::vector<Node> nodes; uint32_t generation = 0; };
 thread_local Tape t_tape;
 thread_local bool t_enabled = true, t_training = true, t_recomputing = false;
+thread_local uint64_t t_rng_counter = 0;        // per-call randomness counter (vearo-core/src/tensor.rs:1240-1285)
 // A leaf is identified by where it lives: slot and offset (several parameters may be views of one slot).
 using LeafKey = uint64_t;
 inline LeafKey leaf_key(const Tensor& t) { return ((uint64_t)t.slot() << 40) ^ (uint64_t)t.desc().offset; }
@@ -509,10 +511,14 @@ void run_backward(const Tensor& y, const Tensor& seed, const NestedInput& nested
         const Tensor x = sv[0];
         const i64 x_token = x.node_id();
         t_tape.nodes.clear(); t_tape.generation++;
+        // rewind the randomness counter to where the block first ran: a dropout inside draws the same mask again (lib.rs:680-690)
+        const uint64_t saved_counter = t_rng_counter;
+        t_rng_counter = node.rng;
         t_enabled = true; t_recomputing = true;
         Tensor y_new;
-        try { y_new = node.fn(x); } catch (...) { t_enabled = false; t_recomputing = false; throw; }
+        try { y_new = node.fn(x); } catch (...) { t_enabled = false; t_recomputing = false; t_rng_counter = saved_counter; throw; }
         t_enabled = false; t_recomputing = false;
+        t_rng_counter = saved_counter;
         Tensor gx;
         NestedInput inner; inner.active = true; inner.key = leaf_key(x); inner.gx = &gx;
         run_backward(y_new, go, inner);
@@ -547,6 +553,7 @@ namespace autograd {
 // only the input, and record one node that re-runs the block when the backward walk reaches it.
 Tensor checkpoint(const Tensor& x, std::function<Tensor(const Tensor&)> f) {
   const bool was = t_enabled;
+  const uint64_t rng_at_entry = t_rng_counter;
   t_enabled = false;
   Tensor out;
   try { out = f(x); } catch (...) { t_enabled = was; throw; }
@@ -555,10 +562,14 @@ Tensor checkpoint(const Tensor& x, std::function<Tensor(const Tensor&)> f) {
     out.set_requires_grad(true);
     Node& n = push(Op::Checkpoint, {&x}, out);
     n.fn = std::move(f);
+    n.rng = rng_at_entry;
   }
   return out;
 }
 bool is_recomputing() { return t_recomputing; }
+uint64_t rng_counter() { return t_rng_counter; }
+void set_rng_counter(uint64_t v) { t_rng_counter = v; }
+uint64_t next_rng_counter() { return t_rng_counter++; }
 }  // namespace autograd
 
 bool Tensor::grad(Tensor* out) const {

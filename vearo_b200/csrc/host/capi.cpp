@@ -114,6 +114,9 @@ int vh_checkpoint(int x, int (*fn)(int, void*), void* user) {
          });
          return put(out));
 }
+int vh_dropout(int x, float p, uint64_t seed) { VH_TRY(return put(nn::Dropout(p, seed).forward(at(x)))); }
+uint64_t vh_rng_counter() { return autograd::rng_counter(); }
+void vh_set_rng_counter(uint64_t v) { autograd::set_rng_counter(v); }
 int vh_is_recomputing() { return autograd::is_recomputing() ? 1 : 0; }
 int vh_gpt_set_checkpointing(int m, int on) {
   VH_TRY(nn::SimpleGPT* g = dynamic_cast<nn::SimpleGPT*>(&model(m)); if (!g) throw Error("not a SimpleGPT"); g->checkpoint_blocks = on != 0; return 0);

@@ -26,6 +26,20 @@ static Tensor filled(const std::vector<i64>& shape, float v) {
   t.set_requires_grad(true);
   return t;
 }
+Tensor Dropout::forward(const Tensor& x) const {
+  if (p <= 0.0f || !autograd::is_training()) return x;
+  const float scale = 1.0f / (1.0f - p);
+  const uint64_t call = autograd::next_rng_counter();
+  uint64_t st = seed ^ (call * 0x9E3779B97F4A7C15ull);
+  if (st == 0) st = 0x123456789ABCDEF0ull;               // SimpleRng::new, lib.rs:22-30
+  std::vector<float> mask((size_t)x.numel());
+  for (float& m : mask) {
+    st ^= st << 13; st ^= st >> 7; st ^= st << 17;       // next_u64, lib.rs:33-40
+    const float u = (float)st / (float)UINT64_MAX;       // next_f32, lib.rs:43-45
+    m = u >= p ? scale : 0.0f;
+  }
+  return x.mul(Tensor::from_f32(mask.data(), x.shape()));
+}
 static Tensor param_zeros(const std::vector<i64>& shape) { Tensor t = Tensor::zeros(shape); t.set_requires_grad(true); return t; }
 
 Linear::Linear(i64 in, i64 out, bool b) : has_bias(b) {

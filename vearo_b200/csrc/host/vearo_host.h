@@ -104,6 +104,9 @@ size_t tape_len();
 // recording, and differentiates that.  While it does, is_recomputing() is true and stateful layers leave their state alone.
 Tensor checkpoint(const Tensor& x, std::function<Tensor(const Tensor&)> f);
 bool is_recomputing();
+// Per-call randomness counter (vearo-core/src/tensor.rs:1240-1285): random layers derive their draw from it instead of holding
+// state, and checkpoint() rewinds it for the recomputation.
+uint64_t rng_counter(); void set_rng_counter(uint64_t v); uint64_t next_rng_counter();
 // Persistent gradient buffers: when a leaf with a registered sink gets its final gradient, the
 // gradient is written into the sink (a view of a flat arena) instead of a fresh tensor, and
 // `on_ready(index)` fires — which is what lets the data-parallel reducer start a bucket's
@@ -169,6 +172,14 @@ std::vector<HostTensor> read_container(const std::string& path);
 
 // ---- layers and the five workload graphs (vearo-nn/src/lib.rs) -------------------------------
 namespace nn {
+// Dropout (vearo-nn/src/lib.rs:308-357): the mask is a pure function of (seed, call counter) drawn from the reference's xorshift64
+// generator on the host, as the reference does for every device, uploaded and multiplied in.  Identity when p <= 0 or not training.
+struct Dropout {
+  float p = 0.0f; uint64_t seed = 0;
+  Dropout() = default;
+  Dropout(float p_, uint64_t seed_) : p(p_), seed(seed_) {}
+  Tensor forward(const Tensor& x) const;
+};
 struct Linear {
   Tensor weight, bias; bool has_bias = false;
   Linear() = default;
