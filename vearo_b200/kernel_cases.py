@@ -9,6 +9,7 @@
   python -m vearo_b200.kernel_cases attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
   python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
   python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
+  python -m vearo_b200.kernel_cases ce_fused      rows 2048, V 50304: loss and gradient in one in-place pass
   python -m vearo_b200.kernel_cases adamw         64 Mi parameters
   python -m vearo_b200.kernel_cases adamw8bit     64 Mi parameters, int8 block-wise moments
 A second argument gives the repetition count (default 3); `time` instead prints the average device
@@ -69,6 +70,14 @@ def build(case):
         def run():
             vb.zero_gradients(); vb.reset_active_tape()
             l.cross_entropy(t).backward()
+        return run
+    if case == "ce_fused":
+        x, w = T(f(2048, 16), True), T(f(16, 50304))
+        t = T(r.integers(0, 50304, 2048).astype(np.float32))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            x.matmul(w).cross_entropy_consuming(t).backward()
         return run
     if case in ("adamw", "adamw8bit"):
         w = T(f(64 << 20), True)
