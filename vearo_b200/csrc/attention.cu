@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(256) k_attn_softmax_long(float* __restrict__ s
 // i_lo, i_cnt: the rows [i_lo, i_lo + i_cnt) of every [sq, sk] matrix are handled by this launch (`rows` = number of matrices).
 // Causal launches go by bands of rows, each with the instance whose register array just covers the band's live columns.
 template <int V>
-__global__ void __launch_bounds__(128) k_attn_softmax_warp(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
+__global__ void __launch_bounds__(128, 6) k_attn_softmax_warp(float* __restrict__ s, const float* __restrict__ mask, MaskStrides ms,
                                                            i64 H, i64 sq, i64 sk, i64 rows, int causal, i64 i_lo, i64 i_cnt) {
   const int lane = threadIdx.x & 31;
   // grid: x = groups of four rows of the band, y = matrices (no division on the way to the row's address)
