@@ -7,6 +7,7 @@
   python -m vearo_b200.kernel_cases gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
   python -m vearo_b200.kernel_cases gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
   python -m vearo_b200.kernel_cases attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
+  python -m vearo_b200.kernel_cases colsum        bias gradients: column sums of [8192,768] and [8192,3072]
   python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
   python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
   python -m vearo_b200.kernel_cases ce_fused      rows 2048, V 50304: loss and gradient in one in-place pass
@@ -56,6 +57,16 @@ def build(case):
         def run():
             vb.zero_gradients(); vb.reset_active_tape()
             qkv.fused_attention_packed(12, mask).mul(go).sum(2, False).sum(1, False).sum(0, False).backward()
+        return run
+    if case == "colsum":
+        a, b = T(f(8192, 768)), T(f(8192, 3072))
+        ba, bb = T(f(768), True), T(f(3072), True)
+
+        def run():      # the bias of a broadcast add gets its gradient as a column sum
+            vb.zero_gradients(); vb.reset_active_tape()
+            a.add(ba).sum(1, False).sum(0, False).backward()
+            vb.zero_gradients(); vb.reset_active_tape()
+            b.add(bb).sum(1, False).sum(0, False).backward()
         return run
     if case == "layernorm_bwd":
         x, w, b, g = T(f(8192, 768), True), T(f(768), True), T(f(768), True), T(f(8192, 768))
