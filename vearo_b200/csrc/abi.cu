@@ -5,6 +5,7 @@
 #include "common.h"
 #include <cmath>
 #include <cstdlib>
+#include <unordered_map>
 #include <cstring>
 
 using namespace vb;
@@ -716,6 +717,43 @@ int vb_fill(const vb_tensor* dst, float value) {
 }
 
 // ---- fused linear layer ------------------------------------------------------------------------
+// TF32 remainders ("lo plane") of a Linear weight, kept beside the weight while its contents stand: the tensor-core GEMM then
+// loads them instead of recomputing them in every tile of the forward product and of the input-gradient product.  Keyed by the
+// weight's slot; valid while the slot's serial is unchanged (every call of this library that writes into an existing slot --
+// vb_write, vb_copy, vb_fill, vb_accumulate, the optimizer steps -- advances it).  One plane covers the whole slot, so
+// parameters that are views of one block share it.  Returns null where the plane does not pay or cannot be had.
+namespace {
+struct LoPlane { vb_slot lo = 0; uint64_t serial = 0; i64 numel = 0; };
+std::unordered_map<vb_slot, LoPlane>& lo_planes() { static auto* m = new std::unordered_map<vb_slot, LoPlane>(); return *m; }
+const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("VB200_WEIGHT_LO"); on = (e && e[0] == '0') ? 0 : 1; }
+  if (!on) return nullptr;
+  float* base; i64 n;
+  if (slot_ptr(w->slot, &base, &n) != VB_OK || n < (i64)1 << 18) return nullptr;       // small weights: their products are not tensor-core bound
+  auto& tab = lo_planes();
+  if (tab.size() > 512) {        // forget planes of slots that have been handed out again since
+    for (auto it = tab.begin(); it != tab.end();) {
+      if (slot_serial(it->first) != it->second.serial) { slot_release(it->second.lo, nullptr); it = tab.erase(it); } else ++it;
+    }
+  }
+  LoPlane& e = tab[w->slot];
+  const uint64_t serial = slot_serial(w->slot);
+  if (e.lo == 0 || e.numel != n) {
+    if (e.lo) { slot_release(e.lo, nullptr); e.lo = 0; }
+    if (slot_alloc(n, false, &e.lo) != VB_OK) { tab.erase(w->slot); return nullptr; }
+    e.numel = n; e.serial = 0;
+  }
+  float* lo;
+  if (slot_ptr(e.lo, &lo) != VB_OK) return nullptr;
+  if (e.serial != serial) {
+    if (launch_tf32_lo(base, lo, n) != VB_OK) return nullptr;
+    e.serial = serial;
+  }
+  return lo + (pw - base);
+}
+}  // namespace
+
 int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias, vb_tensor* out) {
   VB_CHECK(weight->rank == 2 && x->rank >= 1, "linear expects weight [out, in]");
   VB_CHECK(x->dims[x->rank - 1] == weight->dims[1], "Incompatible dimensions for matmul");
@@ -735,6 +773,7 @@ int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias
   g.A = px; g.a_rs = in; g.a_cs = 1;
   g.B = pw; g.b_rs = weight->strides[1]; g.b_cs = weight->strides[0];   // W^T
   g.C = po; g.c_rs = g.N; g.c_cs = 1; g.bias = pb;
+  if (rows >= 1024) g.B_lo = weight_lo_plane(weight, pw);
   return launch_gemm(g);
 }
 // gw_into / gb_into: existing contiguous tensors the weight and bias gradients are written into (a parameter's slice of
@@ -759,6 +798,7 @@ static int linear_backward_impl(const vb_tensor* x, const vb_tensor* weight, con
       g.A = pg; g.a_rs = outf; g.a_cs = 1;
       g.B = pw; g.b_rs = weight->strides[0]; g.b_cs = weight->strides[1];
       g.C = p; g.c_rs = in; g.c_cs = 1;
+      if (rows >= 1024) g.B_lo = weight_lo_plane(weight, pw);
       VB_TRY(launch_gemm(g));
     }
   }

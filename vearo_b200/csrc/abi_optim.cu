@@ -49,6 +49,7 @@ int vb_adamw_step(const vb_tensor* param, const vb_tensor* grad, vb_slot m, vb_s
   VB_CHECK(nm == n, "Momentum vector m must match parameter length");
   VB_CHECK(nv == n, "Variance vector v must match parameter length");
   float bc1 = 1.0f - powi(beta1, (int)t), bc2 = 1.0f - powi(beta2, (int)t);
+  slot_touch(param->slot);
   return launch_adamw_single(pw, pg, pm, pv, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2);
 }
 int vb_sgd_step(const vb_tensor* param, const vb_tensor* grad, vb_slot velocity, float lr, float momentum, float weight_decay) {
@@ -58,6 +59,7 @@ int vb_sgd_step(const vb_tensor* param, const vb_tensor* grad, vb_slot velocity,
   float *pw, *pg, *pv; i64 nv;
   VB_TRY(tensor_ptr(param, &pw)); VB_TRY(tensor_ptr(grad, &pg)); VB_TRY(slot_ptr(velocity, &pv, &nv));
   VB_CHECK(nv == numel(*param), "Velocity vector must match parameter length");
+  slot_touch(param->slot);
   return launch_sgd_single(pw, pg, pv, numel(*param), lr, momentum, weight_decay);
 }
 
@@ -207,6 +209,7 @@ int vb_opt_step(int id, const uint8_t* active, float max_norm, float grad_scale,
   if (c.kind != VB_OPT_SGD) { bc1 = 1.0f - powi(c.beta1, (int)o->t); bc2 = 1.0f - powi(c.beta2, (int)o->t); }
   VB_TRY(launch_opt_multi((const OptChunk*)o->d_chunks, o->nchunks, d_active, c.kind, d_normsq, max_norm, grad_scale,
                           c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.momentum, bc1, bc2));
+  for (size_t i = 0; i < o->retained.size(); i += 2) slot_touch(o->retained[i]);      // the parameters' contents changed
   if (total_norm) {
     float h = 0.0f;
     if (o->nchunks > 0) {

@@ -148,8 +148,12 @@ struct GemmArgs {
   //   3  A[m, k] == 0 for k < m (A is a transposed view of such a matrix): the k range starts at the tile's first row (P^T.dO, dS^T.Q)
   // Kernels that do not exploit it compute the full product, which gives the same values.
   int causal;
+  // Optional: the TF32 remainders of B (lo = tf32(b - cut_to_tf32(b)), what the tensor-core kernel otherwise computes for every
+  // k-block of every tile), laid out exactly like B.  Worth it for an operand used by many tiles and several products (weights).
+  const float* B_lo;
 };
 int launch_gemm(const GemmArgs& g);
+int launch_tf32_lo(const float* x, float* lo, i64 n);      // gemm_tc.cu: lo[i] as above
 int gemm_tc_reset_state();   // gemm_tc.cu: clears kernel-side bookkeeping after a reported device error
 inline GemmArgs gemm_args() { GemmArgs g{}; g.nb1 = g.nb2 = 1; g.alpha = 1.0f; g.beta = 0.0f; return g; }
 

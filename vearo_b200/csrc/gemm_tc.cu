@@ -67,6 +67,7 @@ struct TcParams {
   i64 nb1, nb2;
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
   int tmem_cols;                                  // tensor-memory columns allocated: bn rounded up to a power of two
+  int b_lo;                                       // the lo part of B comes pre-split from memory (map_blo) instead of from the converters
   int tma_out;                                    // results leave through TMA stores of the staged 32 x 32 blocks (map_c)
   int bk;                                         // k per stage: 16, or 32 for the narrow (64-wide) tiles whose per-stage hand-offs dominate
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
@@ -385,7 +386,8 @@ __device__ __forceinline__ void trace_event(const TcParams& p, int ev, int kb) {
 
 template <int CG, int CW>
 __global__ void __launch_bounds__(64 + 32 * CW, CW == 8 ? 2 : 1)
-k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, TcParams p) {
+k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+          const __grid_constant__ CUtensorMap map_blo, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ]
   // (doubles as the epilogue's staging area: nothing converts while a tile is being stored), barriers.
@@ -409,7 +411,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], CW * CG); mbar_init(&lo_empty[s], 1); }
+    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], CW * CG + (p.b_lo ? 1 : 0)); mbar_init(&lo_empty[s], 1); }    // (+1: the producer's expect_tx arrival for the pre-split lo part of B)
     mbar_init(tmem_full, 1);
     mbar_init(tmem_empty, kEpiWarps * CG);
     *abort_flag = 0;
@@ -458,6 +460,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           mbar_arrive_expect_tx(&full[s], raw_bytes);
           tma_load_tile(st, &map_a, &full[s], amode, BM, m0, k, ab2, ab1, bk);
           tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bnc, n0, k, bb2, bb1, bk);
+          if (p.b_lo) {
+            // the lo part of B lands straight in the lo stage (the converters fill only the A part); it completes on the stage's
+            // `conv` barrier together with their arrivals
+            const int l = it % lstages;                                   // (derived, not carried: this role has no register to spare)
+            const uint32_t lph = (((uint32_t)(it / lstages)) & 1u) ^ 1u;    // parity of `lo_empty` that says the slot was released
+            if (it >= lstages && !mbar_wait(&lo_empty[l], lph, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(&conv[l], b_bytes);
+            tma_load_tile(lo_ring + (size_t)l * raw_bytes + a_bytes, &map_blo, &conv[l], bmode, bnc, n0, k, bb2, bb1, bk);
+          }
           trace_event(p, 1, it);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
@@ -466,6 +477,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       if (*abort_flag)
         for (int kb = (it > stages ? it - stages : 0); kb < it; ++kb) {
           uint32_t addr = smem_u32(&full[kb % stages]), php = (uint32_t)(kb / stages) & 1, done = 0;
+          for (uint32_t n = 0; n < (1u << 16) && !done; ++n)
+            asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}" : "=r"(done) : "r"(addr), "r"(php) : "memory");
+        }
+      // (the pre-split lo copies complete on `conv`, which also needs the converters: polled for the same bounded time, as a delay)
+      if (*abort_flag && p.b_lo)
+        for (int kb = (it > lstages ? it - lstages : 0); kb < it; ++kb) {
+          uint32_t addr = smem_u32(&conv[kb % lstages]), php = (uint32_t)(kb / lstages) & 1, done = 0;
           for (uint32_t n = 0; n < (1u << 16) && !done; ++n)
             asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}" : "=r"(done) : "r"(addr), "r"(php) : "memory");
         }
@@ -567,7 +585,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         if (ct == 0) trace_event(p, 2, it);
         float4* hi = (float4*)(smem + (size_t)s * raw_bytes);
         float4* lo = (float4*)(lo_ring + (size_t)l * raw_bytes);
-        const int n4 = (int)(raw_bytes / 16);
+        const int n4 = (p.b_lo || (kTiming && (p.debug & 256))) ? (int)(a_bytes / 16) : (int)(raw_bytes / 16);     // (timing experiment 256: only the A part is split)
         if (kTiming && (p.debug & 1)) {
         } else if (p.raw_hi) {
 #pragma unroll 3
@@ -808,6 +826,17 @@ __global__ void k_repack_kmajor(const float* __restrict__ src, float* __restrict
   }
 }
 
+// lo[i] = the TF32 remainder of x[i], exactly what the converters compute
+__global__ void __launch_bounds__(256) k_tf32_lo(const float* __restrict__ x, float* __restrict__ lo, i64 n) {
+  const i64 stride = (i64)gridDim.x * blockDim.x;
+  const i64 n4 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(lo)) & 15) == 0 ? n / 4 : 0;
+  for (i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<float4*>(lo)[i] = make_float4(tf32_lo_of_raw(v.x), tf32_lo_of_raw(v.y), tf32_lo_of_raw(v.z), tf32_lo_of_raw(v.w));
+  }
+  for (i64 i = n4 * 4 + blockIdx.x * (i64)blockDim.x + threadIdx.x; i < n; i += stride) lo[i] = tf32_lo_of_raw(x[i]);
+}
+
 // ---- host side --------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -891,6 +920,16 @@ int* g_tile_counters = nullptr;     // stream-K arrival counters (zero between l
 // After a device-side wait ran out a tile may have been left half counted: start from zero again.
 int gemm_tc_reset_state() {
   if (g_tile_counters) VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
+  return VB_OK;
+}
+
+int launch_tf32_lo(const float* x, float* lo, i64 n) {
+  if (n <= 0) return VB_OK;
+  ProfScope prof("tf32_lo", 8.0 * (double)n);
+  i64 blocks = (n / 4 + 255) / 256, cap = (i64)ctx().sm_count * 16;
+  if (blocks > cap) blocks = cap; if (blocks < 1) blocks = 1;
+  k_tf32_lo<<<(unsigned)blocks, 256, 0, ctx().stream>>>(x, lo, n);
+  VB_LAUNCH_CHECK();
   return VB_OK;
 }
 
@@ -1067,14 +1106,27 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   memset(&map_c, 0, sizeof map_c);
   static int tma_out_env = -1;
   if (tma_out_env < 0) { const char* e = getenv("VB200_TC_TMA_OUT"); tma_out_env = (e && e[0] == '0') ? 0 : 1; }
-  if (tma_out_env && g.beta == 0.0f && !(kTiming && getenv("VB200_TC_DEBUG"))) {
+  if (tma_out_env && g.beta == 0.0f && !(kTiming && getenv("VB200_TC_DEBUG") && (atoi(getenv("VB200_TC_DEBUG")) & ~256))) {
     if (splits == 1) p.tma_out = make_out_map(&map_c, g.C, g.N, g.M, g.nb2, g.nb1, g.c_rs, g.c_b2, g.c_b1) ? 1 : 0;
     else p.tma_out = make_out_map(&map_c, (float*)part.p, g.N, g.M, (i64)splits * nb, 1, g.N, g.M * g.N, 0) ? 1 : 0;
+  }
+
+  // Pre-split lo part of B: tiled launches only (in the persistent modes the producer runs ahead into the next tile while the lo
+  // ring is the epilogue's staging area), B consumed in place (the lo plane has B's layout), raw hi operand.
+  CUtensorMap map_blo;
+  memset(&map_blo, 0, sizeof map_blo);
+  static int blo_env = -1;
+  if (blo_env < 0) { const char* e = getenv("VB200_TC_B_LO"); blo_env = (e && e[0] == '0') ? 0 : 1; }
+  if (blo_env && g.B_lo && !hold_b.p && CG == 1 && !persistent && !round_robin && !(kTiming && getenv("VB200_TC_DEBUG"))) {
+    Operand obl = ob; obl.p = g.B_lo;
+    bool f2 = false;
+    if (tma_ok(obl, g.nb1, g.nb2) && make_map(&map_blo, obl, g.K, g.nb1, g.nb2, p.bn / CG, bk, &f2) == VB_OK && f2 == fold_b) p.b_lo = 1;
   }
 
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
   p.raw_hi = raw_hi_env;
+  if (!p.raw_hi) p.b_lo = 0;           // the plane holds remainders against the raw (cut) hi operand
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("VB200_TC_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
   { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 220 * 1024 && (size_t)l * raw_bytes >= 32 * 1024) { p.stages = r; p.lstages = l; } } }
   size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 2) * sizeof(uint64_t) + 16 + 1024;
@@ -1106,12 +1158,12 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
       cfg.attrs = attr; cfg.numAttrs = 1;
       { static int occ = -1; if (occ < 0) { const char* e = getenv("VB200_TC_OCC"); occ = (e && e[0] == '1') ? 1 : 0; }
         if (occ) { int n = 0; cudaError_t r = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<2, 8>, &cfg); fprintf(stderr, "[gemm_tc] max active clusters %d (err %d), smem %zu, grid %u\n", n, (int)r, smem, grid.x * grid.y * grid.z); occ = 0; } }
-      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, map_c, p));
-      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, map_c, p));
+      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, map_c, map_blo, p));
+      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, map_c, map_blo, p));
     } else if (CW == 16) {
-      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, map_c, p);
+      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, p);
     } else {
-      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, map_c, p);
+      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, p);
     }
     VB_LAUNCH_CHECK();
     if (kTiming && (p.debug & 64)) {
