@@ -753,6 +753,27 @@ const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
   return lo + (pw - base);
 }
 }  // namespace
+extern "C++" {
+namespace vb {
+float* lo_plane_base_for(vb_slot weight_slot, float** weight_base) {
+  auto& tab = lo_planes();
+  auto it = tab.find(weight_slot);
+  if (it == tab.end() || it->second.lo == 0) return nullptr;
+  float *base, *lo; i64 n;
+  if (slot_ptr(weight_slot, &base, &n) != VB_OK || n != it->second.numel || slot_ptr(it->second.lo, &lo) != VB_OK) return nullptr;
+  if (weight_base) *weight_base = base;
+  return lo;
+}
+bool lo_plane_is_current(vb_slot weight_slot) {
+  auto it = lo_planes().find(weight_slot);
+  return it != lo_planes().end() && it->second.lo != 0 && it->second.serial == slot_serial(weight_slot);
+}
+void lo_plane_mark_current(vb_slot weight_slot) {
+  auto it = lo_planes().find(weight_slot);
+  if (it != lo_planes().end()) it->second.serial = slot_serial(weight_slot);
+}
+}  // namespace vb
+}  // extern "C++"
 
 int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias, vb_tensor* out) {
   VB_CHECK(weight->rank == 2 && x->rank >= 1, "linear expects weight [out, in]");

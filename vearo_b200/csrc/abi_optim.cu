@@ -28,6 +28,8 @@ struct Opt {
   void* d_partials = nullptr;  // float[nchunks]
   void* d_active = nullptr;    // uint8[nparams]
   std::vector<vb_slot> retained;
+  std::vector<OptChunk> h_chunks;          // host copy of the chunk table (re-uploaded when a weight gains or loses its lo plane)
+  std::vector<float*> lo_base;             // per parameter: the lo plane its chunks write to (null: none)
   // 8-bit AdamW: byte offset of every parameter's share of the int8 planes, their common length, and the parameter sizes
   std::vector<i64> off8, numel8; i64 total8 = 0;
 };
@@ -127,7 +129,7 @@ int vb_opt_create(const vb_opt_config* cfg, const vb_tensor* params, const vb_te
     float *pw, *pg; VB_TRY(tensor_ptr(&params[i], &pw)); VB_TRY(tensor_ptr(&grads[i], &pg));
     i64 cnt = numel(params[i]);
     for (i64 c = 0; c < cnt; c += kChunk) {
-      OptChunk ch; ch.w = pw + c; ch.g = pg + c; ch.ms = ch.vs = nullptr;
+      OptChunk ch; ch.w = pw + c; ch.g = pg + c; ch.ms = ch.vs = nullptr; ch.lo = nullptr;
       if (q8) {
         ch.m = reinterpret_cast<float*>(st8 + off + c); ch.v = reinterpret_cast<float*>(st8 + total + off + c);
         ch.ms = scales8 + (off + c) / 256; ch.vs = scales8 + total / 256 + (off + c) / 256;
@@ -140,6 +142,7 @@ int vb_opt_create(const vb_opt_config* cfg, const vb_tensor* params, const vb_te
     VB_TRY(slot_retain(grads[i].slot)); o->retained.push_back(grads[i].slot);
   }
   o->nchunks = (int)chunks.size();
+  o->h_chunks = chunks; o->lo_base.assign((size_t)n, nullptr);
   VB_TRY(scratch_alloc((chunks.size() + 1) * sizeof(OptChunk), &o->d_chunks));
   VB_TRY(scratch_alloc((chunks.size() + 1) * sizeof(float), &o->d_partials));
   VB_TRY(scratch_alloc((size_t)n + 16, &o->d_active));
@@ -205,11 +208,30 @@ int vb_opt_step(int id, const uint8_t* active, float max_norm, float grad_scale,
     VB_TRY(launch_sumsq_chunks((const OptChunk*)o->d_chunks, o->nchunks, d_active, (float*)o->d_partials));
     VB_TRY(launch_sum_partials((const float*)o->d_partials, o->nchunks, d_normsq));
   }
+  // weights that keep a lo plane for the tensor-core GEMM get it rewritten by the update itself
+  {
+    bool changed = false;
+    std::vector<float*> wbase((size_t)o->nparams, nullptr);
+    for (int i = 0; i < o->nparams; ++i) {
+      float* lb = lo_plane_base_for(o->retained[2 * (size_t)i], &wbase[i]);
+      if (lb != o->lo_base[i]) { o->lo_base[i] = lb; changed = true; }
+    }
+    if (changed && o->nchunks > 0) {
+      for (OptChunk& ch : o->h_chunks) ch.lo = o->lo_base[ch.param] ? o->lo_base[ch.param] + (ch.w - wbase[ch.param]) : nullptr;
+      VB_CUDA(cudaMemcpyAsync(o->d_chunks, o->h_chunks.data(), o->h_chunks.size() * sizeof(OptChunk), cudaMemcpyHostToDevice, ctx().stream));
+    }
+  }
   float bc1 = 1.0f, bc2 = 1.0f;
   if (c.kind != VB_OPT_SGD) { bc1 = 1.0f - powi(c.beta1, (int)o->t); bc2 = 1.0f - powi(c.beta2, (int)o->t); }
   VB_TRY(launch_opt_multi((const OptChunk*)o->d_chunks, o->nchunks, d_active, c.kind, d_normsq, max_norm, grad_scale,
                           c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.momentum, bc1, bc2));
-  for (size_t i = 0; i < o->retained.size(); i += 2) slot_touch(o->retained[i]);      // the parameters' contents changed
+  // the updated parameters' contents changed; a lo plane that was current before stays so (the kernel rewrote the updated part)
+  {
+    std::vector<uint8_t> was((size_t)o->nparams, 0);
+    for (int i = 0; i < o->nparams; ++i) was[i] = o->lo_base[i] && lo_plane_is_current(o->retained[2 * (size_t)i]);
+    for (int i = 0; i < o->nparams; ++i) if (!(active && !active[i])) slot_touch(o->retained[2 * (size_t)i]);
+    for (int i = 0; i < o->nparams; ++i) if (was[i]) lo_plane_mark_current(o->retained[2 * (size_t)i]);
+  }
   if (total_norm) {
     float h = 0.0f;
     if (o->nchunks > 0) {

@@ -164,7 +164,21 @@ int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 
 
 // optim.cu
 // (8-bit AdamW: m and v point at int8 values, ms and vs at the scales of the chunk's 256-element blocks)
-struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param; float* ms; float* vs; };
+// (lo: where the TF32 remainders of the updated weights go when the weight keeps a lo plane for the tensor-core GEMM, else null)
+struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param; float* ms; float* vs; float* lo; };
+// abi.cu: the lo plane kept for a weight slot (null if none) and the slot's base address; and the note that the plane was just
+// brought up to date with the slot's present contents by the caller
+float* lo_plane_base_for(vb_slot weight_slot, float** weight_base);
+void lo_plane_mark_current(vb_slot weight_slot);
+bool lo_plane_is_current(vb_slot weight_slot);
+#ifdef __CUDACC__
+// lo part of x when the tensor core takes the raw x as hi (it reads x cut to 10 mantissa bits): the remainder is exact in f32 and
+// is rounded to TF32 (nearest, ties away) with integer arithmetic on the bit pattern
+__device__ __forceinline__ float tf32_remainder(float x) {
+  float d = x - __uint_as_float(__float_as_uint(x) & 0xffffe000u);
+  return __uint_as_float((__float_as_uint(d) + 0x1000u) & 0xffffe000u);
+}
+#endif
 int launch_adamw_single(float* w, const float* g, float* m, float* v, i64 n, float lr, float b1, float b2, float eps, float wd,
                         float bc1, float bc2);
 int launch_sgd_single(float* w, const float* g, float* vel, i64 n, float lr, float mu, float wd);

@@ -37,7 +37,7 @@ __device__ __forceinline__ float clip_scale(const float* normsq, float max_norm,
 
 template <int KIND>
 __device__ __forceinline__ void update_range(float* __restrict__ w, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
-                                             int n, float gs, const Hyper& h) {
+                                             int n, float gs, const Hyper& h, float* __restrict__ lo = nullptr) {
   bool vec = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
                (KIND == 0 ? reinterpret_cast<uintptr_t>(v) : 0)) & 15) == 0;
   int n4 = vec ? n / 4 : 0;
@@ -53,11 +53,13 @@ __device__ __forceinline__ void update_range(float* __restrict__ w, const float*
       sgd_elem(ww.x, gg.x, mm.x, h); sgd_elem(ww.y, gg.y, mm.y, h); sgd_elem(ww.z, gg.z, mm.z, h); sgd_elem(ww.w, gg.w, mm.w, h);
     }
     reinterpret_cast<float4*>(w)[i] = ww; reinterpret_cast<float4*>(m)[i] = mm;
+    if (lo) reinterpret_cast<float4*>(lo)[i] = make_float4(tf32_remainder(ww.x), tf32_remainder(ww.y), tf32_remainder(ww.z), tf32_remainder(ww.w));
   }
   for (int i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
     float ww = w[i], gg = g[i] * gs, mm = m[i];
     if (KIND == 0) { float vv = v[i]; adamw_elem(ww, gg, mm, vv, h); v[i] = vv; } else sgd_elem(ww, gg, mm, h);
     w[i] = ww; m[i] = mm;
+    if (lo) lo[i] = tf32_remainder(ww);
   }
 }
 
@@ -141,6 +143,7 @@ __global__ void __launch_bounds__(256, 4) k_opt_adamw8(const OptChunk* __restric
       for (int hf = 0; hf < 2; ++hf) {
         const int e = base + hf * 128 + lane * 4;
         *reinterpret_cast<float4*>(c.w + e) = make_float4(w[hf * 4], w[hf * 4 + 1], w[hf * 4 + 2], w[hf * 4 + 3]);
+        if (c.lo) *reinterpret_cast<float4*>(c.lo + e) = make_float4(tf32_remainder(w[hf * 4]), tf32_remainder(w[hf * 4 + 1]), tf32_remainder(w[hf * 4 + 2]), tf32_remainder(w[hf * 4 + 3]));
         *reinterpret_cast<char4*>(m8 + e) = make_char4((signed char)qm[hf * 4], (signed char)qm[hf * 4 + 1], (signed char)qm[hf * 4 + 2], (signed char)qm[hf * 4 + 3]);
         *reinterpret_cast<char4*>(v8 + e) = make_char4((signed char)qv[hf * 4], (signed char)qv[hf * 4 + 1], (signed char)qv[hf * 4 + 2], (signed char)qv[hf * 4 + 3]);
       }
@@ -148,7 +151,7 @@ __global__ void __launch_bounds__(256, 4) k_opt_adamw8(const OptChunk* __restric
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const int o = (k >> 2) * 128 + lane * 4 + (k & 3);
-        if (ok[k]) { c.w[base + o] = w[k]; m8[base + o] = (int8_t)qm[k]; v8[base + o] = (int8_t)qv[k]; }
+        if (ok[k]) { c.w[base + o] = w[k]; m8[base + o] = (int8_t)qm[k]; v8[base + o] = (int8_t)qv[k]; if (c.lo) c.lo[base + o] = tf32_remainder(w[k]); }
       }
     }
     if (lane == 0) { c.ms[b] = __fdiv_rn(mx_m, 127.0f); c.vs[b] = __fdiv_rn(mx_v, 127.0f); }
@@ -161,7 +164,7 @@ __global__ void __launch_bounds__(256) k_opt_multi(const OptChunk* __restrict__ 
   OptChunk c = chunks[blockIdx.x];
   if (active && !active[c.param]) return;
   float gs = clip_scale(normsq, max_norm, grad_scale);
-  update_range<KIND>(c.w, c.g, c.m, c.v, c.n, gs, h);
+  update_range<KIND>(c.w, c.g, c.m, c.v, c.n, gs, h, c.lo);
 }
 int launch_opt_multi(const OptChunk* chunks, int nchunks, const uint8_t* active, int kind, const float* normsq,
                      float max_norm, float grad_scale, float lr, float b1, float b2, float eps, float wd, float mu,
