@@ -401,7 +401,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   uint64_t* full = bars; uint64_t* empty = bars + stages; uint64_t* conv = bars + 2 * stages; uint64_t* lo_empty = conv + lstages;
   uint64_t* tmem_full = lo_empty + lstages;
   uint64_t* tmem_empty = tmem_full + 1;
-  uint32_t* tmem_slot = (uint32_t*)(tmem_empty + 1);
+  uint64_t* stg_free = tmem_empty + 1;          // pre-split B in the persistent modes: the epilogue has left the staging area (= the lo ring)
+  uint32_t* tmem_slot = (uint32_t*)(stg_free + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   volatile int* last_flag = abort_flag + 1;
 
@@ -414,6 +415,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], CW * CG + (p.b_lo ? 1 : 0)); mbar_init(&lo_empty[s], 1); }    // (+1: the producer's expect_tx arrival for the pre-split lo part of B)
     mbar_init(tmem_full, 1);
     mbar_init(tmem_empty, kEpiWarps * CG);
+    mbar_init(stg_free, CW);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -448,7 +450,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       int s = 0; uint32_t ph = 1;       // ring slot and the parity of `empty` that says the slot was released
       bool ok = true;
       const int amode = p.a_mn + p.a_fold, bmode = p.b_mn + p.b_fold;
+      int unit = 0;
       while (ok && wi.next(p, wk)) {
+        // pre-split B, persistent modes: the lo ring doubles as the epilogue's staging area, so the lo parts of this unit may not
+        // land before the converter warps have finished the previous unit's epilogue
+        if (p.b_lo && p.persistent && unit > 0 && !mbar_wait(stg_free, (uint32_t)(unit - 1) & 1, abort_flag)) { ok = false; break; }
+        ++unit;
         const int ab2 = p.a_bcast2 ? 0 : wk.b2, ab1 = p.a_bcast1 ? 0 : wk.b1, bb2 = p.b_bcast2 ? 0 : wk.b2, bb1 = p.b_bcast1 ? 0 : wk.b1;
         const int m0 = (wk.tile_m * CG + (int)rank) * BM, n0 = wk.tile_n * bn + (int)rank * bnc;
         int k = wk.kb0 * bk;
@@ -763,6 +770,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       }
       // the staging area is the lo ring, and last_flag is per unit: nobody starts converting the next unit before all have finished this one
       if (p.persistent) asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
+      if (p.b_lo && p.persistent && lane == 0) mbar_arrive(stg_free);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1111,13 +1119,15 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     else p.tma_out = make_out_map(&map_c, (float*)part.p, g.N, g.M, (i64)splits * nb, 1, g.N, g.M * g.N, 0) ? 1 : 0;
   }
 
-  // Pre-split lo part of B: tiled launches only (in the persistent modes the producer runs ahead into the next tile while the lo
-  // ring is the epilogue's staging area), B consumed in place (the lo plane has B's layout), raw hi operand.
+  // Pre-split lo part of B: B consumed in place (the lo plane has B's layout), raw hi operand.  (In the persistent modes the
+  // producer holds the lo parts of the next tile back until the epilogue has left the lo ring, its staging area.)
   CUtensorMap map_blo;
   memset(&map_blo, 0, sizeof map_blo);
   static int blo_env = -1;
   if (blo_env < 0) { const char* e = getenv("VB200_TC_B_LO"); blo_env = (e && e[0] == '0') ? 0 : 1; }
-  if (blo_env && g.B_lo && !hold_b.p && CG == 1 && !persistent && !round_robin && !(kTiming && getenv("VB200_TC_DEBUG"))) {
+  static int blo_p_env = -1;
+  if (blo_p_env < 0) { const char* e = getenv("VB200_TC_B_LO_PERSISTENT"); blo_p_env = (e && e[0] == '0') ? 0 : 1; }
+  if (blo_env && g.B_lo && !hold_b.p && CG == 1 && (blo_p_env || (!persistent && !round_robin)) && !(kTiming && getenv("VB200_TC_DEBUG"))) {
     Operand obl = ob; obl.p = g.B_lo;
     bool f2 = false;
     if (tma_ok(obl, g.nb1, g.nb2) && make_map(&map_blo, obl, g.K, g.nb1, g.nb2, p.bn / CG, bk, &f2) == VB_OK && f2 == fold_b) p.b_lo = 1;
@@ -1129,7 +1139,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   if (!p.raw_hi) p.b_lo = 0;           // the plane holds remainders against the raw (cut) hi operand
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("VB200_TC_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
   { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 220 * 1024 && (size_t)l * raw_bytes >= 32 * 1024) { p.stages = r; p.lstages = l; } } }
-  size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 2) * sizeof(uint64_t) + 16 + 1024;
+  size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 3) * sizeof(uint64_t) + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
