@@ -674,6 +674,43 @@ def test_matmul_tensor_core_batched_views(vb):
     both(vb, case)
 
 
+def test_linear_weight_lo_plane_exact_and_never_stale(vb):
+    """A Linear weight of 2^18 elements or more keeps its TF32 remainders beside it and the GEMM loads them instead of
+    recomputing them.  The product must be bit-identical to the same product without the plane (a plain matmul with the
+    transposed view), and the plane must follow every change of the weight: a write through the ABI, an in-place
+    accumulate, an optimizer step."""
+    x0, w0, w1 = rnd(401, 1024, 512, scale=0.5), rnd(402, 512, 512, scale=0.05), rnd(403, 512, 512, scale=0.05)
+    T = vb.Tensor
+    x, w = T.from_numpy(x0), T.from_numpy(w0, True)
+
+    def check(tag):
+        a = x.linear(w, None).numpy()
+        b = x.matmul(w.transpose(0, 1)).numpy()
+        assert np.array_equal(a, b), tag
+        return a
+    y0 = check("fresh plane")
+    assert np.array_equal(check("plane reused"), y0)
+    w.write(w1)                                            # vb_write advances the slot's serial
+    y1 = check("after write")
+    assert not np.array_equal(y0, y1)
+    ref = x0.astype(np.float64) @ w1.T.astype(np.float64)
+    assert np.abs(y1 - ref).max() < 1e-4
+    opt = vb.AdamW([w], 1e-2, 0.9, 0.999, 1e-8, 0.0)      # the update rewrites the plane itself
+    for _ in range(2):
+        vb.zero_gradients(); vb.reset_active_tape()
+        x.linear(w, None).mul(T.from_numpy(rnd(404, 1024, 512))).sum(1, False).sum(0, False).backward()
+        opt.step()
+        y2 = check("after optimizer step")
+    assert not np.array_equal(y1, y2)
+    gx = T.from_numpy(x0, True)                            # the input-gradient product uses the plane too
+    vb.zero_gradients(); vb.reset_active_tape()
+    go = rnd(405, 1024, 512)
+    gx.linear(w, None).mul(T.from_numpy(go)).sum(1, False).sum(0, False).backward()
+    want = T.from_numpy(go).matmul(w).numpy()
+    assert np.array_equal(gx.grad().numpy(), want)
+    vb.check_errors()
+
+
 def test_linear_tensor_core_with_bias_and_backward(vb):
     x0, w0, b0, go = rnd(65, 512, 384, scale=0.5), rnd(66, 640, 384, scale=0.05), rnd(67, 640), rnd(68, 512, 640, scale=0.1)
 
