@@ -208,6 +208,7 @@ int vb_softmax_backward(const vb_tensor* x, const vb_tensor* g, int dim, vb_tens
   return inner == 1 ? launch_softmax_backward_rows(px, pg, po, outer, d) : launch_softmax_backward_strided(px, pg, po, outer, d, inner);
 }
 
+namespace { bool activation_lo_enabled(); void lo_plane_adopt(vb_slot slot, vb_slot lo, i64 n); }     // defined with the lo-plane table below
 int vb_layernorm(const vb_tensor* x, const vb_tensor* w, const vb_tensor* b, float eps, vb_tensor* out) {
   VB_CHECK(x->rank >= 1, "LayerNorm input must be at least rank 1");
   i64 rows, c; VB_TRY(rows_of(x, &rows, &c));
@@ -217,7 +218,14 @@ int vb_layernorm(const vb_tensor* x, const vb_tensor* w, const vb_tensor* b, flo
   VB_TRY(contiguous_ptr(x, &px, hx)); VB_TRY(contiguous_ptr(w, &pw, hw)); VB_TRY(contiguous_ptr(b, &pb, hb));
   VB_TRY(new_output(out, x->rank, x->dims));
   float* po; VB_TRY(slot_ptr(out->slot, &po));
-  return launch_layernorm(px, pw, pb, po, rows, c, eps);
+  // A large normalised activation is about to be the B operand of a weight-gradient product: its TF32 remainders are written
+  // along with it (4 more bytes per element) and kept as the lo plane of the output's slot until that slot is released.
+  vb_slot lo_slot = 0; float* plo = nullptr;
+  if (activation_lo_enabled() && rows >= 1024 && rows * c >= ((i64)1 << 18) && slot_alloc(rows * c, false, &lo_slot) == VB_OK) slot_ptr(lo_slot, &plo);
+  bool lo_done = false;
+  int rc = launch_layernorm(px, pw, pb, po, rows, c, eps, plo, &lo_done);
+  if (lo_slot) { if (rc == VB_OK && lo_done) lo_plane_adopt(out->slot, lo_slot, rows * c); else slot_release(lo_slot, nullptr); }
+  return rc;
 }
 int vb_layernorm_backward(const vb_tensor* x, const vb_tensor* w, const vb_tensor* b, const vb_tensor* g, float eps,
                           vb_tensor* gx, vb_tensor* gw, vb_tensor* gb) {
@@ -725,6 +733,26 @@ int vb_fill(const vb_tensor* dst, float value) {
 namespace {
 struct LoPlane { vb_slot lo = 0; uint64_t serial = 0; i64 numel = 0; };
 std::unordered_map<vb_slot, LoPlane>& lo_planes() { static auto* m = new std::unordered_map<vb_slot, LoPlane>(); return *m; }
+bool activation_lo_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("VB200_ACT_LO"); const char* w = getenv("VB200_WEIGHT_LO"); on = ((e && e[0] == '0') || (w && w[0] == '0')) ? 0 : 1; }
+  return on != 0;
+}
+// the plane `lo` (a slot of its own) now belongs to `slot`, whose present contents it matches
+void lo_plane_adopt(vb_slot slot, vb_slot lo, i64 n) {
+  LoPlane& e = lo_planes()[slot];
+  if (e.lo) slot_release(e.lo, nullptr);
+  e.lo = lo; e.numel = n; e.serial = slot_serial(slot);
+}
+// the plane of an activation, if its producer left one and the contents have not changed since (never made here)
+const float* existing_lo_plane(const vb_tensor* t, const float* pt) {
+  auto& tab = lo_planes();
+  auto it = tab.find(t->slot);
+  if (it == tab.end() || it->second.lo == 0 || it->second.serial != slot_serial(t->slot)) return nullptr;
+  float *base, *lo; i64 n;
+  if (slot_ptr(t->slot, &base, &n) != VB_OK || n != it->second.numel || slot_ptr(it->second.lo, &lo) != VB_OK) return nullptr;
+  return lo + (pt - base);
+}
 const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
   static int on = -1;
   if (on < 0) { const char* e = getenv("VB200_WEIGHT_LO"); on = (e && e[0] == '0') ? 0 : 1; }
@@ -755,6 +783,15 @@ const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
 }  // namespace
 extern "C++" {
 namespace vb {
+void lo_plane_on_release(vb_slot slot) {
+  auto& tab = lo_planes();
+  if (tab.empty()) return;
+  auto it = tab.find(slot);
+  if (it == tab.end()) return;
+  vb_slot lo = it->second.lo;
+  tab.erase(it);
+  if (lo) slot_release(lo, nullptr);
+}
 float* lo_plane_base_for(vb_slot weight_slot, float** weight_base) {
   auto& tab = lo_planes();
   auto it = tab.find(weight_slot);
@@ -834,6 +871,7 @@ static int linear_backward_impl(const vb_tensor* x, const vb_tensor* weight, con
       g.A = pg; g.a_rs = 1; g.a_cs = outf;
       g.B = px; g.b_rs = in; g.b_cs = 1;
       g.C = p; g.c_rs = in; g.c_cs = 1;
+      if (!hx.p) g.B_lo = existing_lo_plane(x, px);        // x consumed in place and its producer left a lo plane
       VB_TRY(launch_gemm(g));
     }
   }

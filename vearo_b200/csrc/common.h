@@ -103,7 +103,7 @@ int launch_softmax_strided(const float* x, float* out, i64 outer, i64 d, i64 inn
 int launch_softmax_backward_rows(const float* x, const float* g, float* out, i64 rows, i64 d);
 int launch_softmax_backward_strided(const float* x, const float* g, float* out, i64 outer, i64 d, i64 inner);
 // norm.cu
-int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps);
+int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps, float* out_lo = nullptr, bool* lo_done = nullptr);
 int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps);
 int launch_batchnorm(const float* x, const float* gamma, const float* beta, float* rm, float* rv, float* out,
                      i64 n, i64 c, i64 hw, bool training, float momentum, float eps);
@@ -171,6 +171,7 @@ struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param
 float* lo_plane_base_for(vb_slot weight_slot, float** weight_base);
 void lo_plane_mark_current(vb_slot weight_slot);
 bool lo_plane_is_current(vb_slot weight_slot);
+void lo_plane_on_release(vb_slot slot);      // the slot is gone: so is a lo plane kept for it
 #ifdef __CUDACC__
 // lo part of x when the tensor core takes the raw x as hi (it reads x cut to 10 mantissa bits): the remainder is exact in f32 and
 // is rounded to TF32 (nearest, ties away) with integer arithmetic on the bit pattern

@@ -33,7 +33,7 @@ __device__ __forceinline__ float bsum(float v, float* red) {
 // ---- LayerNorm, warp-per-row register-resident path (C % 4 == 0, C <= 128 * VPT) ------------
 template <int VPT>
 __global__ void __launch_bounds__(256) k_ln_fwd_warp(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
-                                                     float* __restrict__ out, i64 rows, int C, float eps) {
+                                                     float* __restrict__ out, i64 rows, int C, float eps, float* __restrict__ out_lo) {
   int lane = threadIdx.x & 31;
   i64 warp = (blockIdx.x * (i64)blockDim.x + threadIdx.x) >> 5;
   i64 nwarps = ((i64)gridDim.x * blockDim.x) >> 5;
@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(256) k_ln_fwd_warp(const float* __restrict__ x
         o.x = ((v[i].x - mean) * inv) * ww.x + bb.x; o.y = ((v[i].y - mean) * inv) * ww.y + bb.y;
         o.z = ((v[i].z - mean) * inv) * ww.z + bb.z; o.w = ((v[i].w - mean) * inv) * ww.w + bb.w;
         orow[i * 32 + lane] = o;
+        // (the TF32 remainders of the output, for the tensor-core product that will take it as its B operand)
+        if (out_lo) reinterpret_cast<float4*>(out_lo + r * C)[i * 32 + lane] = make_float4(tf32_remainder(o.x), tf32_remainder(o.y), tf32_remainder(o.z), tf32_remainder(o.w));
       }
     }
   }
@@ -216,7 +218,8 @@ __global__ void k_ln_bwd_cols(const float* __restrict__ x, const float* __restri
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps) {
+int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps, float* out_lo, bool* lo_done) {
+  if (lo_done) *lo_done = false;
   if (rows <= 0 || c <= 0) return VB_OK;
   cudaStream_t st = ctx().stream;
   ProfScope prof("layernorm_fwd", 2.0 * (double)rows * (double)c * 4.0);
@@ -224,9 +227,11 @@ int launch_layernorm(const float* x, const float* w, const float* b, float* out,
   if (fast) {
     int vpt = (int)((c + 127) / 128);
     i64 blocks = (rows + 7) / 8; i64 cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
-#define LN_FWD(V) case V: k_ln_fwd_warp<V><<<(unsigned)blocks, 256, 0, st>>>(x, w, b, out, rows, (int)c, eps); break;
+    float* lo = (out_lo && al16(out_lo)) ? out_lo : nullptr;
+#define LN_FWD(V) case V: k_ln_fwd_warp<V><<<(unsigned)blocks, 256, 0, st>>>(x, w, b, out, rows, (int)c, eps, lo); break;
     switch (vpt) { LN_FWD(1) LN_FWD(2) LN_FWD(3) LN_FWD(4) LN_FWD(5) LN_FWD(6) LN_FWD(7) LN_FWD(8) }
 #undef LN_FWD
+    if (lo && lo_done) *lo_done = true;
   } else {
     int t = 32; while (t < 256 && t * 4 < c) t <<= 1;
     k_ln_fwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, b, out, nullptr, c, eps);

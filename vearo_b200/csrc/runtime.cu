@@ -110,6 +110,7 @@ int slot_release(vb_slot s, int* freed) {
   Slot* sl; VB_TRY(slot_get(s, &sl));
   if (freed) *freed = 0;
   if (--sl->refs == 0) {
+    lo_plane_on_release(s);
     arena_free(sl->ptr);
     sl->ptr = nullptr; sl->numel = 0;
     g_free_ids.push_back(s);
