@@ -832,6 +832,7 @@ int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias
   g.B = pw; g.b_rs = weight->strides[1]; g.b_cs = weight->strides[0];   // W^T
   g.C = po; g.c_rs = g.N; g.c_cs = 1; g.bias = pb;
   if (rows >= 1024) g.B_lo = weight_lo_plane(weight, pw);
+  if (g.B_lo && !hx.p) g.A_lo = existing_lo_plane(x, px);        // a normalised input brings its own remainders
   return launch_gemm(g);
 }
 // gw_into / gb_into: existing contiguous tensors the weight and bias gradients are written into (a parameter's slice of

@@ -151,6 +151,7 @@ struct GemmArgs {
   // Optional: the TF32 remainders of B (lo = tf32(b - cut_to_tf32(b)), what the tensor-core kernel otherwise computes for every
   // k-block of every tile), laid out exactly like B.  Worth it for an operand used by many tiles and several products (weights).
   const float* B_lo;
+  const float* A_lo;      // the same for A (an activation whose producer wrote its remainders)
 };
 int launch_gemm(const GemmArgs& g);
 int launch_tf32_lo(const float* x, float* lo, i64 n);      // gemm_tc.cu: lo[i] as above

@@ -68,6 +68,7 @@ struct TcParams {
   int a_bcast1, a_bcast2, b_bcast1, b_bcast2;     // 1: batch level is broadcast for that operand (coordinate 0)
   int tmem_cols;                                  // tensor-memory columns allocated: bn rounded up to a power of two
   int b_lo;                                       // the lo part of B comes pre-split from memory (map_blo) instead of from the converters
+  int a_lo;                                       // ... and the lo part of A (map_alo); a_lo implies b_lo (the converters then have nothing to split)
   int tma_out;                                    // results leave through TMA stores of the staged 32 x 32 blocks (map_c)
   int bk;                                         // k per stage: 16, or 32 for the narrow (64-wide) tiles whose per-stage hand-offs dominate
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
@@ -387,7 +388,7 @@ __device__ __forceinline__ void trace_event(const TcParams& p, int ev, int kb) {
 template <int CG, int CW>
 __global__ void __launch_bounds__(64 + 32 * CW, CW == 8 ? 2 : 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
-          const __grid_constant__ CUtensorMap map_blo, TcParams p) {
+          const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_alo, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ]
   // (doubles as the epilogue's staging area: nothing converts while a tile is being stored), barriers.
@@ -473,8 +474,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             const int l = it % lstages;                                   // (derived, not carried: this role has no register to spare)
             const uint32_t lph = (((uint32_t)(it / lstages)) & 1u) ^ 1u;    // parity of `lo_empty` that says the slot was released
             if (it >= lstages && !mbar_wait(&lo_empty[l], lph, abort_flag)) { ok = false; break; }
-            mbar_arrive_expect_tx(&conv[l], b_bytes);
+            mbar_arrive_expect_tx(&conv[l], p.a_lo ? raw_bytes : b_bytes);
             tma_load_tile(lo_ring + (size_t)l * raw_bytes + a_bytes, &map_blo, &conv[l], bmode, bnc, n0, k, bb2, bb1, bk);
+            if (p.a_lo) tma_load_tile(lo_ring + (size_t)l * raw_bytes, &map_alo, &conv[l], amode, BM, m0, k, ab2, ab1, bk);
           }
           trace_event(p, 1, it);
           if (++s == stages) { s = 0; ph ^= 1; }
@@ -592,7 +594,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         if (ct == 0) trace_event(p, 2, it);
         float4* hi = (float4*)(smem + (size_t)s * raw_bytes);
         float4* lo = (float4*)(lo_ring + (size_t)l * raw_bytes);
-        const int n4 = (p.b_lo || (kTiming && (p.debug & 256))) ? (int)(a_bytes / 16) : (int)(raw_bytes / 16);     // (timing experiment 256: only the A part is split)
+        const int n4 = p.a_lo ? 0 : ((p.b_lo || (kTiming && (p.debug & 256))) ? (int)(a_bytes / 16) : (int)(raw_bytes / 16));     // (timing experiment 256: only the A part is split)
         if (kTiming && (p.debug & 1)) {
         } else if (p.raw_hi) {
 #pragma unroll 3
@@ -1132,11 +1134,20 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     bool f2 = false;
     if (tma_ok(obl, g.nb1, g.nb2) && make_map(&map_blo, obl, g.K, g.nb1, g.nb2, p.bn / CG, bk, &f2) == VB_OK && f2 == fold_b) p.b_lo = 1;
   }
+  CUtensorMap map_alo;
+  memset(&map_alo, 0, sizeof map_alo);
+  static int alo_env = -1;
+  if (alo_env < 0) { const char* e = getenv("VB200_TC_A_LO"); alo_env = (e && e[0] == '0') ? 0 : 1; }
+  if (alo_env && p.b_lo && g.A_lo && !hold_a.p) {
+    Operand oal = oa; oal.p = g.A_lo;
+    bool f2 = false;
+    if (tma_ok(oal, g.nb1, g.nb2) && make_map(&map_alo, oal, g.K, g.nb1, g.nb2, BM, bk, &f2) == VB_OK && f2 == fold_a) p.a_lo = 1;
+  }
 
   static int raw_hi_env = -1;
   if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
   p.raw_hi = raw_hi_env;
-  if (!p.raw_hi) p.b_lo = 0;           // the plane holds remainders against the raw (cut) hi operand
+  if (!p.raw_hi) p.b_lo = p.a_lo = 0;           // the plane holds remainders against the raw (cut) hi operand
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("VB200_TC_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
   { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 220 * 1024 && (size_t)l * raw_bytes >= 32 * 1024) { p.stages = r; p.lstages = l; } } }
   size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 3) * sizeof(uint64_t) + 16 + 1024;
@@ -1168,12 +1179,12 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
       cfg.attrs = attr; cfg.numAttrs = 1;
       { static int occ = -1; if (occ < 0) { const char* e = getenv("VB200_TC_OCC"); occ = (e && e[0] == '1') ? 1 : 0; }
         if (occ) { int n = 0; cudaError_t r = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<2, 8>, &cfg); fprintf(stderr, "[gemm_tc] max active clusters %d (err %d), smem %zu, grid %u\n", n, (int)r, smem, grid.x * grid.y * grid.z); occ = 0; } }
-      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, map_c, map_blo, p));
-      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, map_c, map_blo, p));
+      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, map_c, map_blo, map_alo, p));
+      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, map_c, map_blo, map_alo, p));
     } else if (CW == 16) {
-      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, p);
+      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, p);
     } else {
-      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, p);
+      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, p);
     }
     VB_LAUNCH_CHECK();
     if (kTiming && (p.debug & 64)) {
