@@ -783,6 +783,7 @@ const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
 }  // namespace
 extern "C++" {
 namespace vb {
+void lo_planes_forget_all() { lo_planes().clear(); }
 void lo_plane_on_release(vb_slot slot) {
   auto& tab = lo_planes();
   if (tab.empty()) return;

@@ -172,6 +172,7 @@ struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param
 float* lo_plane_base_for(vb_slot weight_slot, float** weight_base);
 void lo_plane_mark_current(vb_slot weight_slot);
 bool lo_plane_is_current(vb_slot weight_slot);
+void lo_planes_forget_all();                 // the slot table is being torn down
 void lo_plane_on_release(vb_slot slot);      // the slot is gone: so is a lo plane kept for it
 #ifdef __CUDACC__
 // lo part of x when the tensor core takes the raw x as hi (it reads x cut to 10 mantissa bits): the remainder is exact in f32 and

@@ -196,6 +196,7 @@ int vb_shutdown(void) {
   if (!g_ctx.ready) return VB_OK;
   cudaStreamSynchronize(g_ctx.stream);
   cudaStreamSynchronize(g_ctx.comm_stream);
+  lo_planes_forget_all();
   for (auto& kv : g_arena.sizes) cudaFree(kv.first);
   g_arena.free_blocks.clear(); g_arena.sizes.clear(); g_arena.cached = g_arena.live = g_arena.peak = 0;
   g_slots.assign(1, Slot()); g_free_ids.clear(); g_live_slots = 0;
