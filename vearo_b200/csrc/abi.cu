@@ -51,22 +51,12 @@ int binary(int op, const vb_tensor* a, const vb_tensor* b, vb_tensor* out) {
   return launch_binary_strided(op, pa, pb, po, n, s);
 }
 
-bool activation_lo_enabled(); void lo_plane_adopt(vb_slot slot, vb_slot lo, i64 n);     // defined with the lo-plane table below
 int unary(int op, const vb_tensor* x, vb_tensor* out) {
   Temp hx; const float* px;
   VB_TRY(contiguous_ptr(x, &px, hx));
   VB_TRY(new_output(out, x->rank, x->dims));
   float* po; VB_TRY(slot_ptr(out->slot, &po));
-  // (experiment, VB200_GELU_LO=1: a large GELU output -- the input of the second MLP projection -- gets a lo plane like a LayerNorm output)
-  static int gelu_lo = -1;
-  if (gelu_lo < 0) { const char* e = getenv("VB200_GELU_LO"); gelu_lo = (e && e[0] == '1') ? 1 : 0; }
-  const i64 n = numel(*x);
-  vb_slot lo_slot = 0; float* plo = nullptr;
-  if (op == 1 && gelu_lo && activation_lo_enabled() && x->rank >= 2 && n >= ((i64)1 << 20) && slot_alloc(n, false, &lo_slot) == VB_OK) slot_ptr(lo_slot, &plo);
-  bool lo_done = false;
-  int rc = launch_unary(op, px, po, n, plo, &lo_done);
-  if (lo_slot) { if (rc == VB_OK && lo_done) lo_plane_adopt(out->slot, lo_slot, n); else slot_release(lo_slot, nullptr); }
-  return rc;
+  return launch_unary(op, px, po, numel(*x));
 }
 int unary_backward(int op, const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) {
   VB_CHECK(same_shape(*x, *g), "x and grad_out shapes differ");
@@ -218,6 +208,7 @@ int vb_softmax_backward(const vb_tensor* x, const vb_tensor* g, int dim, vb_tens
   return inner == 1 ? launch_softmax_backward_rows(px, pg, po, outer, d) : launch_softmax_backward_strided(px, pg, po, outer, d, inner);
 }
 
+namespace { bool activation_lo_enabled(); void lo_plane_adopt(vb_slot slot, vb_slot lo, i64 n); }     // defined with the lo-plane table below
 int vb_layernorm(const vb_tensor* x, const vb_tensor* w, const vb_tensor* b, float eps, vb_tensor* out) {
   VB_CHECK(x->rank >= 1, "LayerNorm input must be at least rank 1");
   i64 rows, c; VB_TRY(rows_of(x, &rows, &c));
@@ -739,7 +730,6 @@ int vb_fill(const vb_tensor* dst, float value) {
 // weight's slot; valid while the slot's serial is unchanged (every call of this library that writes into an existing slot --
 // vb_write, vb_copy, vb_fill, vb_accumulate, the optimizer steps -- advances it).  One plane covers the whole slot, so
 // parameters that are views of one block share it.  Returns null where the plane does not pay or cannot be had.
-extern "C++" {
 namespace {
 struct LoPlane { vb_slot lo = 0; uint64_t serial = 0; i64 numel = 0; };
 std::unordered_map<vb_slot, LoPlane>& lo_planes() { static auto* m = new std::unordered_map<vb_slot, LoPlane>(); return *m; }
@@ -791,6 +781,7 @@ const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
   return lo + (pw - base);
 }
 }  // namespace
+extern "C++" {
 namespace vb {
 void lo_planes_forget_all() { lo_planes().clear(); }
 void lo_plane_on_release(vb_slot slot) {

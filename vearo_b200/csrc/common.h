@@ -88,7 +88,7 @@ int launch_binary(int op, const float* a, const float* b, float* out, i64 n);   
 int launch_binary_rowvec(int op, const float* a, const float* b, float* out, i64 n, i64 c, bool b_is_vec); // b (or a) is a length-c vector over the last dim
 int launch_binary_scalar(int op, const float* a, const float* b, float* out, i64 n, bool b_is_scalar);
 int launch_binary_strided(int op, const float* a, const float* b, float* out, i64 n, const Strided& s);
-int launch_unary(int op, const float* x, float* out, i64 n, float* out_lo = nullptr, bool* lo_done = nullptr);          // 0 relu 1 gelu
+int launch_unary(int op, const float* x, float* out, i64 n);          // 0 relu 1 gelu
 int launch_unary_backward(int op, const float* x, const float* g, float* out, i64 n);  // 0 relu 1 gelu
 int launch_scale(const float* x, float alpha, float* out, i64 n);
 int launch_axpy(float* dst, const float* src, i64 n);                 // dst += src

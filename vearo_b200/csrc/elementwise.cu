@@ -142,7 +142,7 @@ int launch_strided_copy(const float* src, float* dst, i64 n, const Strided& s) {
 // Unary forward (OP 0 relu, 1 gelu) and backward (dx = g * f'(x), the mask then a separate
 // multiply as the reference's Relu / Gelu arms do).  12 bytes per element for the backward.
 template <int OP, bool BWD>
-__global__ void k_unary_vec(const float4* __restrict__ x, const float4* __restrict__ g, float4* __restrict__ o, i64 n4, float4* __restrict__ o_lo = nullptr) {
+__global__ void k_unary_vec(const float4* __restrict__ x, const float4* __restrict__ g, float4* __restrict__ o, i64 n4) {
   for (i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x; i < n4; i += (i64)gridDim.x * blockDim.x) {
     float4 v = x[i], r;
     if (BWD) {
@@ -154,7 +154,6 @@ __global__ void k_unary_vec(const float4* __restrict__ x, const float4* __restri
       else { r.x = gelu_f(v.x); r.y = gelu_f(v.y); r.z = gelu_f(v.z); r.w = gelu_f(v.w); }
     }
     o[i] = r;
-    if (!BWD && o_lo) o_lo[i] = make_float4(tf32_remainder(r.x), tf32_remainder(r.y), tf32_remainder(r.z), tf32_remainder(r.w));   // lo plane of the output
   }
 }
 template <int OP, bool BWD>
@@ -166,22 +165,19 @@ __global__ void k_unary_tail(const float* x, const float* g, float* o, i64 start
   else o[i] = OP == 0 ? relu_f(v) : gelu_f(v);
 }
 template <int OP, bool BWD>
-static int unary_impl(const float* x, const float* g, float* o, i64 n, float* o_lo = nullptr, bool* lo_done = nullptr) {
-  if (lo_done) *lo_done = false;
+static int unary_impl(const float* x, const float* g, float* o, i64 n) {
   if (n <= 0) return VB_OK;
   ProfScope prof(BWD ? (OP == 0 ? "relu_bwd" : "gelu_bwd") : (OP == 0 ? "relu_fwd" : "gelu_fwd"), (BWD ? 3.0 : 2.0) * (double)n * 4.0);
   cudaStream_t st = ctx().stream;
   i64 n4 = (aligned16(x) && aligned16(o) && (!BWD || aligned16(g))) ? n / 4 : 0;
-  const bool with_lo = !BWD && o_lo && aligned16(o_lo) && n4 * 4 == n;
-  if (n4) k_unary_vec<OP, BWD><<<grid_for(n4, 256), 256, 0, st>>>((const float4*)x, (const float4*)g, (float4*)o, n4, with_lo ? (float4*)o_lo : nullptr);
-  if (with_lo && lo_done) *lo_done = true;
+  if (n4) k_unary_vec<OP, BWD><<<grid_for(n4, 256), 256, 0, st>>>((const float4*)x, (const float4*)g, (float4*)o, n4);
   i64 rest = n - n4 * 4;
   if (rest) k_unary_tail<OP, BWD><<<(int)((rest + 255) / 256), 256, 0, st>>>(x, g, o, n4 * 4, n);
   VB_LAUNCH_CHECK();
   return VB_OK;
 }
-int launch_unary(int op, const float* x, float* o, i64 n, float* o_lo, bool* lo_done) {
-  return op == 0 ? unary_impl<0, false>(x, nullptr, o, n, o_lo, lo_done) : unary_impl<1, false>(x, nullptr, o, n, o_lo, lo_done);
+int launch_unary(int op, const float* x, float* o, i64 n) {
+  return op == 0 ? unary_impl<0, false>(x, nullptr, o, n) : unary_impl<1, false>(x, nullptr, o, n);
 }
 int launch_unary_backward(int op, const float* x, const float* g, float* o, i64 n) {
   return op == 0 ? unary_impl<0, true>(x, g, o, n) : unary_impl<1, true>(x, g, o, n);
