@@ -30,15 +30,23 @@ WORKLOADS = {
     "gpt-medium": dict(vocab=50304, T=1024, d=1024, heads=16, layers=24, ff=4096, micro_batch=4, lr=6e-4, wd=0.1, clip=1.0),
     # configs[3]: 3 x [conv3x3 -> BatchNorm -> ReLU -> MaxPool] -> AvgPool -> Linear -> cross-entropy, SGD momentum; images/s
     "convnet": dict(kind="convnet", channels=(3, 64, 128, 256), classes=10, hw=32, micro_batch=256, lr=0.1, momentum=0.9, clip=0.0),
+    # configs[1]: the fused-op backward chain, LayerNorm -> GELU -> Linear 768 -> 50304 -> cross-entropy on 8192 rows; rows/s
+    "fused-op": dict(kind="fused-op", N=8192, C=768, V=50304),
     # a seconds-long case for plumbing checks
     "gpt-tiny": dict(vocab=512, T=64, d=128, heads=4, layers=2, ff=512, micro_batch=4, lr=6e-4, wd=0.1, clip=1.0),
 }
 
 
-# ncu, one launch of k_gemm_tc on 8192x768 . 768x3072 (dram__bytes_read.sum + dram__bytes_write.sum); the operands and the
-# result of that launch are 25.2 + 9.4 + 100.7 MB: every operand byte is read once, part of the result is still in L2 at exit
-NCU_TRAFFIC_GEMM_FC1 = {"traffic": 82.7e6, "traffic_unit": "bytes per launch", "traffic_launch": "M8192 N3072 K768 (GPT-small fc1 forward)",
-                        "traffic_algorithmic": 135.3e6}
+# DRAM bytes of ONE launch of the dominant kernel, read from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of
+# `python kernel_cases.py gemm_fc1`: x[8192,768] . W[3072,768]^T with the weight's lo plane loaded beside it.  Operands and result
+# of that launch: 25.2 + 9.4 (+ 9.4 lo plane) + 100.7 MB.  It is a figure from a profile, not of this run: the key says so.
+TRAFFIC_FROM_PROFILE = {"traffic": 82.7e6, "traffic_unit": "bytes per launch", "traffic_launch": "M8192 N3072 K768 (GPT-small fc1 forward)",
+                        "traffic_algorithmic": 135.3e6, "traffic_from_profile": "profiles/gemm_tc_fc1_and_dw.md"}
+
+# Dense TF32 rate of this pool's B200s, measured with `python bench.py --measure-tf32-peak` (torch.matmul, TF32 allowed, 8192^3;
+# best of 10 and a 4 s back-to-back loop, like the bf16 figures of MEASURED_PEAKS.json).  Until that has been run the figures
+# are the bf16 ones halved.
+TF32_PEAK = {"tflops_burst": 1649.5 / 2, "tflops_sustained": 1396.7 / 2, "source": "derived: measured bf16 / 2 (TF32 not measured yet)"}
 
 
 def flops_per_token(c):
@@ -110,7 +118,7 @@ def cpu_baseline_sample(cfg, T=None, threads=0):
     (layers - 1) x (the 2-block time minus the 1-block time)."""
     from oracle import oracle as orc
     from oracle import models as om
-    from tests import modelspec as ms
+    from vearo_b200 import modelspec as ms
     T = T or cfg["T"]
     orc.set_threads(threads)
     times = {}
@@ -138,7 +146,7 @@ def cpu_convnet_step_time(cfg, images=16, steps=1, warmup=0, threads=0):
     """Seconds per step of the CPU oracle on a batch of `images` images of the ConvNet workload (SGD step included)."""
     from oracle import oracle as orc
     from oracle import models as om
-    from tests import modelspec as ms
+    from vearo_b200 import modelspec as ms
     orc.set_threads(threads); orc.reset_all()
     m = om.ConvNet(ms.convnet_params(cfg["channels"], cfg["classes"]))
     opt = orc.SGD(m.parameters(), cfg["lr"], cfg["momentum"], 0.0)
@@ -175,46 +183,224 @@ def run_reference_convnet(args, cfg):
 
 def run_reference(args, cfg, rank):
     """The reference arm: the CPU restatement of the reference's implementation (the Rust crate cannot be
-    built here: no cargo/rustc), all host threads the reference itself would use."""
+    built here: no cargo/rustc), all host threads the reference itself would use.
+
+    Every step is a real step of the stated configuration -- all blocks, full sequence length, full vocabulary,
+    clip + AdamW -- on ONE sequence (micro-batch 1; the cost is linear in the batch).  Such a step takes about a
+    minute of CPU time, so the run is held to a wall budget: one warm-up step, then as many of the requested
+    steps as fit (`steps_timed`); `ms_per_step` is the mean of the steps that were timed, nothing is
+    extrapolated."""
     if rank != 0:
         return
     if cfg.get("kind") == "convnet":
         return run_reference_convnet(args, cfg)
+    if cfg.get("kind") == "fused-op":
+        return run_reference_fused_op(args, cfg)
     from oracle import build as ob
     ob.build()
     from oracle import oracle as orc
     from oracle import models as om
-    from tests import modelspec as ms
-    total = args.steps + args.warmup
-    T = cfg["T"] if total <= 12 else min(cfg["T"], 256)
-    tps0, desc, cores, t1, block = cpu_baseline_sample(cfg, T)          # also yields the per-block time
-    # timed steps: each step is one pass of the 1-block sample; the other blocks are added from `block`
-    params = ms.gpt_params(cfg["vocab"], T, cfg["d"], 1, cfg["ff"])
-    m = om.SimpleGPT(params, cfg["d"], cfg["heads"], 1)
+    from vearo_b200 import modelspec as ms
+    budget = float(os.environ.get("VB200_REF_BUDGET_S", "420"))
+    t_begin = time.perf_counter()
+    orc.set_threads(0); orc.reset_all()
+    T, L = cfg["T"], cfg["layers"]
+    m = om.SimpleGPT(ms.gpt_params(cfg["vocab"], T, cfg["d"], L, cfg["ff"]), cfg["d"], cfg["heads"], L)
     opt = orc.AdamW(m.parameters(), cfg["lr"], 0.9, 0.999, 1e-8, cfg["wd"])
-    ids, tg = ms.gpt_batch(cfg["vocab"], 1, T)
-    durs = []
-    for s in range(total):
+    batches = [ms.gpt_batch(cfg["vocab"], 1, T, seed=i) for i in range(2)]
+
+    def step(i):
+        ids, tg = batches[i % 2]
         t0 = time.perf_counter()
         orc.zero_gradients(); orc.reset_active_tape()
         _, loss = m.forward(orc.Tensor.from_numpy(ids), orc.Tensor.from_numpy(tg))
         loss.backward(); orc.clip_grad_norm(m.parameters(), cfg["clip"]); opt.step()
-        if s >= args.warmup:
-            durs.append(time.perf_counter() - t0 + (cfg["layers"] - 1) * block)
+        return time.perf_counter() - t0, float(loss.numpy()[0])
+    warm = min(args.warmup, 1)
+    for i in range(warm):
+        step(i)
+    durs, loss = [], None
+    while len(durs) < args.steps:
+        d, loss = step(warm + len(durs))
+        durs.append(d)
+        if time.perf_counter() - t_begin + 1.15 * d > budget:
+            break
+    cores = orc.get_threads()
+    orc.reset_all()
     step_s = float(np.mean(durs))
     value = T / step_s
-    sample = ("each step = one T=%d sequence through a 1-block model (measured) + %d x the per-block time %.2f s "
-              "(2-block minus 1-block, measured once before the timed steps)" % (T, cfg["layers"] - 1, block))
-    if T != cfg["T"]:
-        sample += "; T shortened from %d to keep the run within minutes (attention cost per token under-counted, which favours this arm)" % cfg["T"]
+    sample = ("each step = fwd + bwd + clip + AdamW of the full model (%d blocks, T=%d, vocab %d) on one sequence; %d warm-up + %d timed steps "
+              "inside a %.0f s wall budget (requested %d + %d); per-step seconds: %s"
+              % (L, T, cfg["vocab"], warm, len(durs), budget, args.warmup, args.steps, ", ".join("%.1f" % d for d in durs)))
     out = {"impl": "reference", "metric": "GPT-small fwd+bwd+AdamW tokens/s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-           "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
+           "steps": args.steps, "warmup": args.warmup, "steps_timed": len(durs), "warmup_run": warm,
+           "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": args.workload, **{k: cfg[k] for k in ("vocab", "T", "d", "heads", "layers", "ff")}, "micro_batch": 1},
+           "config": {"workload": args.workload, "n_layer": L, "n_head": cfg["heads"], "d_model": cfg["d"], "d_ff": cfg["ff"],
+                      "vocab": cfg["vocab"], "seq_len": T, "micro_batch_per_gpu": 1, "global_batch": 1,
+                      "optimizer": "AdamW lr %g wd %g, clip %g" % (cfg["lr"], cfg["wd"], cfg["clip"])},
            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-           "gpu_launches": 0}
+           "gpu_launches": 0, "last_loss": loss}
     print(json.dumps(out), flush=True)
+
+
+def run_reference_fused_op(args, cfg):
+    """Config 2 on the CPU restatement: LayerNorm -> GELU -> Linear C->V -> cross-entropy, forward + backward, on a row sample."""
+    from oracle import build as ob
+    ob.build()
+    from oracle import oracle as orc
+    from vearo_b200 import modelspec as ms
+    rows = 256
+    x, g, b, W, labels = ms.microbench_inputs(N=rows, C=cfg["C"], V=cfg["V"])
+    orc.set_threads(0)
+    durs = []
+    for s in range(min(args.warmup, 1) + min(args.steps, 5)):
+        orc.reset_all()
+        cx = orc.Tensor.from_numpy(x, True)
+        cg, cb, cw = orc.Tensor.from_numpy(g, True), orc.Tensor.from_numpy(b, True), orc.Tensor.from_numpy(W, True)
+        lab = orc.Tensor.from_numpy(labels)
+        t0 = time.perf_counter()
+        cx.layernorm(cg, cb, 1e-5).gelu().matmul(cw.transpose(0, 1)).cross_entropy(lab).backward()
+        if s >= min(args.warmup, 1):
+            durs.append(time.perf_counter() - t0)
+    cores = orc.get_threads(); orc.reset_all()
+    step_s = float(np.mean(durs)); value = rows / step_s
+    sample = "each step = forward + backward of the chain on %d of the %d rows (cost is linear in rows), %d steps timed" % (rows, cfg["N"], len(durs))
+    out = {"impl": "reference", "metric": "fused-op fwd+bwd rows/s", "value": value, "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps,
+           "warmup": args.warmup, "steps_timed": len(durs), "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "f32", "data": "synthetic", "config": {"workload": args.workload, "rows": rows, "C": cfg["C"], "V": cfg["V"]},
+           "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": "port", "sample": sample},
+           "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(out), flush=True)
+
+
+def read_profile(vb, L, C, steps, pk, clocks_mhz):
+    """Per-family kernel figures from the library's event records: (kernels, gemm_shapes)."""
+    buf = C.create_string_buffer(1 << 16)
+    vb.vb_check(L.vb_profile_families(buf, 1 << 16))
+    acc, gemm_shapes = {}, {}                              # family -> [ms, launches, units, dense units]
+    for name in [f for f in buf.value.decode().split(",") if f]:
+        t, n, u, du = C.c_double(0), C.c_int64(0), C.c_double(0), C.c_double(0)
+        vb.vb_check(L.vb_profile_read(name.encode(), C.byref(t), C.byref(n), C.byref(u), C.byref(du)))
+        if n.value == 0:
+            continue
+        fam = name
+        if name.startswith("gemm_tc M"):                 # "gemm_tc M.. N.. K.. nb.. a. b. bn.. sk.. [streamk]": one family, shapes kept aside
+            fam = "gemm_tc" if " nb1 " in name else "gemm_tc_batched"
+            gemm_shapes[name[len("gemm_tc "):]] = {"launches_per_step": n.value / steps, "us_per_launch": 1e3 * t.value / n.value,
+                                                   "tflops": u.value / (t.value * 1e-3) / 1e12 if t.value > 0 else 0.0}
+        a = acc.setdefault(fam, [0.0, 0, 0.0, 0.0])
+        a[0] += t.value; a[1] += n.value; a[2] += u.value; a[3] += du.value
+    kernels = {}
+    tf32_useful = TF32_PEAK["tflops_sustained"] / 3.0
+    for fam, (t, n, u, du) in acc.items():
+        tensor = fam.startswith("gemm") or fam.startswith("attn_fused") or fam.startswith("conv_igemm")
+        rate = u / (t * 1e-3) if t > 0 else 0.0
+        k = {"launches_per_step": n / steps, "ms_per_step": t / steps, "bound": "tensor" if tensor else "hbm",
+             "achieved": rate / 1e12 if tensor else rate / 1e9, "unit": "TFLOP/s" if tensor else "GB/s"}
+        if tensor:
+            # FP32-accurate products issue three TF32 MMAs each: the useful-flop ceiling is the measured TF32 rate / 3
+            k["frac"] = k["achieved"] / tf32_useful
+            k["frac_of_bf16_peak"] = k["achieved"] / pk["bf16_tflops_sustained"]
+        else:
+            k["frac"] = k["achieved"] / pk["hbm_gbs"]
+        if du > u * 1.0001:                             # the launches skipped part of the dense problem (causal attention)
+            k["dense_equivalent"] = (du / (t * 1e-3)) / (1e12 if tensor else 1e9) if t > 0 else 0.0
+        if clocks_mhz:
+            k["mcycles_per_step"] = k["ms_per_step"] * clocks_mhz      # time x median SM MHz of this pass: compares runs under different power caps
+        kernels[fam] = k
+    return kernels, gemm_shapes
+
+
+def other_workload_lines(vb, L, C, torch, stream, pk, local):
+    """Driver-run records for the configurations that are not the headline: config 2 (the fused-op backward chain at
+    N = 8192 rows) and config 4 (the conv net step), a few steps each after the timed region of the main workload."""
+    from vearo_b200 import modelspec as ms
+    out = {}
+
+    def run(name, make, steps=5):
+        fn, units, unit = make()
+        for i in range(3):
+            fn(i)
+        vb.sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as ck:
+            with torch.cuda.stream(stream):
+                e0.record()
+            for i in range(steps):
+                fn(i)
+            with torch.cuda.stream(stream):
+                e1.record()
+            vb.sync(); torch.cuda.synchronize()
+        ms_step = e0.elapsed_time(e1) / steps
+        vb.vb_check(L.vb_profile_reset()); vb.vb_check(L.vb_profile_enable(1))
+        for i in range(2):
+            fn(i)
+        vb.sync(); vb.vb_check(L.vb_profile_enable(0))
+        kernels, _ = read_profile(vb, L, C, 2, pk, None)
+        vb.vb_check(L.vb_profile_reset())
+        out[name] = {"value": units / (ms_step * 1e-3), "unit": unit, "ms_per_step": ms_step, "steps": steps, "kernels": kernels,
+                     "clocks": ck.summary()}
+
+    def fused_op():
+        c = WORKLOADS["fused-op"]
+        x, g, b, W, labels = ms.microbench_inputs(N=c["N"], C=c["C"], V=c["V"])
+        m = vb.FusedOpBench(c["C"], c["V"]); m.load([g, b, W])
+        gx, lab = vb.Tensor.from_numpy(x, True), vb.Tensor.from_numpy(labels)
+        keep = []
+
+        def fn(i):
+            vb.zero_gradients(); vb.reset_active_tape()
+            l = m.loss(gx, lab); l.backward()
+            keep[:] = [l, m]
+        return fn, c["N"], "rows/s"
+
+    def convnet():
+        c = WORKLOADS["convnet"]
+        m = vb.ConvNet(list(c["channels"]), c["classes"]); m.load(ms.convnet_params(c["channels"], c["classes"]))
+        opt = vb.SGD(m.parameters(), c["lr"], c["momentum"], 0.0)
+        x, y = ms.convnet_batch(c["micro_batch"], c["hw"], c["classes"])
+        xr, yr = vb.Tensor.from_numpy(x), vb.Tensor.from_numpy(y)
+        keep = []
+
+        def fn(i):
+            keep[:] = [m.train_step_resident(opt, xr, yr, 0.0), opt]
+        return fn, c["micro_batch"], "images/s"
+    run("fused-op", fused_op)
+    run("convnet", convnet, steps=20)
+    return out
+
+
+def measure_tf32_peak():
+    """torch.matmul with TF32 allowed on 8192^3, the way MEASURED_PEAKS.json measures bf16: best of 10 (burst) and back to
+    back for 4 s (sustained), SM clock sampled.  Prints one JSON line (the figure recorded in TF32_PEAK)."""
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    n = 8192
+    a = torch.randn(n, n, device="cuda"); b = torch.randn(n, n, device="cuda")
+    for _ in range(3):
+        torch.matmul(a, b)
+    torch.cuda.synchronize()
+    best = 1e9
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); torch.matmul(a, b); e1.record(); torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    with ClockSampler(0) as ck:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter(); reps = 0
+        e0.record()
+        while time.perf_counter() - t0 < 4.0:
+            for _ in range(10):
+                torch.matmul(a, b)
+            reps += 10
+            torch.cuda.synchronize()
+        e1.record(); torch.cuda.synchronize()
+    sustained_ms = e0.elapsed_time(e1) / reps
+    fl = 2.0 * n ** 3
+    print(json.dumps({"tf32_tflops_burst": fl / (best * 1e-3) / 1e12, "tf32_tflops_sustained": fl / (sustained_ms * 1e-3) / 1e12,
+                      "how": "torch.matmul f32 with allow_tf32, 8192^3, best of 10 / back to back for 4 s", "clocks": ck.summary()}), flush=True)
 
 
 def main():
@@ -225,10 +411,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gpt-small", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true", help="skip the short fused-op and convnet records appended to the default 1-GPU line")
     ap.add_argument("--checkpoint-blocks", action="store_true", help="GPT workloads: every transformer block under activation checkpointing")
     ap.add_argument("--adamw8bit", action="store_true", help="GPT workloads: AdamW with block-wise int8 moments")
     ap.add_argument("--profile-steps", type=int, default=2)
+    ap.add_argument("--measure-tf32-peak", action="store_true", help="measure the dense TF32 rate of torch.matmul on this GPU and exit")
     args = ap.parse_args()
+    if args.measure_tf32_peak:
+        return measure_tf32_peak()
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
@@ -240,7 +430,7 @@ def main():
     import ctypes as C
     import torch
     import vearo_b200 as vb
-    from tests import modelspec as ms
+    from vearo_b200 import modelspec as ms
 
     os.environ.setdefault("VB200_PROF_SHAPES", "1")      # the profiling pass keeps GEMM launches apart by shape
     torch.cuda.set_device(local)
@@ -268,26 +458,33 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    convnet = cfg.get("kind") == "convnet"
-    B = cfg["micro_batch"]
+    kind = cfg.get("kind", "gpt")
+    convnet, fused_op = kind == "convnet", kind == "fused-op"
+    opt = None
     if convnet:
-        T = V = 0
+        B = cfg["micro_batch"]; T = V = 0
         model = vb.ConvNet(list(cfg["channels"]), cfg["classes"])
         model.load(ms.convnet_params(cfg["channels"], cfg["classes"]))                  # identical on every rank
         opt = vb.SGD(model.parameters(), cfg["lr"], cfg["momentum"], 0.0, data_parallel=world > 1)
         batches = [ms.convnet_batch(B, cfg["hw"], cfg["classes"], seed=1000 * rank + i) for i in range(4)]
-        units_per_rank, unit = B, "images/s"
+        units_per_rank, unit, metric = B, "images/s", "ConvNet fwd+bwd+SGD images/s"
+    elif fused_op:
+        B = cfg["N"]; T = V = 0
+        x, g, b, W, labels = ms.microbench_inputs(N=cfg["N"], C=cfg["C"], V=cfg["V"])
+        model = vb.FusedOpBench(cfg["C"], cfg["V"]); model.load([g, b, W])
+        batches = [(x, labels)]
+        units_per_rank, unit, metric = B, "rows/s", "fused-op fwd+bwd rows/s"
     else:
-        T, V = cfg["T"], cfg["vocab"]
+        B, T, V = cfg["micro_batch"], cfg["T"], cfg["vocab"]
         model = vb.SimpleGPT(V, T, cfg["d"], cfg["heads"], cfg["layers"], cfg["ff"])
         model.load(ms.gpt_params(V, T, cfg["d"], cfg["layers"], cfg["ff"], seed=0))      # identical on every rank
         if args.checkpoint_blocks: model.set_checkpointing(True)
         Opt = vb.AdamW8bit if args.adamw8bit else vb.AdamW
         opt = Opt(model.parameters(), cfg["lr"], 0.9, 0.999, 1e-8, cfg["wd"], data_parallel=world > 1)
         batches = [ms.gpt_batch(V, B, T, seed=1000 * rank + i) for i in range(4)]      # per-rank data
-        units_per_rank, unit = B * T, "tokens/s"
+        units_per_rank, unit, metric = B * T, "tokens/s", "GPT-small fwd+bwd+AdamW tokens/s"
     n_params = sum(int(np.prod(p.shape)) for p in model.parameters())
-    resident = [(vb.Tensor.from_numpy(a), vb.Tensor.from_numpy(b)) for a, b in batches]
+    resident = [(vb.Tensor.from_numpy(a, fused_op), vb.Tensor.from_numpy(b)) for a, b in batches]
     pinned = []
     for a, b in batches:
         pa = torch.empty(a.shape, dtype=torch.float32, pin_memory=True); pa.numpy()[:] = a
@@ -313,7 +510,12 @@ def main():
 
     def step_resident(i):
         x, y = resident[i % len(resident)]
-        keep.append(model.train_step_resident(opt, x, y, cfg["clip"]))
+        if fused_op:                        # config 2 has no optimizer: forward + backward of the chain
+            vb.zero_gradients(); vb.reset_active_tape()
+            l = model.loss(x, y); l.backward()
+            keep.append(l)
+        else:
+            keep.append(model.train_step_resident(opt, x, y, cfg["clip"]))
         if len(keep) > 2:
             keep.pop(0)
 
@@ -321,7 +523,12 @@ def main():
 
     def step_host(i):
         a, b = pinned[i % len(pinned)]
-        losses.append(model.train_step(opt, a.numpy(), b.numpy(), cfg["clip"])[0])
+        if fused_op:
+            vb.zero_gradients(); vb.reset_active_tape()
+            l = model.loss(vb.Tensor.from_numpy(a.numpy(), True), vb.Tensor.from_numpy(b.numpy())); l.backward()
+            losses.append(float(l.numpy()[0]))
+        else:
+            losses.append(model.train_step(opt, a.numpy(), b.numpy(), cfg["clip"])[0])
 
     for i in range(max(args.warmup, 3)):
         step_resident(i)
@@ -338,55 +545,57 @@ def main():
     e2e_ms = timed(step_host, args.steps) / args.steps
     e2e_value = tokens / (e2e_ms * 1e-3)
 
+    # data-parallel evidence: after the same number of steps from the same start, every rank must hold bit-identical weights
+    replicas_identical = None
+    if dist is not None:
+        import zlib
+        crc = 0
+        for prm in model.parameters():
+            crc = zlib.crc32(prm.numpy().tobytes(), crc)
+        cr = torch.tensor([crc], dtype=torch.int64, device="cuda")
+        lo, hi = cr.clone(), cr.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        replicas_identical = bool(lo.item() == hi.item())
+
     # untimed profiling pass: per-family kernel time from CUDA events on the compute stream
     pk = peaks()
-    kernels, roofline = {}, None
+    kernels, roofline, gemm_shapes, prof_clocks = {}, None, {}, None
     if args.profile_steps > 0:          # every rank runs the steps (they contain collectives); rank 0 reads
         vb.vb_check(L.vb_profile_reset()); vb.vb_check(L.vb_profile_enable(1))
-        for i in range(args.profile_steps):
-            step_resident(i)
-        vb.sync(); vb.vb_check(L.vb_profile_enable(0))
-    gemm_shapes = {}
+        with ClockSampler(local) as pclk:
+            for i in range(max(args.profile_steps, 2)):
+                step_resident(i)
+            vb.sync()
+        vb.vb_check(L.vb_profile_enable(0))
+        prof_clocks = pclk.summary()
     if rank == 0 and args.profile_steps > 0:
-        buf = C.create_string_buffer(1 << 16)
-        vb.vb_check(L.vb_profile_families(buf, 1 << 16))
-        acc = {}                                         # family -> [ms, launches, units]
-        for name in [f for f in buf.value.decode().split(",") if f]:
-            t, n, u = C.c_double(0), C.c_int64(0), C.c_double(0)
-            vb.vb_check(L.vb_profile_read(name.encode(), C.byref(t), C.byref(n), C.byref(u)))
-            if n.value == 0:
-                continue
-            fam = name
-            if name.startswith("gemm_tc M"):             # "gemm_tc M.. N.. K.. nb.. a. b. bn.. sk.. [streamk]": one family, shapes kept aside
-                fam = "gemm_tc" if " nb1 " in name else "gemm_tc_batched"
-                gemm_shapes[name[len("gemm_tc "):]] = {"launches_per_step": n.value / args.profile_steps, "us_per_launch": 1e3 * t.value / n.value,
-                                                       "tflops": u.value / (t.value * 1e-3) / 1e12 if t.value > 0 else 0.0}
-            a = acc.setdefault(fam, [0.0, 0, 0.0])
-            a[0] += t.value; a[1] += n.value; a[2] += u.value
-        for fam, (t, n, u) in acc.items():
-            is_gemm = fam.startswith("gemm")
-            rate = u / (t * 1e-3) if t > 0 else 0.0
-            kernels[fam] = {"launches_per_step": n / args.profile_steps, "ms_per_step": t / args.profile_steps,
-                            "bound": "tensor" if is_gemm else "hbm",
-                            "achieved": rate / 1e12 if is_gemm else rate / 1e9, "unit": "TFLOP/s" if is_gemm else "GB/s",
-                            "frac": (rate / 1e12 / pk["bf16_tflops_sustained"]) if is_gemm else (rate / 1e9 / pk["hbm_gbs"])}
+        kernels, gemm_shapes = read_profile(vb, L, C, max(args.profile_steps, 2), pk, prof_clocks.get("sm_mhz"))
         vb.vb_check(L.vb_profile_reset())
         if kernels:
             dom = max(kernels, key=lambda k: kernels[k]["ms_per_step"])
             k = kernels[dom]
-            roofline = {"kernel": dom, "bound": k["bound"], "achieved": k["achieved"], "peak": pk["bf16_tflops_sustained"] if k["bound"] == "tensor" else pk["hbm_gbs"],
-                        "unit": k["unit"], "frac": k["frac"], "traffic": None, "peak_source": pk["source"],
-                        "share_of_step": k["ms_per_step"] / ms_per_step}
-            if k["bound"] == "tensor":
-                # 3xTF32: three TF32 MMAs per useful product and TF32 runs at half the bf16 rate
-                roofline["peak_3xtf32_useful"] = pk["bf16_tflops_sustained"] / 6.0
+            tensor = k["bound"] == "tensor"
+            roofline = {"kernel": dom, "bound": k["bound"], "achieved": k["achieved"], "unit": k["unit"],
+                        "peak": pk["bf16_tflops_sustained"] if tensor else pk["hbm_gbs"], "peak_source": pk["source"],
+                        "frac": k["achieved"] / (pk["bf16_tflops_sustained"] if tensor else pk["hbm_gbs"]),
+                        "traffic": None, "share_of_step": k["ms_per_step"] / ms_per_step}
+            if tensor:
+                # the kernel is an FP32-accurate 3xTF32 product: three TF32 MMAs per useful multiply-add, so its own ceiling is
+                # the measured dense TF32 rate / 3 (`frac` above is against the bf16 figure of MEASURED_PEAKS.json)
+                roofline["peak_tf32_measured"] = TF32_PEAK
+                roofline["peak_3xtf32_useful"] = TF32_PEAK["tflops_sustained"] / 3.0
                 roofline["frac_of_3xtf32_peak"] = k["achieved"] / roofline["peak_3xtf32_useful"]
-            if dom == "gemm_tc" and not convnet:
-                # DRAM bytes of ONE launch, from the ncu capture of the fc1-shaped product (profiles/gemm_tc_fc1_and_dw.md);
-                # `achieved` above averages all launches of the kernel, whose shapes differ
-                roofline.update(NCU_TRAFFIC_GEMM_FC1)
+            if dom == "gemm_tc" and kind == "gpt":
+                roofline.update(TRAFFIC_FROM_PROFILE)
+
+    other = None
+    if rank == 0 and world == 1 and args.workload == "gpt-small" and not args.no_other_workloads:
+        del keep[:]
+        other = other_workload_lines(vb, L, C, torch, stream, pk, local)
 
     if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
         return
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -396,6 +605,8 @@ def main():
             durs, cores = cpu_convnet_step_time(cfg, 16, 1, 0)
             cpu = {"value": 16 / durs[0], "unit": unit, "cores": cores, "kind": "port",
                    "sample": "one fwd + bwd + SGD step on 16 images (%.1f s); cost is linear in images" % durs[0]}
+        elif fused_op:
+            cpu = None
         else:
             tps, desc, cores, _, _ = cpu_baseline_sample(cfg)
             cpu = {"value": tps, "unit": unit, "cores": cores, "kind": "port", "sample": desc}
@@ -403,9 +614,14 @@ def main():
         config = {"workload": args.workload, "channels": list(cfg["channels"]), "classes": cfg["classes"], "image": [3, cfg["hw"], cfg["hw"]],
                   "micro_batch_per_gpu": B, "global_batch": world * B, "params": n_params,
                   "optimizer": "SGD lr %g momentum %g" % (cfg["lr"], cfg["momentum"]), "parallelism": "dp%d" % world,
-                  "matmul_precision": "fp32 (convolutions unfolded onto the 3xTF32 tensor-core GEMM)",
+                  "matmul_precision": "fp32 (convolutions on the 3xTF32 tensor-core GEMM)",
                   "l2": "activations of one step (about 1 GB) exceed the 126 MB L2"}
         h2d = int(world * (B * 3 * cfg["hw"] * cfg["hw"] + B) * 4)
+    elif fused_op:
+        config = {"workload": args.workload, "rows": cfg["N"], "C": cfg["C"], "V": cfg["V"], "params": n_params,
+                  "chain": "LayerNorm -> GELU -> Linear C->V (no bias) -> cross-entropy; forward + backward (dX, dW, dgamma, dbeta)",
+                  "l2": "the logits alone (1.65 GB) exceed the 126 MB L2"}
+        h2d = int(world * (cfg["N"] * cfg["C"] + cfg["N"]) * 4)
     else:
         config = {"workload": args.workload, "n_layer": cfg["layers"], "n_head": cfg["heads"], "d_model": cfg["d"], "d_ff": cfg["ff"],
                   "vocab": V, "seq_len": T, "micro_batch_per_gpu": B, "global_batch": world * B, "params": n_params,
@@ -414,18 +630,22 @@ def main():
                   "matmul_precision": "fp32 (3xTF32 on tensor cores where the tensor-core kernel applies, exact fp32 FMA otherwise)",
                   "l2": "working set per step (weights, activations, optimizer state: several GB) exceeds the 126 MB L2 many times over"}
         h2d = int(world * 2 * B * T * 4)
+    tc = C.c_int64(0); L.vb_tc_launch_count(C.byref(tc))
     out = {
-        "metric": "ConvNet fwd+bwd+SGD images/s" if convnet else "GPT-small fwd+bwd+AdamW tokens/s", "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": config,
-        "useful_tflops": None if convnet else flops_per_token(cfg) * tokens / (ms_per_step * 1e-3) / 1e12,
+        "useful_tflops": flops_per_token(cfg) * tokens / (ms_per_step * 1e-3) / 1e12 if kind == "gpt" else None,
         "e2e": {"value": e2e_value, "unit": unit, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(world * 8)},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": int(world * (4 if fused_op else 8))},
         "gpu_launches": int(launches1.value - launches0.value),
+        "tensor_core_gemm_launches_total": int(tc.value),
         "device_memory": vb.memory_stats(),
-        "clocks": clocks.summary(),
+        "clocks": clocks.summary(), "profile_pass_clocks": prof_clocks,
+        "replicas_identical": replicas_identical,
         "roofline": roofline, "kernels": kernels, "gemm_shapes": gemm_shapes, "cpu_baseline": cpu,
+        "other_workloads": other,
         "last_loss": losses[-1] if losses else None,
     }
     print(json.dumps(out), flush=True)

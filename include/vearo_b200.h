@@ -185,8 +185,9 @@ int vb_fill(const vb_tensor* dst, float value);
  * the library image, present on every GPU that loads the library until the process exits.
  *   - Limits: c a multiple of 4 and <= 1024; x, w, grad_out, gx 16-byte aligned.  Anything else is
  *     rejected with VB_ERR_UNSUPPORTED and a message; use vb_layernorm_backward there.
- *   - The first call on each device looks up the array's device address; make that call before
- *     starting any stream capture.  Later calls do no set-up.
+ *   - The first call on each device looks up the array's device address and raises the shared-memory
+ *     limit of the two widest kernel instances; make that call before starting any stream capture.
+ *     Later calls do no set-up: they only launch kernels.
  *   - All calls share the one array: two calls whose kernels may overlap on the GPU (different
  *     streams) race on it.  Calls on one stream are safe back to back; nothing needs clearing between
  *     them, since every partial row is rewritten in full.
@@ -251,13 +252,17 @@ int vb_opt_step(int opt, const uint8_t* active, float max_norm, float grad_scale
  * When enabled, every launch of a kernel family is bracketed by CUDA events on the compute stream.
  * vb_profile_read synchronises and returns, for `family` ("gemm_tc", "gemm_simt", "layernorm_bwd",
  * "gelu_bwd", "cross_entropy_bwd", "adamw", "attn_softmax", ...): total milliseconds, number of
- * launches, and the summed algorithmic units (bytes for HBM-bound families, flops for GEMMs).
+ * launches, and the summed algorithmic units (bytes for HBM-bound families, flops for GEMMs) -- `units`
+ * counts what the launches really moved or issued (a causal attention product skips the tiles above
+ * the diagonal), `dense_units` (may be NULL) the same for the dense problem.
  * vb_profile_families writes a comma-separated list of the families seen so far. */
 /* Number of kernel-launcher invocations so far (each enqueues at least one kernel of this library). */
 int vb_launch_count(int64_t* count);
+/* Number of launches of the tcgen05 tensor-core GEMM kernel so far. */
+int vb_tc_launch_count(int64_t* count);
 int vb_profile_enable(int on);
 int vb_profile_reset(void);
-int vb_profile_read(const char* family, double* total_ms, int64_t* launches, double* units);
+int vb_profile_read(const char* family, double* total_ms, int64_t* launches, double* units, double* dense_units);
 int vb_profile_families(char* buf, int buflen);
 
 /* ---- data parallel -----------------------------------------------------------------------

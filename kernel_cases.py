@@ -1,18 +1,18 @@
 """Small single-kernel cases of the library's hot kernels, for profiling with ncu and quick timing.
 
-  python -m vearo_b200.kernel_cases gemm_fc1      x[8192,768] . W[3072,768]^T   (Linear forward)
-  python -m vearo_b200.kernel_cases gemm_proj     x[8192,768] . W[768,768]^T    (192 tiles of 128 x 256 for 296 CTA slots)
-  python -m vearo_b200.kernel_cases gemm_dx       g[8192,3072] . W[3072,768]    (B consumed as a transposed view)
-  python -m vearo_b200.kernel_cases gemm_dw       g[8192,3072]^T . x[8192,768]  (both operands transposed views, split-K)
-  python -m vearo_b200.kernel_cases gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
-  python -m vearo_b200.kernel_cases gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
-  python -m vearo_b200.kernel_cases attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
-  python -m vearo_b200.kernel_cases colsum        bias gradients: column sums of [8192,768] and [8192,3072]
-  python -m vearo_b200.kernel_cases layernorm_bwd rows 8192, C 768
-  python -m vearo_b200.kernel_cases ce_bwd        rows 2048, V 50304
-  python -m vearo_b200.kernel_cases ce_fused      rows 2048, V 50304: loss and gradient in one in-place pass
-  python -m vearo_b200.kernel_cases adamw         64 Mi parameters
-  python -m vearo_b200.kernel_cases adamw8bit     64 Mi parameters, int8 block-wise moments
+  python kernel_cases.py gemm_fc1      x[8192,768] . W[3072,768]^T   (Linear forward)
+  python kernel_cases.py gemm_proj     x[8192,768] . W[768,768]^T    (192 tiles of 128 x 256 for 296 CTA slots)
+  python kernel_cases.py gemm_dx       g[8192,3072] . W[3072,768]    (B consumed as a transposed view)
+  python kernel_cases.py gemm_dw       g[8192,3072]^T . x[8192,768]  (both operands transposed views, split-K)
+  python kernel_cases.py gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
+  python kernel_cases.py gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
+  python kernel_cases.py attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
+  python kernel_cases.py colsum        bias gradients: column sums of [8192,768] and [8192,3072]
+  python kernel_cases.py layernorm_bwd rows 8192, C 768
+  python kernel_cases.py ce_bwd        rows 2048, V 50304
+  python kernel_cases.py ce_fused      rows 2048, V 50304: loss and gradient in one in-place pass
+  python kernel_cases.py adamw         64 Mi parameters
+  python kernel_cases.py adamw8bit     64 Mi parameters, int8 block-wise moments
 A second argument gives the repetition count (default 3); `time` instead prints the average device
 time per repetition over 20 repetitions (CUDA events through the library's profiling hooks are not
 used here: the loop is synchronised on both sides and timed on the host).
@@ -125,7 +125,7 @@ def main(case, mode):
         vb.vb_check(L.vb_profile_families(buf, 4096))
         for fam in [f for f in buf.value.decode().split(",") if f]:
             t, n, u = C.c_double(0), C.c_int64(0), C.c_double(0)
-            vb.vb_check(L.vb_profile_read(fam.encode(), C.byref(t), C.byref(n), C.byref(u)))
+            vb.vb_check(L.vb_profile_read(fam.encode(), C.byref(t), C.byref(n), C.byref(u), None))
             if n.value:
                 print("  %-28s %4d launches  %9.1f us each (device)" % (fam, n.value, 1e3 * t.value / n.value))
     else:

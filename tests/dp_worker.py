@@ -13,7 +13,7 @@ sys.path.insert(0, ROOT)
 def main():
     rank, world, out_dir, steps = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], int(sys.argv[4])
     import vearo_b200 as vb
-    from tests import modelspec as ms
+    from vearo_b200 import modelspec as ms
     vb.init(rank)
     L = vb.lib()
     uid = (C.c_uint8 * 128)()

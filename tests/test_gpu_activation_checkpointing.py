@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle as orc
-from tests import modelspec as ms
+from vearo_b200 import modelspec as ms
 from tests.test_gpu_ops import assert_close, rnd
 
 pytestmark = pytest.mark.gpu

@@ -4,7 +4,7 @@ import struct
 import numpy as np
 import pytest
 
-from tests import modelspec as ms
+from vearo_b200 import modelspec as ms
 
 pytestmark = pytest.mark.gpu
 

@@ -9,7 +9,7 @@ import pytest
 
 from oracle import oracle as orc
 from oracle import models as om
-from tests import modelspec as ms
+from vearo_b200 import modelspec as ms
 from tests.test_gpu_ops import assert_close
 
 pytestmark = pytest.mark.gpu

@@ -711,6 +711,39 @@ def test_linear_weight_lo_plane_exact_and_never_stale(vb):
     vb.check_errors()
 
 
+def test_activation_lo_plane_follows_in_place_writers(vb):
+    """A LayerNorm output of 2^18 elements or more carries a lo plane.  Entry points that overwrite such a slot in place
+    (the fused cross-entropy leaves the gradient where the logits were; vb_linear_backward_into writes into a given
+    destination) must void the plane: the next product over the slot has to equal the plane-free product bit for bit."""
+    import ctypes as C
+    T = vb.Tensor
+    x0, w0 = rnd(411, 1024, 512), rnd(412, 512, 512, scale=0.05)
+    g1, b1 = T.from_numpy(np.ones(512, np.float32)), T.from_numpy(np.zeros(512, np.float32))
+    w = T.from_numpy(w0)
+    y = T.from_numpy(x0).layernorm(g1, b1, 1e-5)           # [1024, 512]: gets a plane from the kernel that writes it
+    before = y.linear(w, None).numpy()
+    assert np.array_equal(before, y.matmul(w.transpose(0, 1)).numpy())
+    tg = T.from_numpy(np.random.default_rng(3).integers(0, 512, 1024).astype(np.float32))
+    loss = vb.VbTensor()
+    yd, td = y.desc(), tg.desc()
+    vb.vb_check(vb.lib().vb_cross_entropy_fused(C.byref(yd), C.byref(td), C.byref(loss)), "vb_cross_entropy_fused")
+    vb.vb_check(vb.lib().vb_release(loss.slot, None))
+    after = y.linear(w, None).numpy()
+    assert not np.array_equal(before, after)
+    assert np.array_equal(after, y.matmul(w.transpose(0, 1)).numpy()), "stale lo plane after the fused cross-entropy"
+    # a destination written by vb_linear_backward_into: a second LayerNorm output, of the shape of a [1024, 512] weight gradient
+    z = T.from_numpy(rnd(413, 1024, 512)).layernorm(g1, b1, 1e-5)       # 2^19 elements -> plane
+    assert np.array_equal(z.linear(w, None).numpy(), z.matmul(w.transpose(0, 1)).numpy())       # (plane in use: 1024 rows)
+    x1, w2, go = T.from_numpy(rnd(414, 256, 512)), T.from_numpy(rnd(416, 1024, 512, scale=0.05)), T.from_numpy(rnd(415, 256, 1024))
+    zd, xd, wd, gd = z.desc(), x1.desc(), w2.desc(), go.desc()
+    gx = vb.VbTensor()
+    L = vb.lib()
+    vb.vb_check(L.vb_linear_backward_into(C.byref(xd), C.byref(wd), C.byref(gd), C.byref(gx), C.byref(zd), None), "vb_linear_backward_into")
+    vb.vb_check(L.vb_release(gx.slot, None))
+    assert np.array_equal(z.linear(w, None).numpy(), z.matmul(w.transpose(0, 1)).numpy()), "stale lo plane after linear_backward_into"
+    vb.check_errors()
+
+
 def test_linear_tensor_core_with_bias_and_backward(vb):
     x0, w0, b0, go = rnd(65, 512, 384, scale=0.5), rnd(66, 640, 384, scale=0.05), rnd(67, 640), rnd(68, 512, 640, scale=0.1)
 

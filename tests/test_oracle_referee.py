@@ -93,7 +93,7 @@ def test_gpt_and_convnet_train():
     """crates/vearo/tests/verification_harness.rs:183-237: the tiny GPT (vocab 8, T 4, d 8, 2 heads,
     1 layer, ff 16) memorises a sequence; here 60 AdamW steps must cut the loss by > 10x."""
     from oracle.models import SimpleGPT
-    from tests.modelspec import gpt_params
+    from vearo_b200.modelspec import gpt_params
     ps = gpt_params(vocab=8, T=4, d=8, n_layer=1, ff=16, seed=1, std=0.3)
     model = SimpleGPT(ps, 8, 2, 1)
     opt = orc.AdamW(model.parameters(), 1e-2)

@@ -1,11 +1,12 @@
-"""The allocation-free LayerNorm backward entry point, checked against the regular one.
+"""The allocation-free LayerNorm backward entry point, checked against the regular one and against the CPU oracle.
 
 Some users of this library run where device allocation is not allowed at call time (inside a
 framework's capture/replay region, under a fixed memory budget, or as a plugin that only owns the
 buffers it is given).  `vb_layernorm_backward_noalloc` serves them: raw pointers in and out, partial
 sums in a fixed array inside the library.  This test drives it through the C ABI twice in a row (the
 array keeps the previous call's contents, so the second call must not depend on a clean array) and
-compares with `vb_layernorm_backward` at the tolerance the other GPU tests use.
+compares with `vb_layernorm_backward` and with the CPU oracle's `layernorm_backward` at the tolerance the
+other GPU tests use.
 
 Collected last on purpose: a run that stops at the first failure has then run everything else.
 """
@@ -78,6 +79,15 @@ def test_noalloc_layernorm_backward_matches_regular_entry_point(rows, c):
             vb.vb_check(L.vb_release(s, None))
         for a, b_, name in zip(got, want, ("gx", "gw", "gb")):
             _close(a, b_, "call %d %s" % (call, name))
+        # ... and against the CPU oracle directly (crates/vearo-backend-cpu/src/lib.rs:745-858 through the LayerNorm arm)
+        from oracle import oracle as orc
+        orc.reset_all()
+        ox, ow, ob = orc.Tensor.from_numpy(x0, True), orc.Tensor.from_numpy(w0, True), orc.Tensor.from_numpy(np.zeros(c, np.float32), True)
+        n = rows * c
+        ox.layernorm(ow, ob, 1e-5).mul(orc.Tensor.from_numpy(g0)).reshape([1, n]).matmul(
+            orc.Tensor.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        for a, t, name in zip(got, (ox, ow, ob), ("gx", "gw", "gb")):
+            _close(a, t.grad().numpy(), "call %d %s vs oracle" % (call, name))
 
 
 def test_noalloc_rejects_sizes_beyond_its_fixed_scratch():

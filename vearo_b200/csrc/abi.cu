@@ -290,6 +290,7 @@ int vb_cross_entropy_fused(const vb_tensor* logits_inout, const vb_tensor* targe
   VB_CHECK(targets->dims[0] == B, "Targets shape must match batch size");
   VB_CHECK(is_contiguous(*logits_inout), "cross_entropy_fused overwrites the logits: they must be contiguous");
   float* pl; VB_TRY(tensor_ptr(logits_inout, &pl));
+  slot_touch(logits_inout->slot);        // overwritten with the gradient
   Temp ht; const float* pt;
   VB_TRY(contiguous_ptr(targets, &pt, ht));
   i64 one = 1;
@@ -728,7 +729,8 @@ int vb_fill(const vb_tensor* dst, float value) {
 // TF32 remainders ("lo plane") of a Linear weight, kept beside the weight while its contents stand: the tensor-core GEMM then
 // loads them instead of recomputing them in every tile of the forward product and of the input-gradient product.  Keyed by the
 // weight's slot; valid while the slot's serial is unchanged (every call of this library that writes into an existing slot --
-// vb_write, vb_copy, vb_fill, vb_accumulate, the optimizer steps -- advances it).  One plane covers the whole slot, so
+// vb_write, vb_copy, vb_fill, vb_accumulate, the optimizer steps, vb_clip_grad_norm, vb_dp_allreduce, vb_cross_entropy_fused,
+// vb_linear_backward_into -- advances it).  One plane covers the whole slot, so
 // parameters that are views of one block share it.  Returns null where the plane does not pay or cannot be had.
 namespace {
 struct LoPlane { vb_slot lo = 0; uint64_t serial = 0; i64 numel = 0; };
@@ -864,7 +866,7 @@ static int linear_backward_impl(const vb_tensor* x, const vb_tensor* weight, con
   }
   if (gw || gw_into) {   // gw[out, in] = gy^T . x
     float* p;
-    if (gw_into) VB_TRY(tensor_ptr(gw_into, &p));
+    if (gw_into) { VB_TRY(tensor_ptr(gw_into, &p)); slot_touch(gw_into->slot); }
     else { i64 wd[2] = {outf, in}; VB_TRY(new_output(gw, 2, wd)); VB_TRY(slot_ptr(gw->slot, &p)); }
     if (rows == 0) VB_TRY(launch_fill(p, 0.0f, outf * in));
     else {
@@ -879,7 +881,7 @@ static int linear_backward_impl(const vb_tensor* x, const vb_tensor* weight, con
   }
   if (gb || gb_into) {
     float* p;
-    if (gb_into) VB_TRY(tensor_ptr(gb_into, &p));
+    if (gb_into) { VB_TRY(tensor_ptr(gb_into, &p)); slot_touch(gb_into->slot); }
     else { VB_TRY(new_output(gb, 1, &outf, true)); VB_TRY(slot_ptr(gb->slot, &p)); }
     if (rows > 0) VB_TRY(launch_colsum(pg, p, rows, outf, false));
     else if (gb_into) VB_TRY(launch_fill(p, 0.0f, outf));

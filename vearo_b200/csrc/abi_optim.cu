@@ -88,6 +88,7 @@ int vb_clip_grad_norm(const vb_tensor* grads, int n, float max_norm, float* tota
   if (rc == VB_OK) rc = launch_sum_partials((const float*)d_pa, (int)chunks.size(), d_norm);
   for (int i = 0; rc == VB_OK && i < n; ++i) {
     float* p; tensor_ptr(&grads[i], &p);
+    slot_touch(grads[i].slot);          // scaled in place: a lo plane or a cached verdict about the old contents is void
     rc = launch_scale_inplace_by_clip(p, numel(grads[i]), d_norm, max_norm);
   }
   float h = 0.0f;
@@ -223,8 +224,10 @@ int vb_opt_step(int id, const uint8_t* active, float max_norm, float grad_scale,
   }
   float bc1 = 1.0f, bc2 = 1.0f;
   if (c.kind != VB_OPT_SGD) { bc1 = 1.0f - powi(c.beta1, (int)o->t); bc2 = 1.0f - powi(c.beta2, (int)o->t); }
+  int lo_chunks = 0;
+  for (const OptChunk& ch : o->h_chunks) if (ch.lo) ++lo_chunks;
   VB_TRY(launch_opt_multi((const OptChunk*)o->d_chunks, o->nchunks, d_active, c.kind, d_normsq, max_norm, grad_scale,
-                          c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.momentum, bc1, bc2));
+                          c.lr, c.beta1, c.beta2, c.eps, c.weight_decay, c.momentum, bc1, bc2, lo_chunks));
   // the updated parameters' contents changed; a lo plane that was current before stays so (the kernel rewrote the updated part)
   {
     std::vector<uint8_t> was((size_t)o->nparams, 0);

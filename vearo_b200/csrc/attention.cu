@@ -197,6 +197,16 @@ __global__ void __launch_bounds__(128) k_attn_softmax_bwd_warp(const float* __re
     }
   }
 }
+// Elements one [sq, sk] matrix moves under a causal mask: `reads` per live score (columns 0..i of row i) plus `writes` per
+// element up to the end of the row's 128-row tile (the zeros the triangular products that follow may touch).
+static inline double causal_elems(i64 sq, i64 sk, double reads, double writes) {
+  double e = 0.0;
+  for (i64 i = 0; i < sq; ++i) {
+    i64 live = i + 1 < sk ? i + 1 : sk, z = ((i >> 7) + 1) << 7; if (z > sk) z = sk;
+    e += reads * (double)live + writes * (double)z;
+  }
+  return e;
+}
 static inline i64 causal_band() { static i64 b = 0; if (!b) { const char* e = getenv("VB200_SOFTMAX_BAND"); b = e ? atoll(e) : 512; if (b < 128) b = 128; } return b; }
 static inline bool al16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -204,7 +214,9 @@ int launch_attn_softmax(float* s, const float* mask, const i64 mstr[4], bool cau
   (void)scale;
   i64 rows = b * h * sq;
   if (rows <= 0 || sk <= 0) return VB_OK;
-  ProfScope prof("attn_softmax", 2.0 * (double)rows * (double)sk * 4.0);
+  // bytes really moved: under a causal mask row i reads its i + 1 live scores and writes up to the end of its 128-row tile
+  const double dense_bytes = 2.0 * (double)rows * (double)sk * 4.0;
+  ProfScope prof("attn_softmax", causal ? (double)(b * h) * causal_elems(sq, sk, 1.0, 1.0) * 4.0 : dense_bytes, dense_bytes);
   MaskStrides ms{0, 0, 0, 0};
   if (mask) ms = MaskStrides{mstr[0], mstr[1], mstr[2], mstr[3]};
   cudaStream_t st = ctx().stream;
@@ -272,7 +284,8 @@ __global__ void __launch_bounds__(256) k_attn_softmax_bwd_long(const float* __re
 int launch_attn_softmax_backward(const float* p, float* dp, i64 rows, i64 sk, float scale, bool causal, i64 sq) {
   if (rows <= 0 || sk <= 0) return VB_OK;
   if (causal && !((sk & 3) == 0 && sk <= 1024 && al16p(p) && al16p(dp) && sq == sk)) return set_error(VB_ERR_UNSUPPORTED, "causal attention softmax needs square S <= 1024, a multiple of 4");
-  ProfScope prof("attn_softmax_bwd", 3.0 * (double)rows * (double)sk * 4.0);
+  const double dense_bytes = 3.0 * (double)rows * (double)sk * 4.0;
+  ProfScope prof("attn_softmax_bwd", causal ? (double)(rows / sq) * causal_elems(sq, sk, 2.0, 1.0) * 4.0 : dense_bytes, dense_bytes);
   cudaStream_t st = ctx().stream;
   if ((sk & 3) == 0 && sk <= 1024 && al16p(p) && al16p(dp)) {
     const i64 mats = causal ? rows / sq : 1, seq = causal ? sq : rows;      // without a causal mask all rows are alike: one band

@@ -33,6 +33,7 @@ int set_error(int status, const std::string& msg);
 #define VB_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return ::vb::set_error(VB_ERR_CUDA, std::string(__func__) + ": " #expr ": " + cudaGetErrorString(e_)); } while (0)
 #define VB_TRY(expr) do { int s_ = (expr); if (s_ != VB_OK) return s_; } while (0)
 extern int64_t g_launcher_calls;   // launcher invocations since start (each enqueues one or more kernels)
+extern int64_t g_tc_launches;      // launches of the tensor-core GEMM kernel since start (gemm_tc.cu)
 #define VB_LAUNCH_CHECK() do { ++::vb::g_launcher_calls; VB_CUDA(cudaGetLastError()); } while (0)
 
 // Slots / arena (runtime.cu).
@@ -189,7 +190,7 @@ int launch_sumsq_chunks(const OptChunk* chunks, int nchunks, const uint8_t* acti
 int launch_sum_partials(const float* partials, int n, float* out);      // out[0] = sum (single block, fixed order)
 int launch_opt_multi(const OptChunk* chunks, int nchunks, const uint8_t* active, int kind, const float* normsq,
                      float max_norm, float grad_scale, float lr, float b1, float b2, float eps, float wd, float mu,
-                     float bc1, float bc2);
+                     float bc1, float bc2, int lo_chunks = 0);     // lo_chunks: how many chunks carry a lo-plane pointer (profiling only)
 int launch_scale_inplace_by_clip(float* g, i64 n, const float* normsq, float max_norm);
 
 
@@ -197,7 +198,9 @@ int launch_scale_inplace_by_clip(float* g, i64 n, const float* normsq, float max
 // default (zero cost); the benchmark switches it on for a separate, untimed pass.
 struct ProfScope {
   int idx = -1;
-  ProfScope(const char* family, double units);   // units: algorithmic bytes or flops of this launch
+  // units: algorithmic bytes or flops this launch really moves / issues; dense_units: the same for the dense problem when the
+  // launch skips part of it (causal attention), else 0 (= units)
+  ProfScope(const char* family, double units, double dense_units = 0.0);
   ~ProfScope();
 };
 

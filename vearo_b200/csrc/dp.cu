@@ -80,6 +80,7 @@ int vb_dp_allreduce(vb_slot slot, int64_t offset, int64_t n) {
   VB_CHECK(offset >= 0 && n >= 0 && offset + n <= cap, "range exceeds the slot");
   if (g_world == 1 || n == 0) return VB_OK;
   if (!g_comm) return set_error(VB_ERR_COMM, "vb_dp_init has not been called");
+  slot_touch(slot);                     // reduced in place: whatever was derived from the old contents (a lo plane) is void
   Ctx& c = ctx();
   VB_CUDA(cudaEventRecord(c.ev_compute, c.stream));
   VB_CUDA(cudaStreamWaitEvent(c.comm_stream, c.ev_compute, 0));

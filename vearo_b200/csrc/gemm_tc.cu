@@ -52,12 +52,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;                    // f32 columns per stage: 64-byte rows, SWIZZLE_64B
-constexpr int kEpiWarps = 8;
-#ifdef VB200_TC_TIMING
-constexpr bool kTiming = true;                // timing experiments compiled in (TcParams::debug); results are wrong while one is active
-#else
-constexpr bool kTiming = false;
-#endif                  // of the converter warps, the first 8 also run the epilogue
+constexpr int kConvWarps = 8;             // converter warps; the same warps run the epilogue
+constexpr int kThreads = 64 + 32 * kConvWarps;
 constexpr uint32_t kSpinLimit = 1u << 20; // polls of try_wait (each waits a bounded time) before giving up
 
 struct TcParams {
@@ -76,8 +72,6 @@ struct TcParams {
   int a_mn, b_mn;                                 // 1: operand tile is MN-contiguous (transposed view), staged as 32-wide boxes, 128-byte swizzle with 32-byte base
   int long_first;                                 // triangular products (causal 2, 3), tiled mode: gridDim = (tiles_n, batch, tiles_m) and the tile rows with the longest k range are dispatched first
   int causal;                                     // see GemmArgs::causal
-  int debug;                                      // timing experiments only (results are wrong): 1 skip the split, 2 issue one MMA of three, 4 MMAs only (no loads), 8 loads only (no MMAs)
-  int raw_hi;                                     // 1: the raw f32 tile is used as the hi operand (the MMA ignores the low 13 mantissa bits)
   float alpha, beta;
   int* err;
   int persistent;                                 // 1: stream-K launch, 2: whole tiles dealt round-robin to resident CTAs (see WorkIter)
@@ -113,35 +107,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   *abort_flag = 1;
   return false;
-}
-
-// Variants for a pair of CTAs that share one MMA (cta_group::2): barriers of the leader CTA collect arrivals from both.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-    if ((it & 1023) == 1023 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
-  asm volatile(
-      "{\n\t.reg .b32 ra;\n\t"
-      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
-      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
-      ::"r"(smem_u32(bar)), "r"(rank) : "memory");
-}
-__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
@@ -207,18 +172,6 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
 }
-// The same for a CTA pair: M = 256 (128 rows from each CTA's shared memory and tensor memory), B rows split between the two.
-__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u) : "memory");
-}
-// Completion of all MMAs issued so far, delivered to the barrier at this offset in both CTAs of the pair.
-__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
-}
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -232,13 +185,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
 }
-__device__ __forceinline__ float tf32_rna(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
-}
-
-// One unit of work of a CTA (or CTA pair): a k-block range of one output tile.
+// One unit of work of a CTA: a k-block range of one output tile.
 struct Work {
   int tile;            // linear tile index (stream-K mode)
   int tile_m, tile_n, bz;
@@ -248,19 +195,18 @@ struct Work {
   int which;           // stream-K: 0 when the range starts at the group's first k-block, else 1 (selects the partial slot)
 };
 
-// Work of this CTA group (CG = 1: one CTA per 128 x bn tile; CG = 2: a pair of CTAs, one cluster, per 256 x bn tile).
-// One launch is either "tiled" (gridDim = tiles*CG x batch*splits, one unit per group, what a group does follows from blockIdx)
-// or "stream-K" (gridDim.x / CG groups share tiles*kblocks k-blocks evenly; group c owns the contiguous range
-// [c*W/G, (c+1)*W/G) of the tile-major k-block sequence, so a tile may be covered by several groups).
-template <int CG>
+// Work of this CTA (one 128 x bn tile at a time).
+// One launch is either "tiled" (gridDim = tiles x batch*splits, one unit per CTA, what a CTA does follows from blockIdx),
+// "stream-K" (gridDim.x CTAs share tiles*kblocks k-blocks evenly; CTA c owns the contiguous range [c*W/G, (c+1)*W/G) of the
+// tile-major k-block sequence, so a tile may be covered by several CTAs) or "round-robin" (whole tiles dealt to resident CTAs).
 struct WorkIter {
   i64 w, w0, w1;
   int done;
   __device__ __forceinline__ void init(const TcParams& p) {
     done = 0;
-    if (p.persistent == 2) { w = blockIdx.x / CG; return; }
+    if (p.persistent == 2) { w = blockIdx.x; return; }
     if (p.persistent) {
-      const i64 G = gridDim.x / CG, c = blockIdx.x / CG;
+      const i64 G = gridDim.x, c = blockIdx.x;
       w0 = (c * p.total_kb) / G; w1 = ((c + 1) * p.total_kb) / G; w = w0;
     }
   }
@@ -271,12 +217,12 @@ struct WorkIter {
       // runs ahead into the next tile while this one is stored.  With tiles skipped above the diagonal (causal 1) only the
       // computed ones are counted, so that every group gets the same number of them.
       if (w >= p.live_tiles) return false;
-      const i64 u = w; w += gridDim.x / CG;
+      const i64 u = w; w += gridDim.x;
       o.bz = (int)(u / p.live_per_batch);
       int j = (int)(u - (i64)o.bz * p.live_per_batch), m = 0;
       if (p.causal == 1) {
         for (;; ++m) {
-          i64 c = (((i64)m + 1) * (BM * CG) + p.bn - 1) / p.bn; if (c > p.tiles_n) c = p.tiles_n;      // computed tiles of tile row m
+          i64 c = (((i64)m + 1) * BM + p.bn - 1) / p.bn; if (c > p.tiles_n) c = p.tiles_n;      // computed tiles of tile row m
           if (j < c) break;
           j -= (int)c;
         }
@@ -305,14 +251,14 @@ struct WorkIter {
     // shortest, over all batches, so that the launch does not end on a few long tiles
     const unsigned gy = p.long_first ? (p.causal == 2 ? gridDim.z - 1 - blockIdx.z : blockIdx.z) : blockIdx.y;
     const unsigned gz = p.long_first ? blockIdx.y : blockIdx.z;
-    o.tile_n = blockIdx.x / CG; o.tile_m = (int)gy; o.tile = 0; o.which = 0;
+    o.tile_n = blockIdx.x; o.tile_m = (int)gy; o.tile = 0; o.which = 0;
     const i64 nbatch = p.nb1 * p.nb2;
     o.bz = (int)(gz % nbatch); o.split = (int)(gz / nbatch);
     o.b1 = o.bz / (int)p.nb2; o.b2 = o.bz % (int)p.nb2;
     i64 kb0 = (i64)o.split * p.kblocks_per_split, kb1 = kb0 + p.kblocks_per_split;
     if (kb1 > kblocks_total) kb1 = kblocks_total;
-    if (p.causal == 2) { i64 lim = (((i64)o.tile_m + 1) * (BM * CG) + p.bk - 1) / p.bk; if (kb1 > lim) kb1 = lim; }
-    if (p.causal == 3) { i64 lo = ((i64)o.tile_m * (BM * CG)) / p.bk; if (kb0 < lo) kb0 = lo; }
+    if (p.causal == 2) { i64 lim = (((i64)o.tile_m + 1) * BM + p.bk - 1) / p.bk; if (kb1 > lim) kb1 = lim; }
+    if (p.causal == 3) { i64 lo = ((i64)o.tile_m * BM) / p.bk; if (kb0 < lo) kb0 = lo; }
     o.kb0 = (int)kb0; o.nkb = (int)(kb1 > kb0 ? kb1 - kb0 : 0); o.whole = p.splits == 1;
     return true;
   }
@@ -371,22 +317,8 @@ __device__ __forceinline__ float tf32_lo_of_raw(float x) {
   return __uint_as_float((__float_as_uint(d) + 0x1000u) & 0xffffe000u);
 }
 
-// CG = 1: the CTA owns a 128 x bn tile.  CG = 2: two CTAs of one cluster own a 256 x bn tile; each stages its own 128 rows of A
-// and its own half of the B rows, converts them, and holds its own 128 x bn accumulator rows in tensor memory; the even CTA
-// issues one MMA for the pair (tcgen05 cta_group::2), which reads both CTAs' shared memory -- per output element each SM then
-// moves a third less through L2 and shared memory than with CG = 1.  Barriers that gate the MMA (conv, tmem_empty) live in the
-// even CTA and collect arrivals from both; completions (empty, lo_empty, tmem_full) are delivered to both CTAs.
-// CW converter warps: 8 with two CTAs per SM, 16 when one CTA with deep rings has an SM to itself.
-// Timing builds only: time stamps of the pipeline events of one CTA (role, k-block) into the scratch area.
-__device__ __forceinline__ void trace_event(const TcParams& p, int ev, int kb) {
-  if (kTiming && (p.debug & 128) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && kb < 256) {
-    unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    ((unsigned long long*)p.ws)[ev * 256 + kb] = t;
-  }
-}
-
-template <int CG, int CW>
-__global__ void __launch_bounds__(64 + 32 * CW, CW == 8 ? 2 : 1)
+// The CTA owns a 128 x bn output tile at a time (see the file header for the roles of its warps).
+__global__ void __launch_bounds__(kThreads, 2)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
           const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_alo, TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -394,9 +326,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   // (doubles as the epilogue's staging area: nothing converts while a tile is being stored), barriers.
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment in the shared window
   const int bn = p.bn, stages = p.stages, lstages = p.lstages;
-  const int bnc = bn / CG;                                   // B rows staged by this CTA
   const int bk = p.bk;
-  const uint32_t a_bytes = BM * bk * 4, b_bytes = (uint32_t)bnc * bk * 4, raw_bytes = a_bytes + b_bytes;
+  const uint32_t a_bytes = BM * bk * 4, b_bytes = (uint32_t)bn * bk * 4, raw_bytes = a_bytes + b_bytes;
   uint8_t* lo_ring = smem + (size_t)stages * raw_bytes;
   uint64_t* bars = (uint64_t*)(lo_ring + (size_t)lstages * raw_bytes);
   uint64_t* full = bars; uint64_t* empty = bars + stages; uint64_t* conv = bars + 2 * stages; uint64_t* lo_empty = conv + lstages;
@@ -408,42 +339,31 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
   volatile int* last_flag = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;    // 0: the CTA that issues the MMAs
-  if (p.causal == 1 && !p.persistent && (i64)(blockIdx.x / CG) * p.bn >= ((i64)blockIdx.y + 1) * (BM * CG)) return;   // whole tile above the diagonal (uniform over the group, nothing allocated yet)
+  if (p.causal == 1 && !p.persistent && (i64)blockIdx.x * p.bn >= ((i64)blockIdx.y + 1) * BM) return;   // whole tile above the diagonal (nothing allocated yet)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], CW * CG + (p.b_lo ? 1 : 0)); mbar_init(&lo_empty[s], 1); }    // (+1: the producer's expect_tx arrival for the pre-split lo part of B)
+    for (int s = 0; s < lstages; ++s) { mbar_init(&conv[s], kConvWarps + (p.b_lo ? 1 : 0)); mbar_init(&lo_empty[s], 1); }    // (+1: the producer's expect_tx arrival for the pre-split lo part of B)
     mbar_init(tmem_full, 1);
-    mbar_init(tmem_empty, kEpiWarps * CG);
-    mbar_init(stg_free, CW);
+    mbar_init(tmem_empty, kConvWarps);
+    mbar_init(stg_free, kConvWarps);
     *abort_flag = 0;
     *last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {   // tensor memory: bn columns hold the 128 x bn f32 accumulator rows of this CTA (so that two CTAs can share an SM's 512 columns)
-    if (CG == 2) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)p.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (CG == 2) cluster_sync();                              // the partner's barriers exist before anything is delivered to them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  long long t_clk0 = 0; unsigned long long t_ns0 = 0;
-  if (kTiming && p.debug && threadIdx.x == 0) {
-    t_clk0 = clock64(); asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns0));
-  }
-  WorkIter<CG> wi; wi.init(p);
+  WorkIter wi; wi.init(p);
   Work wk;
   if (warp == 0) {
-    // ---- TMA producer (every CTA stages its own rows) ------------------------------------------
+    // ---- TMA producer ---------------------------------------------------------------------------
     // One thread: everything it does per k-block is on the critical path, so ring position and phase are carried in
     // registers instead of being derived from the k-block count.
     if (lane == 0) {
@@ -458,16 +378,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         if (p.b_lo && p.persistent && unit > 0 && !mbar_wait(stg_free, (uint32_t)(unit - 1) & 1, abort_flag)) { ok = false; break; }
         ++unit;
         const int ab2 = p.a_bcast2 ? 0 : wk.b2, ab1 = p.a_bcast1 ? 0 : wk.b1, bb2 = p.b_bcast2 ? 0 : wk.b2, bb1 = p.b_bcast1 ? 0 : wk.b1;
-        const int m0 = (wk.tile_m * CG + (int)rank) * BM, n0 = wk.tile_n * bn + (int)rank * bnc;
+        const int m0 = wk.tile_m * BM, n0 = wk.tile_n * bn;
         int k = wk.kb0 * bk;
         for (int kb = 0; kb < wk.nkb; ++kb, ++it, k += bk) {
-          if (kTiming && (p.debug & 4)) continue;
           if (it >= stages && !mbar_wait(&empty[s], ph, abort_flag)) { ok = false; break; }
-          trace_event(p, 0, it);
           uint8_t* st = smem + (size_t)s * raw_bytes;
           mbar_arrive_expect_tx(&full[s], raw_bytes);
           tma_load_tile(st, &map_a, &full[s], amode, BM, m0, k, ab2, ab1, bk);
-          tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bnc, n0, k, bb2, bb1, bk);
+          tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bn, n0, k, bb2, bb1, bk);
           if (p.b_lo) {
             // the lo part of B lands straight in the lo stage (the converters fill only the A part); it completes on the stage's
             // `conv` barrier together with their arrivals
@@ -475,10 +393,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             const uint32_t lph = (((uint32_t)(it / lstages)) & 1u) ^ 1u;    // parity of `lo_empty` that says the slot was released
             if (it >= lstages && !mbar_wait(&lo_empty[l], lph, abort_flag)) { ok = false; break; }
             mbar_arrive_expect_tx(&conv[l], p.a_lo ? raw_bytes : b_bytes);
-            tma_load_tile(lo_ring + (size_t)l * raw_bytes + a_bytes, &map_blo, &conv[l], bmode, bnc, n0, k, bb2, bb1, bk);
+            tma_load_tile(lo_ring + (size_t)l * raw_bytes + a_bytes, &map_blo, &conv[l], bmode, bn, n0, k, bb2, bb1, bk);
             if (p.a_lo) tma_load_tile(lo_ring + (size_t)l * raw_bytes, &map_alo, &conv[l], amode, BM, m0, k, ab2, ab1, bk);
           }
-          trace_event(p, 1, it);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
@@ -498,11 +415,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer (the even CTA of a pair issues for both) -----------------------------------
+    // ---- MMA issuer -----------------------------------------------------------------------------
     // One thread again: descriptors of every ring slot differ only in the start-address field, so they are advanced by
     // additions; nothing else is computed per k-block.
-    if (lane == 0 && rank == 0) {
-      const uint32_t idesc = make_idesc(BM * CG, bn, p.a_mn, p.b_mn);
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, bn, p.a_mn, p.b_mn);
       const uint64_t a_hi0 = make_desc(smem_u32(smem), 0, p.a_mn, bk), b_hi0 = make_desc(smem_u32(smem) + a_bytes, 0, p.b_mn, bk);
       const uint64_t a_lo0 = make_desc(smem_u32(lo_ring), 0, p.a_mn, bk), b_lo0 = make_desc(smem_u32(lo_ring) + a_bytes, 0, p.b_mn, bk);
       const uint64_t a_ks = p.a_mn ? (1024 >> 4) : (32 >> 4), b_ks = p.b_mn ? (1024 >> 4) : (32 >> 4);   // second 8-wide k step of a k-block
@@ -514,71 +431,44 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
       while (ok && wi.next(p, wk)) {
         if (wk.nkb == 0) continue;
         if (unit > 0) {                 // the previous unit's accumulator must have left tensor memory
-          ok = CG == 2 ? mbar_wait_cluster(tmem_empty, (uint32_t)(unit - 1) & 1, abort_flag) : mbar_wait(tmem_empty, (uint32_t)(unit - 1) & 1, abort_flag);
+          ok = mbar_wait(tmem_empty, (uint32_t)(unit - 1) & 1, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
         uint32_t acc = 0;
         for (int kb = 0; kb < wk.nkb; ++kb) {
-          if (kTiming && (p.debug & 8)) {            // timing experiment: loads only
-            ok = mbar_wait(&full[s], lph, abort_flag);   // (rings of equal depth only)
-            if (!ok) break;
-            mbar_arrive(&empty[s]);
-          } else {
-            if (!(kTiming && (p.debug & 4))) ok = CG == 2 ? mbar_wait_cluster(&conv[l], lph, abort_flag) : mbar_wait(&conv[l], lph, abort_flag);
-            if (!ok) break;
-            trace_event(p, 4, kb);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // one MMA covers 8 k: 32 bytes along a K-major row, or one 1024-byte k group of an MN-major tile
-            if (CG == 2) {
-              if (kTiming && (p.debug & 2)) { mma_tf32_pair(tmem_base, a_hi, b_hi, idesc, acc); mma_tf32_pair(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u); }
-              else {
-                mma_tf32_pair(tmem_base, a_lo, b_hi, idesc, acc);
-                mma_tf32_pair(tmem_base, a_hi, b_lo, idesc, 1u);
-                mma_tf32_pair(tmem_base, a_hi, b_hi, idesc, 1u);
-                mma_tf32_pair(tmem_base, a_lo + a_ks, b_hi + b_ks, idesc, 1u);
-                mma_tf32_pair(tmem_base, a_hi + a_ks, b_lo + b_ks, idesc, 1u);
-                mma_tf32_pair(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u);
-              }
-            } else {
-              if (kTiming && (p.debug & 2)) { mma_tf32(tmem_base, a_hi, b_hi, idesc, acc); mma_tf32(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u); }
-              else {
-                mma_tf32(tmem_base, a_lo, b_hi, idesc, acc);
-                mma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
-                mma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
-                mma_tf32(tmem_base, a_lo + a_ks, b_hi + b_ks, idesc, 1u);
-                mma_tf32(tmem_base, a_hi + a_ks, b_lo + b_ks, idesc, 1u);
-                mma_tf32(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u);
-                if (bk == 32) {         // two more 8-wide k steps
-                  mma_tf32(tmem_base, a_lo + 2 * a_ks, b_hi + 2 * b_ks, idesc, 1u);
-                  mma_tf32(tmem_base, a_hi + 2 * a_ks, b_lo + 2 * b_ks, idesc, 1u);
-                  mma_tf32(tmem_base, a_hi + 2 * a_ks, b_hi + 2 * b_ks, idesc, 1u);
-                  mma_tf32(tmem_base, a_lo + 3 * a_ks, b_hi + 3 * b_ks, idesc, 1u);
-                  mma_tf32(tmem_base, a_hi + 3 * a_ks, b_lo + 3 * b_ks, idesc, 1u);
-                  mma_tf32(tmem_base, a_hi + 3 * a_ks, b_hi + 3 * b_ks, idesc, 1u);
-                }
-              }
-            }
-            acc = 1u;
-            if (!(kTiming && (p.debug & 4))) {
-              // frees the raw stage and the lo stage (in both CTAs of a pair) once these MMAs have read them
-              if (CG == 2) { mma_commit_pair(&empty[s]); mma_commit_pair(&lo_empty[l]); }
-              else { mma_commit(&empty[s]); mma_commit(&lo_empty[l]); }
-            }
-            trace_event(p, 5, kb);
+          ok = mbar_wait(&conv[l], lph, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          // one MMA covers 8 k: 32 bytes along a K-major row, or one 1024-byte k group of an MN-major tile
+          mma_tf32(tmem_base, a_lo, b_hi, idesc, acc);
+          mma_tf32(tmem_base, a_hi, b_lo, idesc, 1u);
+          mma_tf32(tmem_base, a_hi, b_hi, idesc, 1u);
+          mma_tf32(tmem_base, a_lo + a_ks, b_hi + b_ks, idesc, 1u);
+          mma_tf32(tmem_base, a_hi + a_ks, b_lo + b_ks, idesc, 1u);
+          mma_tf32(tmem_base, a_hi + a_ks, b_hi + b_ks, idesc, 1u);
+          if (bk == 32) {         // two more 8-wide k steps
+            mma_tf32(tmem_base, a_lo + 2 * a_ks, b_hi + 2 * b_ks, idesc, 1u);
+            mma_tf32(tmem_base, a_hi + 2 * a_ks, b_lo + 2 * b_ks, idesc, 1u);
+            mma_tf32(tmem_base, a_hi + 2 * a_ks, b_hi + 2 * b_ks, idesc, 1u);
+            mma_tf32(tmem_base, a_lo + 3 * a_ks, b_hi + 3 * b_ks, idesc, 1u);
+            mma_tf32(tmem_base, a_hi + 3 * a_ks, b_lo + 3 * b_ks, idesc, 1u);
+            mma_tf32(tmem_base, a_hi + 3 * a_ks, b_hi + 3 * b_ks, idesc, 1u);
           }
+          acc = 1u;
+          // frees the raw stage and the lo stage once these MMAs have read them
+          mma_commit(&empty[s]); mma_commit(&lo_empty[l]);
           if (++s == stages) { s = 0; a_hi = a_hi0; b_hi = b_hi0; } else { a_hi += stage16; b_hi += stage16; }
           if (++l == lstages) { l = 0; lph ^= 1; a_lo = a_lo0; b_lo = b_lo0; } else { a_lo += stage16; b_lo += stage16; }
         }
-        if (ok) { if (CG == 2) mma_commit_pair(tmem_full); else mma_commit(tmem_full); }    // accumulator complete
+        if (ok) mma_commit(tmem_full);    // accumulator complete
         ++unit;
       }
     }
   } else {
     // ---- converters, then epilogue ------------------------------------------------------------
-    const int cw = warp - 2, ct = cw * 32 + lane;            // 0 .. 32*CW-1
-    constexpr int kConvThreads = 32 * CW;
-    const bool epi = cw < kEpiWarps;                         // this warp also stores results
+    const int cw = warp - 2, ct = cw * 32 + lane;            // 0 .. 255
+    constexpr int kConvThreads = 32 * kConvWarps;
     const int q = warp & 3;                                  // TMEM lane quarter this warp may read
     const int half = cw >> 2, ncol_half = bn / 2;            // two warps share a lane quarter; each takes half the columns
     float4* stg = (float4*)(lo_ring + (size_t)cw * 4096);    // staging block of this warp (the lo ring is at least 32 KB)
@@ -587,52 +477,35 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
     int s = 0, l = 0; uint32_t ph = 0, lph = 1;   // ring slots; parities of `full` (tile landed) and `lo_empty` (lo slot released)
     while (wi.next(p, wk)) {            // every warp walks the whole list (the named barriers below need all of them), aborted or not
       for (int kb = 0; kb < wk.nkb && ok; ++kb, ++it) {
-        if (kTiming && (p.debug & 12)) continue;
         if (it >= lstages) ok = mbar_wait(&lo_empty[l], lph, abort_flag);
         if (ok) ok = mbar_wait(&full[s], ph, abort_flag);
         if (!ok) break;
-        if (ct == 0) trace_event(p, 2, it);
         float4* hi = (float4*)(smem + (size_t)s * raw_bytes);
         float4* lo = (float4*)(lo_ring + (size_t)l * raw_bytes);
-        const int n4 = p.a_lo ? 0 : ((p.b_lo || (kTiming && (p.debug & 256))) ? (int)(a_bytes / 16) : (int)(raw_bytes / 16));     // (timing experiment 256: only the A part is split)
-        if (kTiming && (p.debug & 1)) {
-        } else if (p.raw_hi) {
+        const int n4 = p.a_lo ? 0 : (p.b_lo ? (int)(a_bytes / 16) : (int)(raw_bytes / 16));     // what is left to split: nothing, the A part, or both parts
 #pragma unroll 3
-          for (int i = ct; i < n4; i += kConvThreads) {
-            float4 x = hi[i], l;
-            l.x = tf32_lo_of_raw(x.x); l.y = tf32_lo_of_raw(x.y); l.z = tf32_lo_of_raw(x.z); l.w = tf32_lo_of_raw(x.w);
-            lo[i] = l;
-          }
-        } else {
-#pragma unroll 3
-          for (int i = ct; i < n4; i += kConvThreads) {
-            float4 x = hi[i], h, l;
-            h.x = tf32_rna(x.x); h.y = tf32_rna(x.y); h.z = tf32_rna(x.z); h.w = tf32_rna(x.w);
-            l.x = tf32_rna(x.x - h.x); l.y = tf32_rna(x.y - h.y); l.z = tf32_rna(x.z - h.z); l.w = tf32_rna(x.w - h.w);
-            hi[i] = h; lo[i] = l;
-          }
+        for (int i = ct; i < n4; i += kConvThreads) {
+          float4 x = hi[i], l;
+          l.x = tf32_lo_of_raw(x.x); l.y = tf32_lo_of_raw(x.y); l.z = tf32_lo_of_raw(x.z); l.w = tf32_lo_of_raw(x.w);
+          lo[i] = l;
         }
-        if (ct == 0) trace_event(p, 7, it);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
-        if (ct == 0) trace_event(p, 6, it + 2);
         __syncwarp();
-        if (lane == 0) { if (rank == 0) mbar_arrive(&conv[l]); else mbar_arrive_remote(&conv[l], 0); }
-        if (ct == 0) trace_event(p, 3, it);
+        if (lane == 0) mbar_arrive(&conv[l]);
         if (++s == stages) { s = 0; ph ^= 1; }
         if (++l == lstages) { l = 0; lph ^= 1; }
       }
       // ---- epilogue of this unit ----
-      bool have = ok && epi;
+      bool have = ok;
       if (have && wk.nkb > 0) have = ok = mbar_wait(tmem_full, (uint32_t)unit & 1, abort_flag);
       if (have) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (ct == 0) trace_event(p, 6, 0);
-      const i64 row0 = ((i64)wk.tile_m * CG + rank) * BM + q * 32;
+      const i64 row0 = (i64)wk.tile_m * BM + q * 32;
       const bool streamk_part = p.persistent && !wk.whole;
       float* cbase = p.C + (i64)wk.b1 * p.c_b1 + (i64)wk.b2 * p.c_b2;
       const bool c_vec = (p.c_rs & 3) == 0 && (((uintptr_t)p.C | (uintptr_t)(p.c_b1 * 4) | (uintptr_t)(p.c_b2 * 4)) & 15) == 0;
       float* pbase = p.partial + ((i64)wk.split * (p.nb1 * p.nb2) + wk.bz) * p.M * p.N;       // split-K scratch of the tiled mode
       const i64 slot_floats = (i64)BM * bn;
-      float4* slot = (float4*)p.ws + (((i64)(2 * (blockIdx.x / CG) + wk.which) * CG + rank) * slot_floats) / 4;     // stream-K partial of this CTA
+      float4* slot = (float4*)p.ws + ((i64)(2 * blockIdx.x + wk.which) * slot_floats) / 4;     // stream-K partial of this CTA
       if (have) {
         for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
           i64 col0 = (i64)wk.tile_n * bn + c0;
@@ -645,9 +518,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0u;
           }
-          if (kTiming && (p.debug & 32)) {
-            if (r[0] == 0x12345u) cbase[0] = 1.0f;       // timing experiment: no stores (the load from tensor memory stays)
-          } else if (streamk_part) {
+          if (streamk_part) {
             // partial sums of a tile shared with other groups: [32-column block][lane quarter][4-column group][lane], 512 contiguous bytes per store
             float4* dst = slot + ((c0 >> 5) * 4 + q) * 256 + lane;
 #pragma unroll
@@ -684,11 +555,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
       }
       if (p.tma_out) { if (lane == 0) tma_store_wait_read(); __syncwarp(); }     // the staging area is the lo ring of the next unit
-      if (ct == 0) trace_event(p, 6, 1);
       if (wk.nkb > 0) {                 // the accumulator has been read: the next unit's first MMA may overwrite it
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
-        if (lane == 0 && have) { if (rank == 0) mbar_arrive(tmem_empty); else mbar_arrive_remote(tmem_empty, 0); }
+        if (lane == 0 && have) mbar_arrive(tmem_empty);
         ++unit;
       }
       if (streamk_part) {
@@ -696,9 +566,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         // counts last adds all parts in k order (its own included, read back from memory: the order of the additions is then
         // the same whichever CTA happens to be last) and writes the result.  Nobody waits for anybody.
         __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConvWarps) : "memory");
         const i64 kblocks_total = (p.K + p.bk - 1) / p.bk;
-        const i64 x0 = (i64)wk.tile * kblocks_total, G = gridDim.x / CG, W = p.total_kb;
+        const i64 x0 = (i64)wk.tile * kblocks_total, G = gridDim.x, W = p.total_kb;
         // first and last group whose range meets [x0, x0 + kblocks_total): group c starts at floor(c*W/G)
         i64 cf = ((x0 + 1) * G + W - 1) / W - 1;
         while (cf + 1 < G && ((cf + 1) * W) / G <= x0) ++cf;
@@ -707,7 +577,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         while (cl + 1 < G && ((cl + 1) * W) / G <= x0 + kblocks_total - 1) ++cl;
         while (cl > 0 && (cl * W) / G > x0 + kblocks_total - 1) --cl;
         const int np = (int)(cl - cf + 1);
-        int* counter = p.counters + (i64)wk.tile * CG + rank;           // each CTA of a pair finishes its own rows
+        int* counter = p.counters + wk.tile;
         if (ct == 0) {
           int last = 0;
           if (!*abort_flag) {
@@ -716,9 +586,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           }
           *last_flag = last;
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kConvWarps) : "memory");
         const int last = *last_flag;
-        if (last && epi && !*abort_flag) {
+        if (last && !*abort_flag) {
           __threadfence();
           for (int c0 = half * ncol_half; c0 < (half + 1) * ncol_half; c0 += 32) {
             i64 col0 = (i64)wk.tile_n * bn + c0;
@@ -730,7 +600,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             for (int i = 0; i < np; ++i) {
               const i64 c = cf + i;
               const int which = ((c * W) / G >= x0) ? 0 : 1;
-              const float4* src = (const float4*)p.ws + (((2 * c + which) * CG + rank) * slot_floats) / 4 + unit;
+              const float4* src = (const float4*)p.ws + ((2 * c + which) * slot_floats) / 4 + unit;
               float4 x[8];
 #pragma unroll
               for (int j4 = 0; j4 < 8; ++j4) x[j4] = __ldcg(src + j4 * 32);
@@ -771,31 +641,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
         }
       }
       // the staging area is the lo ring, and last_flag is per unit: nobody starts converting the next unit before all have finished this one
-      if (p.persistent) asm volatile("bar.sync 1, %0;" ::"n"(32 * CW) : "memory");
+      if (p.persistent) asm volatile("bar.sync 1, %0;" ::"n"(32 * kConvWarps) : "memory");
       if (p.b_lo && p.persistent && lane == 0) mbar_arrive(stg_free);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (CG == 2) cluster_sync();          // nothing of the partner's may still be in flight towards this CTA (remote arrivals, MMA reads) when it leaves
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
-    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)p.tmem_cols) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.err, ERRBIT_WAIT_TIMEOUT);
-  if (kTiming && p.debug && p.counters && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {
-    unsigned long long t_ns1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns1));
-    long long* out = (long long*)(p.counters + 4000);
-    out[0] = clock64() - t_clk0; out[1] = (long long)(t_ns1 - t_ns0);
-  }
-  if (kTiming && (p.debug & 64) && p.ws && threadIdx.x == 0) {      // residency trace: SM, start, end of every CTA
-    unsigned long long t_ns1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns1));
-    unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    long long lin = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
-    long long* tr = (long long*)p.ws + 3 * lin;
-    tr[0] = smid; tr[1] = (long long)t_ns0; tr[2] = (long long)t_ns1;
-  }
 }
 
 // Sum the split-K partial tiles in split order, then apply alpha / beta / bias.
@@ -927,6 +783,8 @@ int* g_tile_counters = nullptr;     // stream-K arrival counters (zero between l
 
 }  // namespace
 
+int64_t g_tc_launches = 0;          // launches of k_gemm_tc so far (vb_tc_launch_count)
+
 // After a device-side wait ran out a tile may have been left half counted: start from zero again.
 int gemm_tc_reset_state() {
   if (g_tile_counters) VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
@@ -961,10 +819,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     *o = Operand{p, rows, rs, sb1, sb2, bc1, bc2, false};
     if (cs == 1 && tma_ok(*o, g.nb1, g.nb2)) return VB_OK;
     // MN-contiguous (a transposed view): consumed in place through MN-major descriptors
-    static int no_mn = -1;
-    if (no_mn < 0) { const char* e = getenv("VB200_TC_NO_MN"); no_mn = (e && e[0] == '1') ? 1 : 0; }
     Operand mn{p, rows, cs, sb1, sb2, bc1, bc2, true};
-    if (!no_mn && rs == 1 && rows >= 32 && tma_ok(mn, g.nb1, g.nb2)) { *o = mn; return VB_OK; }
+    if (rs == 1 && rows >= 32 && tma_ok(mn, g.nb1, g.nb2)) { *o = mn; return VB_OK; }
     // repack into K-contiguous scratch, one plane per (non-broadcast) batch
     i64 e1 = bc1 ? 1 : g.nb1, e2 = bc2 ? 1 : g.nb2;
     i64 Kp = (g.K + 3) & ~i64(3);
@@ -982,21 +838,10 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   VB_TRY(prepare(g.B, g.N, g.b_cs, g.b_rs, g.b_b1, g.b_b2, hold_b, &ob));   // B^T rows are the columns of B
 
   TcParams p{};
-  // CTA pairs (256-row tiles, one MMA for two SMs) are opt-in: they move a third less through L2 and shared memory, but as
-  // measured the cross-CTA hand-offs cost more than that saves (fc1 of GPT-small: 268 us against 224 us with single CTAs).
-  static int cg_env = -1;
-  if (cg_env < 0) { const char* e = getenv("VB200_TC_CG"); cg_env = e ? atoi(e) : 1; }
-  const int CG = (cg_env == 2 && g.M > BM && !g.causal) ? 2 : 1;
   // 64-wide tiles do a quarter of the work of 256-wide ones per k-block but pay the same hand-offs: twice the k per stage
-  static int bk32_env = -1;
-  if (bk32_env < 0) { const char* e = getenv("VB200_TC_BK32"); bk32_env = (e && e[0] == '0') ? 0 : 1; }
-  const int bk = (bk32_env && CG == 1 && g.N <= 64 && g.K >= 64) ? 32 : BK;
+  const int bk = (g.N <= 64 && g.K >= 64) ? 32 : BK;
   const i64 kblocks = (g.K + bk - 1) / bk;
-  static int cw_env = -1;
-  if (cw_env < 0) { const char* e = getenv("VB200_TC_CW"); cw_env = (e && atoi(e) == 16) ? 16 : 8; }
-  const int CW = cw_env;
-  const i64 BMT = (i64)BM * CG;
-  const i64 slots = (i64)ctx().sm_count * (CW == 8 ? 2 : 1) / CG;     // resident groups: two CTAs per SM (one with 16 converter warps)
+  const i64 slots = (i64)ctx().sm_count * 2;     // resident CTAs: two per SM
   p.bn = g.N <= 64 ? 64 : (g.N <= 128 ? 128 : 256);
   int splits = 1;
   if (p.bn == 256) {
@@ -1007,10 +852,10 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     // 192-wide tiles only where they make a single wave fuller (8192 x 768 . 768 x 768: 256 tiles instead of 192 for 296 slots,
     // 62.7 us against 74.7 us); on multi-wave products they measured no better than 256
     for (int bn : {256, 192, 128}) {
-      i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
+      i64 tiles = ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * nb;
       for (int sk : {1, 2, 3, 4, 5, 6, 8, 10, 12, 16}) {
         if (sk > 1 && kblocks / sk < 24) break;
-        if (bn == 192 && (sk > 1 || tiles > slots || CG != 1)) break;
+        if (bn == 192 && (sk > 1 || tiles > slots)) break;
         i64 units = tiles * sk, waves = (units + slots - 1) / slots;
         double kb_cost = bn == 256 ? 1.0 : (bn == 192 ? 0.81 : 0.62), epi = bn == 256 ? 10.0 : (bn == 192 ? 8.0 : 6.0);
         double t = (double)waves * ((double)((kblocks + sk - 1) / sk) * kb_cost + epi);
@@ -1019,56 +864,47 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
       }
     }
   } else {
-    i64 tiles = ((g.M + BMT - 1) / BMT) * nb;
+    i64 tiles = ((g.M + BM - 1) / BM) * nb;
     if (tiles < slots && kblocks >= 48) { splits = (int)((slots + tiles - 1) / tiles); if (splits > kblocks / 24) splits = (int)(kblocks / 24); if (splits < 1) splits = 1; }
   }
-  // Stream-K instead of split-K where a tile would be shared by three or four groups at most: the k-blocks of all tiles are
-  // dealt evenly to one group per slot and shared tiles are finished inside the kernel (no pass over partial tiles).
-  // Measured slower than plain tiles when nothing needs splitting (groups at different k positions stop sharing
-  // operand lines in L2) and when a tile has many parts (the group finishing a tile adds them alone).
-  static int persist_env = -1;
-  if (persist_env < 0) { const char* e = getenv("VB200_TC_STREAMK"); persist_env = e ? atoi(e) : 1; }
+  // Stream-K instead of split-K where a tile would be shared by three or four CTAs at most: the k-blocks of all tiles are
+  // dealt evenly to one CTA per slot and shared tiles are finished inside the kernel (no pass over partial tiles).
+  // Measured slower than plain tiles when nothing needs splitting (CTAs at different k positions stop sharing
+  // operand lines in L2) and when a tile has many parts (the CTA finishing a tile adds them alone).
   bool persistent = false;
   i64 streamk_groups = 0;
   // ... and where whole 256-wide tiles would fill one wave and less than half of a second one (measured on 4096 x 1024 . 1024 x 3072:
   // 384 tiles for 296 slots, 157 us against 187 us with 128-wide tiles)
-  const i64 tiles256 = ((g.M + BMT - 1) / BMT) * ((g.N + 255) / 256) * nb;
+  const i64 tiles256 = ((g.M + BM - 1) / BM) * ((g.N + 255) / 256) * nb;
   const bool ragged_wave = splits == 1 && g.N > 128 && tiles256 > slots && 2 * tiles256 <= 3 * slots && kblocks >= 32;
-  if (persist_env && !g.causal && p.bn >= 128 && (splits > 1 || ragged_wave || persist_env == 2)) {
+  if (!g.causal && p.bn >= 128 && (splits > 1 || ragged_wave)) {
     int bn = 256;
     if (g.N <= 128 || ((g.N + 127) / 128) * 128 * 5 <= ((g.N + 255) / 256) * 256 * 4) bn = 128;     // a 256-wide last tile would be mostly padding
-    i64 tiles = ((g.M + BMT - 1) / BMT) * ((g.N + bn - 1) / bn) * nb;
+    i64 tiles = ((g.M + BM - 1) / BM) * ((g.N + bn - 1) / bn) * nb;
     i64 W = tiles * kblocks, G = slots;
-    if (G > W / 8) G = W / 8;                          // at least 8 k-blocks per group
+    if (G > W / 8) G = W / 8;                          // at least 8 k-blocks per CTA
     if (G < 1) G = 1;
     // (very long K: plain split-K measured faster, 2.74 ms against 2.90 ms for 8192 x 50304 . 50304 x 768)
-    if (tiles * CG <= 4096 && (persist_env == 2 || (W / G >= kblocks / 3 && kblocks <= 1024))) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
+    if (tiles <= 4096 && W / G >= kblocks / 3 && kblocks <= 1024) { persistent = true; streamk_groups = G; p.bn = bn; splits = 1; }
   }
-  { const char* e = getenv("VB200_TC_BN"); if (e && !persistent && p.bn == 256 && atoi(e) == 192) p.bn = 192; }
   p.tmem_cols = p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256);
-  const i64 tiles_m = (g.M + BMT - 1) / BMT, tiles_n = (g.N + p.bn - 1) / p.bn;
+  const i64 tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + p.bn - 1) / p.bn;
   // Short-K products with many tiles per slot (attention scores, the vocabulary projection): resident CTAs take whole tiles
   // round-robin instead of one launch slot per tile.
   const int causal_eff = (splits == 1 && !persistent && g.M == (g.causal == 1 ? g.N : g.K)) ? g.causal : 0;
   i64 live_per_batch = tiles_m * tiles_n;
   if (causal_eff == 1) {
     live_per_batch = 0;
-    for (i64 m = 0; m < tiles_m; ++m) { i64 c = ((m + 1) * BMT + p.bn - 1) / p.bn; live_per_batch += c < tiles_n ? c : tiles_n; }
+    for (i64 m = 0; m < tiles_m; ++m) { i64 c = ((m + 1) * BM + p.bn - 1) / p.bn; live_per_batch += c < tiles_n ? c : tiles_n; }
   }
-  static int rr_env = -1;
-  if (rr_env < 0) { const char* e = getenv("VB200_TC_ROUNDROBIN"); rr_env = (e && e[0] == '0') ? 0 : 1; }
-  const bool round_robin = rr_env && !persistent && splits == 1 && kblocks <= 64 && causal_eff <= 1 && live_per_batch * nb >= 4 * slots;
-  const size_t raw_bytes = (size_t)(BM + p.bn / CG) * bk * 4;
+  const bool round_robin = !persistent && splits == 1 && kblocks <= 64 && causal_eff <= 1 && live_per_batch * nb >= 4 * slots;
+  const size_t raw_bytes = (size_t)(BM + p.bn) * bk * 4;
   p.bk = bk;
   // Small rings on purpose: two CTAs then share an SM, and one CTA's epilogue and pipeline bubbles are covered by
   // the other's main loop; measured faster than one CTA per SM with a deep ring.  The lo ring is at least 32 KB
   // because the epilogue stages its stores there.
   p.lstages = (int)((32 * 1024 + raw_bytes - 1) / raw_bytes); if (p.lstages < 2) p.lstages = 2;
   p.stages = (int)((100 * 1024 - (size_t)p.lstages * raw_bytes) / raw_bytes); if (p.stages > 4) p.stages = 4; if (p.stages < 2) p.stages = 2;
-  if (CW == 16) {       // one CTA per SM: rings as deep as shared memory allows
-    if (p.lstages < 3) p.lstages = 3;
-    p.stages = (int)((208 * 1024 - (size_t)p.lstages * raw_bytes) / raw_bytes); if (p.stages > 8) p.stages = 8;
-  }
   p.kblocks_per_split = (int)((kblocks + splits - 1) / splits);
   splits = (int)((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split);
   p.splits = splits;
@@ -1077,7 +913,7 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   CUtensorMap map_a, map_b;
   bool fold_a = false, fold_b = false;
   VB_TRY(make_map(&map_a, oa, g.K, g.nb1, g.nb2, BM, bk, &fold_a));
-  VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn / CG, bk, &fold_b));
+  VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn, bk, &fold_b));
   p.a_fold = fold_a; p.b_fold = fold_b;
   Temp part, ws;
   if (splits > 1) VB_TRY(scratch_alloc((size_t)((i64)splits * nb * g.M * g.N) * sizeof(float), &part.p));
@@ -1086,19 +922,9 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
       VB_CUDA(cudaMalloc(&g_tile_counters, 4096 * sizeof(int)));
       VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
     }
-    VB_TRY(scratch_alloc((size_t)streamk_groups * CG * 2 * BM * p.bn * sizeof(float), &ws.p));
+    VB_TRY(scratch_alloc((size_t)streamk_groups * 2 * BM * p.bn * sizeof(float), &ws.p));
     p.persistent = 1; p.total_kb = tiles_m * tiles_n * nb * kblocks; p.tiles_m = tiles_m; p.tiles_n = tiles_n;
     p.ws = (float*)ws.p; p.counters = g_tile_counters;
-  }
-  if (kTiming && !g_tile_counters) {
-    VB_CUDA(cudaMalloc(&g_tile_counters, 4096 * sizeof(int)));
-    VB_CUDA(cudaMemsetAsync(g_tile_counters, 0, 4096 * sizeof(int), ctx().stream));
-  }
-  if (kTiming) p.counters = g_tile_counters;
-  if (kTiming && !persistent) {
-    const char* e = getenv("VB200_TC_DEBUG");
-    if (e && (atoi(e) & 128)) { VB_TRY(scratch_alloc(8 * 256 * 8, &ws.p)); p.ws = (float*)ws.p; VB_CUDA(cudaMemsetAsync(ws.p, 0, 8 * 256 * 8, ctx().stream)); }
-    else if (e && (atoi(e) & 64)) { VB_TRY(scratch_alloc((size_t)tiles_n * CG * tiles_m * nb * splits * 24 + 1024, &ws.p)); p.ws = (float*)ws.p; }
   }
   p.C = g.C; p.bias = g.bias; p.bias_m = g.bias_m; p.partial = (float*)part.p;
   p.M = g.M; p.N = g.N; p.K = g.K; p.c_rs = g.c_rs; p.c_b1 = g.c_b1; p.c_b2 = g.c_b2; p.nb1 = g.nb1; p.nb2 = g.nb2;
@@ -1106,135 +932,65 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   p.a_mn = oa.mn; p.b_mn = ob.mn;
   p.alpha = g.alpha; p.beta = g.beta; p.err = ctx().d_err;
   p.causal = causal_eff;
-  static int lf_env = -1;
-  if (lf_env < 0) { const char* e = getenv("VB200_TC_LONG_FIRST"); lf_env = (e && e[0] == '0') ? 0 : 1; }
-  p.long_first = (lf_env && !persistent && !round_robin && causal_eff >= 2 && tiles_m <= 65535 && nb * splits <= 65535) ? 1 : 0;
+  p.long_first = (!persistent && !round_robin && causal_eff >= 2 && tiles_m <= 65535 && nb * splits <= 65535) ? 1 : 0;
   if (round_robin) { p.persistent = 2; p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.live_per_batch = live_per_batch; p.live_tiles = live_per_batch * nb; }
 
   // Results leave through the copy engine when the layout allows and nothing has to be read back (beta = 0).
   CUtensorMap map_c;
   memset(&map_c, 0, sizeof map_c);
-  static int tma_out_env = -1;
-  if (tma_out_env < 0) { const char* e = getenv("VB200_TC_TMA_OUT"); tma_out_env = (e && e[0] == '0') ? 0 : 1; }
-  if (tma_out_env && g.beta == 0.0f && !(kTiming && getenv("VB200_TC_DEBUG") && (atoi(getenv("VB200_TC_DEBUG")) & ~256))) {
+  if (g.beta == 0.0f) {
     if (splits == 1) p.tma_out = make_out_map(&map_c, g.C, g.N, g.M, g.nb2, g.nb1, g.c_rs, g.c_b2, g.c_b1) ? 1 : 0;
     else p.tma_out = make_out_map(&map_c, (float*)part.p, g.N, g.M, (i64)splits * nb, 1, g.N, g.M * g.N, 0) ? 1 : 0;
   }
 
-  // Pre-split lo part of B: B consumed in place (the lo plane has B's layout), raw hi operand.  (In the persistent modes the
+  // Pre-split lo part of B: B consumed in place (the lo plane has B's layout).  (In the persistent modes the
   // producer holds the lo parts of the next tile back until the epilogue has left the lo ring, its staging area.)
   CUtensorMap map_blo;
   memset(&map_blo, 0, sizeof map_blo);
-  static int blo_env = -1;
-  if (blo_env < 0) { const char* e = getenv("VB200_TC_B_LO"); blo_env = (e && e[0] == '0') ? 0 : 1; }
-  static int blo_p_env = -1;
-  if (blo_p_env < 0) { const char* e = getenv("VB200_TC_B_LO_PERSISTENT"); blo_p_env = (e && e[0] == '0') ? 0 : 1; }
-  if (blo_env && g.B_lo && !hold_b.p && CG == 1 && (blo_p_env || (!persistent && !round_robin)) && !(kTiming && getenv("VB200_TC_DEBUG"))) {
+  if (g.B_lo && !hold_b.p) {
     Operand obl = ob; obl.p = g.B_lo;
     bool f2 = false;
-    if (tma_ok(obl, g.nb1, g.nb2) && make_map(&map_blo, obl, g.K, g.nb1, g.nb2, p.bn / CG, bk, &f2) == VB_OK && f2 == fold_b) p.b_lo = 1;
+    if (tma_ok(obl, g.nb1, g.nb2) && make_map(&map_blo, obl, g.K, g.nb1, g.nb2, p.bn, bk, &f2) == VB_OK && f2 == fold_b) p.b_lo = 1;
   }
   CUtensorMap map_alo;
   memset(&map_alo, 0, sizeof map_alo);
-  static int alo_env = -1;
-  if (alo_env < 0) { const char* e = getenv("VB200_TC_A_LO"); alo_env = (e && e[0] == '0') ? 0 : 1; }
-  if (alo_env && p.b_lo && g.A_lo && !hold_a.p) {
+  if (p.b_lo && g.A_lo && !hold_a.p) {
     Operand oal = oa; oal.p = g.A_lo;
     bool f2 = false;
     if (tma_ok(oal, g.nb1, g.nb2) && make_map(&map_alo, oal, g.K, g.nb1, g.nb2, BM, bk, &f2) == VB_OK && f2 == fold_a) p.a_lo = 1;
   }
 
-  static int raw_hi_env = -1;
-  if (raw_hi_env < 0) { const char* e = getenv("VB200_TC_RAW_HI"); raw_hi_env = (e && e[0] == '0') ? 0 : 1; }
-  p.raw_hi = raw_hi_env;
-  if (!p.raw_hi) p.b_lo = p.a_lo = 0;           // the plane holds remainders against the raw (cut) hi operand
-  { static int dbg = -1; if (dbg < 0) { const char* e = getenv("VB200_TC_DEBUG"); dbg = e ? atoi(e) : 0; } p.debug = dbg; }
-  { const char* e = getenv("VB200_TC_STAGES"); if (e) { int r = 0, l = 0; if (sscanf(e, "%d,%d", &r, &l) == 2 && r >= 1 && l >= 1 && (size_t)(r + l) * raw_bytes <= 220 * 1024 && (size_t)l * raw_bytes >= 32 * 1024) { p.stages = r; p.lstages = l; } } }
   size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 3) * sizeof(uint64_t) + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<2, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<2, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
   {
     static int shapes = -1;
     if (shapes < 0) { const char* e = getenv("VB200_PROF_SHAPES"); shapes = (e && e[0] == '1') ? 1 : 0; }
     char fam[96];
-    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d%s", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits, persistent ? " streamk" : (round_robin ? " roundrobin" : (CG == 2 ? " pair" : "")));
+    if (shapes) snprintf(fam, sizeof fam, "gemm_tc M%lld N%lld K%lld nb%lld a%d b%d bn%d sk%d%s", (long long)g.M, (long long)g.N, (long long)g.K, (long long)nb, (int)oa.mn, (int)ob.mn, p.bn, splits, persistent ? " streamk" : (round_robin ? " roundrobin" : ""));
     else snprintf(fam, sizeof fam, "%s", nb > 1 ? "gemm_tc_batched" : "gemm_tc");
-    ProfScope prof(fam, 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb);
-    dim3 grid((unsigned)(tiles_n * CG), (unsigned)tiles_m, (unsigned)(nb * splits));
-    if (p.long_first) grid = dim3((unsigned)(tiles_n * CG), (unsigned)(nb * splits), (unsigned)tiles_m);
-    if (persistent) grid = dim3((unsigned)(streamk_groups * CG), 1, 1);
-    if (round_robin) grid = dim3((unsigned)(slots * CG), 1, 1);
-    if (CG == 2) {
-      cudaLaunchConfig_t cfg{};
-      cfg.gridDim = grid; cfg.blockDim = dim3(64 + 32 * CW, 1, 1); cfg.dynamicSmemBytes = smem; cfg.stream = ctx().stream;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr; cfg.numAttrs = 1;
-      { static int occ = -1; if (occ < 0) { const char* e = getenv("VB200_TC_OCC"); occ = (e && e[0] == '1') ? 1 : 0; }
-        if (occ) { int n = 0; cudaError_t r = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<2, 8>, &cfg); fprintf(stderr, "[gemm_tc] max active clusters %d (err %d), smem %zu, grid %u\n", n, (int)r, smem, grid.x * grid.y * grid.z); occ = 0; } }
-      if (CW == 16) VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 16>, map_a, map_b, map_c, map_blo, map_alo, p));
-      else VB_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_tc<2, 8>, map_a, map_b, map_c, map_blo, map_alo, p));
-    } else if (CW == 16) {
-      k_gemm_tc<1, 16><<<grid, 64 + 32 * 16, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, p);
-    } else {
-      k_gemm_tc<1, 8><<<grid, 64 + 32 * 8, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, p);
+    // flops of the tiles and k ranges that are actually issued (a causal product skips or clamps some), next to the dense count
+    const double dense = 2.0 * (double)g.M * (double)g.N * (double)g.K * (double)nb;
+    double issued = dense;
+    if (causal_eff == 1) issued = 2.0 * (double)live_per_batch * BM * p.bn * (double)g.K * (double)nb;
+    else if (causal_eff >= 2) {
+      issued = 0.0;
+      for (i64 m = 0; m < tiles_m; ++m) {
+        i64 kr = causal_eff == 2 ? ((m + 1) * BM < g.K ? (m + 1) * BM : g.K) : (g.K - m * BM > 0 ? g.K - m * BM : 0);
+        issued += 2.0 * BM * (double)g.N * (double)kr * (double)nb;
+      }
     }
+    ProfScope prof(fam, issued < dense ? issued : dense, dense);
+    dim3 grid((unsigned)tiles_n, (unsigned)tiles_m, (unsigned)(nb * splits));
+    if (p.long_first) grid = dim3((unsigned)tiles_n, (unsigned)(nb * splits), (unsigned)tiles_m);
+    if (persistent) grid = dim3((unsigned)streamk_groups, 1, 1);
+    if (round_robin) grid = dim3((unsigned)slots, 1, 1);
+    k_gemm_tc<<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, p);
     VB_LAUNCH_CHECK();
-    if (kTiming && (p.debug & 64)) {
-      static int traced = 0;
-      if (!traced) {
-        traced = 1;
-        cudaStreamSynchronize(ctx().stream);
-        size_t n = (size_t)grid.x * grid.y * grid.z;
-        std::vector<long long> h(3 * n);
-        cudaMemcpy(h.data(), p.ws, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
-        // for every SM: the largest number of CTAs alive at once
-        int worst = 0, best = 1 << 30; long long t0 = h[1];
-        for (size_t i = 0; i < n; ++i) if (h[3 * i + 1] < t0) t0 = h[3 * i + 1];
-        for (int sm = 0; sm < 160; ++sm) {
-          int peak = 0;
-          for (size_t i = 0; i < n; ++i) if (h[3 * i] == sm) {
-            int alive = 0;
-            for (size_t j = 0; j < n; ++j) if (h[3 * j] == sm && h[3 * j + 1] <= h[3 * i + 1] && h[3 * j + 2] > h[3 * i + 1]) ++alive;
-            if (alive > peak) peak = alive;
-          }
-          if (peak) { if (peak > worst) worst = peak; if (peak < best) best = peak; }
-        }
-        fprintf(stderr, "[gemm_tc trace] %zu CTAs; CTAs alive at once per SM: min %d max %d\n", n, best, worst);
-        for (size_t i = 0; i < 6 && i < n; ++i) fprintf(stderr, "   cta %zu sm %lld start %lld end %lld\n", i, h[3 * i], h[3 * i + 1] - t0, h[3 * i + 2] - t0);
-      }
-    }
-    if (kTiming && (p.debug & 128)) {
-      static int dumped = 0;
-      if (dumped < 2 && ++dumped == 2) {       // second launch: warm
-        cudaStreamSynchronize(ctx().stream);
-        std::vector<unsigned long long> h(8 * 256);
-        cudaMemcpy(h.data(), p.ws, h.size() * 8, cudaMemcpyDeviceToHost);
-        unsigned long long t0 = h[0];
-        fprintf(stderr, "[gemm_tc pipeline] ns since first event, CTA 0:  kb | empty seen, TMA issued | full seen, converted | conv seen, MMAs issued\n");
-        for (int kb = 0; kb < 48; ++kb)
-          fprintf(stderr, "  %3d | %7lld %7lld | %7lld (stored %5lld fenced %5lld) %7lld | %7lld %7lld\n", kb, (long long)(h[kb] - t0), (long long)(h[256 + kb] - t0), (long long)(h[512 + kb] - t0),
-                  (long long)(h[1792 + kb] - h[512 + kb]), (long long)(h[1536 + kb + 2] - h[512 + kb]), (long long)(h[768 + kb] - t0), (long long)(h[1024 + kb] - t0), (long long)(h[1280 + kb] - t0));
-        fprintf(stderr, "  epilogue: tmem_full seen %lld, stores done %lld\n", (long long)(h[1536] - t0), (long long)(h[1537] - t0));
-      }
-    }
-    if (kTiming && p.debug) {
-      static int shown = 0;
-      if (shown < 3) {
-        long long h[2] = {0, 0};
-        cudaStreamSynchronize(ctx().stream);
-        cudaMemcpy(h, g_tile_counters + 4000, sizeof h, cudaMemcpyDeviceToHost);
-        fprintf(stderr, "[gemm_tc timing] CTA 0: %lld SM cycles in %lld ns = %.0f MHz\n", h[0], h[1], h[1] ? 1e3 * (double)h[0] / (double)h[1] : 0.0);
-        ++shown;
-      }
-    }
+    ++g_tc_launches;
     if (splits > 1) {
       i64 total = nb * g.M * g.N;
       i64 blocks = (total + 255) / 256, cap = (i64)ctx().sm_count * 16; if (blocks > cap) blocks = cap;

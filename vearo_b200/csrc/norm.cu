@@ -222,8 +222,9 @@ int launch_layernorm(const float* x, const float* w, const float* b, float* out,
   if (lo_done) *lo_done = false;
   if (rows <= 0 || c <= 0) return VB_OK;
   cudaStream_t st = ctx().stream;
-  ProfScope prof("layernorm_fwd", 2.0 * (double)rows * (double)c * 4.0);
   bool fast = (c % 4 == 0) && c <= 1024 && al16(x) && al16(w) && al16(b) && al16(out);
+  // x read, y written, and y's lo plane written where the caller asked for one
+  ProfScope prof("layernorm_fwd", ((fast && out_lo && al16(out_lo)) ? 3.0 : 2.0) * (double)rows * (double)c * 4.0);
   if (fast) {
     int vpt = (int)((c + 127) / 128);
     i64 blocks = (rows + 7) / 8; i64 cap = (i64)ctx().sm_count * 8; if (blocks > cap) blocks = cap;
@@ -255,7 +256,7 @@ int launch_layernorm_backward(const float* x, const float* w, const float* g, fl
     VB_TRY(scratch_alloc((size_t)(2 * blocks * c) * sizeof(float), &part));
     float* pw = (float*)part; float* pb = pw + blocks * c;
 #define LN_BWD(V) case V: \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(k_ln_bwd_warp<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(k_ln_bwd_warp<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, warps * 2 * 128 * V * (int)sizeof(float)); /* the instance's largest row, not this call's */ \
       k_ln_bwd_warp<V><<<(unsigned)blocks, warps * 32, smem, st>>>(x, w, g, gx, pw, pb, rows, (int)c, eps); break;
     switch (vpt) { LN_BWD(1) LN_BWD(2) LN_BWD(3) LN_BWD(4) LN_BWD(5) LN_BWD(6) LN_BWD(7) LN_BWD(8) }
 #undef LN_BWD
@@ -403,6 +404,9 @@ extern "C" int vb_layernorm_backward_noalloc(const float* x, const float* w, con
     float* p = nullptr;
     VB_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_bwd_noalloc_scratch));
     VB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    // rows of more than 768 floats need more than the default 48 KB of shared memory: raise the two instances' limit once, here
+    VB_CUDA(cudaFuncSetAttribute(k_ln_bwd_warp<7>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * kNoAllocMaxC * (int)sizeof(float)));
+    VB_CUDA(cudaFuncSetAttribute(k_ln_bwd_warp<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * kNoAllocMaxC * (int)sizeof(float)));
     d.scratch = p; d.ready = true;
   }
   cudaStream_t st = (cudaStream_t)stream;
@@ -421,7 +425,6 @@ extern "C" int vb_layernorm_backward_noalloc(const float* x, const float* w, con
   size_t smem = (size_t)warps * 2 * C * sizeof(float);
   int vpt = (C + 127) / 128;
 #define LN_BWD_NA(V) case V: \
-    if (smem > 48 * 1024) VB_CUDA(cudaFuncSetAttribute(k_ln_bwd_warp<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     k_ln_bwd_warp<V><<<(unsigned)ctas, warps * 32, smem, st>>>(x, w, grad_out, gx, pw, pb, rows, C, eps); break;
   switch (vpt) { LN_BWD_NA(1) LN_BWD_NA(2) LN_BWD_NA(3) LN_BWD_NA(4) LN_BWD_NA(5) LN_BWD_NA(6) LN_BWD_NA(7) LN_BWD_NA(8) }
 #undef LN_BWD_NA

@@ -168,10 +168,11 @@ __global__ void __launch_bounds__(256) k_opt_multi(const OptChunk* __restrict__ 
 }
 int launch_opt_multi(const OptChunk* chunks, int nchunks, const uint8_t* active, int kind, const float* normsq,
                      float max_norm, float grad_scale, float lr, float b1, float b2, float eps, float wd, float mu,
-                     float bc1, float bc2) {
+                     float bc1, float bc2, int lo_chunks) {
   if (nchunks <= 0) return VB_OK;
+  // bytes per parameter: g, w, m, v read and w, m, v written (AdamW); +4 where the chunk also rewrites the weight's lo plane
   ProfScope prof(kind == VB_OPT_ADAMW ? "adamw" : (kind == VB_OPT_ADAMW8BIT ? "adamw8bit" : "sgd"),
-                 (kind == VB_OPT_ADAMW ? 28.0 : (kind == VB_OPT_ADAMW8BIT ? 16.0625 : 20.0)) * 16384.0 * (double)nchunks);
+                 (kind == VB_OPT_ADAMW ? 28.0 : (kind == VB_OPT_ADAMW8BIT ? 16.0625 : 20.0)) * 16384.0 * (double)nchunks + 4.0 * 16384.0 * (double)lo_chunks);
   Hyper h{lr, b1, b2, eps, wd, mu, bc1, bc2};
   if (kind == VB_OPT_ADAMW8BIT) k_opt_adamw8<<<nchunks, 256, 0, ctx().stream>>>(chunks, active, normsq, max_norm, grad_scale, h);
   else if (kind == VB_OPT_ADAMW) k_opt_multi<0><<<nchunks, 256, 0, ctx().stream>>>(chunks, active, normsq, max_norm, grad_scale, h);

@@ -7,7 +7,7 @@
 
 namespace vb {
 namespace {
-struct Rec { int family; cudaEvent_t a, b; double units; };
+struct Rec { int family; cudaEvent_t a, b; double units, dense; };
 bool g_on = false;
 std::vector<std::string>& g_names = *new std::vector<std::string>();
 std::vector<Rec>& g_recs = *new std::vector<Rec>();
@@ -22,9 +22,9 @@ int family_id(const char* f) {
 }
 }  // namespace
 
-ProfScope::ProfScope(const char* family, double units) {
+ProfScope::ProfScope(const char* family, double units, double dense_units) {
   if (!g_on || g_recs.size() > 200000) return;
-  Rec r; r.family = family_id(family); r.a = get_event(); r.b = get_event(); r.units = units;
+  Rec r; r.family = family_id(family); r.a = get_event(); r.b = get_event(); r.units = units; r.dense = dense_units > 0.0 ? dense_units : units;
   cudaEventRecord(r.a, ctx().stream);
   g_recs.push_back(r); idx = (int)g_recs.size() - 1;
 }
@@ -40,16 +40,16 @@ int vb_profile_reset(void) {
   g_recs.clear();
   return VB_OK;
 }
-int vb_profile_read(const char* family, double* total_ms, int64_t* launches, double* units) {
+int vb_profile_read(const char* family, double* total_ms, int64_t* launches, double* units, double* dense_units) {
   if (!ctx().ready) return set_error(VB_ERR_NOT_INIT, "vb_init has not been called");
   VB_CUDA(cudaStreamSynchronize(ctx().stream));
-  double ms = 0, u = 0; int64_t n = 0;
+  double ms = 0, u = 0, du = 0; int64_t n = 0;
   for (Rec& r : g_recs) {
     if (g_names[r.family] != family) continue;
     float t = 0; VB_CUDA(cudaEventElapsedTime(&t, r.a, r.b));
-    ms += t; u += r.units; ++n;
+    ms += t; u += r.units; du += r.dense; ++n;
   }
-  if (total_ms) *total_ms = ms; if (launches) *launches = n; if (units) *units = u;
+  if (total_ms) *total_ms = ms; if (launches) *launches = n; if (units) *units = u; if (dense_units) *dense_units = du;
   return VB_OK;
 }
 int vb_profile_families(char* buf, int buflen) {

@@ -238,6 +238,7 @@ int vb_check_errors(void) {
 }
 
 int vb_launch_count(int64_t* n) { *n = g_launcher_calls; return VB_OK; }
+int vb_tc_launch_count(int64_t* n) { *n = g_tc_launches; return VB_OK; }
 int vb_alloc(int64_t n, int zero_fill, vb_slot* out) { return slot_alloc(n, zero_fill != 0, out); }
 int vb_retain(vb_slot s) { return slot_retain(s); }
 int vb_release(vb_slot s, int* freed) { return slot_release(s, freed); }

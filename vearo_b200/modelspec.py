@@ -1,7 +1,7 @@
 """Seeded synthetic parameters and inputs for the five workloads, as NumPy arrays.
 
-Both the CPU oracle and the CUDA library are fed these same arrays, so parity never depends
-on two random generators agreeing.  Parameter order is the order of the reference's
+The CPU checker of the tests and the CUDA library are fed these same arrays, so parity never depends
+on two random generators agreeing; the benchmark draws its synthetic workloads from here too.  Parameter order is the order of the reference's
 `parameters()` methods (crates/vearo-nn/src/lib.rs:679-687, 797-806).
 """
 import numpy as np
