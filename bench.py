@@ -44,9 +44,10 @@ TRAFFIC_FROM_PROFILE = {"traffic": 82.7e6, "traffic_unit": "bytes per launch", "
                         "traffic_algorithmic": 135.3e6, "traffic_from_profile": "profiles/gemm_tc_fc1_and_dw.md"}
 
 # Dense TF32 rate of this pool's B200s, measured with `python bench.py --measure-tf32-peak` (torch.matmul, TF32 allowed, 8192^3;
-# best of 10 and a 4 s back-to-back loop, like the bf16 figures of MEASURED_PEAKS.json).  Until that has been run the figures
-# are the bf16 ones halved.
-TF32_PEAK = {"tflops_burst": 1649.5 / 2, "tflops_sustained": 1396.7 / 2, "source": "derived: measured bf16 / 2 (TF32 not measured yet)"}
+# best of 10 and a 4 s back-to-back loop, like the bf16 figures of MEASURED_PEAKS.json).  Under the 1000 W cap the sustained loop
+# ran at a median 1080 MHz SM clock (sw_power_cap the only reason active).
+TF32_PEAK = {"tflops_burst": 708.2, "tflops_sustained": 619.3, "sm_mhz_sustained": 1080.0,
+             "source": "measured: torch.matmul allow_tf32 8192^3, burst best of 10 / 4 s loop"}
 
 
 def flops_per_token(c):

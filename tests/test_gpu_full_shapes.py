@@ -142,7 +142,12 @@ def test_config4_convnet_real_channels(vb):
     vb.check_errors()
     assert_close(gl.numpy(), l.numpy(), "loss")
     for i, (cp, gp) in enumerate(zip(cm.parameters(), gm.parameters())):
-        close_and_l2(gp.grad().numpy(), cp.grad().contiguous().numpy(), "convnet grad %d %s" % (i, tuple(cp.shape)))
+        # (a conv bias ahead of a BatchNorm has a gradient that is zero in exact arithmetic: rounding noise on both sides, so
+        # only the element-wise bar applies to parameters 1, 5 and 9)
+        if i % 4 == 1 and i < 12:
+            assert_close(gp.grad().numpy(), cp.grad().contiguous().numpy(), "convnet grad %d" % i, guard=False)
+        else:
+            close_and_l2(gp.grad().numpy(), cp.grad().contiguous().numpy(), "convnet grad %d %s" % (i, tuple(cp.shape)))
     for s in range(3):
         np.testing.assert_allclose(gm.running(s, 0).numpy(), cm.stages[s]["rm"].numpy(), rtol=1e-4, atol=1e-6)
         np.testing.assert_allclose(gm.running(s, 1).numpy(), cm.stages[s]["rv"].numpy(), rtol=1e-4, atol=1e-6)

@@ -477,6 +477,12 @@ static bool attention_is_causal(const vb_tensor* mask, const vb_tensor* q, i64 S
   c.slot = mask->slot; c.serial = slot_serial(mask->slot); c.offset = mask->offset; c.S = S; c.rs = rs; c.causal = h == 1;
   return c.causal;
 }
+// VB200_ATTN_FUSED=0 keeps attention on the GEMM + row-kernel route (the route every additive mask other than the causal one takes)
+static bool attn_fused_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("VB200_ATTN_FUSED"); on = (e && e[0] == '0') ? 0 : 1; }
+  return on != 0;
+}
 static void qk_gemm_operand(const vb_tensor* t, i64* rs, i64* cs, i64* b1, i64* b2) {
   *b1 = t->strides[0]; *b2 = t->strides[1]; *rs = t->strides[2]; *cs = t->strides[3];
 }
@@ -507,6 +513,17 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
   float* pp; VB_TRY(slot_ptr(ptmp.slot, &pp));
   float scale = 1.0f / sqrtf((float)dk);
   const bool causal = attention_is_causal(mask, q, S, dk);
+  if (causal || !mask) {
+    // one kernel for scores, softmax and the product with V (attn_fused.cu); the probabilities leave the SM only when asked for
+    const AttnOperand oq{pq, q->strides[0], q->strides[1], q->strides[2], q->strides[3]};
+    const AttnOperand ok{pk, k->strides[0], k->strides[1], k->strides[2], k->strides[3]};
+    const AttnOperand ov{pv, v->strides[0], v->strides[1], v->strides[2], v->strides[3]};
+    if (attn_fused_enabled() && attn_fused_supported(oq, ok, ov, B, H, S, dk)) {
+      int rc = launch_attn_fwd_fused(oq, ok, ov, po, H * dk, S * H * dk, probs ? pp : nullptr, B, H, S, causal, scale);
+      if (rc == VB_OK && probs) *probs = ptmp; else slot_release(ptmp.slot, nullptr);
+      return rc;
+    }
+  }
   GemmArgs g = gemm_args();
   g.M = S; g.N = S; g.K = dk; g.alpha = scale; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
   g.A = pq; qk_gemm_operand(q, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);

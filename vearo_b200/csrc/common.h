@@ -164,6 +164,15 @@ int launch_attn_softmax(float* s, const float* mask, const i64 mask_strides[4], 
 int launch_mask_is_causal(const float* mask, i64 s, i64 row_stride, int* d_flag);   // d_flag <- 0 when some entry breaks the causal pattern
 int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 sk, float scale, bool causal, i64 sq);
 
+// attn_fused.cu: attention with the score matrix kept on the SM (head size 64, no mask or the causal mask, S >= 128).
+// An operand is a [B,H,S,64] view given by its element strides.
+struct AttnOperand { const float* p; i64 sb, sh, ss, sd; };
+bool attn_fused_supported(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, i64 B, i64 H, i64 S, i64 dk);
+// out: rows of 64 floats per head at out + b*o_sb + s*o_ss + h*64; probs: contiguous [B,H,S,S] (final probabilities, written
+// up to the end of each row's 128-wide diagonal tile under the causal mask) or null
+int launch_attn_fwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, float* out, i64 o_ss, i64 o_sb, float* probs,
+                          i64 B, i64 H, i64 S, bool causal, float scale);
+
 // optim.cu
 // (8-bit AdamW: m and v point at int8 values, ms and vs at the scales of the chunk's 256-element blocks)
 // (lo: where the TF32 remainders of the updated weights go when the weight keeps a lo plane for the tensor-core GEMM, else null)
