@@ -147,7 +147,12 @@ int vb_bn_relu_maxpool_backward(const vb_tensor* x, const vb_tensor* gamma, cons
  * buffers, which makes the layer's following transpose(1,2).reshape a view instead of a copy.
  * When the mask is a [S,S] causal mask (0 on/below the diagonal, <= -1e9 above; S a multiple of 128, <= 1024) the
  * triangular structure is exploited; `probs` is then only defined up to the end of each row's 128-wide diagonal tile
- * and must be handed to the backward call together with the same mask. */
+ * and must be handed to the backward call together with the same mask.
+ * With no mask or the causal mask, head size 64, S >= 128 and 16-byte-aligned operands, the forward is ONE kernel
+ * (scores, softmax and the product with V on the SM: the S x S matrix reaches memory only when `probs` is asked
+ * for) and the backward fuses dP, the softmax backward and dQ.  The slot `probs` then names is larger than its
+ * [B,H,S,S] descriptor says: a [B,H,S,dk] copy of the output follows the probabilities, which the backward kernel
+ * reads; treat the tensor as an opaque token between the two calls.  VB200_ATTN_FUSED=0 switches this route off. */
 int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,
                        vb_tensor* out, vb_tensor* probs);
 int vb_fused_attention_backward(const vb_tensor* q, const vb_tensor* k, const vb_tensor* v, const vb_tensor* mask_or_null,

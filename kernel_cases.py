@@ -7,6 +7,7 @@
   python kernel_cases.py gemm_qk       scores of 96 heads: [1024,64] . [1024,64]^T
   python kernel_cases.py gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
   python kernel_cases.py attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
+  python kernel_cases.py attention_fwd  the same forward alone, nothing kept for a backward pass (no probabilities written)
   python kernel_cases.py colsum        bias gradients: column sums of [8192,768] and [8192,3072]
   python kernel_cases.py layernorm_bwd rows 8192, C 768
   python kernel_cases.py ce_bwd        rows 2048, V 50304
@@ -58,6 +59,10 @@ def build(case):
             vb.zero_gradients(); vb.reset_active_tape()
             qkv.fused_attention_packed(12, mask).mul(go).sum(2, False).sum(1, False).sum(0, False).backward()
         return run
+    if case == "attention_fwd":
+        qkv = T(f(8, 1024, 2304))
+        mask = T(np.triu(np.full((1024, 1024), -1e9, np.float32), 1))
+        return lambda: qkv.fused_attention_packed(12, mask)
     if case == "colsum":
         a, b = T(f(8192, 768)), T(f(8192, 3072))
         ba, bb = T(f(768), True), T(f(3072), True)

@@ -507,23 +507,32 @@ int vb_fused_attention(const vb_tensor* q, const vb_tensor* k, const vb_tensor* 
   VB_TRY(new_output_bshd(out, B, H, S, dk));
   if (numel(*q) == 0) { if (probs) { i64 pd[4] = {B, H, S, S}; VB_TRY(new_output(probs, 4, pd)); } return VB_OK; }
   float* po; VB_TRY(slot_ptr(out->slot, &po));
-  // scores / probabilities
-  vb_tensor ptmp; i64 pd[4] = {B, H, S, S};
-  VB_TRY(new_output(&ptmp, 4, pd));
-  float* pp; VB_TRY(slot_ptr(ptmp.slot, &pp));
+  i64 pd[4] = {B, H, S, S};
   float scale = 1.0f / sqrtf((float)dk);
   const bool causal = attention_is_causal(mask, q, S, dk);
   if (causal || !mask) {
-    // one kernel for scores, softmax and the product with V (attn_fused.cu); the probabilities leave the SM only when asked for
+    // one kernel for scores, softmax and the product with V (attn_fused.cu); the probabilities leave the SM only when asked for,
+    // and then the slot that takes them also takes a copy of the output behind them: the backward kernel wants both
     const AttnOperand oq{pq, q->strides[0], q->strides[1], q->strides[2], q->strides[3]};
     const AttnOperand ok{pk, k->strides[0], k->strides[1], k->strides[2], k->strides[3]};
     const AttnOperand ov{pv, v->strides[0], v->strides[1], v->strides[2], v->strides[3]};
     if (attn_fused_enabled() && attn_fused_supported(oq, ok, ov, B, H, S, dk)) {
-      int rc = launch_attn_fwd_fused(oq, ok, ov, po, H * dk, S * H * dk, probs ? pp : nullptr, B, H, S, causal, scale);
-      if (rc == VB_OK && probs) *probs = ptmp; else slot_release(ptmp.slot, nullptr);
+      vb_tensor saved; saved.slot = 0;
+      float* ps = nullptr;
+      if (probs) {
+        vb_slot sl; VB_TRY(slot_alloc(B * H * S * (S + dk), false, &sl));
+        set_contiguous(saved, 4, pd); saved.slot = sl;
+        VB_TRY(slot_ptr(sl, &ps));
+      }
+      int rc = launch_attn_fwd_fused(oq, ok, ov, po, H * dk, S * H * dk, ps, B, H, S, causal, scale);
+      if (rc == VB_OK && probs) *probs = saved; else if (saved.slot) slot_release(saved.slot, nullptr);
       return rc;
     }
   }
+  // scores / probabilities
+  vb_tensor ptmp;
+  VB_TRY(new_output(&ptmp, 4, pd));
+  float* pp; VB_TRY(slot_ptr(ptmp.slot, &pp));
   GemmArgs g = gemm_args();
   g.M = S; g.N = S; g.K = dk; g.alpha = scale; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
   g.A = pq; qk_gemm_operand(q, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);
@@ -576,6 +585,21 @@ static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const
   void* dpv = nullptr;
   int rc = scratch_alloc((size_t)(B * H * SS) * sizeof(float), &dpv);
   float* pdp = (float*)dpv;
+  // The probabilities of the fused forward kernel come with the output behind them: then dP, the softmax backward and dQ are one
+  // kernel, which also leaves dS (scaled) in `pdp` for the dK product below.
+  bool fused_dq = false;
+  if (rc == VB_OK && probs && (causal || !mask) && attn_fused_enabled() && (ld & 3) == 0 && ((uintptr_t)pdq & 15) == 0) {
+    const AttnOperand oq{pq, q->strides[0], q->strides[1], q->strides[2], q->strides[3]};
+    const AttnOperand ok{pk, k->strides[0], k->strides[1], k->strides[2], k->strides[3]};
+    const AttnOperand ov{pv, v->strides[0], v->strides[1], v->strides[2], v->strides[3]};
+    const AttnOperand og{pg, gout->strides[0], gout->strides[1], gout->strides[2], gout->strides[3]};
+    float* base; i64 cap = 0;
+    if (attn_fused_supported(oq, ok, ov, B, H, S, dk) && attn_fused_operand_ok(og, B, H) && probs->offset == 0 &&
+        slot_ptr(probs->slot, &base, &cap) == VB_OK && cap >= B * H * S * (S + dk)) {
+      rc = launch_attn_bwd_dq_fused(ok, ov, og, pp, pdp, pdq, ld, S * ld, B, H, S, causal, scale);
+      fused_dq = true;
+    }
+  }
   if (rc == VB_OK) {   // dV = P^T . dO
     GemmArgs g = gemm_args();
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 3 : 0;
@@ -584,7 +608,7 @@ static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const
     g.C = pdv; g.c_rs = ld; g.c_cs = 1; g.c_b1 = S * ld; g.c_b2 = dk;
     rc = launch_gemm(g);
   }
-  if (rc == VB_OK) {   // dP = dO . V^T
+  if (rc == VB_OK && !fused_dq) {   // dP = dO . V^T
     GemmArgs g = gemm_args();
     g.M = S; g.N = S; g.K = dk; g.nb1 = B; g.nb2 = H; g.causal = causal ? 1 : 0;
     g.A = pg; qk_gemm_operand(gout, &g.a_rs, &g.a_cs, &g.a_b1, &g.a_b2);
@@ -592,8 +616,8 @@ static int attention_backward_core(const vb_tensor* q, const vb_tensor* k, const
     g.C = pdp; g.c_rs = S; g.c_cs = 1; g.c_b1 = H * SS; g.c_b2 = SS;
     rc = launch_gemm(g);
   }
-  if (rc == VB_OK) rc = launch_attn_softmax_backward(pp, pdp, B * H * S, S, scale, causal, S);   // dS * scale, in place
-  if (rc == VB_OK) {   // dQ = dS . K
+  if (rc == VB_OK && !fused_dq) rc = launch_attn_softmax_backward(pp, pdp, B * H * S, S, scale, causal, S);   // dS * scale, in place
+  if (rc == VB_OK && !fused_dq) {   // dQ = dS . K
     GemmArgs g = gemm_args();
     g.M = S; g.N = dk; g.K = S; g.nb1 = B; g.nb2 = H; g.causal = causal ? 2 : 0;
     g.A = pdp; g.a_rs = S; g.a_cs = 1; g.a_b1 = H * SS; g.a_b2 = SS;

@@ -168,8 +168,12 @@ int launch_attn_softmax_backward(const float* p, float* dp_inout, i64 rows, i64 
 // An operand is a [B,H,S,64] view given by its element strides.
 struct AttnOperand { const float* p; i64 sb, sh, ss, sd; };
 bool attn_fused_supported(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, i64 B, i64 H, i64 S, i64 dk);
-// out: rows of 64 floats per head at out + b*o_sb + s*o_ss + h*64; probs: contiguous [B,H,S,S] (final probabilities, written
-// up to the end of each row's 128-wide diagonal tile under the causal mask) or null
+bool attn_fused_operand_ok(const AttnOperand& o, i64 B, i64 H);
+// out: rows of 64 floats per head at out + b*o_sb + s*o_ss + h*64; probs: null, or room for B*H*S*(S + 64) floats: the [B,H,S,S]
+// probabilities (written up to the end of each row's 128-wide diagonal tile under the causal mask) followed by a [B,H,S,64] copy
+// of the output, which is what launch_attn_bwd_dq_fused wants as `saved`
+int launch_attn_bwd_dq_fused(const AttnOperand& k, const AttnOperand& v, const AttnOperand& gout, const float* saved, float* ds,
+                             float* dq, i64 dq_ss, i64 dq_sb, i64 B, i64 H, i64 S, bool causal, float scale);
 int launch_attn_fwd_fused(const AttnOperand& q, const AttnOperand& k, const AttnOperand& v, float* out, i64 o_ss, i64 o_sb, float* probs,
                           i64 B, i64 H, i64 S, bool causal, float scale);
 

@@ -24,6 +24,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 // Bounded wait; false when the limit ran out (or another role already aborted).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   uint32_t addr = smem_u32(bar);
+  {   // the phase is often complete already: ask without the (potentially suspending) wait first
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     uint32_t done;
     asm volatile(
