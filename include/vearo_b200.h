@@ -210,6 +210,11 @@ int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_ten
                        vb_tensor* gx, vb_tensor* gw, vb_tensor* gb);
 /* The same with the weight and bias gradients written into existing tensors (NULL: not wanted) -- a parameter's slice of a flat
  * gradient buffer -- so that no copy follows the GEMM.  No reference counterpart (the reference allocates every gradient). */
+/* vb_linear followed by GELU (TransformerBlock::forward's fc1 -> gelu, crates/vearo-nn/src/lib.rs:666-675) with both results
+ * returned: `pre` = x.W^T + b, which the GELU backward arm needs, and `act` = gelu(pre).  Where the tensor-core kernel takes the
+ * product as whole tiles the activation is formed in its epilogue from the values being stored; the results equal
+ * vb_linear + vb_gelu bit for bit either way. */
+int vb_linear_gelu(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias_or_null, vb_tensor* pre, vb_tensor* act);
 int vb_linear_backward_into(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* grad_out, vb_tensor* gx_or_null,
                             const vb_tensor* gw_into_or_null, const vb_tensor* gb_into_or_null);
 

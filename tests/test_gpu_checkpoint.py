@@ -79,3 +79,42 @@ def test_resume_reproduces_the_uninterrupted_run(vb, tmp_path):
     assert straight == resumed
     for a, b in zip(m.parameters(), m2.parameters()):
         assert np.array_equal(a.numpy(), b.numpy())
+
+
+def test_optimizer_state_file_carries_the_exact_step_and_the_rng_counter(vb, tmp_path):
+    """The state file restores the per-call randomness counter (vearo-core/src/tensor.rs:1240-1285) and a step counter beyond
+    2^24 exactly, so that a resumed run draws the dropout masks and applies the bias corrections of the uninterrupted one."""
+    import ctypes as C
+    m, _, _ = tiny_gpt(vb)
+    opt = vb.AdamW(m.parameters(), 1e-3, 0.9, 0.999, 1e-8, 0.1)
+    L = vb.lib()
+    L.vh_opt_handle.restype = C.c_int
+    big = (1 << 24) + 12345                                  # not representable as one f32
+    vb.vb_check(L.vb_opt_set_step(L.vh_opt_handle(opt.o), C.c_uint32(big)))
+    vb.set_rng_counter((1 << 40) + 77)
+    opt.save_state(tmp_path / "o.ve")
+    vb.set_rng_counter(5)
+    opt2 = vb.AdamW(m.parameters(), 1e-3, 0.9, 0.999, 1e-8, 0.1)
+    opt2.load_state(tmp_path / "o.ve")
+    assert vb.rng_counter() == (1 << 40) + 77
+    st, n, step = C.c_uint32(0), C.c_int64(0), C.c_uint32(0)
+    vb.vb_check(L.vb_opt_state(L.vh_opt_handle(opt2.o), C.byref(st), C.byref(n), C.byref(step)))
+    assert step.value == big
+    vb.set_rng_counter(0)
+
+
+def test_damaged_files_are_refused_before_anything_is_allocated(vb, tmp_path):
+    """A foreign or truncated file must not be trusted for its length fields (a count or rank of billions)."""
+    import struct
+    m, params, _ = tiny_gpt(vb)
+    path = tmp_path / "bad.ve"
+    path.write_bytes(struct.pack("<I", len(params)) + struct.pack("<I", 0xfffffff0))      # absurd rank
+    with pytest.raises(vb.VearoError, match="damaged|shape does not match"):
+        m.load_checkpoint(path)
+    opt = vb.AdamW(m.parameters(), 1e-3)
+    path.write_bytes(struct.pack("<I", 0xffffffff))                                         # absurd tensor count
+    with pytest.raises(vb.VearoError, match="damaged"):
+        opt.load_state(path)
+    path.write_bytes(struct.pack("<III", 1, 1, 1000) + struct.pack("<I", 1000))             # says 1000 floats, holds none
+    with pytest.raises(vb.VearoError):
+        opt.load_state(path)

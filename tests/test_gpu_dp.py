@@ -25,10 +25,10 @@ def _gpu_count():
         return 0
 
 
-def _run(world, out_dir, steps=4):
+def _run(world, out_dir, steps=4, mode="train"):
     os.makedirs(out_dir, exist_ok=True)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "dp_worker.py"), str(r), str(world), out_dir, str(steps)], env=env)
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "dp_worker.py"), str(r), str(world), out_dir, str(steps), mode], env=env)
              for r in range(world)]
     for p in procs:
         assert p.wait(timeout=300) == 0
@@ -52,3 +52,18 @@ def test_two_ranks_match_single_process(tmp_path):
             # of a row equally), so what AdamW normalises there is rounding noise and the two runs need not agree
             continue
         np.testing.assert_allclose(two[0][k], one[k], rtol=2e-3, atol=2e-5, err_msg=k)
+
+
+def test_gradient_on_one_rank_only_and_repeated_backward(tmp_path):
+    """A parameter that gets gradient on rank 0 only must still be updated identically on both ranks (the update uses the reduced
+    sum, not the local "got a gradient" mask), and a second backward() before the step is refused under data parallel instead of
+    silently overwriting gradients that were already reduced."""
+    if _gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    two = _run(2, str(tmp_path / "w2"), steps=3, mode="partial")
+    keys = [k for k in two[0].files if k.startswith("p")]
+    for k in keys:
+        assert (two[0][k].view(np.uint32) == two[1][k].view(np.uint32)).all(), k
+    lone = two[0][keys[-1]] if keys[-1] == "p%d" % (len(keys) - 1) else two[0]["p%d" % (len(keys) - 1)]
+    assert not np.allclose(lone, np.linspace(-1, 1, 40).astype(np.float32))      # it did move
+    assert two[0]["refused"][0] == 1 and two[1]["refused"][0] == 1

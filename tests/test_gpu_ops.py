@@ -744,6 +744,31 @@ def test_activation_lo_plane_follows_in_place_writers(vb):
     vb.check_errors()
 
 
+@pytest.mark.parametrize("rows,inf,outf", [(1024, 768, 3072), (512, 384, 640), (260, 96, 200), (6, 5, 7)])
+def test_linear_gelu_epilogue_equals_the_two_ops(vb, rows, inf, outf):
+    """fc1 -> gelu with the activation formed in the GEMM's epilogue: same values as linear followed by gelu, bit for bit, and the
+    same gradients (the tape holds the same two nodes); against the oracle at the usual bar."""
+    x0, w0, b0, go = rnd(71, rows, inf, scale=0.3), rnd(72, outf, inf, scale=0.08), rnd(73, outf, scale=0.3), rnd(74, rows, outf, scale=0.01)
+
+    def run(T, fused):
+        x, w, b = T.from_numpy(x0, True), T.from_numpy(w0, True), T.from_numpy(b0, True)
+        a = x.linear_gelu(w, b) if fused else x.matmul(w.transpose(0, 1)).add(b).gelu()
+        n = go.size
+        a.mul(T.from_numpy(go)).reshape([1, n]).matmul(T.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        return [t.numpy() for t in (a, x.grad(), w.grad().contiguous(), b.grad())]
+    orc.reset_all()
+    cpu = run(orc.Tensor, False)
+    vb.zero_gradients(); vb.reset_active_tape()
+    got = run(vb.Tensor, True)
+    vb.check_errors()
+    for g, c, n in zip(got, cpu, "act gx gw gb".split()):
+        assert_close(g, c, "linear_gelu %s" % n)
+    # the two-op form on the device (vb_linear, then vb_gelu): identical bits
+    vb.zero_gradients(); vb.reset_active_tape()
+    x, w, b = vb.Tensor.from_numpy(x0), vb.Tensor.from_numpy(w0), vb.Tensor.from_numpy(b0)
+    assert np.array_equal(x.linear(w, b).gelu().numpy(), x.linear_gelu(w, b).numpy())
+
+
 def test_linear_tensor_core_with_bias_and_backward(vb):
     x0, w0, b0, go = rnd(65, 512, 384, scale=0.5), rnd(66, 640, 384, scale=0.05), rnd(67, 640), rnd(68, 512, 640, scale=0.1)
 

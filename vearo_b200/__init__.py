@@ -15,7 +15,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libvearo_b200.so")
+# VB200_LIB selects another build of the library (the bounds-check build, libvearo_b200_bc.so)
+LIB_PATH = os.environ.get("VB200_LIB") or os.path.join(_HERE, "libvearo_b200.so")
 
 c_f32p = C.POINTER(C.c_float)
 c_i64p = C.POINTER(C.c_int64)
@@ -226,6 +227,10 @@ class Tensor:
         return Tensor(lib().vh_fused_attention_packed(self.h, int(n_head), -1 if mask is None else mask.h))
 
     def linear(self, w, b=None): return Tensor(lib().vh_linear(self.h, w.h, -1 if b is None else b.h))
+
+    def linear_gelu(self, w, b=None):
+        """self.linear(w, b).gelu() in one device call (the activation comes out of the GEMM's epilogue)."""
+        return Tensor(lib().vh_linear_gelu(self.h, w.h, -1 if b is None else b.h))
 
     def reshape(self, shape):
         sh, r = _shape_arg(shape)

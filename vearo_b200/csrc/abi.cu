@@ -856,7 +856,17 @@ void lo_plane_mark_current(vb_slot weight_slot) {
 }  // namespace vb
 }  // extern "C++"
 
+static int linear_forward_impl(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias, vb_tensor* out, vb_tensor* act);
 int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias, vb_tensor* out) {
+  return linear_forward_impl(x, weight, bias, out, nullptr);
+}
+int vb_linear_gelu(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias, vb_tensor* pre, vb_tensor* act) {
+  VB_CHECK(pre && act, "linear_gelu needs both outputs");
+  return linear_forward_impl(x, weight, bias, pre, act);
+}
+// act (optional): GELU(out), formed in the GEMM's epilogue from the values it is storing anyway where the tensor-core kernel
+// takes the product as whole tiles, else by the activation kernel
+static int linear_forward_impl(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias, vb_tensor* out, vb_tensor* act) {
   VB_CHECK(weight->rank == 2 && x->rank >= 1, "linear expects weight [out, in]");
   VB_CHECK(x->dims[x->rank - 1] == weight->dims[1], "Incompatible dimensions for matmul");
   Temp hx, hb; const float* px; VB_TRY(contiguous_ptr(x, &px, hx));
@@ -867,8 +877,10 @@ int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias
   for (int i = 0; i < x->rank - 1; ++i) od[i] = x->dims[i];
   od[x->rank - 1] = weight->dims[0];
   VB_TRY(new_output(out, x->rank, od));
+  if (act) VB_TRY(new_output(act, x->rank, od));
   if (numel(*out) == 0) return VB_OK;
   float* po; VB_TRY(slot_ptr(out->slot, &po));
+  float* pa = nullptr; if (act) VB_TRY(slot_ptr(act->slot, &pa));
   i64 rows, in; VB_TRY(rows_of(x, &rows, &in));
   GemmArgs g = gemm_args();
   g.M = rows; g.N = weight->dims[0]; g.K = in;
@@ -877,7 +889,11 @@ int vb_linear(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias
   g.C = po; g.c_rs = g.N; g.c_cs = 1; g.bias = pb;
   if (rows >= 1024) g.B_lo = weight_lo_plane(weight, pw);
   if (g.B_lo && !hx.p) g.A_lo = existing_lo_plane(x, px);        // a normalised input brings its own remainders
-  return launch_gemm(g);
+  int fused = 0;
+  g.act_out = pa; g.act_fused = &fused;
+  VB_TRY(launch_gemm(g));
+  if (act && !fused) VB_TRY(launch_unary(1, po, pa, numel(*out)));
+  return VB_OK;
 }
 // gw_into / gb_into: existing contiguous tensors the weight and bias gradients are written into (a parameter's slice of
 // the flat gradient arena) instead of fresh outputs.

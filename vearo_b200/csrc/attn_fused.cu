@@ -546,7 +546,7 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int u = e * 32 + lane, r = u >> 3, c4 = u & 7;
-          const bool valid = row0 + r < p.S && col0 + 4 * c4 < p.S;
+          const bool valid = row0 + r < p.S && col0 + 4 * c4 < p.S && VB_BC(r * 128 + ((c4 ^ (r & 7)) << 4), 4096);
           const float* src = valid ? p.P + ((i64)bh * p.S + row0 + r) * p.S + col0 + 4 * c4 : p.P;
           cp_async16(dst + r * 128 + ((c4 ^ (r & 7)) << 4), src, valid);
         }

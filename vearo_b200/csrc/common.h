@@ -12,7 +12,7 @@ namespace vb {
 using i64 = int64_t;
 
 // Bits of the device error word (reported as VB_ERR_BAD_INDEX by vb_check_errors).
-enum : int { ERRBIT_NEG_ID = 1, ERRBIT_OOB_ID = 2, ERRBIT_WAIT_TIMEOUT = 4 };
+enum : int { ERRBIT_NEG_ID = 1, ERRBIT_OOB_ID = 2, ERRBIT_WAIT_TIMEOUT = 4, ERRBIT_BOUNDS = 8 };
 
 struct Ctx {
   bool ready = false;
@@ -133,6 +133,11 @@ int launch_avgpool2d_backward(const float* g, float* gx, i64 nc, i64 h, i64 w, i
 
 // gemm.cu: C[b] = alpha * A[b] . B[b] (+ beta * C[b]) (+ bias[n]); A logical [M,K], B logical [K,N],
 // every operand addressed through element strides, two batch levels (b = b1 * nb2 + b2).
+// A zero-padded NHWC image batch xp [n, h + 2, w + 2, c] standing in for its unfolded ("im2col") matrix as the B operand of a
+// product (3 x 3 window, stride 1, padding 1): cols[(n, y, x), (i, j, ch)] = xp[n, y + i, x + j, ch].
+//   mode 1: B = cols[image]^T, i.e. the product is batched over the n images (nb2 = n), N = h * w pixels, K = 9 * c
+//   mode 2: B = cols, N = 9 * c taps, K = n * h * w pixels
+struct ConvOperand { const float* xp; i64 n, h, w, c; int mode; };
 struct GemmArgs {
   const float* A; const float* B; float* C; const float* bias;   // bias: length N or null
   const float* bias_m;                                            // per-row bias: length M or null (output channels of a convolution)
@@ -153,6 +158,14 @@ struct GemmArgs {
   // k-block of every tile), laid out exactly like B.  Worth it for an operand used by many tiles and several products (weights).
   const float* B_lo;
   const float* A_lo;      // the same for A (an activation whose producer wrote its remainders)
+  // Optional second output: GELU(C) in C's layout, written by the tensor-core kernel's epilogue when it can (*act_fused = 1);
+  // otherwise left untouched, and the caller applies the activation itself.
+  float* act_out;
+  int* act_fused;
+  // Optional: B given as an implicit im2col view (then B and its strides are ignored).  Only the tensor-core kernel can read it:
+  // *conv_used is set to 1 when it did; otherwise nothing was launched and the caller falls back to an unfolded matrix.
+  const ConvOperand* conv;
+  int* conv_used;
 };
 int launch_gemm(const GemmArgs& g);
 int launch_tf32_lo(const float* x, float* lo, i64 n);      // gemm_tc.cu: lo[i] as above
@@ -188,7 +201,45 @@ void lo_plane_mark_current(vb_slot weight_slot);
 bool lo_plane_is_current(vb_slot weight_slot);
 void lo_planes_forget_all();                 // the slot table is being torn down
 void lo_plane_on_release(vb_slot slot);      // the slot is gone: so is a lo plane kept for it
+// ---- bounds-check build (-DVB200_BOUNDS_CHECK; `python vearo_b200/build.py --bounds-check`) ------------------------------------
+// The stand-in for a memory checker on pools where none may run: kernels that compute gather / scatter indices wrap the index in
+// VB_BC(index, extent).  In the checked build an index outside [0, extent) sets ERRBIT_BOUNDS in the device error word (reported by
+// vb_check_errors as VB_ERR_BAD_INDEX, "a computed index left its tensor") and the access is skipped -- never a trap, never a
+// fault; in the normal build the macro is the constant `true` and costs nothing.  Each translation unit keeps its own pointer to
+// the error word (no relocatable device code is used); vb_init hands it to every unit through the registrars below.
+#ifdef VB200_BOUNDS_CHECK
+void bc_register(void (*setter)(int*));          // runtime.cu: remembers a unit's setter; vb_init calls them all
+std::vector<void (*)(int*)>& bc_setters();
 #ifdef __CUDACC__
+static __device__ int* bc_err_word;
+static void bc_set_err_word(int* p) { cudaMemcpyToSymbol(bc_err_word, &p, sizeof p); }
+namespace { struct BcRegistrar { BcRegistrar() { bc_register(bc_set_err_word); } } bc_registrar_instance; }
+__device__ __forceinline__ bool bc_check(long long idx, long long extent) {
+  if (idx >= 0 && idx < extent) return true;
+  if (bc_err_word) atomicOr(bc_err_word, ERRBIT_BOUNDS);
+  return false;
+}
+#define VB_BC(idx, extent) (::vb::bc_check((long long)(idx), (long long)(extent)))
+#endif
+#else
+#define VB_BC(idx, extent) (true)
+#endif
+
+#ifdef __CUDACC__
+// tanh(y) = 1 - 2 / (1 + e^(2y)) with the exponential on the special-function unit (2^x, relative error about 2^-22) and an
+// approximate division: absolute error of a few 1e-7 over the whole range (exact limits +-1 for large |y|), i.e. the same few
+// units in the last place as libm's tanhf for the uses below, at a quarter of its instructions.
+__device__ __forceinline__ float tanh_fast(float y) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y * 2.8853900817779268f));      // e^(2y) = 2^(2y log2 e)
+  return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+// GELU, tanh form, with the reference's constants (crates/vearo-backend-cpu/src/lib.rs:458-497)
+__device__ __forceinline__ float gelu_value(float v) {
+  const float v3 = v * v * v;
+  const float inner = 0.79788456f * (v + 0.044715f * v3);
+  return 0.5f * v * (1.0f + tanh_fast(inner));
+}
 // lo part of x when the tensor core takes the raw x as hi (it reads x cut to 10 mantissa bits): the remainder is exact in f32 and
 // is rounded to TF32 (nearest, ties away) with integer arithmetic on the bit pattern
 __device__ __forceinline__ float tf32_remainder(float x) {

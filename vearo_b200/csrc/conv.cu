@@ -6,7 +6,15 @@
 // (strict >) and never selects a padded tap; average-pool divides by the number of valid taps.
 // All kernels are gather formulations: no atomics, bit-reproducible.
 //
-// Convolutions with enough work run on the tensor cores instead: the padded input windows are unfolded into a
+// 3 x 3, stride-1, padding-1 convolutions over a multiple of 32 channels are IMPLICIT GEMMs on the tensor cores: the input
+// (or, for the input gradient, the output gradient) is copied once into a zero-padded channels-last buffer [N, H+2, W+2, C],
+// and the unfolded matrix cols[(n,y,x), (i,j,c)] = xp[n, y+i, x+j, c] is never written: because a tap row's (j, c) entries
+// are contiguous in that buffer, the whole matrix is one 5-D tensor map over it, and the GEMM's TMA boxes are its tiles.
+//   forward         out[n] [Cout, HW]   = Wr [Cout, 9 Cin] . cols[n]^T           (Wr = weights in (i, j, c) order)
+//   input gradient  dX[n]  [Cin, HW]    = Wf [Cin, 9 Cout] . cols_g[n]^T         (cols_g over the padded gradient, Wf = flipped, transposed weights)
+//   weight gradient dWr    [Cout, 9 Cin] = g^T [Cout, N HW] . cols                (K = all pixels of all images)
+// NCHW stays at the interface: results land in NCHW straight from the GEMM epilogue (dW through a reorder of 9 Cin columns).
+// Other convolutions with enough work unfold explicitly: the padded input windows are written into a
 // [N*OH*OW, Cin*KH*KW] matrix (rows padded to a multiple of 4 floats) and the three products become GEMMs of the
 // FP32-accurate tcgen05 kernel -- forward  out[n] = W . cols[n]^T + b  (batched over images, written straight in
 // NCHW with a per-row bias), input gradient  dcols[n] = g[n]^T . W  folded back by a gather, weight gradient
@@ -54,7 +62,7 @@ __global__ void k_im2col(const float* __restrict__ x, float* __restrict__ cols, 
       float e = 0.0f;
       if (k < kc) {
         int ih = y * stride + i - pad, iw = xo * stride + j - pad;
-        if (ih >= 0 && ih < h && iw >= 0 && iw < wd) e = x[(((i64)nn * cin + c) * h + ih) * wd + iw];
+        if (ih >= 0 && ih < h && iw >= 0 && iw < wd && VB_BC((((i64)nn * cin + c) * h + ih) * wd + iw, (i64)n * cin * h * wd)) e = x[(((i64)nn * cin + c) * h + ih) * wd + iw];
       }
       v[t] = e;
       ++k; if (++j == kw) { j = 0; if (++i == kh) { i = 0; ++c; } }
@@ -79,7 +87,7 @@ __global__ void k_col2im(const float* __restrict__ dcols, float* __restrict__ gx
         int tx = iw + pad - j;
         if (tx < 0 || tx % stride) continue;
         int xo = tx / stride; if (xo >= ow) continue;
-        acc += dcols[(((i64)nn * oh + y) * ow + xo) * kp + (c * kh + i) * kw + j];
+        if (VB_BC((((i64)nn * oh + y) * ow + xo) * kp + (c * kh + i) * kw + j, (i64)n * oh * ow * kp)) acc += dcols[(((i64)nn * oh + y) * ow + xo) * kp + (c * kh + i) * kw + j];
       }
     }
     gx[idx] = acc;
@@ -117,6 +125,63 @@ static bool conv_as_gemm(i64 n, i64 cin, i64 cout, i64 kh, i64 kw, i64 oh, i64 o
   double macs = (double)n * (double)oh * (double)ow * (double)cin * (double)kh * (double)kw * (double)cout;
   return macs >= 2.0e6 && n <= 60000 && (i64)oh * ow < 0x7fffffffLL && cin * kh * kw < (1 << 24);
 }
+// x [n, c, h, w] -> xp [n, h + 2, w + 2, c], border zero.  One CTA per padded row: the [c, w] slab of an image row goes
+// through shared memory so that both the reads (along x) and the writes (along c) are contiguous.
+__global__ void __launch_bounds__(256) k_nchw_to_padded_nhwc(const float* __restrict__ x, float* __restrict__ xp, int c, int h, int w) {
+  extern __shared__ float tile[];                  // [w][c + 1]
+  const int yp = blockIdx.x, n = blockIdx.y;
+  float* row = xp + ((i64)n * (h + 2) + yp) * (i64)(w + 2) * c;
+  const int total = (w + 2) * c;
+  if (yp == 0 || yp == h + 1) { for (int i = threadIdx.x; i < total; i += blockDim.x) row[i] = 0.0f; return; }
+  const float* src = x + (i64)n * c * h * w + (i64)(yp - 1) * w;
+  for (int i = threadIdx.x; i < c * w; i += blockDim.x) { const int cc = i / w, xx = i - cc * w; tile[xx * (c + 1) + cc] = src[(i64)cc * h * w + xx]; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int xx = i / c, cc = i - xx * c;
+    if (VB_BC((xx == 0 || xx == w + 1) ? 0 : (xx - 1) * (c + 1) + cc, w * (c + 1))) row[i] = (xx == 0 || xx == w + 1) ? 0.0f : tile[(xx - 1) * (c + 1) + cc];
+  }
+}
+// Weights [cout, cin, 3, 3] -> wr [cout, (i, j, c)] (forward / weight-gradient order) and back; -> wf [cin, (i, j, co)] with the
+// window flipped (the input gradient is the correlation of the padded output gradient with the flipped weights).
+__global__ void k_weights_to_taps(const float* __restrict__ w, float* __restrict__ wr, int cout, int cin, int flip_transpose) {
+  const int total = cout * cin * 9;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int j = idx % 3, i = (idx / 3) % 3, c = (idx / 9) % cin, co = idx / (9 * cin);
+    const i64 dst = !flip_transpose ? (i64)co * 9 * cin + (i * 3 + j) * cin + c : (i64)c * 9 * cout + ((2 - i) * 3 + (2 - j)) * cout + co;
+    if (VB_BC(dst, total)) wr[dst] = w[idx];
+  }
+}
+__global__ void k_taps_to_weights(const float* __restrict__ wr, float* __restrict__ w, int cout, int cin) {
+  const int total = cout * cin * 9;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int j = idx % 3, i = (idx / 3) % 3, c = (idx / 9) % cin, co = idx / (9 * cin);
+    w[idx] = wr[(i64)co * 9 * cin + (i * 3 + j) * cin + c];
+  }
+}
+static bool conv_implicit_ok(i64 n, i64 c, i64 h, i64 wd, i64 kh, i64 kw, i64 stride, i64 pad) {
+  static int off = -1;
+  if (off < 0) { const char* e = getenv("VB200_CONV_IMPLICIT"); off = (e && e[0] == '0') ? 1 : 0; }
+  return !off && kh == 3 && kw == 3 && stride == 1 && pad == 1 && c % 32 == 0 && c <= 1024 && wd <= 128 && (wd & (wd - 1)) == 0 && wd >= 4 &&
+         (h * wd) % 32 == 0 && n >= 1 && n <= 60000 && (size_t)wd * (c + 1) * sizeof(float) <= 48 * 1024;
+}
+static int to_padded_nhwc(const float* x, float* xp, i64 n, i64 c, i64 h, i64 wd) {
+  ProfScope prof("conv_nhwc", ((double)n * c * h * wd + (double)n * (h + 2) * (wd + 2) * c) * 4.0);
+  k_nchw_to_padded_nhwc<<<dim3((unsigned)(h + 2), (unsigned)n), 256, (size_t)wd * (c + 1) * sizeof(float), ctx().stream>>>(x, xp, (int)c, (int)h, (int)wd);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+// out[n] [m, hw] = taps [m, 9 c] . cols(xp)[n]^T (+ bias per row m): the forward product, and the input gradient with the roles
+// of the channel counts swapped.  *used = 0 when the tensor-core kernel declined (nothing was written).
+static int implicit_product(const float* taps, const float* xp, const float* bias_m, float* out, i64 n, i64 m, i64 c, i64 h, i64 wd, int* used) {
+  ConvOperand cv{xp, n, h, wd, c, 1};
+  GemmArgs g = gemm_args();
+  g.A = taps; g.M = m; g.K = 9 * c; g.a_rs = 9 * c; g.a_cs = 1;
+  g.N = h * wd; g.C = out; g.c_rs = h * wd; g.c_cs = 1;
+  g.nb1 = 1; g.nb2 = n; g.a_b2 = 0; g.c_b2 = m * h * wd;
+  g.bias_m = bias_m;
+  g.conv = &cv; g.conv_used = used;
+  return launch_gemm(g);
+}
 static int unfold(const float* x, float* cols, i64 n, i64 cin, i64 h, i64 wd, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad, i64 kc, i64 kp) {
   ProfScope prof("conv_unfold", ((double)n * cin * h * wd + (double)n * oh * ow * kp) * 4.0);
   i64 total = n * oh * ow * (kp / 4);
@@ -130,6 +195,17 @@ int launch_conv2d(const float* x, const float* w, const float* b, float* out, i6
                   i64 cout, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad) {
   i64 total = n * cout * oh * ow;
   if (total <= 0) return VB_OK;
+  if (conv_as_gemm(n, cin, cout, kh, kw, oh, ow) && conv_implicit_ok(n, cin, h, wd, kh, kw, stride, pad) && cout >= 32) {
+    Temp xp, wr;
+    VB_TRY(scratch_alloc((size_t)(n * (h + 2) * (wd + 2) * cin) * sizeof(float), &xp.p));
+    VB_TRY(scratch_alloc((size_t)(cout * 9 * cin) * sizeof(float), &wr.p));
+    VB_TRY(to_padded_nhwc(x, (float*)xp.p, n, cin, h, wd));
+    k_weights_to_taps<<<(unsigned)((cout * cin * 9 + 255) / 256), 256, 0, ctx().stream>>>(w, (float*)wr.p, (int)cout, (int)cin, 0);
+    VB_LAUNCH_CHECK();
+    int used = 0;
+    VB_TRY(implicit_product((const float*)wr.p, (const float*)xp.p, b, out, n, cout, cin, h, wd, &used));
+    if (used) return VB_OK;
+  }
   if (conv_as_gemm(n, cin, cout, kh, kw, oh, ow)) {
     const i64 kc = cin * kh * kw, kp = unfolded_row(kc), ohw = oh * ow;
     Temp cols;
@@ -212,6 +288,49 @@ __global__ void k_conv2d_bwd_input(const float* __restrict__ w, const float* __r
 int launch_conv2d_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb,
                            i64 n, i64 cin, i64 h, i64 wd, i64 cout, i64 kh, i64 kw, i64 oh, i64 ow, i64 stride, i64 pad) {
   cudaStream_t st = ctx().stream;
+  // implicit forms: the weight gradient over the padded input, the input gradient over the padded output gradient
+  bool dw_done = false, dx_done = false;
+  if (n * cout * oh * ow > 0 && cin > 0 && conv_as_gemm(n, cin, cout, kh, kw, oh, ow) && cout % 32 == 0) {
+    const i64 ohw = oh * ow, rows = n * ohw;
+    if (conv_implicit_ok(n, cin, h, wd, kh, kw, stride, pad)) {
+      Temp xp, gt, dwr;
+      VB_TRY(scratch_alloc((size_t)(n * (h + 2) * (wd + 2) * cin) * sizeof(float), &xp.p));
+      VB_TRY(scratch_alloc((size_t)(rows * cout) * sizeof(float), &gt.p));
+      VB_TRY(scratch_alloc((size_t)(cout * 9 * cin) * sizeof(float), &dwr.p));
+      VB_TRY(to_padded_nhwc(x, (float*)xp.p, n, cin, h, wd));
+      {
+        ProfScope prof("conv_nhwc", 2.0 * (double)rows * cout * 4.0);
+        dim3 grid((unsigned)((ohw + 31) / 32), (unsigned)((cout + 31) / 32), (unsigned)n), block(32, 8);
+        k_nchw_to_rows<<<grid, block, 0, st>>>(g, (float*)gt.p, cout, ohw);
+        VB_LAUNCH_CHECK();
+      }
+      ConvOperand cv{(const float*)xp.p, n, h, wd, cin, 2};
+      int used = 0;
+      GemmArgs a = gemm_args();          // dWr [cout, 9 cin] = g^T [cout, rows] . cols [rows, 9 cin]
+      a.A = (const float*)gt.p; a.M = cout; a.K = rows; a.a_rs = 1; a.a_cs = cout;
+      a.N = 9 * cin; a.C = (float*)dwr.p; a.c_rs = 9 * cin; a.c_cs = 1;
+      a.conv = &cv; a.conv_used = &used;
+      VB_TRY(launch_gemm(a));
+      if (used) {
+        k_taps_to_weights<<<(unsigned)((cout * cin * 9 + 255) / 256), 256, 0, st>>>((const float*)dwr.p, gw, (int)cout, (int)cin);
+        VB_LAUNCH_CHECK();
+        VB_TRY(launch_colsum((const float*)gt.p, gb, rows, cout, false));
+        dw_done = true;
+      }
+    }
+    if (gx && conv_implicit_ok(n, cout, h, wd, kh, kw, stride, pad) && cin >= 32) {
+      Temp gp, wf;
+      VB_TRY(scratch_alloc((size_t)(n * (h + 2) * (wd + 2) * cout) * sizeof(float), &gp.p));
+      VB_TRY(scratch_alloc((size_t)(cin * 9 * cout) * sizeof(float), &wf.p));
+      VB_TRY(to_padded_nhwc(g, (float*)gp.p, n, cout, h, wd));
+      k_weights_to_taps<<<(unsigned)((cout * cin * 9 + 255) / 256), 256, 0, st>>>(w, (float*)wf.p, (int)cout, (int)cin, 1);
+      VB_LAUNCH_CHECK();
+      int used = 0;
+      VB_TRY(implicit_product((const float*)wf.p, (const float*)gp.p, nullptr, gx, n, cin, cout, h, wd, &used));
+      dx_done = used != 0;
+    }
+    if (dw_done && (dx_done || !gx)) return VB_OK;
+  }
   if (n * cout * oh * ow > 0 && cin > 0 && conv_as_gemm(n, cin, cout, kh, kw, oh, ow)) {
     const i64 kc = cin * kh * kw, kp = unfolded_row(kc), ohw = oh * ow, rows = n * ohw;
     Temp cols, gt;
@@ -224,6 +343,7 @@ int launch_conv2d_backward(const float* x, const float* w, const float* g, float
       VB_LAUNCH_CHECK();
     }
     // db = column sums of g^T; dW [cout, kc] = g^T^T [cout, rows] . cols [rows, kc]
+    if (!dw_done) {
     VB_TRY(launch_colsum((const float*)gt.p, gb, rows, cout, false));
     VB_TRY(unfold(x, (float*)cols.p, n, cin, h, wd, kh, kw, oh, ow, stride, pad, kc, kp));
     GemmArgs a = gemm_args();
@@ -240,7 +360,8 @@ int launch_conv2d_backward(const float* x, const float* w, const float* g, float
     } else {
       VB_TRY(launch_gemm(a));
     }
-    if (gx) {
+    }
+    if (gx && !dx_done) {
       // dcols[img] [ohw, kc] = g[img]^T [ohw, cout] . W [cout, kc], over the same scratch as cols; then folded back
       GemmArgs d = gemm_args();
       d.A = g; d.M = ohw; d.K = cout; d.a_rs = 1; d.a_cs = ohw;
@@ -278,6 +399,7 @@ __global__ void k_maxpool_fwd(const float* __restrict__ x, float* __restrict__ o
       i64 ih = y * s + i - p; if (ih < 0 || ih >= h) continue;
       for (i64 j = 0; j < k; ++j) {
         i64 iw = xo * s + j - p; if (iw < 0 || iw >= w) continue;
+        if (!VB_BC((c * h + ih) * w + iw, nc * h * w)) continue;
         float v = x[(c * h + ih) * w + iw];
         if (v > best) best = v;
       }

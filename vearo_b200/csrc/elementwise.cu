@@ -22,15 +22,11 @@ __device__ __forceinline__ float binop(int op, float a, float b) {
   }
 }
 __device__ __forceinline__ float relu_f(float v) { return v > 0.0f ? v : 0.0f; }
-__device__ __forceinline__ float gelu_f(float v) {
-  float v3 = v * v * v;
-  float inner = kSqrt2OverPi * (v + kGeluCoeff * v3);
-  return 0.5f * v * (1.0f + tanhf(inner));
-}
+__device__ __forceinline__ float gelu_f(float v) { return gelu_value(v); }      // (common.h: shared with the GEMM epilogue)
 __device__ __forceinline__ float gelu_grad_f(float v) {
   float v3 = v * v * v;
   float inner = kSqrt2OverPi * (v + kGeluCoeff * v3);
-  float t = tanhf(inner);
+  float t = tanh_fast(inner);
   float sech_sq = 1.0f - t * t;
   float inner_deriv = kSqrt2OverPi * (1.0f + kGeluDeriv * v * v);
   return 0.5f * (1.0f + t) + 0.5f * v * sech_sq * inner_deriv;

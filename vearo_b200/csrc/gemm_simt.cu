@@ -101,6 +101,7 @@ int launch_gemm(const GemmArgs& g) {
   bool handled = false;
   VB_TRY(launch_gemm_tc(g, &handled));
   if (handled) return VB_OK;
+  if (g.conv) return VB_OK;      // an implicit im2col operand exists for the tensor-core kernel only: *conv_used stays 0, the caller unfolds
   // a caller that relies on triangular structure leaves parts of its operands unwritten: only the tensor-core kernel honours that
   if (g.causal) return set_error(VB_ERR_UNSUPPORTED, "triangular (causal) product outside the tensor-core kernel's shape rules");
   return launch_gemm_simt(g);

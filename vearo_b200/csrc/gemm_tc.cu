@@ -68,6 +68,12 @@ struct TcParams {
   int b_lo;                                       // the lo part of B comes pre-split from memory (map_blo) instead of from the converters
   int a_lo;                                       // ... and the lo part of A (map_alo); a_lo implies b_lo (the converters then have nothing to split)
   int tma_out;                                    // results leave through TMA stores of the staged 32 x 32 blocks (map_c)
+  int act;                                        // 1: the epilogue also stores GELU(result) through map_act (whole tiles, tma_out only)
+  // B is the unfolded ("im2col") matrix of a zero-padded NHWC image batch, never materialised: a 5-D tensor map {(j,c), x, y, tap row i, n}
+  // whose boxes are the tiles (see GemmArgs::conv).  1: K-major, rows = the pixels of image b2 (forward / input gradient);
+  // 2: MN-major, K = all pixels of all images, N = the taps (weight gradient)
+  int b_conv;
+  int cv_run, cv_w, cv_h;                         // floats per tap row (3 * C), image width and height
   int bk;                                         // k per stage: 16, or 32 for the narrow (64-wide) tiles whose per-stage hand-offs dominate
   int bn, stages, lstages, splits, kblocks_per_split;   // stages: raw-tile ring (TMA in flight); lstages: lo-tile ring
   int a_fold, b_fold;                             // 1: MN-contiguous operand whose tensor map is folded into 32-wide blocks (one TMA box per tile)
@@ -217,9 +223,12 @@ __device__ __forceinline__ void stage_write_out(const TcParams& p, float4* stg, 
 }
 
 // The CTA owns a 128 x bn output tile at a time (see the file header for the roles of its warps).
+// ACT: the instance whose epilogue also stores GELU(result) (kept apart: the activation's registers would spill the plain kernel).
+template <bool ACT>
 __global__ void __launch_bounds__(kThreads, 2)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
-          const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_alo, TcParams p) {
+          const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_alo, const __grid_constant__ CUtensorMap map_act,
+          TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // carve: raw ring [stages][ A | B ] (TMA destination, read by the MMA as the hi operand), lo ring [lstages][ A_lo | B_lo ]
   // (doubles as the epilogue's staging area: nothing converts while a tile is being stored), barriers.
@@ -284,6 +293,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
           uint8_t* st = smem + (size_t)s * raw_bytes;
           mbar_arrive_expect_tx(&full[s], raw_bytes);
           tma_load_tile(st, &map_a, &full[s], amode, BM, m0, k, ab2, ab1, bk);
+          if (p.b_conv == 1) {
+            // tile rows n0 .. n0 + bn are the pixels (y0 .., all x) of image bb2; k = (tap row, position inside its run of 3 * C floats)
+            tma_load_5d(st + a_bytes, &map_b, &full[s], k % p.cv_run, 0, n0 / p.cv_w, k / p.cv_run, bb2);
+          } else if (p.b_conv == 2) {
+            // k = (image, y, x) of the first of bk pixels; every 32-wide block of taps is one box (blocks past the last tap read zeros)
+            const int kx = k % p.cv_w, ky = (k / p.cv_w) % p.cv_h, kn = k / (p.cv_w * p.cv_h);
+            for (int j = 0; j < bn / 32; ++j) {
+              const int nn = n0 + 32 * j;
+              tma_load_5d(st + a_bytes + j * (bk * 128), &map_b, &full[s], nn % p.cv_run, kx, ky, nn / p.cv_run, kn);
+            }
+          } else
           tma_load_tile(st + a_bytes, &map_b, &full[s], bmode, bn, n0, k, bb2, bb1, bk);
           if (p.b_lo) {
             // the lo part of B lands straight in the lo stage (the converters fill only the A part); it completes on the stage's
@@ -445,6 +465,20 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUt
             if (lane == 0 && row0 < p.M) {
               if (wk.whole) tma_store_block(&map_c, stg, (int)col0, (int)row0, wk.b2, wk.b1);
               else tma_store_block(&map_c, stg, (int)col0, (int)row0, (int)((i64)wk.split * (p.nb1 * p.nb2) + wk.bz), 0);
+            }
+            if (ACT && p.act && wk.whole) {
+              // the activation of the block just stored, from the same registers: GELU as the standalone kernel computes it
+              // (crates/vearo-backend-cpu/src/lib.rs:458-497)
+              // (staged in a block of its own, in the raw ring: this launch mode has one unit per CTA, whose loads are all consumed)
+              float4* stg2 = (float4*)(smem + (size_t)cw * 4096);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(gelu_value(__uint_as_float(r[j])));
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4)
+                stage_put(stg2, lane, j4, make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]), __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3])));
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0 && row0 < p.M) tma_store_block(&map_act, stg2, (int)col0, (int)row0, wk.b2, wk.b1);
             }
           } else if (wk.whole) {
             store_block(p, r, stg, lane, cbase, p.c_rs, row0, col0, true, c_vec);
@@ -678,6 +712,29 @@ bool make_out_map(CUtensorMap* map, float* base, i64 N, i64 M, i64 d2, i64 d3, i
   return r == CUDA_SUCCESS;
 }
 
+// The unfolded matrix of a zero-padded NHWC batch xp [n, H + 2, W + 2, C] (3 x 3 window, stride 1) as a tensor map:
+// dims {3C (tap column j and channel, contiguous), W (x), H (y), 3 (tap row i), n}; element (jc, x, y, i, n) = xp[n, y + i, x, jc].
+// mode 1: boxes {bk, W, rows / W, 1, 1} (K-major tile of `rows` pixels); mode 2: boxes {32, bx, bk / bx, 1, 1} (MN-major, bk pixels).
+bool make_conv_map(CUtensorMap* map, const ConvOperand& cv, int mode, int rows, int bk) {
+  const i64 C = cv.c, W = cv.w, H = cv.h;
+  if (((uintptr_t)cv.xp & 15) || (C & 3) || W <= 0 || H <= 0) return false;
+  cuuint64_t dims[5] = {(cuuint64_t)(3 * C), (cuuint64_t)W, (cuuint64_t)H, 3, (cuuint64_t)cv.n};
+  cuuint64_t strides[4] = {(cuuint64_t)C * 4, (cuuint64_t)(W + 2) * C * 4, (cuuint64_t)(W + 2) * C * 4, (cuuint64_t)(H + 2) * (W + 2) * C * 4};
+  cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+  if (mode == 1) {
+    if (rows % W || rows / W > 256 || W > 256) return false;
+    box[0] = (cuuint32_t)bk; box[1] = (cuuint32_t)W; box[2] = (cuuint32_t)(rows / W); box[3] = 1; box[4] = 1;
+  } else {
+    const i64 bx = W < bk ? W : bk;
+    if (bk % bx || W % bx) return false;
+    box[0] = 32; box[1] = (cuuint32_t)bx; box[2] = (cuuint32_t)(bk / bx); box[3] = 1; box[4] = 1;
+  }
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, (void*)cv.xp, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           mode == 2 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B),
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int* g_tile_counters = nullptr;     // stream-K arrival counters (zero between launches)
 
 }  // namespace
@@ -734,6 +791,14 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   };
   Operand oa, ob;
   VB_TRY(prepare(g.A, g.M, g.a_rs, g.a_cs, g.a_b1, g.a_b2, hold_a, &oa));
+  const int b_conv = g.conv ? g.conv->mode : 0;
+  if (b_conv) {
+    // B is described by the padded image batch itself; the geometry has to fit whole boxes
+    const ConvOperand& cv = *g.conv;
+    if (hold_a.p || (3 * cv.c) % 32 || (b_conv == 1 && (g.nb1 != 1 || g.nb2 != cv.n || g.N != cv.h * cv.w || g.K != 9 * cv.c)) ||
+        (b_conv == 2 && (nb != 1 || g.N != 9 * cv.c || g.K != cv.n * cv.h * cv.w || (cv.h * cv.w) % 32))) return VB_OK;
+    ob = Operand{cv.xp, g.N, 0, 0, 0, false, false, b_conv == 2};
+  } else
   VB_TRY(prepare(g.B, g.N, g.b_cs, g.b_rs, g.b_b1, g.b_b2, hold_b, &ob));   // B^T rows are the columns of B
 
   TcParams p{};
@@ -812,6 +877,15 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   CUtensorMap map_a, map_b;
   bool fold_a = false, fold_b = false;
   VB_TRY(make_map(&map_a, oa, g.K, g.nb1, g.nb2, BM, bk, &fold_a));
+  if (b_conv) {
+    const ConvOperand& cv = *g.conv;
+    // tiles must be whole image rows (mode 1) / the k-blocks whole runs of pixels inside an image (mode 2); split-K ranges and the
+    // stream-K deal keep k-block granularity, so they need nothing more
+    if ((b_conv == 1 && p.bn % cv.w) || (3 * cv.c) % bk ||
+        !make_conv_map(&map_b, cv, b_conv, p.bn, bk)) return VB_OK;
+    p.b_conv = b_conv; p.cv_run = (int)(3 * cv.c); p.cv_w = (int)cv.w; p.cv_h = (int)cv.h;
+    if (g.conv_used) *g.conv_used = 1;
+  } else
   VB_TRY(make_map(&map_b, ob, g.K, g.nb1, g.nb2, p.bn, bk, &fold_b));
   p.a_fold = fold_a; p.b_fold = fold_b;
   Temp part, ws;
@@ -835,11 +909,18 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   if (round_robin) { p.persistent = 2; p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.live_per_batch = live_per_batch; p.live_tiles = live_per_batch * nb; }
 
   // Results leave through the copy engine when the layout allows and nothing has to be read back (beta = 0).
-  CUtensorMap map_c;
-  memset(&map_c, 0, sizeof map_c);
+  CUtensorMap map_c, map_act;
+  memset(&map_c, 0, sizeof map_c); memset(&map_act, 0, sizeof map_act);
   if (g.beta == 0.0f) {
     if (splits == 1) p.tma_out = make_out_map(&map_c, g.C, g.N, g.M, g.nb2, g.nb1, g.c_rs, g.c_b2, g.c_b1) ? 1 : 0;
     else p.tma_out = make_out_map(&map_c, (float*)part.p, g.N, g.M, (i64)splits * nb, 1, g.N, g.M * g.N, 0) ? 1 : 0;
+  }
+  // GELU of the result as a second output of the epilogue (same layout as C): whole tiles stored by the copy engine only; in
+  // every other mode the caller runs the activation as a kernel of its own
+  if (g.act_out && p.tma_out && splits == 1 && !persistent && !round_robin && g.alpha == 1.0f && (size_t)p.stages * raw_bytes >= 32 * 1024 &&
+      make_out_map(&map_act, g.act_out, g.N, g.M, g.nb2, g.nb1, g.c_rs, g.c_b2, g.c_b1)) {
+    p.act = 1;
+    if (g.act_fused) *g.act_fused = 1;
   }
 
   // Pre-split lo part of B: B consumed in place (the lo plane has B's layout).  (In the persistent modes the
@@ -862,7 +943,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
   size_t smem = (size_t)(p.stages + p.lstages) * raw_bytes + (2 * p.stages + 2 * p.lstages + 3) * sizeof(uint64_t) + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
-    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    VB_CUDA(cudaFuncSetAttribute(k_gemm_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set = true;
   }
   {
@@ -887,7 +969,8 @@ int launch_gemm_tc(const GemmArgs& g, bool* handled) {
     if (p.long_first) grid = dim3((unsigned)tiles_n, (unsigned)(nb * splits), (unsigned)tiles_m);
     if (persistent) grid = dim3((unsigned)streamk_groups, 1, 1);
     if (round_robin) grid = dim3((unsigned)slots, 1, 1);
-    k_gemm_tc<<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, p);
+    if (p.act) k_gemm_tc<true><<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, map_act, p);
+    else k_gemm_tc<false><<<grid, kThreads, smem, ctx().stream>>>(map_a, map_b, map_c, map_blo, map_alo, map_act, p);
     VB_LAUNCH_CHECK();
     ++g_tc_launches;
     if (splits > 1) {

@@ -280,6 +280,17 @@ Tensor Tensor::linear(const Tensor& weight, const Tensor* bias) const {
   record(Op::Linear, ins, out);
   return out;
 }
+// linear followed by gelu: one device call, two tape nodes (exactly what x.linear(w, b).gelu() records)
+Tensor Tensor::linear_gelu(const Tensor& weight, const Tensor* bias) const {
+  vb_tensor pre_{}, act_{};
+  check(vb_linear_gelu(&d_, &weight.d_, bias ? &bias->d_ : nullptr, &pre_, &act_), "linear_gelu");
+  Tensor pre = Tensor::adopt(pre_), act = Tensor::adopt(act_);
+  std::vector<const Tensor*> ins = {this, &weight};
+  if (bias) ins.push_back(bias);
+  record(Op::Linear, ins, pre);
+  record(Op::Gelu, {&pre}, act);
+  return act;
+}
 // reshape / transpose / permute: views (tensor.rs:493-642); reshape of a strided view copies first.
 Tensor Tensor::reshape(const std::vector<i64>& shape) const {
   i64 n = 1; for (i64 d : shape) n *= d;

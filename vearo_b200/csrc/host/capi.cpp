@@ -71,6 +71,7 @@ int vh_batchnorm(int x, int g, int b, int rm, int rv, int training, float mom, f
 }
 int vh_fused_attention(int q, int k, int v, int mask) { VH_TRY(return put(at(q).fused_attention(at(k), at(v), mask >= 0 ? &at(mask) : nullptr))); }
 int vh_linear(int x, int w, int b) { VH_TRY(return put(at(x).linear(at(w), b >= 0 ? &at(b) : nullptr))); }
+int vh_linear_gelu(int x, int w, int b) { VH_TRY(return put(at(x).linear_gelu(at(w), b >= 0 ? &at(b) : nullptr))); }
 int vh_reshape(int a, const int64_t* shape, int rank) { VH_TRY(return put(at(a).reshape(std::vector<i64>(shape, shape + rank)))); }
 int vh_transpose(int a, int d0, int d1) { VH_TRY(return put(at(a).transpose(d0, d1))); }
 int vh_permute(int a, const int64_t* axes, int rank) { VH_TRY(return put(at(a).permute(std::vector<i64>(axes, axes + rank)))); }
@@ -148,6 +149,7 @@ int vh_opt_save_state(int o, const char* path) { VH_TRY(opt(o).save_state(path);
 int vh_opt_load_state(int o, const char* path) { VH_TRY(opt(o).load_state(path); return 0); }
 int vh_save_checkpoint(int m, const char* path) { VH_TRY(checkpoint::save_checkpoint(model(m).parameters(), path); return 0); }
 int vh_load_checkpoint(int m, const char* path) { VH_TRY(checkpoint::load_checkpoint(model(m).parameters(), path); return 0); }
+int vh_opt_handle(int o) { VH_TRY(return opt(o).handle()); }       // the library's vb_opt_* handle of this optimizer
 int vh_opt_set_lr(int o, float lr) { VH_TRY(opt(o).set_lr(lr); return 0); }
 int vh_clip_grad_norm(const int* params, int n, float max_norm, float* norm) {
   VH_TRY(std::vector<Tensor> ps; for (int i = 0; i < n; ++i) ps.push_back(at(params[i])); *norm = optim::clip_grad_norm(ps, max_norm); return 0);

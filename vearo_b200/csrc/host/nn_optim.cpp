@@ -12,6 +12,7 @@
 // clip_grad_norm (360-383), CosineSchedule::lr_at (336-348) — with state on the device and one
 // fused launch for all parameters.
 #include "vearo_host.h"
+#include <cstdlib>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -78,7 +79,7 @@ void MultiHeadAttention::parameters(std::vector<Tensor>& out) const { q.paramete
 TransformerBlock::TransformerBlock(i64 d, i64 h, i64 ff) : ln1(d), ln2(d), attn(d, h), fc1(d, ff, true), fc2(ff, d, true) {}
 Tensor TransformerBlock::forward(const Tensor& x, const Tensor* mask) const {
   Tensor x1 = x.add(attn.forward(ln1.forward(x), mask));
-  return x1.add(fc2.forward(fc1.forward(ln2.forward(x1)).gelu()));
+  return x1.add(fc2.forward(ln2.forward(x1).linear_gelu(fc1.weight, fc1.has_bias ? &fc1.bias : nullptr)));
 }
 void TransformerBlock::parameters(std::vector<Tensor>& out) const {
   ln1.parameters(out); attn.parameters(out); ln2.parameters(out); fc1.parameters(out); fc2.parameters(out);
@@ -212,11 +213,22 @@ void Optimizer::on_ready(int idx, void* self) {
     if (o->world_ > 1) throw Error("a parameter that gets gradient from several checkpointed regions is not supported under data parallel: its bucket may already have been reduced");
     return;
   }
-  if (o->ready_[idx]) return;
+  if (o->ready_[idx]) {
+    // a second backward pass before step(): on one GPU the sink is simply overwritten, as the reference's gradient map is; under
+    // data parallel the bucket holding it has been reduced already and would not be reduced again
+    if (o->world_ > 1) throw Error("backward() ran twice before the optimizer step: not supported under data parallel (the first pass's gradients were already reduced)");
+    return;
+  }
   o->ready_[idx] = 1;
   if (o->world_ <= 1) return;
   Bucket& b = o->buckets_[o->bucket_of_[idx]];
   if (--b.pending == 0) check(vb_dp_allreduce(o->arena_.slot(), b.offset, b.numel), "dp_allreduce");
+}
+// Host deadline for the step's collectives, in milliseconds: VB200_DP_TIMEOUT_MS, 30 s by default.
+static int collective_timeout_ms() {
+  static int ms = -1;
+  if (ms < 0) { const char* e = std::getenv("VB200_DP_TIMEOUT_MS"); ms = (e && std::atoi(e) > 0) ? std::atoi(e) : 30000; }
+  return ms;
 }
 // Buckets with a parameter that received no gradient this step are still reduced (every rank must
 // issue the same collectives): their stale ranges are zeroed first.
@@ -228,19 +240,22 @@ void Optimizer::finish_reduce() {
         Bucket& b = buckets_[bucket_of_[i]];
         if (--b.pending == 0) check(vb_dp_allreduce(arena_.slot(), b.offset, b.numel), "dp_allreduce");
       }
-    check(vb_dp_finish(30000), "dp_finish");
+    check(vb_dp_finish(collective_timeout_ms()), "dp_finish");
     for (Bucket& b : buckets_) b.pending = b.nparams;
   }
 }
+// Which parameters the update touches: on one GPU those that received a gradient this step (vearo-optim/src/lib.rs:106-108 skips the
+// others); under data parallel ALL of them -- a parameter may have received gradient on some ranks only, every rank holds the same
+// reduced sum after finish_reduce (zero-filled where nothing was produced locally), and replicas must apply the same update.
 void Optimizer::step() {
   finish_reduce();
-  check(vb_opt_step(opt_, ready_.data(), 0.0f, 1.0f / (float)world_, nullptr), "opt_step");
+  check(vb_opt_step(opt_, world_ > 1 ? nullptr : ready_.data(), 0.0f, 1.0f / (float)world_, nullptr), "opt_step");
   std::fill(ready_.begin(), ready_.end(), 0);
 }
 float Optimizer::clip_and_step(float max_norm, bool read_norm) {
   finish_reduce();
   float norm = 0.0f;
-  check(vb_opt_step(opt_, ready_.data(), max_norm, 1.0f / (float)world_, read_norm ? &norm : nullptr), "opt_step");
+  check(vb_opt_step(opt_, world_ > 1 ? nullptr : ready_.data(), max_norm, 1.0f / (float)world_, read_norm ? &norm : nullptr), "opt_step");
   std::fill(ready_.begin(), ready_.end(), 0);
   return norm;
 }
@@ -300,15 +315,38 @@ void write_container(const std::vector<HostTensor>& ts, const std::string& path)
   }
   if (std::fflush(fl.f) != 0) throw Error("checkpoint write failed");
 }
+// Bytes left in the file from the current position (so that a length field is never trusted beyond what the file can hold).
+static uint64_t bytes_left(FILE* f) {
+  long here = std::ftell(f);
+  if (here < 0 || std::fseek(f, 0, SEEK_END) != 0) throw Error("checkpoint read failed");
+  long end = std::ftell(f);
+  if (end < here || std::fseek(f, here, SEEK_SET) != 0) throw Error("checkpoint read failed");
+  return (uint64_t)(end - here);
+}
+// One tensor record; `expect` (may be null) is the shape it must have, checked before any of its data is read.
+static HostTensor read_record(FILE* f, const std::vector<i64>* expect) {
+  HostTensor t;
+  const uint32_t rank = get_u32(f);
+  if (rank > 8 || (uint64_t)rank * 4 > bytes_left(f)) throw Error("checkpoint is damaged: tensor rank " + std::to_string(rank));
+  t.dims.resize(rank);
+  for (i64& d : t.dims) d = get_u32(f);
+  if (expect && t.dims != *expect) throw Error("Checkpoint shape does not match parameter shape");
+  const uint32_t n = get_u32(f);
+  uint64_t prod = 1;
+  for (i64 d : t.dims) { prod *= (uint64_t)d; if (prod > 0xffffffffull) break; }
+  if (prod != n) throw Error("Checkpoint shape does not match parameter shape");        // (the reference's copy_from_slice panics on this)
+  if ((uint64_t)n * 4 > bytes_left(f)) throw Error("failed to fill whole buffer");
+  t.data.resize(n);
+  if (n && std::fread(t.data.data(), sizeof(float), n, f) != n) throw Error("failed to fill whole buffer");
+  return t;
+}
 std::vector<HostTensor> read_container(const std::string& path) {
   File fl(path, "rb");
-  std::vector<HostTensor> ts(get_u32(fl.f));
-  for (HostTensor& t : ts) {
-    t.dims.resize(get_u32(fl.f));
-    for (i64& d : t.dims) d = get_u32(fl.f);
-    t.data.resize(get_u32(fl.f));
-    if (!t.data.empty() && std::fread(t.data.data(), sizeof(float), t.data.size(), fl.f) != t.data.size()) throw Error("failed to fill whole buffer");
-  }
+  const uint32_t count = get_u32(fl.f);
+  if ((uint64_t)count * 8 > bytes_left(fl.f)) throw Error("checkpoint is damaged: tensor count " + std::to_string(count));      // a record is at least 8 bytes
+  std::vector<HostTensor> ts;
+  ts.reserve(count);
+  for (uint32_t i = 0; i < count; ++i) ts.push_back(read_record(fl.f, nullptr));
   return ts;
 }
 void save_checkpoint(const std::vector<Tensor>& params, const std::string& path) {
@@ -316,33 +354,44 @@ void save_checkpoint(const std::vector<Tensor>& params, const std::string& path)
   for (const Tensor& p : params) ts.push_back(HostTensor{p.shape(), p.to_vec_f32()});
   write_container(ts, path);
 }
+// As crates/vearo/src/checkpoint.rs:42-86: the count is compared first, then every tensor's shape before its data is read
+// (nothing is written to a parameter until its own record has been validated; earlier parameters keep what was loaded).
 void load_checkpoint(const std::vector<Tensor>& params, const std::string& path) {
-  std::vector<HostTensor> ts = read_container(path);
-  if (ts.size() != params.size()) throw Error("Checkpoint tensor count does not match model parameter count");
-  for (size_t i = 0; i < ts.size(); ++i)
-    if (ts[i].dims != params[i].shape()) throw Error("Checkpoint shape does not match parameter shape");
-  for (size_t i = 0; i < ts.size(); ++i) {
-    if ((i64)ts[i].data.size() != params[i].numel()) throw Error("Checkpoint shape does not match parameter shape");
-    params[i].write_f32(ts[i].data.data());
+  File fl(path, "rb");
+  if (get_u32(fl.f) != params.size()) throw Error("Checkpoint tensor count does not match model parameter count");
+  for (const Tensor& p : params) {
+    const std::vector<i64> shape = p.shape();
+    HostTensor t = read_record(fl.f, &shape);
+    p.write_f32(t.data.data());
   }
 }
 }  // namespace checkpoint
 
 namespace optim {
+// State file: tensor 0 = [6] exact small integers held as f32 -- the step counter t as two 16-bit halves (low, high) and the
+// per-call randomness counter (vearo-core/src/tensor.rs:1240-1285) as four 16-bit parts, low first; tensor 1 = the flat state
+// array.  (Files written before the counter was added hold tensor 0 = [t] as one f32; they still load.)
 void Optimizer::save_state(const std::string& path) const {
   vb_slot st; int64_t n = 0; uint32_t t = 0;
   check(vb_opt_state(opt_, &st, &n, &t), "opt_state");
-  checkpoint::HostTensor step{{1}, {(float)t}}, state{{n}, std::vector<float>((size_t)n)};
+  const uint64_t rng = autograd::rng_counter();
+  checkpoint::HostTensor head{{6}, {(float)(t & 0xffffu), (float)(t >> 16), (float)(rng & 0xffffu), (float)((rng >> 16) & 0xffffu),
+                                    (float)((rng >> 32) & 0xffffu), (float)((rng >> 48) & 0xffffu)}};
+  checkpoint::HostTensor state{{n}, std::vector<float>((size_t)n)};
   if (n) check(vb_read(st, 0, state.data.data(), n), "read optimizer state");
-  checkpoint::write_container({step, state}, path);
+  checkpoint::write_container({head, state}, path);
 }
 void Optimizer::load_state(const std::string& path) {
   std::vector<checkpoint::HostTensor> ts = checkpoint::read_container(path);
   vb_slot st; int64_t n = 0;
   check(vb_opt_state(opt_, &st, &n, nullptr), "opt_state");
-  if (ts.size() != 2 || ts[0].data.size() != 1 || (int64_t)ts[1].data.size() != n) throw Error("optimizer state file does not match this optimizer");
+  if (ts.size() != 2 || (ts[0].data.size() != 1 && ts[0].data.size() != 6) || (int64_t)ts[1].data.size() != n)
+    throw Error("optimizer state file does not match this optimizer");
   if (n) check(vb_write(st, 0, ts[1].data.data(), n), "write optimizer state");
-  check(vb_opt_set_step(opt_, (uint32_t)ts[0].data[0]), "opt_set_step");
+  const std::vector<float>& h = ts[0].data;
+  if (h.size() == 1) { check(vb_opt_set_step(opt_, (uint32_t)h[0]), "opt_set_step"); return; }
+  check(vb_opt_set_step(opt_, (uint32_t)h[0] | ((uint32_t)h[1] << 16)), "opt_set_step");
+  autograd::set_rng_counter((uint64_t)h[2] | ((uint64_t)h[3] << 16) | ((uint64_t)h[4] << 32) | ((uint64_t)h[5] << 48));
 }
 }  // namespace optim
 

@@ -77,6 +77,7 @@ class Tensor {
   // Recorded on the tape: its gradient is handed back to a, b and c as row blocks.
   static Tensor pack_rows(const Tensor& a, const Tensor& b, const Tensor& c);
   Tensor linear(const Tensor& weight, const Tensor* bias) const;   // fused x.W^T + b
+  Tensor linear_gelu(const Tensor& weight, const Tensor* bias) const;   // linear(...).gelu() with the activation formed in the GEMM's epilogue
   Tensor reshape(const std::vector<i64>& shape) const;
   Tensor transpose(int d0, int d1) const;
   Tensor permute(const std::vector<i64>& axes) const;
@@ -128,8 +129,9 @@ class Optimizer {
   void set_lr(float lr); float lr() const { return cfg_.lr; }
   const std::vector<Tensor>& params() const { return params_; }
   const std::vector<Tensor>& grads() const { return sinks_; }
-  // Optimizer state as a `.ve` container (see checkpoint::): tensor 0 = [t] (the AdamW step counter as f32), tensor 1 =
-  // the flat state array (m then v, or the velocity).  The reference's optimizers have no save of their own.
+  // Optimizer state as a `.ve` container (see checkpoint::): tensor 0 = the AdamW step counter t and the per-call randomness
+  // counter, as exact 16-bit parts; tensor 1 = the flat state array (m then v, or the velocity).  Loading restores all
+  // three.  The reference's optimizers have no save of their own.
   void save_state(const std::string& path) const;
   void load_state(const std::string& path);
   int handle() const { return opt_; }          // the library's optimizer handle (vb_opt_*)

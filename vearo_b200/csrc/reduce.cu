@@ -176,7 +176,7 @@ int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulat
 
 // General broadcast-gradient reduction: one thread per output element walks the reduced index
 // space in row-major order (the order reduce_to adds in).
-__global__ void k_reduce_general(const float* __restrict__ g, float* __restrict__ out, i64 out_numel, Strided kept, Strided red, i64 red_count) {
+__global__ void k_reduce_general(const float* __restrict__ g, float* __restrict__ out, i64 out_numel, Strided kept, Strided red, i64 red_count, i64 g_numel) {
   i64 idx = blockIdx.x * (i64)blockDim.x + threadIdx.x;
   if (idx >= out_numel) return;
   i64 rem = idx, base = 0;
@@ -185,13 +185,13 @@ __global__ void k_reduce_general(const float* __restrict__ g, float* __restrict_
   for (i64 r = 0; r < red_count; ++r) {
     i64 rr = r, off = base;
     for (int d = red.rank - 1; d >= 0; --d) { i64 c = rr % red.dims[d]; rr /= red.dims[d]; off += c * red.sa[d]; }
-    s += g[off];
+    if (VB_BC(off, g_numel)) s += g[off];
   }
   out[idx] = s;
 }
 int launch_reduce_general(const float* g, float* out, i64 out_numel, const Strided& kept, const Strided& red, i64 red_count) {
   if (out_numel <= 0) return VB_OK;
-  k_reduce_general<<<(unsigned)((out_numel + 127) / 128), 128, 0, ctx().stream>>>(g, out, out_numel, kept, red, red_count);
+  k_reduce_general<<<(unsigned)((out_numel + 127) / 128), 128, 0, ctx().stream>>>(g, out, out_numel, kept, red, red_count, out_numel * red_count);
   VB_LAUNCH_CHECK();
   return VB_OK;
 }

@@ -157,6 +157,10 @@ int contiguous_ptr(const vb_tensor* t, const float** p, Temp& hold) {
   return VB_OK;
 }
 
+#ifdef VB200_BOUNDS_CHECK
+std::vector<void (*)(int*)>& bc_setters() { static auto* v = new std::vector<void (*)(int*)>(); return *v; }
+void bc_register(void (*setter)(int*)) { bc_setters().push_back(setter); }
+#endif
 }  // namespace vb
 
 using namespace vb;
@@ -188,6 +192,10 @@ int vb_init(int device_ordinal) {
   VB_CUDA(cudaMalloc(&g_ctx.d_scalars, 64 * sizeof(float)));
   VB_CUDA(cudaMemset(g_ctx.d_scalars, 0, 64 * sizeof(float)));
   VB_CUDA(cudaMallocHost(&g_ctx.h_pinned, 64 * sizeof(float)));
+#ifdef VB200_BOUNDS_CHECK
+  for (void (*set)(int*) : bc_setters()) set(g_ctx.d_err);          // every translation unit learns where the error word is
+  VB_CUDA(cudaGetLastError());
+#endif
   g_ctx.ready = true;
   return VB_OK;
 }
@@ -232,6 +240,7 @@ int vb_check_errors(void) {
     if (h & ERRBIT_NEG_ID) m += "Token ID / target class cannot be negative; ";
     if (h & ERRBIT_OOB_ID) m += "Token ID / target class out of bounds; ";
     if (h & ERRBIT_WAIT_TIMEOUT) m += "a device-side wait ran out; ";
+    if (h & ERRBIT_BOUNDS) m += "a computed index left its tensor (bounds-check build); ";
     return set_error(VB_ERR_BAD_INDEX, m);
   }
   return VB_OK;
