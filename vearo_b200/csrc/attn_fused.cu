@@ -20,7 +20,8 @@
 //   pass 2: S again, p = exp(s - max) / (sum + 1e-9) exactly as the reference forms it, P -> tensor memory (hi, lo) and -- when
 //           the caller keeps the probabilities for the backward pass -- to global memory through staged TMA block stores, then
 //           O += P.V.  No running rescale of O is ever needed, and the stored P is final.
-// Backward (dQ part), one CTA per 128 query rows, 64-key blocks (V and K double-buffered), same warp roles:
+// Backward (dQ part), one CTA per 128 query rows, same warp roles; dP is formed 128 keys at a time (one V tile), dS and dQ in
+// 64-key halves (K double-buffered):
 //   the dO rows go to tensor memory once (hi, lo: the A operand of dP = dO.V^T); per block the row warps take their P block
 //   (asynchronous copies two blocks ahead), ds = p * (dp - delta) * scale with delta = dO.O (= sum_j dp_j p_j, the reference's
 //   row term), dS -> tensor memory (hi, lo) and global memory (for the dK product), dQ += dS.K.
@@ -378,7 +379,7 @@ struct AttnBwdParams {
   const float* dO; i64 do_sb, do_sh, do_ss;     // [B,H,S,64] view of the output gradient
   int* err;
 };
-enum { D_VFULL0 = 0, D_VFULL1, D_VCONV0, D_VCONV1, D_VFREE0, D_VFREE1, D_KFULL0, D_KFULL1, D_KCONV0, D_KCONV1, D_KFREE0, D_KFREE1,
+enum { D_VFULL = 0, D_VCONV, D_VFREE, D_KFULL0, D_KFULL1, D_KCONV0, D_KCONV1, D_KFREE0, D_KFREE1,
        D_DPFULL, D_DPFREE, D_DSREADY, D_DQDONE, D_DOREADY, D_COUNT };
 constexpr int kHalfTile = 64 * 64 * 4;          // a 64-key operand block: 16 KB (two 32-column chunks of 8 KB)
 
@@ -395,8 +396,11 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
               const __grid_constant__ CUtensorMap map_dq, AttnBwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* vbuf[2] = {smem, smem + 2 * kHalfTile};                          // [hi | lo] per stage, K-major (V as the B operand of dO.V^T)
-  uint8_t* kbuf[2] = {smem + 4 * kHalfTile, smem + 6 * kHalfTile};          // [hi | lo] per stage, MN-major (K as the B operand of dS.K)
+  // V: one 128-key K-major tile [hi | lo] (the B operand of dP = dO.V^T, N = 128: an MMA instruction costs its issuer about the
+  // same whether it is 64 or 128 wide, so dP is formed 128 keys at a time); K: 64-key MN-major blocks, two stages [hi | lo] (the B
+  // operand of dQ += dS.K, whose width is the head size)
+  uint8_t* v_hi = smem; uint8_t* v_lo = smem + kTile;
+  uint8_t* kbuf[2] = {smem + 4 * kHalfTile, smem + 6 * kHalfTile};
   uint8_t* staging = smem + 8 * kHalfTile;                                  // 8 row warps x 3 blocks of 4 KB
   uint64_t* bars = (uint64_t*)(staging + kRowWarpsFwd * 3 * 4096);
   float* xd = (float*)(bars + D_COUNT);                                     // delta halves [2][128]
@@ -406,15 +410,14 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
   const int qt = p.n_qtiles - 1 - (int)blockIdx.y;
-  const int n_all = (p.S + 63) / 64;
-  const int n_kv = p.causal ? (2 * qt + 2 < n_all ? 2 * qt + 2 : n_all) : n_all;
+  const int n_all = (p.S + 127) / 128;
+  const int n_big = p.causal ? (qt + 1 < n_all ? qt + 1 : n_all) : n_all;      // 128-key blocks
+  const int n_kv = 2 * n_big;                                                   // 64-key sub-blocks (one past the end of S reads zeros)
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars[D_VFULL0 + i], 1); mbar_init(&bars[D_VCONV0 + i], 4); mbar_init(&bars[D_VFREE0 + i], 2);
-      mbar_init(&bars[D_KFULL0 + i], 1); mbar_init(&bars[D_KCONV0 + i], 4); mbar_init(&bars[D_KFREE0 + i], 2);
-    }
-    mbar_init(&bars[D_DPFULL], 2); mbar_init(&bars[D_DPFREE], kRowWarpsFwd); mbar_init(&bars[D_DSREADY], kRowWarpsFwd);
+    mbar_init(&bars[D_VFULL], 1); mbar_init(&bars[D_VCONV], 4); mbar_init(&bars[D_VFREE], 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars[D_KFULL0 + i], 1); mbar_init(&bars[D_KCONV0 + i], 4); mbar_init(&bars[D_KFREE0 + i], 2); }
+    mbar_init(&bars[D_DPFULL], 1); mbar_init(&bars[D_DPFREE], kRowWarpsFwd); mbar_init(&bars[D_DSREADY], kRowWarpsFwd);
     mbar_init(&bars[D_DQDONE], 2); mbar_init(&bars[D_DOREADY], kRowWarpsFwd);          // (two lanes issue the MMAs, each commits its own)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -427,9 +430,8 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  // (dP and dQ each have two accumulators taking alternate k steps, so that consecutive MMAs do not wait on each other's result)
-  const uint32_t t_dohi = tmem, t_dolo = tmem + 64, t_dp = tmem + 128, t_dp2 = tmem + 192, t_dshi = tmem + 256, t_dslo = tmem + 320,
-                 t_dq = tmem + 384, t_dq2 = tmem + 448;
+  // (dQ has two accumulators taking alternate k steps, one per issuing lane)
+  const uint32_t t_dohi = tmem, t_dolo = tmem + 64, t_dp = tmem + 128, t_dshi = tmem + 256, t_dslo = tmem + 320, t_dq = tmem + 384, t_dq2 = tmem + 448;
 
   if (warp == 0) {
     // ---- TMA producer ---------------------------------------------------------------------------------------------------
@@ -437,11 +439,13 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j & 1, u = j >> 1;
-        if (u > 0) ok = mbar_wait(&bars[D_VFREE0 + st], (uint32_t)(u - 1) & 1, abort_flag);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&bars[D_VFULL0 + st], kHalfTile);
-        tma_load_4d(vbuf[st], &map_v, &bars[D_VFULL0 + st], 0, j * 64, h, b);
-        tma_load_4d(vbuf[st] + kHalfTile / 2, &map_v, &bars[D_VFULL0 + st], 32, j * 64, h, b);
+        if ((j & 1) == 0) {          // the 128-key V tile of block J = j / 2
+          if (u > 0) ok = mbar_wait(&bars[D_VFREE], (uint32_t)(u - 1) & 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars[D_VFULL], kTile);
+          tma_load_4d(v_hi, &map_v, &bars[D_VFULL], 0, u * 128, h, b);
+          tma_load_4d(v_hi + kChunk, &map_v, &bars[D_VFULL], 32, u * 128, h, b);
+        }
         if (u > 0) ok = mbar_wait(&bars[D_KFREE0 + st], (uint32_t)(u - 1) & 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars[D_KFULL0 + st], kHalfTile);
@@ -449,48 +453,45 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
         tma_load_4d(kbuf[st] + kHalfTile / 2, &map_k, &bars[D_KFULL0 + st], 32, j * 64, h, b);
       }
       if (*abort_flag)        // give copies already issued a bounded time to land before the CTA exits
-        for (int i = 0; i < 2; ++i)
-          for (int which = 0; which < 2; ++which) {
-            uint32_t addr = smem_u32(&bars[(which ? D_KFULL0 : D_VFULL0) + i]), done = 0;
-            for (uint32_t n = 0; n < (1u << 14) && !done; ++n)
-              asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}" : "=r"(done) : "r"(addr), "r"(0u) : "memory");
-          }
+        for (int i = 0; i < 3; ++i) {
+          uint32_t addr = smem_u32(&bars[i == 2 ? D_VFULL : D_KFULL0 + i]), done = 0;
+          for (uint32_t n = 0; n < (1u << 14) && !done; ++n)
+            asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}" : "=r"(done) : "r"(addr), "r"(0u) : "memory");
+        }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ------------------------------------------------------------------------------------------------------
     // (two lanes issue, each the k steps of one parity into its own accumulator: see the forward kernel)
     if (lane < 2) {
-      const uint32_t idesc_dp = make_idesc(128, 64, 0, 0), idesc_dq = make_idesc(128, 64, 0, 1);
-      uint64_t dv_hi[2], dv_lo[2], dk_hi[2], dk_lo[2];
-      for (int i = 0; i < 2; ++i) {
-        dv_hi[i] = make_desc_k(smem_u32(vbuf[i]), 32); dv_lo[i] = make_desc_k(smem_u32(vbuf[i] + kHalfTile), 32);
-        dk_hi[i] = desc_mn(smem_u32(kbuf[i]), 64); dk_lo[i] = desc_mn(smem_u32(kbuf[i] + kHalfTile), 64);
-      }
+      const uint32_t idesc_dq = make_idesc(128, 64, 0, 1);
+      const uint32_t idesc_dp128 = make_idesc(128, 128, 0, 0);
+      const uint64_t dv_hi = make_desc_k(smem_u32(v_hi), 32), dv_lo = make_desc_k(smem_u32(v_lo), 32);
+      uint64_t dk_hi[2], dk_lo[2];
+      for (int i = 0; i < 2; ++i) { dk_hi[i] = desc_mn(smem_u32(kbuf[i]), 64); dk_lo[i] = desc_mn(smem_u32(kbuf[i] + kHalfTile), 64); }
       bool ok = mbar_wait(&bars[D_DOREADY], 0, abort_flag);
-      auto issue_dp = [&](int j) -> bool {
-        const int st = j & 1, u = j >> 1;
-        if (!mbar_wait(&bars[D_VCONV0 + st], (uint32_t)u & 1, abort_flag)) return false;
-        if (j > 0 && !mbar_wait(&bars[D_DPFREE], (uint32_t)(j - 1) & 1, abort_flag)) return false;
+      // dP of the 128-key block J (lane 0 alone: 128-wide instructions keep the tensor pipe busy by themselves)
+      auto issue_dp = [&](int J) -> bool {
+        if (!mbar_wait(&bars[D_VCONV], (uint32_t)J & 1, abort_flag)) return false;
+        if (J > 0 && !mbar_wait(&bars[D_DPFREE], (uint32_t)(J - 1) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t acc = lane ? t_dp2 : t_dp;
 #pragma unroll
-        for (int t2 = 0; t2 < 4; ++t2) {
-          const int t = 2 * t2 + lane;
-          const uint64_t off = (uint64_t)(((t >> 2) * (kHalfTile / 2) + (t & 3) * 32) >> 4);
-          mma_tf32_ta(acc, t_dolo + 8 * t, dv_hi[st] + off, idesc_dp, t2 > 0 ? 1u : 0u);
-          mma_tf32_ta(acc, t_dohi + 8 * t, dv_lo[st] + off, idesc_dp, 1u);
-          mma_tf32_ta(acc, t_dohi + 8 * t, dv_hi[st] + off, idesc_dp, 1u);
+        for (int t = 0; t < 8; ++t) {
+          const uint64_t off = (uint64_t)(((t >> 2) * kChunk + (t & 3) * 32) >> 4);
+          mma_tf32_ta(t_dp, t_dolo + 8 * t, dv_hi + off, idesc_dp128, t > 0 ? 1u : 0u);
+          mma_tf32_ta(t_dp, t_dohi + 8 * t, dv_lo + off, idesc_dp128, 1u);
+          mma_tf32_ta(t_dp, t_dohi + 8 * t, dv_hi + off, idesc_dp128, 1u);
         }
-        mma_commit(&bars[D_VFREE0 + st]);
+        mma_commit(&bars[D_VFREE]);
         mma_commit(&bars[D_DPFULL]);
         return true;
       };
-      if (ok) ok = issue_dp(0);
+      if (ok && lane == 0) ok = issue_dp(0);
       for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) { ok = issue_dp(j + 1); if (!ok) break; }          // the next block's dP runs under this block's row work
         const int st = j & 1, u = j >> 1;
-        ok = mbar_wait(&bars[D_DSREADY], (uint32_t)j & 1, abort_flag);
-        ok = ok && mbar_wait(&bars[D_KCONV0 + st], (uint32_t)u & 1, abort_flag);
+        // order on the pipe: dQ(J, first half), dP(J + 1), dQ(J, second half) -- the next block's V has landed by then and its
+        // dP runs while the row warps work on the second half
+        if (lane == 0 && (j & 1) == 1 && u + 1 < n_big) { ok = issue_dp(u + 1); if (!ok) break; }
+        ok = mbar_wait(&bars[D_DSREADY], (uint32_t)j & 1, abort_flag) && mbar_wait(&bars[D_KCONV0 + st], (uint32_t)u & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc = lane ? t_dq2 : t_dq;
@@ -512,23 +513,27 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int st = j & 1, u = j >> 1;
-      for (int which = 0; which < 2 && ok; ++which) {
-        uint8_t* buf = which ? kbuf[st] : vbuf[st];
-        ok = mbar_wait(&bars[(which ? D_KFULL0 : D_VFULL0) + st], (uint32_t)u & 1, abort_flag);
+      if ((j & 1) == 0) {
+        ok = mbar_wait(&bars[D_VFULL], (uint32_t)u & 1, abort_flag);
         if (!ok) break;
-        const float4* s = (const float4*)buf; float4* d = (float4*)(buf + kHalfTile);
-        float4 x[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = s[tid + i * 128];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float4 l;
-          l.x = tf32_lo_of_raw(x[i].x); l.y = tf32_lo_of_raw(x[i].y); l.z = tf32_lo_of_raw(x[i].z); l.w = tf32_lo_of_raw(x[i].w);
-          d[tid + i * 128] = l;
-        }
+        convert_tile(v_hi, v_lo, tid, 128);
         fence_async_smem(); __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[(which ? D_KCONV0 : D_VCONV0) + st]);
+        if (lane == 0) mbar_arrive(&bars[D_VCONV]);
       }
+      ok = mbar_wait(&bars[D_KFULL0 + st], (uint32_t)u & 1, abort_flag);
+      if (!ok) break;
+      const float4* s4 = (const float4*)kbuf[st]; float4* d4 = (float4*)(kbuf[st] + kHalfTile);
+      float4 x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = s4[tid + i * 128];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float4 l;
+        l.x = tf32_lo_of_raw(x[i].x); l.y = tf32_lo_of_raw(x[i].y); l.z = tf32_lo_of_raw(x[i].z); l.w = tf32_lo_of_raw(x[i].w);
+        d4[tid + i * 128] = l;
+      }
+      fence_async_smem(); __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[D_KCONV0 + st]);
     }
   } else {
     // ---- row warps -------------------------------------------------------------------------------------------------------
@@ -598,18 +603,18 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
       float pv[32];
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) { const float4 x = buf[lane * 8 + (j4 ^ (lane & 7))]; pv[4 * j4] = x.x; pv[4 * j4 + 1] = x.y; pv[4 * j4 + 2] = x.z; pv[4 * j4 + 3] = x.w; }
-      ok = mbar_wait(&bars[D_DPFULL], (uint32_t)j & 1, abort_flag);
-      if (!ok) break;
+      // dP holds 128 keys: this warp's 32 columns of sub-block j & 1; the accumulator is released after the second sub-block's read
+      if ((j & 1) == 0) { ok = mbar_wait(&bars[D_DPFULL], (uint32_t)(j >> 1) & 1, abort_flag); if (!ok) break; }
       tc_fence_after();
-      uint32_t v2[32];
-      tmem_ld32(t_dp + lane_off + (uint32_t)(half * 32), v);
-      tmem_ld32(t_dp2 + lane_off + (uint32_t)(half * 32), v2);
+      tmem_ld32(t_dp + lane_off + (uint32_t)((j & 1) * 64 + half * 32), v);
       tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[D_DPFREE]);
+      if (j & 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[D_DPFREE]);
+      }
 #pragma unroll
-      for (int c = 0; c < 32; ++c) pv[c] = (pv[c] * ((__uint_as_float(v[c]) + __uint_as_float(v2[c])) - delta)) * p.scale;
+      for (int c = 0; c < 32; ++c) pv[c] = (pv[c] * (__uint_as_float(v[c]) - delta)) * p.scale;
       if (j > 0) { ok = mbar_wait(&bars[D_DQDONE], (uint32_t)(j - 1) & 1, abort_flag); if (!ok) break; tc_fence_after(); }
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(pv[c]) & 0xffffe000u;
@@ -627,8 +632,10 @@ k_attn_bwd_dq(const __grid_constant__ CUtensorMap map_v, const __grid_constant__
       fence_async_smem();
       __syncwarp();
       if (lane == 0) {
-        tma_store_3d(&map_ds, buf, j * 64 + half * 32, qt * 128 + quarter * 32, bh);
-        tma_store_wait_read1();          // the store before this one has left its buffer: that buffer takes the P block two ahead
+        if (j * 64 + half * 32 < p.S) {
+          tma_store_3d(&map_ds, buf, j * 64 + half * 32, qt * 128 + quarter * 32, bh);
+          tma_store_wait_read1();        // the store before this one has left its buffer: that buffer takes the P block two ahead
+        } else tma_store_wait_read();    // (a sub-block past the last key: nothing to store)
       }
       __syncwarp();
       prefetch_p(j + 2);
@@ -757,8 +764,8 @@ int launch_attn_fwd_fused(const AttnOperand& q, const AttnOperand& k, const Attn
 int launch_attn_bwd_dq_fused(const AttnOperand& k, const AttnOperand& v, const AttnOperand& gout, const float* saved, float* ds,
                              float* dq, i64 dq_ss, i64 dq_sb, i64 B, i64 H, i64 S, bool causal, float scale) {
   CUtensorMap mv, mk, mds, mdq;
-  VB_TRY(head_map(&mv, v.p, S, H, B, v.ss, v.sh, v.sb, 64, CU_TENSOR_MAP_SWIZZLE_128B));
-  VB_TRY(head_map(&mk, k.p, S, H, B, k.ss, k.sh, k.sb, 64, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));
+  VB_TRY(head_map(&mv, v.p, S, H, B, v.ss, v.sh, v.sb, 128, CU_TENSOR_MAP_SWIZZLE_128B));              // 128-key tiles (dP)
+  VB_TRY(head_map(&mk, k.p, S, H, B, k.ss, k.sh, k.sb, 64, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B));      // 64-key blocks (dQ)
   VB_TRY(square_map(&mds, ds, S, B * H, 32));
   VB_TRY(head_map(&mdq, dq, S, H, B, dq_ss, 64, dq_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B));
   AttnBwdParams p{};
