@@ -8,6 +8,8 @@
   python kernel_cases.py gemm_pv       96 heads: P[1024,1024] . V[1024,64]  (64-wide tiles, 32-wide k-blocks)
   python kernel_cases.py attention     causal attention forward + backward, packed qkv [8,1024,2304], 12 heads
   python kernel_cases.py attention_fwd  the same forward alone, nothing kept for a backward pass (no probabilities written)
+  python kernel_cases.py conv_bwd       conv 3x3 (64 -> 128 channels) on [256,64,16,16], forward + backward: implicit GEMMs over the padded NHWC copy
+  python kernel_cases.py bn_bwd         fused BatchNorm -> ReLU -> MaxPool on [256,128,16,16], forward + backward
   python kernel_cases.py colsum        bias gradients: column sums of [8192,768] and [8192,3072]
   python kernel_cases.py layernorm_bwd rows 8192, C 768
   python kernel_cases.py ce_bwd        rows 2048, V 50304
@@ -63,6 +65,23 @@ def build(case):
         qkv = T(f(8, 1024, 2304))
         mask = T(np.triu(np.full((1024, 1024), -1e9, np.float32), 1))
         return lambda: qkv.fused_attention_packed(12, mask)
+    if case == "conv_bwd":
+        x, w, b = T(f(256, 64, 16, 16), True), T(f(128, 64, 3, 3), True), T(f(128), True)
+        go = T(f(256, 128, 16, 16))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            x.conv2d(w, b, 1, 1).mul(go).sum(3, False).sum(2, False).sum(1, False).sum(0, False).backward()
+        return run
+    if case == "bn_bwd":
+        x, g, b = T(f(256, 128, 16, 16), True), T(f(128) + 1.0, True), T(f(128), True)
+        rm, rv = T(np.zeros(128, np.float32)), T(np.ones(128, np.float32))
+        go = T(f(256, 128, 8, 8))
+
+        def run():
+            vb.zero_gradients(); vb.reset_active_tape()
+            x.bn_relu_maxpool(g, b, rm, rv, True, 0.1, 1e-5).mul(go).sum(3, False).sum(2, False).sum(1, False).sum(0, False).backward()
+        return run
     if case == "colsum":
         a, b = T(f(8192, 768)), T(f(8192, 3072))
         ba, bb = T(f(768), True), T(f(3072), True)
