@@ -234,6 +234,14 @@ __device__ __forceinline__ float tanh_fast(float y) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(y * 2.8853900817779268f));      // e^(2y) = 2^(2y log2 e)
   return 1.0f - __fdividef(2.0f, 1.0f + e);
 }
+// e^x for x <= 0 (softmax numerators) on the special-function unit: 2^(x log2 e).  The product is rounded once (6e-8 relative of
+// the argument, i.e. an absolute 1.2e-6 in the exponent at x = -20) and 2^y is good to 2^-22: results within about 1.5e-6
+// relative of expf over the range that matters, two orders inside the parity bar; -inf gives 0, underflow flushes to 0.
+__device__ __forceinline__ float exp_neg_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
 // GELU, tanh form, with the reference's constants (crates/vearo-backend-cpu/src/lib.rs:458-497)
 __device__ __forceinline__ float gelu_value(float v) {
   const float v3 = v * v * v;

@@ -200,12 +200,12 @@ int launch_embedding_backward(const float* ids, const float* g, float* gw, i64 n
 // ---- cross-entropy ---------------------------------------------------------------------------
 // Online (max, sum): folding a value or another pair keeps sum = sum exp(x - max).
 __device__ __forceinline__ void online_add(float& m, float& s, float x) {
-  if (x > m) { s = s * expf(m - x) + 1.0f; m = x; }
-  else s += expf(x - m);
+  if (x > m) { s = s * exp_neg_fast(m - x) + 1.0f; m = x; }
+  else s += exp_neg_fast(x - m);
 }
 __device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
-  if (m2 > m) { s = s * expf(m - m2) + s2; m = m2; }
-  else if (m2 != -INFINITY) s += s2 * expf(m2 - m);
+  if (m2 > m) { s = s * exp_neg_fast(m - m2) + s2; m = m2; }
+  else if (m2 != -INFINITY) s += s2 * exp_neg_fast(m2 - m);
 }
 __device__ void row_max_sum(const float* __restrict__ row, i64 v, float& m_out, float& s_out, float* red) {
   float m = -INFINITY, s = 0.0f;
@@ -214,7 +214,7 @@ __device__ void row_max_sum(const float* __restrict__ row, i64 v, float& m_out, 
     for (i64 i = threadIdx.x; i < v / 4; i += blockDim.x) {
       float4 x = r4[i];
       float lm = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
-      float ls = expf(x.x - lm) + expf(x.y - lm) + expf(x.z - lm) + expf(x.w - lm);
+      float ls = exp_neg_fast(x.x - lm) + exp_neg_fast(x.y - lm) + exp_neg_fast(x.z - lm) + exp_neg_fast(x.w - lm);
       online_merge(m, s, lm, ls);
     }
   } else for (i64 i = threadIdx.x; i < v; i += blockDim.x) online_add(m, s, row[i]);
@@ -295,14 +295,14 @@ __global__ void k_ce_backward(const float* __restrict__ logits, const float* __r
     for (i64 i = threadIdx.x; i < v / 4; i += blockDim.x) {
       float4 x = r4[i], o;
       i64 c = i * 4;
-      o.x = g * (expf(x.x - m) / s - (c == cls ? 1.0f : 0.0f)) / fb;
-      o.y = g * (expf(x.y - m) / s - (c + 1 == cls ? 1.0f : 0.0f)) / fb;
-      o.z = g * (expf(x.z - m) / s - (c + 2 == cls ? 1.0f : 0.0f)) / fb;
-      o.w = g * (expf(x.w - m) / s - (c + 3 == cls ? 1.0f : 0.0f)) / fb;
+      o.x = g * (exp_neg_fast(x.x - m) / s - (c == cls ? 1.0f : 0.0f)) / fb;
+      o.y = g * (exp_neg_fast(x.y - m) / s - (c + 1 == cls ? 1.0f : 0.0f)) / fb;
+      o.z = g * (exp_neg_fast(x.z - m) / s - (c + 2 == cls ? 1.0f : 0.0f)) / fb;
+      o.w = g * (exp_neg_fast(x.w - m) / s - (c + 3 == cls ? 1.0f : 0.0f)) / fb;
       o4[i] = o;
     }
   } else {
-    for (i64 c = threadIdx.x; c < v; c += blockDim.x) orow[c] = g * (expf(row[c] - m) / s - (c == cls ? 1.0f : 0.0f)) / fb;
+    for (i64 c = threadIdx.x; c < v; c += blockDim.x) orow[c] = g * (exp_neg_fast(row[c] - m) / s - (c == cls ? 1.0f : 0.0f)) / fb;
   }
 }
 // Forward and backward in one pass over the logits, in place: the row's (max, sum) pass is followed, while the row is still in
@@ -332,13 +332,13 @@ __global__ void k_ce_fused(float* __restrict__ logits, const float* __restrict__
     for (i64 i = threadIdx.x; i < v / 4; i += blockDim.x) {
       const float4 x = r4[i];
       float4 o;
-      o.x = expf(x.x - m) * inv_s; o.y = expf(x.y - m) * inv_s; o.z = expf(x.z - m) * inv_s; o.w = expf(x.w - m) * inv_s;
+      o.x = exp_neg_fast(x.x - m) * inv_s; o.y = exp_neg_fast(x.y - m) * inv_s; o.z = exp_neg_fast(x.z - m) * inv_s; o.w = exp_neg_fast(x.w - m) * inv_s;
       if (i == cq) reinterpret_cast<float*>(&o)[cls & 3] -= 1.0f;
       o.x *= inv_fb; o.y *= inv_fb; o.z *= inv_fb; o.w *= inv_fb;
       r4[i] = o;
     }
   } else {
-    for (i64 c = threadIdx.x; c < v; c += blockDim.x) row[c] = (expf(row[c] - m) * inv_s - (c == cls ? 1.0f : 0.0f)) * inv_fb;
+    for (i64 c = threadIdx.x; c < v; c += blockDim.x) row[c] = (exp_neg_fast(row[c] - m) * inv_s - (c == cls ? 1.0f : 0.0f)) * inv_fb;
   }
 }
 int launch_cross_entropy_fused(float* logits, const float* targets, float* loss, i64 rows, i64 v) {
