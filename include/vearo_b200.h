@@ -210,13 +210,22 @@ int vb_linear_backward(const vb_tensor* x, const vb_tensor* weight, const vb_ten
                        vb_tensor* gx, vb_tensor* gw, vb_tensor* gb);
 /* The same with the weight and bias gradients written into existing tensors (NULL: not wanted) -- a parameter's slice of a flat
  * gradient buffer -- so that no copy follows the GEMM.  No reference counterpart (the reference allocates every gradient). */
+int vb_linear_backward_into(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* grad_out, vb_tensor* gx_or_null,
+                            const vb_tensor* gw_into_or_null, const vb_tensor* gb_into_or_null);
 /* vb_linear followed by GELU (TransformerBlock::forward's fc1 -> gelu, crates/vearo-nn/src/lib.rs:666-675) with both results
  * returned: `pre` = x.W^T + b, which the GELU backward arm needs, and `act` = gelu(pre).  Where the tensor-core kernel takes the
  * product as whole tiles the activation is formed in its epilogue from the values being stored; the results equal
  * vb_linear + vb_gelu bit for bit either way. */
 int vb_linear_gelu(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* bias_or_null, vb_tensor* pre, vb_tensor* act);
-int vb_linear_backward_into(const vb_tensor* x, const vb_tensor* weight, const vb_tensor* grad_out, vb_tensor* gx_or_null,
-                            const vb_tensor* gw_into_or_null, const vb_tensor* gb_into_or_null);
+/* vb_layernorm_backward with the input gradient added to an existing gradient of x in place (grad_in += dx; grad_in contiguous,
+ * of x's shape): the accumulation the reference's gradient map does when x has a second consumer, e.g. a residual connection
+ * (vearo-autograd/src/lib.rs:733-741), without writing dx out and reading it back. */
+int vb_layernorm_backward_accum(const vb_tensor* x, const vb_tensor* w, const vb_tensor* b, const vb_tensor* grad_out, float eps,
+                                const vb_tensor* grad_in, vb_tensor* gw, vb_tensor* gb);
+/* Bias gradients.  vb_gelu_backward / vb_relu_backward, vb_layernorm_backward and vb_layernorm_backward_accum leave the column
+ * sums of the (large, rank >= 2) gradient they write beside it; vb_linear_backward[_into], given that same tensor unchanged as
+ * grad_out, copies them as gb instead of summing the columns again.  The sums are dropped as soon as the tensor is written to
+ * through this library or released.  VB200_COLSUM_REUSE=0 in the environment switches this off. */
 
 /* ---- optimizer ---------------------------------------------------------------------------
  * Single-tensor steps replace the CUDA branches of Tensor::adamw_step / sgd_step

@@ -11,6 +11,7 @@
   python kernel_cases.py conv_bwd       conv 3x3 (64 -> 128 channels) on [256,64,16,16], forward + backward: implicit GEMMs over the padded NHWC copy
   python kernel_cases.py bn_bwd         fused BatchNorm -> ReLU -> MaxPool on [256,128,16,16], forward + backward
   python kernel_cases.py colsum        bias gradients: column sums of [8192,768] and [8192,3072]
+  python kernel_cases.py gelu_bwd      GELU backward over [8192,3072], with the column sums of the result
   python kernel_cases.py layernorm_bwd rows 8192, C 768
   python kernel_cases.py ce_bwd        rows 2048, V 50304
   python kernel_cases.py ce_fused      rows 2048, V 50304: loss and gradient in one in-place pass
@@ -91,6 +92,13 @@ def build(case):
             a.add(ba).sum(1, False).sum(0, False).backward()
             vb.zero_gradients(); vb.reset_active_tape()
             b.add(bb).sum(1, False).sum(0, False).backward()
+        return run
+    if case == "gelu_bwd":
+        x, g = T(f(8192, 3072), True), T(f(8192, 3072))
+
+        def run():      # the backward kernel also leaves the column sums of its result (the bias gradient of the layer before)
+            vb.zero_gradients(); vb.reset_active_tape()
+            x.gelu().mul(g).sum(1, False).sum(0, False).backward()
         return run
     if case == "layernorm_bwd":
         x, w, b, g = T(f(8192, 768), True), T(f(768), True), T(f(768), True), T(f(8192, 768))

@@ -105,6 +105,7 @@ unsafe extern "C" {
     pub fn vb_linear(x: T, weight: T, bias_or_null: T, out: O) -> c_int;
     pub fn vb_linear_backward(x: T, weight: T, grad_out: T, gx: O, gw: O, gb: O) -> c_int;
     pub fn vb_linear_gelu(x: T, weight: T, bias_or_null: T, pre: O, act: O) -> c_int;
+    pub fn vb_layernorm_backward_accum(x: T, w: T, b: T, grad_out: T, eps: f32, grad_in: T, gw: O, gb: O) -> c_int;
     pub fn vb_linear_backward_into(x: T, weight: T, grad_out: T, gx_or_null: O, gw_into_or_null: T, gb_into_or_null: T) -> c_int;
     // optimizer
     pub fn vb_adamw_step(param: T, grad: T, m: vb_slot, v: vb_slot, t: u32, lr: f32, beta1: f32, beta2: f32, eps: f32, weight_decay: f32) -> c_int;

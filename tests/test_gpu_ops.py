@@ -784,3 +784,79 @@ def test_linear_tensor_core_with_bias_and_backward(vb):
     for g, c, n in zip(run(vb.Tensor, True), cpu, "y gx gw gb".split()):
         assert_close(g, c, "linear(tc) " + n)
     vb.check_errors()
+
+
+# ---- bias gradients from the producer's column sums; LayerNorm backward that adds into an existing gradient --------------------
+def _raw_out(vb, t):
+    a = np.empty(t.shape, np.float32)
+    vb.vb_check(vb.lib().vb_read(t.slot, 0, a.ctypes.data_as(vb.c_f32p), a.size))
+    return a
+
+
+@pytest.mark.parametrize("rows,c", [(2048, 768), (1536, 1024), (1100, 200), (64, 96), (33, 50)])
+def test_layernorm_backward_accum_matches_oracle(vb, rows, c):
+    """grad_in += dx in the kernel that forms dx (vearo-autograd/src/lib.rs:733-741 does the addition on the gradient map):
+    against the oracle's LayerNorm backward plus the existing gradient, for the register kernel (with and without masked
+    columns), for short inputs and for a row length the generic route takes."""
+    import ctypes as C
+    x0, w0, b0, go, acc0 = rnd(501, rows, c) * 1.5 + 0.3, rnd(502, c), rnd(503, c), rnd(504, rows, c, scale=0.05), rnd(505, rows, c, scale=0.05)
+    # (gradients of size 0.05: dgamma / dbeta are sums over up to 2048 rows, and the absolute part of the bar is 1e-5)
+    orc.reset_all()
+    xr, wr, br = orc.Tensor.from_numpy(x0, True), orc.Tensor.from_numpy(w0, True), orc.Tensor.from_numpy(b0, True)
+    n = x0.size
+    xr.layernorm(wr, br, 1e-5).mul(orc.Tensor.from_numpy(go)).reshape([1, n]).matmul(orc.Tensor.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+    want_x, want_w, want_b = xr.grad().numpy() + acc0, wr.grad().numpy(), br.grad().numpy()
+    T = vb.Tensor
+    x, w, b, g, acc = (T.from_numpy(a) for a in (x0, w0, b0, go, acc0))
+    gw, gb = vb.VbTensor(), vb.VbTensor()
+    L = vb.lib()
+    xd, wd, bd, gd, ad = x.desc(), w.desc(), b.desc(), g.desc(), acc.desc()
+    vb.vb_check(L.vb_layernorm_backward_accum(C.byref(xd), C.byref(wd), C.byref(bd), C.byref(gd), 1e-5, C.byref(ad), C.byref(gw), C.byref(gb)),
+                "vb_layernorm_backward_accum")
+    assert_close(acc.numpy(), want_x, "grad_in + dx")
+    assert_close(_raw_out(vb, gw), want_w, "dgamma"); assert_close(_raw_out(vb, gb), want_b, "dbeta")
+    # the accumulated gradient as the output gradient of a Linear layer: its bias gradient is the column sum of what is there NOW
+    xin, wl = T.from_numpy(rnd(506, rows, 32)), T.from_numpy(rnd(507, c, 32, scale=0.1))
+    for step in range(2):
+        gbias = vb.VbTensor()
+        xi, wi = xin.desc(), wl.desc()
+        vb.vb_check(L.vb_linear_backward(C.byref(xi), C.byref(wi), C.byref(ad), None, None, C.byref(gbias)), "vb_linear_backward")
+        now = acc.numpy()
+        assert_close(_raw_out(vb, gbias), now.astype(np.float64).sum(0).astype(np.float32), "bias gradient, pass %d" % step, atol=1e-4 * np.sqrt(rows))
+        vb.vb_check(L.vb_release(gbias.slot, None))
+        if step == 0:       # an in-place writer voids the kept sums
+            extra = T.from_numpy(rnd(508, rows, c)); ed = extra.desc()
+            vb.vb_check(L.vb_accumulate(C.byref(ad), C.byref(ed)), "vb_accumulate")
+    for t in (gw, gb):
+        vb.vb_check(L.vb_release(t.slot, None))
+    vb.check_errors()
+
+
+@pytest.mark.parametrize("rows,c", [(2048, 3072), (1024, 132), (300, 256)])
+def test_activation_backward_leaves_the_bias_gradient(vb, rows, c):
+    """GELU / ReLU backward over a large [rows, c] gradient also sums its columns; Linear backward given that tensor as grad_out
+    takes the sums as its bias gradient.  Values against the oracle (dx) and against an f64 column sum of the dx actually
+    produced; VB200_COLSUM_REUSE=0 is the same computation through the separate column-sum kernel (small case: never summed)."""
+    import ctypes as C
+    x0, go = rnd(511, rows, c), rnd(512, rows, c, scale=0.1)
+    T = vb.Tensor
+    L = vb.lib()
+    for op, fwd in (("gelu", "gelu"), ("relu", "relu")):
+        orc.reset_all()
+        xr = orc.Tensor.from_numpy(x0, True)
+        n = x0.size
+        getattr(xr, fwd)().mul(orc.Tensor.from_numpy(go)).reshape([1, n]).matmul(orc.Tensor.from_numpy(np.ones((n, 1), np.float32))).reshape([1]).backward()
+        want = xr.grad().numpy()
+        x, g = T.from_numpy(x0), T.from_numpy(go)
+        gx, gbias = vb.VbTensor(), vb.VbTensor()
+        xd, gd = x.desc(), g.desc()
+        vb.vb_check(getattr(L, "vb_%s_backward" % op)(C.byref(xd), C.byref(gd), C.byref(gx)), op)
+        got = _raw_out(vb, gx)
+        assert_close(got, want, op + " backward")
+        xin, wl = T.from_numpy(rnd(513, rows, 16)), T.from_numpy(rnd(514, c, 16, scale=0.1))
+        xi, wi = xin.desc(), wl.desc()
+        vb.vb_check(L.vb_linear_backward(C.byref(xi), C.byref(wi), C.byref(gx), None, None, C.byref(gbias)), "vb_linear_backward")
+        assert_close(_raw_out(vb, gbias), got.astype(np.float64).sum(0).astype(np.float32), op + " bias gradient", atol=1e-4 * np.sqrt(rows))
+        for t in (gx, gbias):
+            vb.vb_check(L.vb_release(t.slot, None))
+    vb.check_errors()

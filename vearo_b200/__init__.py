@@ -93,6 +93,7 @@ def lib():
         L.vb_fill.argtypes = [C.POINTER(VbTensor), C.c_float]
         L.vb_layernorm.argtypes = [C.POINTER(VbTensor)] * 3 + [C.c_float, C.POINTER(VbTensor)]
         L.vb_layernorm_backward.argtypes = [C.POINTER(VbTensor)] * 4 + [C.c_float] + [C.POINTER(VbTensor)] * 3
+        L.vb_layernorm_backward_accum.argtypes = [C.POINTER(VbTensor)] * 4 + [C.c_float] + [C.POINTER(VbTensor)] * 3
         L.vb_adamw_step.argtypes = [C.POINTER(VbTensor), C.POINTER(VbTensor), C.c_uint32, C.c_uint32, C.c_uint32] + [C.c_float] * 5
         L.vb_sgd_step.argtypes = [C.POINTER(VbTensor), C.POINTER(VbTensor), C.c_uint32] + [C.c_float] * 3
         L.vb_clip_grad_norm.argtypes = [C.POINTER(VbTensor), C.c_int, C.c_float, c_f32p]

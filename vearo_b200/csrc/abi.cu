@@ -177,8 +177,28 @@ int vb_div(const vb_tensor* a, const vb_tensor* b, vb_tensor* out) { return bina
 int vb_matmul(const vb_tensor* a, const vb_tensor* b, vb_tensor* out) { return matmul_impl(a, b, out, 1.0f, nullptr); }
 int vb_relu(const vb_tensor* x, vb_tensor* out) { return unary(0, x, out); }
 int vb_gelu(const vb_tensor* x, vb_tensor* out) { return unary(1, x, out); }
-int vb_relu_backward(const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) { return unary_backward(0, x, g, gx); }
-int vb_gelu_backward(const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) { return unary_backward(1, x, g, gx); }
+namespace { bool col_sums_enabled(); void col_sums_adopt(const vb_tensor* t, i64 rows, i64 cols, vb_slot sums); }     // defined with the table below
+// A large activation gradient is about to be the output gradient of a Linear layer: the kernel leaves its column sums (that
+// layer's bias gradient) beside it.
+static int unary_backward_summed(int op, const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) {
+  i64 rows = 0, cols = 0;
+  if (x->rank >= 2) { cols = x->dims[x->rank - 1]; rows = cols ? numel(*x) / cols : 0; }
+  if (!col_sums_enabled() || rows < 1024 || cols < 128 || cols > 4096 || (cols & 3) || !is_contiguous(*x) || !is_contiguous(*g)) return unary_backward(op, x, g, gx);
+  VB_CHECK(same_shape(*x, *g), "x and grad_out shapes differ");
+  float *px, *pg; VB_TRY(tensor_ptr(x, &px)); VB_TRY(tensor_ptr(g, &pg));
+  if (((reinterpret_cast<uintptr_t>(px) | reinterpret_cast<uintptr_t>(pg)) & 15) != 0) return unary_backward(op, x, g, gx);
+  vb_slot sums = 0;
+  if (slot_alloc(cols, false, &sums) != VB_OK) return unary_backward(op, x, g, gx);
+  float* ps = nullptr; slot_ptr(sums, &ps);
+  int rc = new_output(gx, x->rank, x->dims);
+  float* po = nullptr;
+  if (rc == VB_OK) rc = slot_ptr(gx->slot, &po);
+  if (rc == VB_OK) rc = launch_unary_backward_colsum(op, px, pg, po, rows, cols, ps);
+  if (rc == VB_OK) col_sums_adopt(gx, rows, cols, sums); else slot_release(sums, nullptr);
+  return rc;
+}
+int vb_relu_backward(const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) { return unary_backward_summed(0, x, g, gx); }
+int vb_gelu_backward(const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) { return unary_backward_summed(1, x, g, gx); }
 int vb_sum(const vb_tensor* x, int dim, int keep, vb_tensor* out) { return reduce_axis(x, dim, keep, false, out); }
 int vb_mean(const vb_tensor* x, int dim, int keep, vb_tensor* out) { return reduce_axis(x, dim, keep, true, out); }
 
@@ -239,7 +259,36 @@ int vb_layernorm_backward(const vb_tensor* x, const vb_tensor* w, const vb_tenso
   VB_TRY(new_output(gw, 1, &c)); VB_TRY(new_output(gb, 1, &c));
   float *pgx, *pgw, *pgb;
   VB_TRY(slot_ptr(gx->slot, &pgx)); VB_TRY(slot_ptr(gw->slot, &pgw)); VB_TRY(slot_ptr(gb->slot, &pgb));
-  return launch_layernorm_backward(px, pw, pg, pgx, pgw, pgb, rows, c, eps);
+  // the input gradient of a residual stream is usually the output gradient of the Linear layer before it: keep its column sums
+  vb_slot sums = 0; float* ps = nullptr;
+  if (col_sums_enabled() && rows >= 1024 && x->rank >= 2 && slot_alloc(c, false, &sums) == VB_OK) slot_ptr(sums, &ps);
+  bool summed = false;
+  int rc = launch_layernorm_backward(px, pw, pg, pgx, pgw, pgb, rows, c, eps, nullptr, ps, &summed);
+  if (sums) { if (rc == VB_OK && summed) col_sums_adopt(gx, rows, c, sums); else slot_release(sums, nullptr); }
+  return rc;
+}
+// The same, added to an existing gradient of x in place: grad_in += dx (one pass instead of a fresh dx and an accumulate).
+int vb_layernorm_backward_accum(const vb_tensor* x, const vb_tensor* w, const vb_tensor* b, const vb_tensor* g, float eps,
+                                const vb_tensor* grad_in, vb_tensor* gw, vb_tensor* gb) {
+  VB_CHECK(x->rank >= 1, "LayerNorm input must be at least rank 1");
+  i64 rows, c; VB_TRY(rows_of(x, &rows, &c));
+  VB_CHECK(w->rank == 1 && b->rank == 1 && w->dims[0] == c && b->dims[0] == c, "Weight/Bias dimension must match norm_dim");
+  VB_CHECK(same_shape(*x, *g), "x and grad_out shapes differ");
+  VB_CHECK(grad_in && same_shape(*x, *grad_in) && is_contiguous(*grad_in), "grad_in must be a contiguous tensor of x's shape");
+  Temp hx, hw, hg; const float *px, *pw, *pg;
+  VB_TRY(contiguous_ptr(x, &px, hx)); VB_TRY(contiguous_ptr(w, &pw, hw)); VB_TRY(contiguous_ptr(g, &pg, hg));
+  float* pacc; VB_TRY(tensor_ptr(grad_in, &pacc));
+  VB_TRY(new_output(gw, 1, &c)); VB_TRY(new_output(gb, 1, &c));
+  float *pgw, *pgb;
+  VB_TRY(slot_ptr(gw->slot, &pgw)); VB_TRY(slot_ptr(gb->slot, &pgb));
+  slot_touch(grad_in->slot);
+  if (rows == 0) return launch_layernorm_backward(px, pw, pg, pacc, pgw, pgb, rows, c, eps);
+  vb_slot sums = 0; float* ps = nullptr;
+  if (col_sums_enabled() && rows >= 1024 && x->rank >= 2 && slot_alloc(c, false, &sums) == VB_OK) slot_ptr(sums, &ps);
+  bool summed = false;
+  int rc = launch_layernorm_backward(px, pw, pg, pacc, pgw, pgb, rows, c, eps, pacc, ps, &summed);
+  if (sums) { if (rc == VB_OK && summed) col_sums_adopt(grad_in, rows, c, sums); else slot_release(sums, nullptr); }
+  return rc;
 }
 
 int vb_embedding(const vb_tensor* ids, const vb_tensor* weight, vb_tensor* out) {
@@ -774,6 +823,37 @@ int vb_fill(const vb_tensor* dst, float value) {
 // vb_linear_backward_into -- advances it).  One plane covers the whole slot, so
 // parameters that are views of one block share it.  Returns null where the plane does not pay or cannot be had.
 namespace {
+// Column sums of a [rows, cols] gradient, left by the kernel that produced it (an activation's backward, LayerNorm backward):
+// the bias gradient of the Linear layer whose output gradient that tensor is.  Keyed by the tensor's slot, valid for exactly
+// the view that was summed and while the slot's serial is unchanged -- the same rule as for the lo planes below.
+struct ColSums { vb_slot sums = 0; uint64_t serial = 0; i64 offset = 0, rows = 0, cols = 0; };
+std::unordered_map<vb_slot, ColSums>& col_sums() { static auto* m = new std::unordered_map<vb_slot, ColSums>(); return *m; }
+bool col_sums_enabled() {
+  static const bool on = [] { const char* e = getenv("VB200_COLSUM_REUSE"); return !(e && e[0] == '0'); }();
+  return on;
+}
+// `sums` (a slot of its own holding cols floats) now describes the contiguous view t = [rows, cols] as it stands
+void col_sums_adopt(const vb_tensor* t, i64 rows, i64 cols, vb_slot sums) {
+  auto& tab = col_sums();
+  if (tab.size() > 64) {        // forget sums of slots that have been handed out again or rewritten since
+    for (auto it = tab.begin(); it != tab.end();) {
+      if (slot_serial(it->first) != it->second.serial) { slot_release(it->second.sums, nullptr); it = tab.erase(it); } else ++it;
+    }
+  }
+  ColSums& e = tab[t->slot];
+  if (e.sums) slot_release(e.sums, nullptr);
+  e.sums = sums; e.serial = slot_serial(t->slot); e.offset = t->offset; e.rows = rows; e.cols = cols;
+}
+const float* col_sums_of(const vb_tensor* t, i64 rows, i64 cols) {
+  if (!col_sums_enabled()) return nullptr;
+  auto& tab = col_sums();
+  auto it = tab.find(t->slot);
+  if (it == tab.end()) return nullptr;
+  const ColSums& e = it->second;
+  if (e.sums == 0 || e.serial != slot_serial(t->slot) || e.offset != t->offset || e.rows != rows || e.cols != cols || !is_contiguous(*t)) return nullptr;
+  float* p;
+  return slot_ptr(e.sums, &p) == VB_OK ? p : nullptr;
+}
 struct LoPlane { vb_slot lo = 0; uint64_t serial = 0; i64 numel = 0; };
 std::unordered_map<vb_slot, LoPlane>& lo_planes() { static auto* m = new std::unordered_map<vb_slot, LoPlane>(); return *m; }
 bool activation_lo_enabled() {
@@ -826,8 +906,13 @@ const float* weight_lo_plane(const vb_tensor* w, const float* pw) {
 }  // namespace
 extern "C++" {
 namespace vb {
-void lo_planes_forget_all() { lo_planes().clear(); }
+void lo_planes_forget_all() { lo_planes().clear(); col_sums().clear(); }
 void lo_plane_on_release(vb_slot slot) {
+  auto& cs = col_sums();
+  if (!cs.empty()) {
+    auto ic = cs.find(slot);
+    if (ic != cs.end()) { vb_slot sums = ic->second.sums; cs.erase(ic); if (sums) slot_release(sums, nullptr); }
+  }
   auto& tab = lo_planes();
   if (tab.empty()) return;
   auto it = tab.find(slot);
@@ -940,7 +1025,9 @@ static int linear_backward_impl(const vb_tensor* x, const vb_tensor* weight, con
     float* p;
     if (gb_into) { VB_TRY(tensor_ptr(gb_into, &p)); slot_touch(gb_into->slot); }
     else { VB_TRY(new_output(gb, 1, &outf, true)); VB_TRY(slot_ptr(gb->slot, &p)); }
-    if (rows > 0) VB_TRY(launch_colsum(pg, p, rows, outf, false));
+    const float* known = (rows > 0 && !hg.p) ? col_sums_of(gout, rows, outf) : nullptr;      // its producer summed the columns already
+    if (known) VB_CUDA(cudaMemcpyAsync(p, known, (size_t)outf * sizeof(float), cudaMemcpyDeviceToDevice, ctx().stream));
+    else if (rows > 0) VB_TRY(launch_colsum(pg, p, rows, outf, false));
     else if (gb_into) VB_TRY(launch_fill(p, 0.0f, outf));
   }
   return VB_OK;

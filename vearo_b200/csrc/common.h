@@ -91,6 +91,8 @@ int launch_binary_scalar(int op, const float* a, const float* b, float* out, i64
 int launch_binary_strided(int op, const float* a, const float* b, float* out, i64 n, const Strided& s);
 int launch_unary(int op, const float* x, float* out, i64 n);          // 0 relu 1 gelu
 int launch_unary_backward(int op, const float* x, const float* g, float* out, i64 n);  // 0 relu 1 gelu
+// the same over [rows, cols] (cols a multiple of 4, 16-byte aligned pointers), also leaving colsum[c] = sum_r out[r, c]
+int launch_unary_backward_colsum(int op, const float* x, const float* g, float* out, i64 rows, i64 cols, float* colsum);
 int launch_scale(const float* x, float alpha, float* out, i64 n);
 int launch_axpy(float* dst, const float* src, i64 n);                 // dst += src
 int launch_fill(float* dst, float v, i64 n);
@@ -98,6 +100,7 @@ int launch_strided_copy(const float* src, float* dst, i64 n, const Strided& s); 
 // reduce.cu
 int launch_sum_axis(const float* x, float* out, i64 outer, i64 d, i64 inner, bool mean);
 int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulate);   // out[c] (+)= sum_r x[r,c]
+int launch_colsum_final(const float* part, float* out, i64 cols, int splits);          // out[c] = sum_i part[i, c], in a fixed order
 int launch_reduce_general(const float* g, float* out, i64 out_numel, const Strided& kept, const Strided& red, i64 red_count);
 int launch_softmax_rows(const float* x, float* out, i64 rows, i64 d);
 int launch_softmax_strided(const float* x, float* out, i64 outer, i64 d, i64 inner);
@@ -105,7 +108,10 @@ int launch_softmax_backward_rows(const float* x, const float* g, float* out, i64
 int launch_softmax_backward_strided(const float* x, const float* g, float* out, i64 outer, i64 d, i64 inner);
 // norm.cu
 int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps, float* out_lo = nullptr, bool* lo_done = nullptr);
-int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps);
+// resid (optional): gx = resid + dx (gx may be resid itself).  out_colsum (optional, c floats): the column sums of what was stored in gx,
+// written only where the fast kernel ran (*colsum_done says so).
+int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps,
+                              const float* resid = nullptr, float* out_colsum = nullptr, bool* colsum_done = nullptr);
 int launch_batchnorm(const float* x, const float* gamma, const float* beta, float* rm, float* rv, float* out,
                      i64 n, i64 c, i64 hw, bool training, float momentum, float eps);
 int launch_batchnorm_backward(const float* x, const float* gamma, const float* rm, const float* rv, const float* g,
@@ -248,6 +254,30 @@ __device__ __forceinline__ float gelu_value(float v) {
   const float inner = 0.79788456f * (v + 0.044715f * v3);
   return 0.5f * v * (1.0f + tanh_fast(inner));
 }
+// Packed pairs of f32: one instruction drives two lanes of the FP32 pipe (PTX add/mul/fma .f32x2, sm_100).  Each lane rounds as
+// the scalar instruction does.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 lo2(const float4& a) { return make_float2(a.x, a.y); }
+__device__ __forceinline__ float2 hi2(const float4& a) { return make_float2(a.z, a.w); }
+__device__ __forceinline__ float4 cat2(float2 a, float2 b) { return make_float4(a.x, a.y, b.x, b.y); }
+
 // lo part of x when the tensor core takes the raw x as hi (it reads x cut to 10 mantissa bits): the remainder is exact in f32 and
 // is rounded to TF32 (nearest, ties away) with integer arithmetic on the bit pattern
 __device__ __forceinline__ float tf32_remainder(float x) {

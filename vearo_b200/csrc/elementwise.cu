@@ -179,6 +179,87 @@ int launch_unary_backward(int op, const float* x, const float* g, float* o, i64 
   return op == 0 ? unary_impl<0, true>(x, g, o, n) : unary_impl<1, true>(x, g, o, n);
 }
 
+// The backward of an activation that follows a Linear layer produces that layer's output gradient; the layer's bias gradient is
+// the column sum of it.  This variant walks [rows, cols] as bands of whole rows -- a CTA of 256 threads owns a contiguous band, a
+// thread the float4 columns t, t + 256, ... (cols <= 4096) with its column sums in registers, four rows in flight -- so that the
+// memory stream is as contiguous as the flat kernel's, and leaves one partial row of column sums per band beside the gradient:
+// the bias gradient then costs a small ordered sum instead of another pass over the tensor.
+template <int OP>
+__device__ __forceinline__ float4 unary_grad4(const float4& v, const float4& gg) {
+  float4 r;
+  if (OP == 0) { r.x = gg.x * (v.x > 0.0f ? 1.0f : 0.0f); r.y = gg.y * (v.y > 0.0f ? 1.0f : 0.0f); r.z = gg.z * (v.z > 0.0f ? 1.0f : 0.0f); r.w = gg.w * (v.w > 0.0f ? 1.0f : 0.0f); }
+  else { r.x = gg.x * gelu_grad_f(v.x); r.y = gg.y * gelu_grad_f(v.y); r.z = gg.z * gelu_grad_f(v.z); r.w = gg.w * gelu_grad_f(v.w); }
+  return r;
+}
+template <int OP, int K>
+__global__ void __launch_bounds__(256) k_unary_bwd_colsum(const float4* __restrict__ x, const float4* __restrict__ g, float4* __restrict__ o,
+                                                          float4* __restrict__ part, i64 rows, int cols4, i64 rows_per_band) {
+  const i64 r0 = (i64)blockIdx.x * rows_per_band;
+  i64 r1 = r0 + rows_per_band; if (r1 > rows) r1 = rows;
+  float2 sa[K], sb[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) { sa[k] = make_float2(0.0f, 0.0f); sb[k] = sa[k]; }
+  i64 r = r0;
+  for (; r + 1 < r1; r += 2) {         // two rows x K columns: 4K loads in flight per thread
+    float4 v0[K], v1[K], g0[K], g1[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = k * 256 + threadIdx.x;
+      if (c < cols4) { v0[k] = x[r * cols4 + c]; g0[k] = g[r * cols4 + c]; v1[k] = x[(r + 1) * cols4 + c]; g1[k] = g[(r + 1) * cols4 + c]; }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = k * 256 + threadIdx.x;
+      if (c < cols4) {
+        const float4 d0 = unary_grad4<OP>(v0[k], g0[k]), d1 = unary_grad4<OP>(v1[k], g1[k]);
+        o[r * cols4 + c] = d0; o[(r + 1) * cols4 + c] = d1;
+        sa[k] = add2(sa[k], lo2(d0)); sb[k] = add2(sb[k], hi2(d0));
+        sa[k] = add2(sa[k], lo2(d1)); sb[k] = add2(sb[k], hi2(d1));
+      }
+    }
+  }
+  if (r < r1) {
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = k * 256 + threadIdx.x;
+      if (c < cols4) {
+        const float4 d = unary_grad4<OP>(x[r * cols4 + c], g[r * cols4 + c]);
+        o[r * cols4 + c] = d;
+        sa[k] = add2(sa[k], lo2(d)); sb[k] = add2(sb[k], hi2(d));
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int c = k * 256 + threadIdx.x;
+    if (c < cols4) part[(i64)blockIdx.x * cols4 + c] = cat2(sa[k], sb[k]);
+  }
+}
+int launch_unary_backward_colsum(int op, const float* x, const float* g, float* o, i64 rows, i64 cols, float* colsum) {
+  if (rows <= 0 || cols <= 0) return VB_OK;
+  const int cols4 = (int)(cols / 4), k = (cols4 + 255) / 256;       // the caller keeps cols <= 4096
+  i64 bands = (i64)ctx().sm_count * (k == 4 ? 2 : 3);      /* one wave at the registers each instance takes */
+  if (bands > rows / 4) bands = rows / 4; if (bands < 1) bands = 1;
+  const i64 rpb = (rows + bands - 1) / bands;
+  bands = (rows + rpb - 1) / rpb;
+  void* part = nullptr;
+  VB_TRY(scratch_alloc((size_t)(bands * cols) * sizeof(float), &part));
+  int rc = VB_OK;
+  {
+    ProfScope prof(op == 0 ? "relu_bwd" : "gelu_bwd", 3.0 * (double)rows * (double)cols * 4.0);
+    cudaStream_t st = ctx().stream;
+#define UBC(OPV, KV) k_unary_bwd_colsum<OPV, KV><<<(unsigned)bands, 256, 0, st>>>((const float4*)x, (const float4*)g, (float4*)o, (float4*)part, rows, cols4, rpb)
+    if (op == 0) { switch (k) { case 1: UBC(0, 1); break; case 2: UBC(0, 2); break; case 3: UBC(0, 3); break; default: UBC(0, 4); break; } }
+    else { switch (k) { case 1: UBC(1, 1); break; case 2: UBC(1, 2); break; case 3: UBC(1, 3); break; default: UBC(1, 4); break; } }
+#undef UBC
+    rc = launch_colsum_final((const float*)part, colsum, cols, (int)bands);
+  }
+  scratch_free(part);
+  VB_TRY(rc);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
+
 __global__ void k_scale(const float* __restrict__ x, float alpha, float* __restrict__ o, i64 n) {
   for (i64 i = blockIdx.x * (i64)blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x) o[i] = x[i] * alpha;
 }

@@ -426,6 +426,13 @@ void run_backward(const Tensor& y, const Tensor& seed, const NestedInput& nested
       case Op::Softmax: { vb_tensor o; check(vb_softmax_backward(&sv[0].desc(), &go.desc(), (int)node.a0, &o), "softmax_backward"); gin = {Tensor::adopt(o)}; break; }
       case Op::LayerNorm: {
         vb_tensor gx, gw, gb;
+        // x already holds a gradient from another consumer (a residual connection) in storage nobody else reads: dx is added to it
+        // by the kernel that forms it, instead of being written out and accumulated afterwards
+        const int xid = node.inputs[0];
+        if (xid >= 0 && gm[xid].defined() && gm[xid].storage_unique() && gm[xid].is_contiguous() && gm[xid].shape() == sv[0].shape()) {
+          check(vb_layernorm_backward_accum(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), &go.desc(), node.f0, &gm[xid].desc(), &gw, &gb), "layernorm_backward");
+          gin = {Tensor(), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
+        }
         check(vb_layernorm_backward(&sv[0].desc(), &sv[1].desc(), &sv[2].desc(), &go.desc(), node.f0, &gx, &gw, &gb), "layernorm_backward");
         gin = {Tensor::adopt(gx), Tensor::adopt(gw), Tensor::adopt(gb)}; break;
       }

@@ -6,11 +6,12 @@
 // BatchNorm follows lib.rs:2067-2364 (biased batch variance for normalisation, Bessel factor only
 // in the running value, eval mode uses the running statistics).
 //
-// LayerNorm backward is the HBM-bound kernel of this file: one warp owns a row, reads x and g
-// exactly once into registers (128-bit loads), reduces with warp shuffles, and keeps its share of
-// dw/db in registers across all the rows it visits; partial dw/db rows (one per CTA) are then
-// summed in a fixed order by the column-sum kernel.  No atomics, bit-reproducible.
-// Algorithmic bytes per call: 3 * rows * C * 4 (read x, read g, write dx).
+// LayerNorm backward is the HBM-bound kernel of this file: one warp owns a row, reads x and g (and, where the caller accumulates
+// into an existing gradient, that gradient) exactly once into registers (128-bit loads), reduces with warp shuffles and does its
+// arithmetic on packed pairs of f32.  Each warp keeps running column sums -- dgamma, dbeta and the sum of the rows it stored, which
+// is the bias gradient of the Linear layer that produced the normalised tensor's input -- in a strip of shared memory that only
+// it touches; one partial row per CTA and sum is then added up in a fixed order.  No atomics, bit-reproducible.
+// Algorithmic bytes per call: 3 * rows * C * 4 (read x, read g, write dx), 4 * rows * C * 4 when accumulating.
 #include "common.h"
 
 namespace vb {
@@ -72,109 +73,119 @@ __global__ void __launch_bounds__(256) k_ln_fwd_warp(const float* __restrict__ x
   }
 }
 
-template <int VPT>
-__global__ void __launch_bounds__(256) k_ln_bwd_warp(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ g,
-                                                     float* __restrict__ gx, float* __restrict__ part_w, float* __restrict__ part_b,
-                                                     i64 rows, int C, float eps) {
-  extern __shared__ float sm[];   // [warps][2][C] for the end-of-kernel combine
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  i64 warp = (i64)blockIdx.x * nw + wid;
-  i64 nwarps = (i64)gridDim.x * nw;
-  float fc = (float)C;
-  float4 aw[VPT], ab[VPT];
+// dx = (g w - mean(g w) - x-hat mean(g w x-hat)) r, written as g w r - (a r / C) - x-hat (c r / C) with a = sum(g w), c = sum(g w x-hat).
+// NSUMS = 3 also keeps the column sums of the stored rows.  ACCUM: the stored row is resid + dx (gx may be resid).
+template <int VPT, bool ACCUM>
+__global__ void __launch_bounds__(256, 2) k_ln_bwd_warp(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ g,
+                                                        const float* resid, float* gx, float* __restrict__ part,
+                                                        i64 rows, int C, float eps, int nsums) {
+  extern __shared__ __align__(16) float sm[];   // [warps][3][C]: running column sums of g * x-hat, of g and of the stored rows
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const i64 warp = (i64)blockIdx.x * nw + wid, nwarps = (i64)gridDim.x * nw;
+  const float rfc = 1.0f / (float)C;
+  const float2 zero2 = make_float2(0.0f, 0.0f);
+  const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float4* acc_w = reinterpret_cast<float4*>(sm + (size_t)wid * 3 * C);
+  float4* acc_b = acc_w + C / 4;
+  float4* acc_o = acc_b + C / 4;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) { aw[i] = make_float4(0, 0, 0, 0); ab[i] = make_float4(0, 0, 0, 0); }
+  for (int i = 0; i < VPT; ++i)      // a lane only ever touches its own columns of the strip: no synchronisation inside the warp
+    if ((i * 32 + lane) * 4 < C) { acc_w[i * 32 + lane] = zero4; acc_b[i * 32 + lane] = zero4; acc_o[i * 32 + lane] = zero4; }
   for (i64 r = warp; r < rows; r += nwarps) {
     const float4* xr = reinterpret_cast<const float4*>(x + r * C);
     const float4* gr = reinterpret_cast<const float4*>(g + r * C);
-    float4 v[VPT], gg[VPT];
-    float s = 0.0f;
+    float4 v[VPT], gg[VPT], rs[ACCUM ? VPT : 1];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      int col = (i * 32 + lane) * 4;
-      bool ok = col < C;
-      v[i] = ok ? xr[i * 32 + lane] : make_float4(0, 0, 0, 0);
-      gg[i] = ok ? gr[i * 32 + lane] : make_float4(0, 0, 0, 0);
-      s += v[i].x + v[i].y + v[i].z + v[i].w;
+      const bool in = (i * 32 + lane) * 4 < C;
+      v[i] = in ? xr[i * 32 + lane] : zero4;
+      gg[i] = in ? gr[i * 32 + lane] : zero4;
+      if (ACCUM) rs[i] = in ? reinterpret_cast<const float4*>(resid + r * C)[i * 32 + lane] : zero4;
     }
-    float mean = wsum(s) / fc;
-    float q = 0.0f;
+    float2 acc = zero2;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      int col = (i * 32 + lane) * 4;
-      if (col < C) { float a = v[i].x - mean, bb = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean; q += a * a + bb * bb + c * c + d * d; }
+    for (int i = 0; i < VPT; ++i) acc = add2(acc, add2(lo2(v[i]), hi2(v[i])));
+    const float mean = wsum(acc.x + acc.y) * rfc;
+    const float2 nmean = make_float2(-mean, -mean);
+    acc = zero2;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {                  // v becomes x - mean
+      float2 a = add2(lo2(v[i]), nmean), b = add2(hi2(v[i]), nmean);
+      if ((i * 32 + lane) * 4 >= C) { a = zero2; b = zero2; }
+      acc = fma2(a, a, acc); acc = fma2(b, b, acc);
+      v[i] = cat2(a, b);
     }
-    float inv = 1.0f / sqrtf(wsum(q) / fc + eps);
-    float s1 = 0.0f, s2 = 0.0f;
+    const float inv = 1.0f / sqrtf(wsum(acc.x + acc.y) * rfc + eps);
+    const float2 inv2 = make_float2(inv, inv);
+    float2 s1 = zero2, s2 = zero2;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      int col = (i * 32 + lane) * 4;
-      if (col < C) {
-        float4 ww = *reinterpret_cast<const float4*>(w + col);
-        // x-hat overwrites x, g*w is recomputed below
-        v[i].x = (v[i].x - mean) * inv; v[i].y = (v[i].y - mean) * inv; v[i].z = (v[i].z - mean) * inv; v[i].w = (v[i].w - mean) * inv;
-        float p0 = gg[i].x * ww.x, p1 = gg[i].y * ww.y, p2 = gg[i].z * ww.z, p3 = gg[i].w * ww.w;
-        s1 += p0 + p1 + p2 + p3;
-        s2 += p0 * v[i].x + p1 * v[i].y + p2 * v[i].z + p3 * v[i].w;
-        aw[i].x += gg[i].x * v[i].x; aw[i].y += gg[i].y * v[i].y; aw[i].z += gg[i].z * v[i].z; aw[i].w += gg[i].w * v[i].w;
-        ab[i].x += gg[i].x; ab[i].y += gg[i].y; ab[i].z += gg[i].z; ab[i].w += gg[i].w;
+    for (int i = 0; i < VPT; ++i) {                  // v becomes x-hat, gg becomes g * w
+      const bool in = (i * 32 + lane) * 4 < C;
+      const float4 ww = in ? *reinterpret_cast<const float4*>(w + (i * 32 + lane) * 4) : zero4;
+      const float2 xa = mul2(lo2(v[i]), inv2), xb = mul2(hi2(v[i]), inv2);
+      const float2 ga = lo2(gg[i]), gb = hi2(gg[i]);
+      if (in) {
+        const float4 cw = acc_w[i * 32 + lane], cb = acc_b[i * 32 + lane];
+        acc_w[i * 32 + lane] = cat2(fma2(ga, xa, lo2(cw)), fma2(gb, xb, hi2(cw)));
+        acc_b[i * 32 + lane] = cat2(add2(ga, lo2(cb)), add2(gb, hi2(cb)));
       }
+      const float2 pa = mul2(ga, lo2(ww)), pb = mul2(gb, hi2(ww));
+      s1 = add2(s1, add2(pa, pb));
+      s2 = fma2(pa, xa, s2); s2 = fma2(pb, xb, s2);
+      v[i] = cat2(xa, xb); gg[i] = cat2(pa, pb);
     }
-    s1 = wsum(s1); s2 = wsum(s2);
+    const float t1 = wsum(s1.x + s1.y), t2 = wsum(s2.x + s2.y);
+    const float na = -(t1 * inv * rfc), nb = -(t2 * inv * rfc);
+    const float2 na2 = make_float2(na, na), nb2 = make_float2(nb, nb);
     float4* orow = reinterpret_cast<float4*>(gx + r * C);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      int col = (i * 32 + lane) * 4;
-      if (col < C) {
-        float4 ww = *reinterpret_cast<const float4*>(w + col), o;
-        o.x = (fc * gg[i].x * ww.x - s1 - v[i].x * s2) * inv / fc;
-        o.y = (fc * gg[i].y * ww.y - s1 - v[i].y * s2) * inv / fc;
-        o.z = (fc * gg[i].z * ww.z - s1 - v[i].z * s2) * inv / fc;
-        o.w = (fc * gg[i].w * ww.w - s1 - v[i].w * s2) * inv / fc;
-        orow[i * 32 + lane] = o;
+      float2 oa = fma2(lo2(gg[i]), inv2, fma2(lo2(v[i]), nb2, na2));
+      float2 ob = fma2(hi2(gg[i]), inv2, fma2(hi2(v[i]), nb2, na2));
+      if (ACCUM) { oa = add2(oa, lo2(rs[i])); ob = add2(ob, hi2(rs[i])); }
+      if ((i * 32 + lane) * 4 < C) {
+        orow[i * 32 + lane] = cat2(oa, ob);
+        if (nsums == 3) {
+          const float4 co = acc_o[i * 32 + lane];
+          acc_o[i * 32 + lane] = cat2(add2(oa, lo2(co)), add2(ob, hi2(co)));
+        }
       }
     }
   }
-  // combine the warps of this CTA in warp order, then write one partial row per CTA
-  float* sw = sm + (size_t)wid * 2 * C;
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    int col = (i * 32 + lane) * 4;
-    if (col < C) { *reinterpret_cast<float4*>(sw + col) = aw[i]; *reinterpret_cast<float4*>(sw + C + col) = ab[i]; }
-  }
+  // combine the warps of this CTA in warp order: one partial row per CTA and sum, part[sum][cta][C]
   __syncthreads();
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+  for (int c = threadIdx.x; c < nsums * C; c += blockDim.x) {
     float t = 0.0f;
-    for (int k = 0; k < nw; ++k) t += sm[(size_t)k * 2 * C + c];
-    if (c < C) part_w[(i64)blockIdx.x * C + c] = t; else part_b[(i64)blockIdx.x * C + (c - C)] = t;
+    for (int k = 0; k < nw; ++k) t += sm[(size_t)k * 3 * C + c];
+    part[((i64)(c / C) * gridDim.x + blockIdx.x) * C + (c % C)] = t;
   }
 }
 
-// Second stage of the fast path: add the per-CTA partial rows of dw and db in a fixed order.  A 32 x 32 block owns
-// 32 columns; its 32 row lanes each add every 32nd partial row (four loads in flight), then lane 0 adds the 32 sums
-// in lane order.
-__global__ void __launch_bounds__(1024) k_ln_partials_sum(const float* __restrict__ part_w, const float* __restrict__ part_b,
-                                                           float* __restrict__ gw, float* __restrict__ gb, int ctas, int C) {
-  __shared__ float sw[32][33], sb[32][33];
+// Second stage of the fast path: add the per-CTA partial rows in a fixed order.  A 32 x 32 block owns 32 columns of one of the
+// sums (blockIdx.y); its 32 row lanes each add every 32nd partial row (four loads in flight), then lane 0 adds the 32 sums in
+// lane order.  out0 / out1 / out2 take dgamma, dbeta and the column sums of the stored rows.
+__global__ void __launch_bounds__(1024) k_ln_partials_sum(const float* __restrict__ part, float* __restrict__ out0, float* __restrict__ out1,
+                                                           float* __restrict__ out2, int ctas, int C) {
+  __shared__ float sw[32][33];
+  const float* p = part + (i64)blockIdx.y * ctas * C;
+  float* out = blockIdx.y == 0 ? out0 : (blockIdx.y == 1 ? out1 : out2);
   int c = blockIdx.x * 32 + threadIdx.x;
-  float a = 0.0f, b = 0.0f;
+  float a = 0.0f;
   if (c < C) {
     int i = threadIdx.y;
     for (; i + 96 < ctas; i += 128) {
-      float a0 = part_w[(i64)i * C + c], a1 = part_w[(i64)(i + 32) * C + c], a2 = part_w[(i64)(i + 64) * C + c], a3 = part_w[(i64)(i + 96) * C + c];
-      float b0 = part_b[(i64)i * C + c], b1 = part_b[(i64)(i + 32) * C + c], b2 = part_b[(i64)(i + 64) * C + c], b3 = part_b[(i64)(i + 96) * C + c];
+      float a0 = p[(i64)i * C + c], a1 = p[(i64)(i + 32) * C + c], a2 = p[(i64)(i + 64) * C + c], a3 = p[(i64)(i + 96) * C + c];
       a += a0; a += a1; a += a2; a += a3;
-      b += b0; b += b1; b += b2; b += b3;
     }
-    for (; i < ctas; i += 32) { a += part_w[(i64)i * C + c]; b += part_b[(i64)i * C + c]; }
+    for (; i < ctas; i += 32) a += p[(i64)i * C + c];
   }
-  sw[threadIdx.y][threadIdx.x] = a; sb[threadIdx.y][threadIdx.x] = b;
+  sw[threadIdx.y][threadIdx.x] = a;
   __syncthreads();
   if (threadIdx.y == 0 && c < C) {
-    float ta = 0.0f, tb = 0.0f;
+    float ta = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) { ta += sw[i][threadIdx.x]; tb += sb[i][threadIdx.x]; }
-    gw[c] = ta; gb[c] = tb;
+    for (int i = 0; i < 32; ++i) ta += sw[i][threadIdx.x];
+    out[c] = ta;
   }
 }
 
@@ -217,6 +228,22 @@ __global__ void k_ln_bwd_cols(const float* __restrict__ x, const float* __restri
 }
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+// The shared-memory strip of an instance is [8 warps][3][128 * VPT] floats: past 48 KB from VPT = 5 on.  Raised once per instance.
+template <int VPT, bool ACCUM>
+static cudaError_t ln_bwd_smem_attr() {
+  static cudaError_t rc = cudaFuncSetAttribute(k_ln_bwd_warp<VPT, ACCUM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 128 * VPT * (int)sizeof(float));
+  return rc;
+}
+template <bool ACCUM>
+static int ln_bwd_launch(int vpt, unsigned blocks, size_t smem, cudaStream_t st, const float* x, const float* w, const float* g, const float* resid,
+                         float* gx, float* part, i64 rows, int c, float eps, int nsums) {
+#define LN_BWD(V) case V: \
+    if (V >= 5) VB_CUDA((ln_bwd_smem_attr<V, ACCUM>())); \
+    k_ln_bwd_warp<V, ACCUM><<<blocks, 256, smem, st>>>(x, w, g, resid, gx, part, rows, c, eps, nsums); break;
+  switch (vpt) { LN_BWD(1) LN_BWD(2) LN_BWD(3) LN_BWD(4) LN_BWD(5) LN_BWD(6) LN_BWD(7) LN_BWD(8) }
+#undef LN_BWD
+  return VB_OK;
+}
 
 int launch_layernorm(const float* x, const float* w, const float* b, float* out, i64 rows, i64 c, float eps, float* out_lo, bool* lo_done) {
   if (lo_done) *lo_done = false;
@@ -241,35 +268,50 @@ int launch_layernorm(const float* x, const float* w, const float* b, float* out,
   return VB_OK;
 }
 
-int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps) {
+int launch_layernorm_backward(const float* x, const float* w, const float* g, float* gx, float* gw, float* gb, i64 rows, i64 c, float eps,
+                              const float* resid, float* out_colsum, bool* colsum_done) {
+  if (colsum_done) *colsum_done = false;
   if (c <= 0) return VB_OK;
   cudaStream_t st = ctx().stream;
   if (rows <= 0) { VB_TRY(launch_fill(gw, 0.0f, c)); return launch_fill(gb, 0.0f, c); }
-  ProfScope prof("layernorm_bwd", 3.0 * (double)rows * (double)c * 4.0);
-  bool fast = (c % 4 == 0) && c <= 1024 && al16(x) && al16(w) && al16(g) && al16(gx);
+  bool fast = (c % 4 == 0) && c <= 1024 && al16(x) && al16(w) && al16(g) && al16(gx) && (!resid || al16(resid));
   if (fast) {
+    ProfScope prof("layernorm_bwd", (resid ? 4.0 : 3.0) * (double)rows * (double)c * 4.0);
     int vpt = (int)((c + 127) / 128);
     const int warps = 8;
+    const int nsums = out_colsum ? 3 : 2;
     i64 blocks = (rows + warps - 1) / warps; i64 cap = (i64)ctx().sm_count * 2; if (blocks > cap) blocks = cap;
-    size_t smem = (size_t)warps * 2 * c * sizeof(float);   // <= 64 KiB at C = 1024
+    size_t smem = (size_t)warps * 3 * c * sizeof(float);   // 96 KiB at C = 1024
     void* part = nullptr;
-    VB_TRY(scratch_alloc((size_t)(2 * blocks * c) * sizeof(float), &part));
-    float* pw = (float*)part; float* pb = pw + blocks * c;
-#define LN_BWD(V) case V: \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(k_ln_bwd_warp<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, warps * 2 * 128 * V * (int)sizeof(float)); /* the instance's largest row, not this call's */ \
-      k_ln_bwd_warp<V><<<(unsigned)blocks, warps * 32, smem, st>>>(x, w, g, gx, pw, pb, rows, (int)c, eps); break;
-    switch (vpt) { LN_BWD(1) LN_BWD(2) LN_BWD(3) LN_BWD(4) LN_BWD(5) LN_BWD(6) LN_BWD(7) LN_BWD(8) }
-#undef LN_BWD
-    k_ln_partials_sum<<<(unsigned)((c + 31) / 32), dim3(32, 32), 0, st>>>(pw, pb, gw, gb, (int)blocks, (int)c);
+    VB_TRY(scratch_alloc((size_t)(nsums * blocks * c) * sizeof(float), &part));
+    int rc = resid ? ln_bwd_launch<true>(vpt, (unsigned)blocks, smem, st, x, w, g, resid, gx, (float*)part, rows, (int)c, eps, nsums)
+                   : ln_bwd_launch<false>(vpt, (unsigned)blocks, smem, st, x, w, g, nullptr, gx, (float*)part, rows, (int)c, eps, nsums);
+    if (rc == VB_OK) {
+      k_ln_partials_sum<<<dim3((unsigned)((c + 31) / 32), (unsigned)nsums), dim3(32, 32), 0, st>>>((const float*)part, gw, gb, out_colsum, (int)blocks, (int)c);
+      if (colsum_done && out_colsum) *colsum_done = true;
+    }
     scratch_free(part);
+    VB_TRY(rc);
   } else {
     void* stats = nullptr;
     VB_TRY(scratch_alloc((size_t)(2 * rows) * sizeof(float), &stats));
-    int t = 32; while (t < 256 && t * 4 < c) t <<= 1;
-    k_ln_fwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, w, nullptr, (float*)stats, c, eps);
-    k_ln_bwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, g, (const float*)stats, gx, c);
-    k_ln_bwd_cols<<<(unsigned)((c + 127) / 128), 128, 0, st>>>(x, g, (const float*)stats, gw, gb, rows, c);
+    float* dx = gx; void* tmp = nullptr;
+    if (resid) { int rc = scratch_alloc((size_t)(rows * c) * sizeof(float), &tmp); if (rc != VB_OK) { scratch_free(stats); return rc; } dx = (float*)tmp; }
+    {
+      ProfScope prof("layernorm_bwd", 3.0 * (double)rows * (double)c * 4.0);
+      int t = 32; while (t < 256 && t * 4 < c) t <<= 1;
+      k_ln_fwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, w, nullptr, (float*)stats, c, eps);
+      k_ln_bwd_block<<<(unsigned)rows, t, 0, st>>>(x, w, g, (const float*)stats, dx, c);
+      k_ln_bwd_cols<<<(unsigned)((c + 127) / 128), 128, 0, st>>>(x, g, (const float*)stats, gw, gb, rows, c);
+    }
     scratch_free(stats);
+    if (resid) {
+      int rc = VB_OK;
+      if (gx != resid) { cudaError_t e = cudaMemcpyAsync(gx, resid, (size_t)(rows * c) * sizeof(float), cudaMemcpyDeviceToDevice, st); if (e != cudaSuccess) rc = set_error(VB_ERR_CUDA, cudaGetErrorString(e)); }
+      if (rc == VB_OK) rc = launch_axpy(gx, dx, rows * c);
+      scratch_free(tmp);
+      VB_TRY(rc);
+    }
   }
   VB_LAUNCH_CHECK();
   return VB_OK;
@@ -404,9 +446,9 @@ extern "C" int vb_layernorm_backward_noalloc(const float* x, const float* w, con
     float* p = nullptr;
     VB_CUDA(cudaGetSymbolAddress((void**)&p, g_ln_bwd_noalloc_scratch));
     VB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
-    // rows of more than 768 floats need more than the default 48 KB of shared memory: raise the two instances' limit once, here
-    VB_CUDA(cudaFuncSetAttribute(k_ln_bwd_warp<7>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * kNoAllocMaxC * (int)sizeof(float)));
-    VB_CUDA(cudaFuncSetAttribute(k_ln_bwd_warp<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * kNoAllocMaxC * (int)sizeof(float)));
+    // rows of more than 512 floats need more than the default 48 KB of shared memory: raise those instances' limit once, here
+    VB_CUDA((ln_bwd_smem_attr<5, false>())); VB_CUDA((ln_bwd_smem_attr<6, false>()));
+    VB_CUDA((ln_bwd_smem_attr<7, false>())); VB_CUDA((ln_bwd_smem_attr<8, false>()));
     d.scratch = p; d.ready = true;
   }
   cudaStream_t st = (cudaStream_t)stream;
@@ -421,11 +463,11 @@ extern "C" int vb_layernorm_backward_noalloc(const float* x, const float* w, con
   i64 cap = (i64)d.sm_count * 2; if (cap > kNoAllocMaxCtas) cap = kNoAllocMaxCtas;
   if (ctas > cap) ctas = cap;
   // every CTA overwrites its own partial row in full, so nothing in the array needs clearing first
-  float* pw = d.scratch; float* pb = d.scratch + (size_t)kNoAllocMaxCtas * kNoAllocMaxC;
-  size_t smem = (size_t)warps * 2 * C * sizeof(float);
+  float* pw = d.scratch; float* pb = d.scratch + (size_t)ctas * C;       // the kernel's layout: [sum][cta][C], two sums here
+  size_t smem = (size_t)warps * 3 * C * sizeof(float);
   int vpt = (C + 127) / 128;
 #define LN_BWD_NA(V) case V: \
-    k_ln_bwd_warp<V><<<(unsigned)ctas, warps * 32, smem, st>>>(x, w, grad_out, gx, pw, pb, rows, C, eps); break;
+    k_ln_bwd_warp<V, false><<<(unsigned)ctas, warps * 32, smem, st>>>(x, w, grad_out, nullptr, gx, pw, rows, C, eps, 2); break;
   switch (vpt) { LN_BWD_NA(1) LN_BWD_NA(2) LN_BWD_NA(3) LN_BWD_NA(4) LN_BWD_NA(5) LN_BWD_NA(6) LN_BWD_NA(7) LN_BWD_NA(8) }
 #undef LN_BWD_NA
   k_ln_noalloc_finish<<<(C + 127) / 128, 128, 0, st>>>(pw, pb, gw, gb, (int)ctas, C);

@@ -142,9 +142,72 @@ __global__ void __launch_bounds__(256) k_colsum_partial_vec(const float4* __rest
     part[(i64)blockIdx.y * cols4 + c] = t;
   }
 }
+// Whole-row bands (cols <= 4096, a multiple of 4): a CTA of 256 threads sums a contiguous band of rows, a thread the float4
+// columns t, t + 256, ... in registers, four rows in flight -- a contiguous memory stream -- and writes one partial row.
+template <int K>
+__global__ void __launch_bounds__(256) k_colsum_bands(const float4* __restrict__ x, float4* __restrict__ part, i64 rows, int cols4, i64 rows_per_band) {
+  const i64 r0 = (i64)blockIdx.x * rows_per_band;
+  i64 r1 = r0 + rows_per_band; if (r1 > rows) r1 = rows;
+  float4 s[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) s[k] = make_float4(0, 0, 0, 0);
+  i64 r = r0;
+  for (; r + 3 < r1; r += 4) {
+    float4 a[K], b[K], c[K], d[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int col = k * 256 + threadIdx.x;
+      if (col < cols4) { a[k] = x[r * cols4 + col]; b[k] = x[(r + 1) * cols4 + col]; c[k] = x[(r + 2) * cols4 + col]; d[k] = x[(r + 3) * cols4 + col]; }
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+      if (k * 256 + threadIdx.x < cols4) {
+        s[k].x += a[k].x; s[k].y += a[k].y; s[k].z += a[k].z; s[k].w += a[k].w;
+        s[k].x += b[k].x; s[k].y += b[k].y; s[k].z += b[k].z; s[k].w += b[k].w;
+        s[k].x += c[k].x; s[k].y += c[k].y; s[k].z += c[k].z; s[k].w += c[k].w;
+        s[k].x += d[k].x; s[k].y += d[k].y; s[k].z += d[k].z; s[k].w += d[k].w;
+      }
+  }
+  for (; r < r1; ++r)
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int col = k * 256 + threadIdx.x;
+      if (col < cols4) { const float4 a = x[r * cols4 + col]; s[k].x += a.x; s[k].y += a.y; s[k].z += a.z; s[k].w += a.w; }
+    }
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int col = k * 256 + threadIdx.x;
+    if (col < cols4) part[(i64)blockIdx.x * cols4 + col] = s[k];
+  }
+}
+int launch_colsum_final(const float* part, float* out, i64 cols, int splits) {
+  if (cols <= 0) return VB_OK;
+  k_colsum_final<<<(unsigned)((cols + 31) / 32), dim3(32, 32), 0, ctx().stream>>>(part, out, cols, splits, false);
+  VB_LAUNCH_CHECK();
+  return VB_OK;
+}
 int launch_colsum(const float* x, float* out, i64 rows, i64 cols, bool accumulate) {
   if (cols <= 0) return VB_OK;
   ProfScope prof("colsum", (double)rows * (double)cols * 4.0);
+  if ((cols & 3) == 0 && cols >= 512 && cols <= 4096 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && rows >= 1024 && !accumulate) {
+    const int cols4 = (int)(cols / 4), k = (cols4 + 255) / 256;
+    i64 bands = (i64)ctx().sm_count * 2; if (bands > rows / 8) bands = rows / 8;      // one wave whatever the instance
+    const i64 rpb = (rows + bands - 1) / bands;
+    bands = (rows + rpb - 1) / rpb;
+    void* part = nullptr;
+    VB_TRY(scratch_alloc((size_t)(bands * cols) * sizeof(float), &part));
+    cudaStream_t st = ctx().stream;
+    switch (k) {
+      case 1: k_colsum_bands<1><<<(unsigned)bands, 256, 0, st>>>((const float4*)x, (float4*)part, rows, cols4, rpb); break;
+      case 2: k_colsum_bands<2><<<(unsigned)bands, 256, 0, st>>>((const float4*)x, (float4*)part, rows, cols4, rpb); break;
+      case 3: k_colsum_bands<3><<<(unsigned)bands, 256, 0, st>>>((const float4*)x, (float4*)part, rows, cols4, rpb); break;
+      default: k_colsum_bands<4><<<(unsigned)bands, 256, 0, st>>>((const float4*)x, (float4*)part, rows, cols4, rpb); break;
+    }
+    k_colsum_final<<<(unsigned)((cols + 31) / 32), dim3(32, 32), 0, st>>>((const float*)part, out, cols, (int)bands, false);
+    scratch_free(part);
+    VB_LAUNCH_CHECK();
+    return VB_OK;
+  }
   if ((cols & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && rows >= 64) {
     i64 cols4 = cols / 4, col_blocks = (cols4 + 31) / 32;
     i64 want = ((i64)ctx().sm_count * 4 + col_blocks - 1) / col_blocks;
