@@ -294,9 +294,15 @@ int vb_dp_world(int* rank, int* world);
 /* Sum-allreduce `numel` floats at slot+offset on the communication stream, ordered after all
  * work enqueued so far on the compute stream.  Returns immediately. */
 int vb_dp_allreduce(vb_slot slot, int64_t offset, int64_t numel);
-/* Make the compute stream wait for all allreduces issued so far; polls for asynchronous NCCL
- * errors with a host deadline (milliseconds, <= 0: no deadline check). */
+/* Make the compute stream wait for all allreduces issued so far.
+ *   timeout_ms > 0: the host also waits for them, polling for asynchronous NCCL errors, until the deadline (milliseconds):
+ *                   VB_ERR_COMM_TIMEOUT / VB_ERR_COMM after aborting the communicator.
+ *   timeout_ms = 0: no host-side check.
+ *   timeout_ms < 0: deferred check with deadline -timeout_ms: returns at once, so the host can keep enqueuing work; the
+ *                   deadline wait for THESE collectives happens at the next vb_dp_finish, vb_dp_wait, vb_sync or vb_read,
+ *                   whichever comes first (they have normally completed long before and nothing waits). */
 int vb_dp_finish(int timeout_ms);
+int vb_dp_wait(void);
 int vb_dp_shutdown(void);
 
 #ifdef __cplusplus

@@ -131,5 +131,6 @@ unsafe extern "C" {
     pub fn vb_dp_world(rank: *mut c_int, world: *mut c_int) -> c_int;
     pub fn vb_dp_allreduce(slot: vb_slot, offset: i64, numel: i64) -> c_int;
     pub fn vb_dp_finish(timeout_ms: c_int) -> c_int;
+    pub fn vb_dp_wait() -> c_int;
     pub fn vb_dp_shutdown() -> c_int;
 }

@@ -205,6 +205,7 @@ struct OptChunk { float* w; const float* g; float* m; float* v; int n; int param
 float* lo_plane_base_for(vb_slot weight_slot, float** weight_base);
 void lo_plane_mark_current(vb_slot weight_slot);
 bool lo_plane_is_current(vb_slot weight_slot);
+int dp_wait_pending();                      // data parallel: the host-side deadline check a deferred vb_dp_finish left open (no-op otherwise)
 void lo_planes_forget_all();                 // the slot table is being torn down
 void lo_plane_on_release(vb_slot slot);      // the slot is gone: so is a lo plane kept for it
 // ---- bounds-check build (-DVB200_BOUNDS_CHECK; `python vearo_b200/build.py --bounds-check`) ------------------------------------

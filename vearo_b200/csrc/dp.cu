@@ -88,28 +88,60 @@ int vb_dp_allreduce(vb_slot slot, int64_t offset, int64_t n) {
   if (rc != ncclSuccess) return nccl_fail("ncclAllReduce", rc);
   return VB_OK;
 }
+// Host-side wait for `ev` with a deadline, polling for asynchronous NCCL errors meanwhile.
+static int wait_with_deadline(cudaEvent_t ev, int timeout_ms) {
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (true) {
+    cudaError_t q = cudaEventQuery(ev);
+    if (q == cudaSuccess) return VB_OK;
+    if (q != cudaErrorNotReady) return set_error(VB_ERR_CUDA, cudaGetErrorString(q));
+    int async_err = ncclSuccess;
+    g_nccl.CommGetAsyncError(g_comm, &async_err);
+    if (async_err != ncclSuccess && async_err != ncclInProgress) { g_nccl.CommAbort(g_comm); g_comm = nullptr; return nccl_fail("asynchronous NCCL error", async_err); }
+    if (std::chrono::steady_clock::now() > deadline) { g_nccl.CommAbort(g_comm); g_comm = nullptr; return set_error(VB_ERR_COMM_TIMEOUT, "allreduce did not complete before the deadline"); }
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+// Deferred checks (vb_dp_finish with a negative deadline): the event of the step whose completion has not been looked at yet.
+static cudaEvent_t g_ev_deferred[2] = {nullptr, nullptr};
+static int g_deferred_at = 0, g_deferred_ms = 0;
+static bool g_deferred_pending = false;
+}  // extern "C"
+namespace vb {
+int dp_wait_pending() {
+  if (!g_deferred_pending) return VB_OK;
+  g_deferred_pending = false;
+  if (!g_comm) return VB_OK;
+  return wait_with_deadline(g_ev_deferred[g_deferred_at], g_deferred_ms);
+}
+}  // namespace vb
+extern "C" {
+int vb_dp_wait(void) { return dp_wait_pending(); }
 int vb_dp_finish(int timeout_ms) {
   if (g_world == 1) return VB_OK;
   if (!g_comm) return set_error(VB_ERR_COMM, "vb_dp_init has not been called");
   Ctx& c = ctx();
+  if (timeout_ms < 0) {
+    // the previous step's collectives first (normally long complete: no waiting), then this step's are only enqueued
+    VB_TRY(dp_wait_pending());
+    if (!g_comm) return set_error(VB_ERR_COMM, "the communicator was aborted");
+    const int at = g_deferred_at ^ 1;
+    if (!g_ev_deferred[at]) VB_CUDA(cudaEventCreateWithFlags(&g_ev_deferred[at], cudaEventDisableTiming));
+    VB_CUDA(cudaEventRecord(g_ev_deferred[at], c.comm_stream));
+    VB_CUDA(cudaStreamWaitEvent(c.stream, g_ev_deferred[at], 0));
+    g_deferred_at = at; g_deferred_ms = -timeout_ms; g_deferred_pending = true;
+    return VB_OK;
+  }
+  VB_TRY(dp_wait_pending());
+  if (!g_comm) return set_error(VB_ERR_COMM, "the communicator was aborted");
   VB_CUDA(cudaEventRecord(c.ev_comm, c.comm_stream));
   VB_CUDA(cudaStreamWaitEvent(c.stream, c.ev_comm, 0));
-  if (timeout_ms > 0) {
-    auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
-    while (true) {
-      cudaError_t q = cudaEventQuery(c.ev_comm);
-      if (q == cudaSuccess) break;
-      if (q != cudaErrorNotReady) return set_error(VB_ERR_CUDA, cudaGetErrorString(q));
-      int async_err = ncclSuccess;
-      g_nccl.CommGetAsyncError(g_comm, &async_err);
-      if (async_err != ncclSuccess && async_err != ncclInProgress) { g_nccl.CommAbort(g_comm); g_comm = nullptr; return nccl_fail("asynchronous NCCL error", async_err); }
-      if (std::chrono::steady_clock::now() > deadline) { g_nccl.CommAbort(g_comm); g_comm = nullptr; return set_error(VB_ERR_COMM_TIMEOUT, "allreduce did not complete before the deadline"); }
-      std::this_thread::sleep_for(std::chrono::microseconds(50));
-    }
-  }
+  if (timeout_ms > 0) return wait_with_deadline(c.ev_comm, timeout_ms);
   return VB_OK;
 }
 int vb_dp_shutdown(void) {
+  g_deferred_pending = false;
+  for (cudaEvent_t& e : g_ev_deferred) if (e) { cudaEventDestroy(e); e = nullptr; }
   if (g_comm) { cudaStreamSynchronize(ctx().comm_stream); g_nccl.CommDestroy(g_comm); g_comm = nullptr; }
   g_world = 1; g_rank = 0;
   return VB_OK;

@@ -182,7 +182,12 @@ Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params
     if (!p.is_contiguous()) throw Error("optimizer parameters must be contiguous");
     numels.push_back(p.numel());
   }
-  BucketPlan bp = plan_buckets(numels, (32ll << 20) / 4);
+  // gradient buckets of at least 128 MiB (VB200_DP_BUCKET_MB overrides the size): with 8 GPUs on NVSwitch every all-reduce kernel
+  // holds 24 SMs while it runs, and few long ones cost the GEMMs beside them less than many short ones (GPT-small step at 8 GPUs:
+  // 46.5 ms with 8 MiB buckets, 46.4 with 32, 45.7 with 128)
+  i64 bucket_mb = 128;
+  if (const char* e = std::getenv("VB200_DP_BUCKET_MB")) { const long v = std::atol(e); if (v >= 1 && v <= 4096) bucket_mb = v; }
+  BucketPlan bp = plan_buckets(numels, (bucket_mb << 20) / 4);
   const i64 total = bp.total;
   const std::vector<i64>& offs = bp.param_offset;
   arena_ = Tensor::zeros({total > 0 ? total : 1});
@@ -197,7 +202,7 @@ Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params
   int rank = 0;
   check(vb_dp_world(&rank, &world_), "dp_world");
   if (!dp_) world_ = 1;
-  // buckets: contiguous arena ranges of >= 32 MiB (see plan_buckets)
+  // buckets: contiguous arena ranges of at least the bucket size (see plan_buckets)
   bucket_of_ = bp.bucket_of;
   for (size_t b = 0; b < bp.bucket_offset.size(); ++b) buckets_.push_back(Bucket{bp.bucket_offset[b], bp.bucket_numel[b], bp.bucket_nparams[b], bp.bucket_nparams[b]});
   ready_.assign(params_.size(), 0);
@@ -206,6 +211,11 @@ Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params
 Optimizer::~Optimizer() {
   autograd::clear_grad_sinks(this);
   if (opt_ >= 0) vb_opt_destroy(opt_);
+}
+// VB200_DP_OVERLAP=0: every bucket is reduced after the backward pass instead of as soon as it is complete (A/B switch).
+static bool dp_overlap() {
+  static const bool on = [] { const char* e = std::getenv("VB200_DP_OVERLAP"); return !(e && e[0] == '0'); }();
+  return on;
 }
 void Optimizer::on_ready(int idx, void* self) {
   Optimizer* o = (Optimizer*)self;
@@ -222,7 +232,7 @@ void Optimizer::on_ready(int idx, void* self) {
   o->ready_[idx] = 1;
   if (o->world_ <= 1) return;
   Bucket& b = o->buckets_[o->bucket_of_[idx]];
-  if (--b.pending == 0) check(vb_dp_allreduce(o->arena_.slot(), b.offset, b.numel), "dp_allreduce");
+  if (--b.pending == 0 && dp_overlap()) check(vb_dp_allreduce(o->arena_.slot(), b.offset, b.numel), "dp_allreduce");
 }
 // Host deadline for the step's collectives, in milliseconds: VB200_DP_TIMEOUT_MS, 30 s by default.
 static int collective_timeout_ms() {
@@ -232,15 +242,18 @@ static int collective_timeout_ms() {
 }
 // Buckets with a parameter that received no gradient this step are still reduced (every rank must
 // issue the same collectives): their stale ranges are zeroed first.
-void Optimizer::finish_reduce() {
+// deferred: the host does not wait for the collectives here (their deadline is checked at the next step's, or at the next
+// read-back / synchronisation through the library) -- for callers that read nothing back from this step.
+void Optimizer::finish_reduce(bool deferred) {
   if (world_ > 1) {
     for (size_t i = 0; i < params_.size(); ++i)
       if (!ready_[i]) {
         check(vb_fill(&sinks_[i].desc(), 0.0f), "fill");
         Bucket& b = buckets_[bucket_of_[i]];
-        if (--b.pending == 0) check(vb_dp_allreduce(arena_.slot(), b.offset, b.numel), "dp_allreduce");
+        if (--b.pending == 0 && dp_overlap()) check(vb_dp_allreduce(arena_.slot(), b.offset, b.numel), "dp_allreduce");
       }
-    check(vb_dp_finish(collective_timeout_ms()), "dp_finish");
+    if (!dp_overlap()) for (Bucket& b : buckets_) check(vb_dp_allreduce(arena_.slot(), b.offset, b.numel), "dp_allreduce");
+    check(vb_dp_finish(deferred ? -collective_timeout_ms() : collective_timeout_ms()), "dp_finish");
     for (Bucket& b : buckets_) b.pending = b.nparams;
   }
 }
@@ -248,12 +261,12 @@ void Optimizer::finish_reduce() {
 // others); under data parallel ALL of them -- a parameter may have received gradient on some ranks only, every rank holds the same
 // reduced sum after finish_reduce (zero-filled where nothing was produced locally), and replicas must apply the same update.
 void Optimizer::step() {
-  finish_reduce();
+  finish_reduce(true);
   check(vb_opt_step(opt_, world_ > 1 ? nullptr : ready_.data(), 0.0f, 1.0f / (float)world_, nullptr), "opt_step");
   std::fill(ready_.begin(), ready_.end(), 0);
 }
 float Optimizer::clip_and_step(float max_norm, bool read_norm) {
-  finish_reduce();
+  finish_reduce(!read_norm);
   float norm = 0.0f;
   check(vb_opt_step(opt_, world_ > 1 ? nullptr : ready_.data(), max_norm, 1.0f / (float)world_, read_norm ? &norm : nullptr), "opt_step");
   std::fill(ready_.begin(), ready_.end(), 0);

@@ -136,7 +136,7 @@ class Optimizer {
   void load_state(const std::string& path);
   int handle() const { return opt_; }          // the library's optimizer handle (vb_opt_*)
  private:
-  void finish_reduce();
+  void finish_reduce(bool deferred = false);
   static void on_ready(int idx, void* self);
   vb_opt_config cfg_;
   std::vector<Tensor> params_, sinks_;

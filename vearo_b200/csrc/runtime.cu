@@ -221,6 +221,7 @@ int vb_device_ordinal(int* ordinal) {
 }
 int vb_sync(void) {
   if (!g_ctx.ready) return set_error(VB_ERR_NOT_INIT, "vb_init has not been called");
+  VB_TRY(dp_wait_pending());      // a collective still unchecked gets its deadline here, not an unbounded wait below
   VB_CUDA(cudaStreamSynchronize(g_ctx.stream));
   return VB_OK;
 }
@@ -264,6 +265,7 @@ int vb_write(vb_slot s, int64_t offset, const float* host, int64_t n) {
 int vb_read(vb_slot s, int64_t offset, float* host, int64_t n) {
   float* p; i64 cap; VB_TRY(slot_ptr(s, &p, &cap));
   VB_CHECK(offset >= 0 && n >= 0 && offset + n <= cap, "range exceeds the slot");
+  VB_TRY(dp_wait_pending());
   if (n) VB_CUDA(cudaMemcpyAsync(host, p + offset, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, g_ctx.stream));
   VB_CUDA(cudaStreamSynchronize(g_ctx.stream));
   return VB_OK;
