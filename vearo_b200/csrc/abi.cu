@@ -183,7 +183,8 @@ namespace { bool col_sums_enabled(); void col_sums_adopt(const vb_tensor* t, i64
 static int unary_backward_summed(int op, const vb_tensor* x, const vb_tensor* g, vb_tensor* gx) {
   i64 rows = 0, cols = 0;
   if (x->rank >= 2) { cols = x->dims[x->rank - 1]; rows = cols ? numel(*x) / cols : 0; }
-  if (!col_sums_enabled() || rows < 1024 || cols < 128 || cols > 4096 || (cols & 3) || !is_contiguous(*x) || !is_contiguous(*g)) return unary_backward(op, x, g, gx);
+  // (rows of fewer than 1024 floats do not fill the band kernel's 256 threads: the flat kernel plus a later column sum is faster there)
+  if (!col_sums_enabled() || rows < 1024 || cols < 1024 || cols > 4096 || (cols & 3) || !is_contiguous(*x) || !is_contiguous(*g)) return unary_backward(op, x, g, gx);
   VB_CHECK(same_shape(*x, *g), "x and grad_out shapes differ");
   float *px, *pg; VB_TRY(tensor_ptr(x, &px)); VB_TRY(tensor_ptr(g, &pg));
   if (((reinterpret_cast<uintptr_t>(px) | reinterpret_cast<uintptr_t>(pg)) & 15) != 0) return unary_backward(op, x, g, gx);
