@@ -12,7 +12,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ASM = "/root/reference/crates/vearo-backend-cpu/src/asm/x86_64/matmul.s"
+# where a checkout of the reference lives (VEARO_REFERENCE_DIR overrides); absent: the assembly kernel is simply not built
+REF_DIR = os.environ.get("VEARO_REFERENCE_DIR", "/root/reference")
+REF_ASM = os.path.join(REF_DIR, "crates/vearo-backend-cpu/src/asm/x86_64/matmul.s")
 
 
 def _stale(target, sources):

@@ -13,7 +13,7 @@ from oracle import oracle as orc
 from oracle.oracle import Tensor as T
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_JSON = "/root/reference/test_data/oracles.json"
+REF_JSON = os.path.join(os.environ.get("VEARO_REFERENCE_DIR", "/root/reference"), "test_data/oracles.json")
 
 
 def f32(*v, shape=None):
