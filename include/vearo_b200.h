@@ -277,6 +277,10 @@ int vb_opt_step(int opt, const uint8_t* active, float max_norm, float grad_scale
  * vb_profile_families writes a comma-separated list of the families seen so far. */
 /* Number of kernel-launcher invocations so far (each enqueues at least one kernel of this library). */
 int vb_launch_count(int64_t* count);
+/* Self-test of the bounded device-side waits: runs one CTA that waits, with a limit of `polls` (1..65536) polls, on a barrier
+ * nothing arrives on.  The wait runs out, the kernel raises the wait-timeout bit and returns; the NEXT vb_check_errors reports
+ * "a device-side wait ran out" (VB_ERR_BAD_INDEX) and the context stays usable.  elapsed_ms (may be NULL): device time of the kernel. */
+int vb_selftest_wait_timeout(uint32_t polls, double* elapsed_ms);
 /* Number of launches of the tcgen05 tensor-core GEMM kernel so far. */
 int vb_tc_launch_count(int64_t* count);
 int vb_profile_enable(int on);

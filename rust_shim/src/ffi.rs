@@ -120,6 +120,7 @@ unsafe extern "C" {
     pub fn vb_opt_step(opt: c_int, active: *const u8, max_norm: f32, grad_scale: f32, total_norm: *mut f32) -> c_int;
     // profiling
     pub fn vb_launch_count(count: *mut i64) -> c_int;
+    pub fn vb_selftest_wait_timeout(polls: u32, elapsed_ms: *mut f64) -> c_int;
     pub fn vb_tc_launch_count(count: *mut i64) -> c_int;
     pub fn vb_profile_enable(on: c_int) -> c_int;
     pub fn vb_profile_reset() -> c_int;

@@ -860,3 +860,29 @@ def test_activation_backward_leaves_the_bias_gradient(vb, rows, c):
         for t in (gx, gbias):
             vb.vb_check(L.vb_release(t.slot, None))
     vb.check_errors()
+
+
+def test_a_device_side_wait_that_runs_out_is_reported_and_survived(vb):
+    """Failure detection on the device, without a fault: a kernel waits (bounded, 4096 polls) on a barrier nothing arrives on,
+    gives up and raises the wait-timeout bit -- the path every tensor-core kernel of the library takes if a copy or a partner
+    never shows up.  The host must see the error at the next check, the error must be cleared by reporting it, and the next
+    tensor-core product must be right."""
+    import ctypes as C
+    L = vb.lib()
+    L.vb_selftest_wait_timeout.argtypes = [C.c_uint32, C.POINTER(C.c_double)]
+    vb.check_errors()
+    ms = C.c_double(0.0)
+    vb.vb_check(L.vb_selftest_wait_timeout(4096, C.byref(ms)), "vb_selftest_wait_timeout")
+    assert 0.0 < ms.value < 2000.0, ms.value            # bounded: the kernel came back by itself
+    with pytest.raises(vb.VearoError, match="a device-side wait ran out"):
+        vb.check_errors()
+    vb.check_errors()                                    # reported once, then clear
+    x0, w0 = rnd(601, 512, 256, scale=0.3), rnd(602, 384, 256, scale=0.1)
+    before = C.c_int64(0); after = C.c_int64(0)
+    L.vb_tc_launch_count(C.byref(before))
+    y = vb.Tensor.from_numpy(x0).linear(vb.Tensor.from_numpy(w0), None).numpy()
+    L.vb_tc_launch_count(C.byref(after))
+    assert after.value > before.value, "the product after the timeout did not run on the tensor-core kernel"
+    assert_close(y, (x0.astype(np.float64) @ w0.astype(np.float64).T).astype(np.float32), "product after a timeout")
+    vb.check_errors()
+    print("give-up time: %.3f ms for 4096 polls -> about %.1f s for the production limit of 2^20" % (ms.value, ms.value * 256 / 1000.0))

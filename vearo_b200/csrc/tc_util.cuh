@@ -22,7 +22,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait; false when the limit ran out (or another role already aborted).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = kSpinLimit) {
   uint32_t addr = smem_u32(bar);
   {   // the phase is often complete already: ask without the (potentially suspending) wait first
     uint32_t done;
@@ -33,7 +33,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
   }
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
