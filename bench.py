@@ -646,6 +646,7 @@ def main():
         "device_memory": vb.memory_stats(),
         "clocks": clocks.summary(), "profile_pass_clocks": prof_clocks,
         "replicas_identical": replicas_identical,
+        "dp_gradients_registered": (opt.gradients_registered() if (dist is not None and opt is not None) else None),
         "roofline": roofline, "kernels": kernels, "gemm_shapes": gemm_shapes, "cpu_baseline": cpu,
         "other_workloads": other,
         "last_loss": losses[-1] if losses else None,

@@ -295,6 +295,12 @@ int vb_profile_families(char* buf, int buflen);
 int vb_dp_unique_id(uint8_t id[128]);
 int vb_dp_init(int rank, int world, const uint8_t id[128]);
 int vb_dp_world(int* rank, int* world);
+/* A slot for data that will be all-reduced in place (a gradient arena).  With more than one rank the memory comes from NCCL's
+ * allocator and is registered with the communicator (the NVLink-switch all-reduce then works on the buffer itself); otherwise,
+ * or when the library refuses, an ordinary slot.  Same ownership rules as vb_alloc.  VB200_DP_REGISTER=0 forces ordinary slots.
+ * vb_dp_is_registered tells which kind a slot is. */
+int vb_dp_alloc(int64_t numel, int zero_fill, vb_slot* out);
+int vb_dp_is_registered(vb_slot slot, int* yes);
 /* Sum-allreduce `numel` floats at slot+offset on the communication stream, ordered after all
  * work enqueued so far on the compute stream.  Returns immediately. */
 int vb_dp_allreduce(vb_slot slot, int64_t offset, int64_t numel);

@@ -130,6 +130,8 @@ unsafe extern "C" {
     pub fn vb_dp_unique_id(id: *mut u8) -> c_int;
     pub fn vb_dp_init(rank: c_int, world: c_int, id: *const u8) -> c_int;
     pub fn vb_dp_world(rank: *mut c_int, world: *mut c_int) -> c_int;
+    pub fn vb_dp_alloc(numel: i64, zero_fill: c_int, out: *mut vb_slot) -> c_int;
+    pub fn vb_dp_is_registered(slot: vb_slot, yes: *mut c_int) -> c_int;
     pub fn vb_dp_allreduce(slot: vb_slot, offset: i64, numel: i64) -> c_int;
     pub fn vb_dp_finish(timeout_ms: c_int) -> c_int;
     pub fn vb_dp_wait() -> c_int;

@@ -274,6 +274,10 @@ class _Opt:
 
     def set_lr(self, lr): _chk(lib().vh_opt_set_lr(self.o, lr))
 
+    def gradients_registered(self):
+        """True when the gradient arena is a buffer registered with the communicator (data parallel, NCCL user buffers)."""
+        return bool(_chk(lib().vh_opt_gradients_registered(self.o)))
+
     def save_state(self, path):
         """m, v (or the velocity) and the step counter, as a `.ve` container."""
         _chk(lib().vh_opt_save_state(self.o, str(path).encode()))

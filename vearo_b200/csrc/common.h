@@ -38,6 +38,7 @@ extern int64_t g_tc_launches;      // launches of the tensor-core GEMM kernel si
 
 // Slots / arena (runtime.cu).
 int slot_alloc(i64 numel, bool zero, vb_slot* out);
+int slot_adopt_external(float* p, i64 numel, void (*free_fn)(void*), vb_slot* out);   // a slot over memory that is not the arena's
 int slot_ptr(vb_slot s, float** p, i64* numel = nullptr);
 int slot_release(vb_slot s, int* freed);
 int slot_retain(vb_slot s);

@@ -12,6 +12,7 @@
 #include <cstring>
 #include <dlfcn.h>
 #include <thread>
+#include <unordered_map>
 
 using namespace vb;
 
@@ -31,7 +32,14 @@ struct Nccl {
   int (*CommAbort)(ncclComm_t) = nullptr;
   int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
+  // optional (user-buffer registration): absent in old libraries, in which case gradients stay in ordinary memory
+  int (*MemAlloc)(void**, size_t) = nullptr;
+  int (*MemFree)(void*) = nullptr;
+  int (*CommRegister)(ncclComm_t, void*, size_t, void**) = nullptr;
+  int (*CommDeregister)(ncclComm_t, void*) = nullptr;
 } g_nccl;
+struct Registered { void* handle; size_t bytes; };
+std::unordered_map<void*, Registered>& registered() { static auto* m = new std::unordered_map<void*, Registered>(); return *m; }
 ncclComm_t g_comm = nullptr;
 int g_rank = 0, g_world = 1;
 
@@ -45,7 +53,22 @@ int load_nccl() {
   SYM(CommDestroy, "ncclCommDestroy") SYM(CommAbort, "ncclCommAbort") SYM(CommGetAsyncError, "ncclCommGetAsyncError")
   SYM(GetErrorString, "ncclGetErrorString")
 #undef SYM
+  *(void**)(&g_nccl.MemAlloc) = dlsym(g_nccl.h, "ncclMemAlloc"); *(void**)(&g_nccl.MemFree) = dlsym(g_nccl.h, "ncclMemFree");
+  *(void**)(&g_nccl.CommRegister) = dlsym(g_nccl.h, "ncclCommRegister"); *(void**)(&g_nccl.CommDeregister) = dlsym(g_nccl.h, "ncclCommDeregister");
   return VB_OK;
+}
+// Releases a buffer made by vb_dp_alloc: nothing of either stream may still be using it.
+void free_registered(void* p) {
+  auto it = registered().find(p);
+  if (it == registered().end()) return;
+  cudaStreamSynchronize(ctx().comm_stream); cudaStreamSynchronize(ctx().stream);
+  if (g_comm && g_nccl.CommDeregister && it->second.handle) g_nccl.CommDeregister(g_comm, it->second.handle);
+  if (g_nccl.MemFree) g_nccl.MemFree(p);
+  registered().erase(it);
+}
+bool registration_enabled() {
+  static const bool on = [] { const char* e = getenv("VB200_DP_REGISTER"); return !(e && e[0] == '0'); }();
+  return on;
 }
 int nccl_fail(const char* what, int rc) {
   return set_error(VB_ERR_COMM, std::string(what) + ": " + (g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "nccl error"));
@@ -71,6 +94,33 @@ int vb_dp_init(int rank, int world, const uint8_t id[128]) {
   ncclUniqueId u; std::memcpy(u.internal, id, 128);
   int rc = g_nccl.CommInitRank(&g_comm, world, u, rank);
   if (rc != ncclSuccess) return nccl_fail("ncclCommInitRank", rc);
+  return VB_OK;
+}
+// Memory for gradients that will be all-reduced in place.  With more than one rank it comes from the communication library's own
+// allocator and is registered with the communicator, so that the NVLink-switch all-reduce can work on the buffer itself instead of
+// staging it through its internal buffers; whenever that is not possible (one rank, an old library, a refusal) it is an ordinary slot.
+int vb_dp_alloc(int64_t numel, int zero_fill, vb_slot* out) {
+  if (!ctx().ready) return set_error(VB_ERR_NOT_INIT, "vb_init has not been called");
+  VB_CHECK(numel >= 0 && out, "bad arguments");
+  if (g_world > 1 && g_comm && numel > 0 && registration_enabled() && g_nccl.MemAlloc && g_nccl.MemFree && g_nccl.CommRegister) {
+    void* p = nullptr;
+    const size_t bytes = (size_t)numel * sizeof(float);
+    if (g_nccl.MemAlloc(&p, bytes) == ncclSuccess && p) {
+      void* handle = nullptr;
+      if (g_nccl.CommRegister(g_comm, p, bytes, &handle) == ncclSuccess) {
+        registered()[p] = Registered{handle, bytes};
+        cudaError_t e = zero_fill ? cudaMemsetAsync(p, 0, bytes, ctx().stream) : cudaSuccess;
+        if (e == cudaSuccess && slot_adopt_external((float*)p, numel, &free_registered, out) == VB_OK) return VB_OK;
+        free_registered(p);
+      } else g_nccl.MemFree(p);
+    }
+    cudaGetLastError();       // fall through to ordinary memory
+  }
+  return slot_alloc(numel, zero_fill != 0, out);
+}
+int vb_dp_is_registered(vb_slot slot, int* yes) {
+  float* p; VB_TRY(slot_ptr(slot, &p));
+  if (yes) *yes = registered().count((void*)p) ? 1 : 0;
   return VB_OK;
 }
 int vb_dp_world(int* rank, int* world) { if (rank) *rank = g_rank; if (world) *world = g_world; return VB_OK; }
@@ -142,7 +192,11 @@ int vb_dp_finish(int timeout_ms) {
 int vb_dp_shutdown(void) {
   g_deferred_pending = false;
   for (cudaEvent_t& e : g_ev_deferred) if (e) { cudaEventDestroy(e); e = nullptr; }
-  if (g_comm) { cudaStreamSynchronize(ctx().comm_stream); g_nccl.CommDestroy(g_comm); g_comm = nullptr; }
+  if (g_comm) {
+    cudaStreamSynchronize(ctx().comm_stream);
+    for (auto& kv : registered()) if (g_nccl.CommDeregister && kv.second.handle) { g_nccl.CommDeregister(g_comm, kv.second.handle); kv.second.handle = nullptr; }
+    g_nccl.CommDestroy(g_comm); g_comm = nullptr;
+  }
   g_world = 1; g_rank = 0;
   return VB_OK;
 }

@@ -41,6 +41,12 @@ Tensor Tensor::zeros(const std::vector<i64>& shape) {
   check(vb_alloc(n, 1, &t.slot), "alloc");
   return adopt(t);
 }
+Tensor Tensor::zeros_for_collectives(const std::vector<i64>& shape) {
+  vb_tensor t = contiguous_desc(shape);
+  i64 n = 1; for (i64 d : shape) n *= d;
+  check(vb_dp_alloc(n, 1, &t.slot), "dp_alloc");
+  return adopt(t);
+}
 Tensor Tensor::from_f32(const float* data, const std::vector<i64>& shape) {
   vb_tensor t = contiguous_desc(shape);
   i64 n = 1; for (i64 d : shape) n *= d;

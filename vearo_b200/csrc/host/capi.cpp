@@ -150,6 +150,7 @@ int vh_opt_load_state(int o, const char* path) { VH_TRY(opt(o).load_state(path);
 int vh_save_checkpoint(int m, const char* path) { VH_TRY(checkpoint::save_checkpoint(model(m).parameters(), path); return 0); }
 int vh_load_checkpoint(int m, const char* path) { VH_TRY(checkpoint::load_checkpoint(model(m).parameters(), path); return 0); }
 int vh_opt_handle(int o) { VH_TRY(return opt(o).handle()); }       // the library's vb_opt_* handle of this optimizer
+int vh_opt_gradients_registered(int o) { VH_TRY(return opt(o).gradients_registered() ? 1 : 0); }
 int vh_opt_set_lr(int o, float lr) { VH_TRY(opt(o).set_lr(lr); return 0); }
 int vh_clip_grad_norm(const int* params, int n, float max_norm, float* norm) {
   VH_TRY(std::vector<Tensor> ps; for (int i = 0; i < n; ++i) ps.push_back(at(params[i])); *norm = optim::clip_grad_norm(ps, max_norm); return 0);

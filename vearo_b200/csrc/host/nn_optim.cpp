@@ -190,7 +190,7 @@ Optimizer::Optimizer(const vb_opt_config& cfg, const std::vector<Tensor>& params
   BucketPlan bp = plan_buckets(numels, (bucket_mb << 20) / 4);
   const i64 total = bp.total;
   const std::vector<i64>& offs = bp.param_offset;
-  arena_ = Tensor::zeros({total > 0 ? total : 1});
+  arena_ = dp_ ? Tensor::zeros_for_collectives({total > 0 ? total : 1}) : Tensor::zeros({total > 0 ? total : 1});
   std::vector<vb_tensor> pd, gd;
   for (size_t i = 0; i < params_.size(); ++i) {
     vb_tensor d = params_[i].desc(); d.slot = arena_.slot(); d.offset = offs[i];

@@ -37,6 +37,7 @@ class Tensor {
   Tensor() = default;
   static Tensor from_f32(const float* data, const std::vector<i64>& shape);   // H2D upload
   static Tensor zeros(const std::vector<i64>& shape);
+  static Tensor zeros_for_collectives(const std::vector<i64>& shape);          // vb_dp_alloc: registered with the communicator where possible
   static Tensor adopt(const vb_tensor& t);                                     // takes ownership of a fresh output
   static Tensor view_of(const Tensor& base, const vb_tensor& d);               // shares storage
 
@@ -135,6 +136,7 @@ class Optimizer {
   void save_state(const std::string& path) const;
   void load_state(const std::string& path);
   int handle() const { return opt_; }          // the library's optimizer handle (vb_opt_*)
+  bool gradients_registered() const { int yes = 0; vb_dp_is_registered(arena_.slot(), &yes); return yes != 0; }   // the gradient arena is a buffer registered with the communicator
  private:
   void finish_reduce(bool deferred = false);
   static void on_ready(int idx, void* self);

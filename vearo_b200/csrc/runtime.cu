@@ -73,7 +73,7 @@ int scratch_alloc(size_t bytes, void** p) { return arena_alloc(bytes ? bytes : 4
 void scratch_free(void* p) { arena_free(p); }
 
 // ---- slots --------------------------------------------------------------------------------
-struct Slot { float* ptr = nullptr; i64 numel = 0; int refs = 0; uint64_t serial = 0; };
+struct Slot { float* ptr = nullptr; i64 numel = 0; int refs = 0; uint64_t serial = 0; void (*ext_free)(void*) = nullptr; };     // ext_free: memory that is not the arena's
 static uint64_t g_serial = 0;
 static std::vector<Slot>& g_slots = *new std::vector<Slot>(1);       // slot 0 = none
 static std::vector<vb_slot>& g_free_ids = *new std::vector<vb_slot>();
@@ -88,7 +88,19 @@ int slot_alloc(i64 n, bool zero, vb_slot* out) {
   vb_slot id;
   if (!g_free_ids.empty()) { id = g_free_ids.back(); g_free_ids.pop_back(); }
   else { id = (vb_slot)g_slots.size(); g_slots.emplace_back(); }
-  g_slots[id].ptr = (float*)p; g_slots[id].numel = n; g_slots[id].refs = 1; g_slots[id].serial = ++g_serial;
+  g_slots[id].ptr = (float*)p; g_slots[id].numel = n; g_slots[id].refs = 1; g_slots[id].serial = ++g_serial; g_slots[id].ext_free = nullptr;
+  ++g_live_slots;
+  *out = id;
+  return VB_OK;
+}
+// A slot over memory obtained elsewhere (a buffer registered with the communication library): released through free_fn.
+int slot_adopt_external(float* p, i64 n, void (*free_fn)(void*), vb_slot* out) {
+  if (!g_ctx.ready) return set_error(VB_ERR_NOT_INIT, "vb_init has not been called");
+  if (!p || n <= 0 || !free_fn) return set_error(VB_ERR_INVALID, "bad external buffer");
+  vb_slot id;
+  if (!g_free_ids.empty()) { id = g_free_ids.back(); g_free_ids.pop_back(); }
+  else { id = (vb_slot)g_slots.size(); g_slots.emplace_back(); }
+  g_slots[id].ptr = p; g_slots[id].numel = n; g_slots[id].refs = 1; g_slots[id].serial = ++g_serial; g_slots[id].ext_free = free_fn;
   ++g_live_slots;
   *out = id;
   return VB_OK;
@@ -111,7 +123,7 @@ int slot_release(vb_slot s, int* freed) {
   if (freed) *freed = 0;
   if (--sl->refs == 0) {
     lo_plane_on_release(s);
-    arena_free(sl->ptr);
+    if (sl->ext_free) { sl->ext_free(sl->ptr); sl->ext_free = nullptr; } else arena_free(sl->ptr);
     sl->ptr = nullptr; sl->numel = 0;
     g_free_ids.push_back(s);
     --g_live_slots;
