@@ -89,6 +89,25 @@ def test_bucket_plan_properties():
     assert one["buckets"] == [(0, 8)] and one["total"] == 8
 
 
+def test_bucket_plan_at_the_headline_model_sizes():
+    """GPT-small's parameter list (token and positional tables, 12 blocks of 16 tensors, the final LayerNorm, the untied head:
+    163,109,376 parameters) cut at the default bucket size of 128 MiB: the head's gradient -- the first to become final in the
+    backward pass -- is reduced first and alone, and the token table, final only with the last backward kernel, sits in the
+    last bucket."""
+    import vearo_b200 as vb
+    d, ff, V, T = 768, 3072, 50304, 1024
+    block = [d, d, d * d, d, d * d, d, d * d, d, d * d, d, d, d, ff * d, ff, d * ff, d]
+    sizes = [V * d, T * d] + block * 12 + [d, d, V * d]
+    assert sum(sizes) == 163109376
+    plan = vb.plan_buckets(sizes, (128 << 20) // 4)
+    buckets = plan["buckets"]
+    assert plan["total"] == 163109376 and sum(n for _, n in buckets) == plan["total"]
+    assert buckets[0] == (plan["total"] - V * d, V * d)                  # the head alone: 154.5 MB >= 128 MiB
+    assert buckets[-1][0] == 0 and buckets[-1][1] >= V * d + T * d       # token + positional tables (+ the rest of block 0)
+    assert all(n * 4 >= (128 << 20) for _, n in buckets[:-1])
+    assert 4 <= len(buckets) <= 6
+
+
 def test_two_ranks_bucketed_allreduce_gloo():
     r0, r1 = _spawn("reduce", 29731)
     assert r0[1] == r1[1]                                   # identical plan on both ranks
